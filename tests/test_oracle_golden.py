@@ -1,0 +1,160 @@
+"""The NumPy oracle against fixtures produced by running the reference (tests/golden)."""
+import numpy as np
+import pytest
+
+from oracle import tq_oracle as o
+
+D = 128
+
+
+def wht_dense(c, seed):
+    return o.wht_as_dense(c[f"wht_s1_{seed}"], c[f"wht_s2_{seed}"])
+
+
+def rot_for(c, mode, seed):
+    return c[f"rot_{seed}"] if mode == "dense" else wht_dense(c, seed)
+
+
+def test_constructors_reproduce_exported_constants(g_const):
+    for seed in (42, 542):
+        assert np.array_equal(o.dense_rotation(D, np.random.default_rng(seed)), g_const[f"rot_{seed}"])
+    assert np.array_equal(o.qjl_matrix(D, np.random.default_rng(1042)), g_const["qjl_1042"])
+    assert np.array_equal(o.qjl_matrix(D, np.random.default_rng(123)), g_const["qjl_123"])
+    for seed in (42, 542, 1042):
+        s1, s2, pd = o.wht_signs(D, np.random.default_rng(seed))
+        assert pd == 128
+        assert np.array_equal(s1, g_const[f"wht_s1_{seed}"]) and np.array_equal(s2, g_const[f"wht_s2_{seed}"])
+    for b in (1, 2, 3, 4):
+        assert np.array_equal(o.centroids(b, D), g_const[f"centroids_b{b}"])
+    for d in (64, 96):
+        assert np.array_equal(o.centroids(3, d), g_const[f"centroids_b3_d{d}"])
+    assert np.array_equal(o.dense_rotation(64, np.random.default_rng(42)), g_const["rot_d64_42"])
+
+
+@pytest.mark.parametrize("mode", ["dense", "wht"])
+@pytest.mark.parametrize("b", [2, 3, 4])
+def test_polar_matches_reference(g_const, g_polar, mode, b):
+    x = g_polar["x"]
+    rot, c = rot_for(g_const, mode, 42), g_const[f"centroids_b{b}"]
+    idx, nrm = o.polar_quantize(x, rot, c)
+    tag = f"{mode}_b{b}"
+    assert np.array_equal(idx.astype(np.uint8), g_polar[f"{tag}_idx"])
+    assert np.array_equal(nrm, g_polar[f"{tag}_norms"]) and nrm.dtype == g_polar[f"{tag}_norms"].dtype
+    assert np.array_equal(o.pack_idx(idx, b), g_polar[f"{tag}_packed"])
+    assert np.array_equal(o.unpack_idx(g_polar[f"{tag}_packed"], b, idx.size).reshape(idx.shape), idx)
+    assert np.array_equal(o.polar_dequantize(idx, nrm, rot, c, True), g_polar[f"{tag}_deq"])
+    assert np.array_equal(o.polar_dequantize(idx, nrm, rot, c, False), g_polar[f"{tag}_deq_nonc"])
+
+
+@pytest.mark.parametrize("mode", ["dense", "wht"])
+@pytest.mark.parametrize("b", [2, 3, 4])
+def test_prod_matches_reference(g_const, g_prod, mode, b):
+    x = g_prod["x"]
+    rot = rot_for(g_const, mode, 42)
+    s = g_const["qjl_1042"] if mode == "dense" else wht_dense(g_const, 1042)
+    c = g_const[f"centroids_b{b - 1}"]
+    code = o.prod_quantize(x, rot, c, s, b)
+    tag = f"{mode}_b{b}"
+    assert np.array_equal(code.mse_indices.astype(np.uint8), g_prod[f"{tag}_idx"])
+    assert np.array_equal(code.vector_norms, g_prod[f"{tag}_norms"])
+    assert np.array_equal(o.pack_signs(code.qjl_signs), g_prod[f"{tag}_signs"])
+    assert np.array_equal(code.residual_norms, g_prod[f"{tag}_rnorms"])
+    assert np.array_equal(o.prod_dequantize(code, rot, c, s), g_prod[f"{tag}_deq"])
+    assert np.array_equal(o.prod_dequantize(code, rot, c, s, shrinkage=2 / np.pi), g_prod[f"{tag}_deq_shrink"])
+    assert np.array_equal(o.pack_idx(code.mse_indices, b - 1), g_prod[f"{tag}_idx_packed"])
+
+
+def test_size_formulae(g_prod, g_prim, g_kv):
+    assert o.prod_size_bits(D, 3, 100) == int(g_prod["size_bits_100_b3"]) == 100 * (128 * 3 + 32)
+    assert o.prod_ratio(D, 3) == float(g_prod["ratio_b3"])
+    fp = o.footprint(1000, D, 3)
+    assert [fp[k] for k in sorted(fp)] == list(g_prim["footprint_vals"])
+    st = o.kv_memory_stats(D, 3, 3, 1024, 32, 32)
+    assert [st[k] for k in sorted(st)] == list(g_kv["stats_vals"])
+
+
+def test_qjl_matches_reference(g_const, g_qjl):
+    s = g_const["qjl_123"]
+    z, n = o.qjl_quantize(g_qjl["r"], s)
+    assert np.array_equal(o.pack_signs(z), g_qjl["signs"])
+    assert np.array_equal(n, g_qjl["norms"]) and n[4] == 0.0
+    assert (z[4] == 1).all()                      # zero residual -> all +1
+    assert np.array_equal(o.qjl_dequantize(z, n, s), g_qjl["deq"])
+    assert np.array_equal(o.qjl_dequantize(z, n, s, 0.5), g_qjl["deq_shrink"])
+
+
+def test_primitives_match_reference(g_prim, g_const):
+    p = g_prim
+    assert np.array_equal(o.fwht(p["fwht_in"]), p["fwht_out"])
+    assert np.array_equal(o.hadamard(8), p["hadamard8"])
+    s1, s2 = p["fast_s1"], p["fast_s2"]
+    assert np.array_equal(o.wht_rotate_batch(p["fast_x"][None], s1, s2, 128)[0], p["fast_y"])
+    assert np.array_equal(o.wht_rotate_transpose_batch(p["fast_x"][None], s1, s2, 128)[0], p["fast_yT"])
+    assert np.array_equal(o.wht_rotate_batch(p["fast_xb"], s1, s2, 128), p["fast_yb"])
+    assert np.array_equal(o.nearest_index(p["nci_vals"], g_const["centroids_b3"]).astype(np.uint8), p["nci_idx"])
+    assert np.array_equal(o.pack_signs(p["bits_in"]), p["bits_packed"])
+    assert np.array_equal(o.pack_signs(p["bits_in1"]), p["bits_packed1"])
+    assert np.array_equal(o.unpack_signs(p["bits_packed"], 21), p["bits_unpacked"])
+    for b in (1, 2, 3, 4, 6):
+        assert np.array_equal(o.pack_idx(p["idx_in"] % (1 << b), b), p[f"idx_packed_b{b}"])
+    with pytest.raises(ValueError):
+        o.pack_idx(p["idx_in"], 9)
+    # tie rule: a value exactly on a boundary takes the lower index
+    c = g_const["centroids_b2"]
+    b = o.boundaries(c)
+    assert list(o.nearest_index(b.copy(), c)) == [0, 1, 2]
+
+
+@pytest.mark.parametrize("mode", ["dense", "wht"])
+@pytest.mark.parametrize("kk", ["prod", "mse"])
+def test_attention_matches_reference(g_const, g_kv, mode, kk):
+    consts = dict(rk=rot_for(g_const, mode, 42), rv=rot_for(g_const, mode, 542),
+                  s=g_const["qjl_1042"] if mode == "dense" else wht_dense(g_const, 1042))
+    kv = o.KVOracle(D, 3, 3, seed=42, mode=mode, k_kind=kk, constants=consts)
+    k, v, q = g_kv["k"], g_kv["v"], g_kv["q"]
+    kh = np.stack([kv.k_roundtrip(k[0, h]) for h in range(2)])[None]
+    vh = np.stack([kv.v_roundtrip(v[0, h]) for h in range(2)])[None]
+    out = o.attend_gqa(q[None], kh, vh)[0]
+    assert np.allclose(out, g_kv[f"{mode}_{kk}_out"], rtol=0, atol=1e-12)
+    # the oracle's own constructors give the same constants as the exported ones
+    kv2 = o.KVOracle(D, 3, 3, seed=42, mode=mode, k_kind=kk)
+    assert np.array_equal(kv2.rk, consts["rk"]) and np.array_equal(kv2.rv, consts["rv"])
+    assert np.array_equal(kv2.s, consts["s"])
+
+
+def test_live_reference_if_present():
+    """Differential check against the reference tree itself where it is mounted."""
+    import os
+    import sys
+    ref = os.environ.get("TQ_REFERENCE", "/root/reference")
+    if not os.path.isdir(os.path.join(ref, "turboquant")):
+        pytest.skip("reference tree not present")
+    sys.path.insert(0, ref)
+    try:
+        from turboquant import TurboQuant, TurboQuantMSE
+    finally:
+        sys.path.remove(ref)
+    x = o.synth_keys(2048, seed=0)
+    for b in (2, 3, 4):
+        m = TurboQuantMSE(D, b, seed=42)
+        i_ref, n_ref = m.quantize(x)
+        i, n = o.polar_quantize(x, m.polar_quant.rotation, m.polar_quant.centroids)
+        assert np.array_equal(i, i_ref) and np.array_equal(n, n_ref)
+        t = TurboQuant(D, b, seed=42)
+        c_ref = t.quantize(x)
+        c = o.prod_quantize(x, t.polar_quant.rotation, t.polar_quant.centroids, t.qjl.S, b)
+        assert np.array_equal(c.qjl_signs, c_ref.qjl_signs)
+        assert np.array_equal(c.residual_norms, c_ref.residual_norms)
+        assert np.array_equal(o.prod_dequantize(c, t.polar_quant.rotation, t.polar_quant.centroids, t.qjl.S),
+                              t.dequantize(c_ref))
+
+
+def test_q8_0_restatement_is_self_consistent():
+    x = o.synth_keys(64, seed=3)
+    x[1] = 0
+    q, s = o.q8_0_quantize(x)
+    assert q.dtype == np.int8 and s.dtype == np.float16 and s.shape == (64, 4)
+    assert (q[1] == 0).all() and (s[1] == 0).all()
+    xh = o.q8_0_dequantize(q, s)
+    blk_max = np.abs(x.reshape(64, 4, 32)).max(axis=2, keepdims=True)
+    assert (np.abs(xh - x).reshape(64, 4, 32) <= blk_max / 127 * 0.51 + blk_max * 1e-3).all()
