@@ -1,0 +1,215 @@
+/*
+ * tq_b200.h -- C ABI of libtq_b200.so: TurboQuant+ KV-cache compression on NVIDIA B200 (sm_100a).
+ *
+ * Every entry point is extern "C", takes plain pointers and sizes, returns TQ_OK (0) or a
+ * negative TQ_ERR_* code, and (except the create/destroy pair and the *_sync helpers) neither
+ * allocates nor synchronises: work is enqueued on the cudaStream_t passed as `stream`
+ * (a void* here so that the header needs no CUDA include).  Pointers named *_dev are device
+ * pointers owned by the caller; pointers in tq_quantizer_desc are host pointers that are read
+ * during tq_quantizer_create only.  A status of TQ_OK means the launch was accepted;
+ * asynchronous faults surface at the caller's next synchronisation.
+ *
+ * The reference project (TheTom/turboquant_plus) is pure Python/NumPy and has no FFI; each
+ * declaration cites the reference function (file:line inside that project) whose arithmetic
+ * the entry point replaces.
+ */
+#ifndef TQ_B200_H
+#define TQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TQ_OK 0
+#define TQ_ERR_INVALID (-1)      /* bad argument (null pointer, negative size, bad enum)       */
+#define TQ_ERR_UNSUPPORTED (-2)  /* combination not built (e.g. WHT mode with d != 128)        */
+#define TQ_ERR_ALIGN (-3)        /* a device pointer or stride is not aligned as documented    */
+#define TQ_ERR_CUDA (-4)         /* a CUDA runtime call failed; see tq_last_error()            */
+#define TQ_ERR_TOO_LARGE (-5)    /* size beyond a documented maximum or workspace too small    */
+#define TQ_ERR_DEVICE (-6)       /* the device is not an sm_100 part / no kernel image         */
+
+/* element types of caller buffers */
+#define TQ_F32 0
+#define TQ_F16 1
+#define TQ_F64 2
+#define TQ_BF16 3
+
+/* rotation kinds */
+#define TQ_ROT_DENSE 0 /* d x d orthogonal matrix: turboquant/rotation.py:25-50             */
+#define TQ_ROT_WHT 1   /* D2 (H/sqrt d) D1 with +-1 sign vectors: turboquant/rotation.py:75-185 */
+
+/* cache formats (per tensor, per layer) */
+#define TQ_FMT_TURBO2 2  /* 2-bit PolarQuant + fp32 scale: 36 B / 128-d vector            */
+#define TQ_FMT_TURBO3 3  /* 3-bit: 52 B                                                   */
+#define TQ_FMT_TURBO4 4  /* 4-bit: 68 B                                                   */
+#define TQ_FMT_Q8_0 8    /* int8 + fp16 scale per 32 values: 136 B                        */
+#define TQ_FMT_PROD2 18  /* 1-bit PolarQuant + 1-bit QJL sketch + 2 fp32: 40 B (K only)   */
+#define TQ_FMT_PROD3 19  /* 2-bit + 1-bit QJL: 56 B (K only)                              */
+#define TQ_FMT_PROD4 20  /* 3-bit + 1-bit QJL: 72 B (K only)                              */
+
+const char* tq_version(void);
+const char* tq_error_string(int code);
+/* message of the last failure on the calling thread ("" if none) */
+const char* tq_last_error(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Quantizer constants.  Mirrors the state a reference quantizer object holds after
+ * construction: PolarQuant.__init__ (turboquant/polar_quant.py:46-54: rotation, centroids),
+ * QJL.__init__ (turboquant/qjl.py:50-70: S) and TurboQuant.__init__
+ * (turboquant/turboquant.py:57-77: PolarQuant(b-1) + QJL(seed+1000)).  The constants are
+ * passed in, never generated here, so that they can be exported from the reference.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct tq_quantizer tq_quantizer;
+
+typedef struct tq_quantizer_desc {
+  int32_t d;               /* vector dimension; WHT mode needs d == 128, dense mode 1..1024     */
+  int32_t bits;            /* PolarQuant bit width, 1..4 (number of centroids = 1 << bits)      */
+  int32_t rotation;        /* TQ_ROT_DENSE or TQ_ROT_WHT                                        */
+  int32_t norm_correction; /* turboquant/polar_quant.py:109-112                                 */
+  const double* rot;       /* dense: d*d row-major, y = rot @ x                                 */
+  const double* signs1;    /* WHT: d values of +-1 applied before the transform                 */
+  const double* signs2;    /* WHT: d values of +-1 applied after the transform                  */
+  const double* centroids; /* 1 << bits sorted values                                           */
+  int32_t qjl;             /* 0: none; 1: residual sketch present (kind follows `rotation`)     */
+  const double* qjl_s;     /* dense: d*d row-major S, z = sign(S r)                             */
+  const double* qjl_signs1;/* WHT: S = D2' (H/sqrt d) D1'                                       */
+  const double* qjl_signs2;
+} tq_quantizer_desc;
+
+/* Allocates a few hundred KB of device memory on the current device and uploads the constants. */
+int tq_quantizer_create(const tq_quantizer_desc* desc, tq_quantizer** out);
+int tq_quantizer_destroy(tq_quantizer* q);
+
+/* ------------------------------------------------------------------------------------------
+ * tq_quantize: PolarQuant.quantize (turboquant/polar_quant.py:56-85), and, when the quantizer
+ * has a QJL stage and out_qjl_dev is given, TurboQuant.quantize
+ * (turboquant/turboquant.py:79-100 = polar_quant.py:121-132 + qjl.py:72-94).
+ *
+ *   x_dev          n vectors of d values, row stride ld (elements), type x_dtype.
+ *                  WHT mode: TQ_F32 / TQ_F16 / TQ_BF16, rows 16-byte aligned.
+ *                  dense mode: TQ_F32 / TQ_F16 / TQ_F64.
+ *   out_packed_dev n * (d*bits/8) bytes, per vector the MSB-first bit stream of
+ *                  utils.pack_indices (turboquant/utils.py:71-98); needs d*bits % 8 == 0; or NULL
+ *   out_idx_dev    n * d bytes, one index per byte; or NULL
+ *   out_norm_dev   n floats, ||x||_2; or NULL
+ *   out_scale_dev  n floats, the factor dequantization multiplies centroids by:
+ *                  ||x|| / ||centroids[idx]|| with norm correction, else ||x||; or NULL
+ *   out_qjl_dev    n * ceil(d/8) bytes, utils.pack_bits order (turboquant/utils.py:20-49); or NULL
+ *   out_rnorm_dev  n floats, ||residual||_2; or NULL
+ * ------------------------------------------------------------------------------------------ */
+int tq_quantize(const tq_quantizer* q, const void* x_dev, int32_t x_dtype, int64_t ld, int64_t n,
+                uint8_t* out_packed_dev, uint8_t* out_idx_dev, float* out_norm_dev,
+                float* out_scale_dev, uint8_t* out_qjl_dev, float* out_rnorm_dev, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * tq_dequantize: PolarQuant.dequantize (turboquant/polar_quant.py:87-119) plus, when qjl_dev is
+ * given, QJL.dequantize (turboquant/qjl.py:96-134) summed as in TurboQuant.dequantize
+ * (turboquant/turboquant.py:102-124).  Exactly one of packed_dev / idx_dev is given.
+ * out_dtype: TQ_F32, TQ_F16 or (dense mode) TQ_F64; out row stride = d.
+ * ------------------------------------------------------------------------------------------ */
+int tq_dequantize(const tq_quantizer* q, const uint8_t* packed_dev, const uint8_t* idx_dev,
+                  const float* norm_dev, const uint8_t* qjl_dev, const float* rnorm_dev,
+                  float shrinkage, int64_t n, void* out_dev, int32_t out_dtype, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Primitives with their own reference functions.
+ * ------------------------------------------------------------------------------------------ */
+/* utils.pack_indices (turboquant/utils.py:71-98): count indices (one per byte) -> MSB-first
+ * stream of ceil(count*bits/8) bytes, bits in 1..4; bits in 5..8 copies the bytes. */
+int tq_pack_indices(const uint8_t* idx_dev, int64_t count, int32_t bits, uint8_t* out_dev, void* stream);
+/* inverse (the reference has none; the decode path needs it) */
+int tq_unpack_indices(const uint8_t* packed_dev, int64_t count, int32_t bits, uint8_t* out_dev, void* stream);
+/* utils.pack_bits / unpack_bits (turboquant/utils.py:20-68): rows of d int8 signs (+1 -> bit 1,
+ * MSB first) <-> rows of ceil(d/8) bytes. */
+int tq_pack_bits(const int8_t* signs_dev, int64_t rows, int32_t d, uint8_t* out_dev, void* stream);
+int tq_unpack_bits(const uint8_t* packed_dev, int64_t rows, int32_t d, int8_t* out_dev, void* stream);
+/* rotation.fast_walsh_hadamard_transform / apply_fast_rotation{,_batch,_transpose}
+ * (turboquant/rotation.py:99-185) in fp64: rows of d values are zero-padded to n (power of two,
+ * <= 4096), multiplied by signs1 (or not, if NULL), transformed, scaled 1/sqrt(n), multiplied by
+ * signs2 (or not), cropped to d. */
+int tq_sign_wht_f64(const double* x_dev, int64_t rows, int32_t d, int32_t n, const double* signs1_dev,
+                    const double* signs2_dev, double* out_dev, void* stream);
+/* codebook.nearest_centroid_indices (turboquant/codebook.py:121-134): index = number of fp64
+ * midpoints strictly below the value. out: one int64 per value. */
+int tq_nearest_centroid_f64(const double* values_dev, int64_t count, const double* centroids_dev,
+                            int32_t n_centroids, int64_t* out_dev, void* stream);
+
+/* QJL.quantize (turboquant/qjl.py:72-94) on its own, fp64 arithmetic, any d: bits of sign(S r) in
+ * utils.pack_bits order (zero counts as +1) and ||r||_2.  Needs a dense-mode quantizer created
+ * with qjl_s (its rot may be NULL).  r dtype TQ_F64 / TQ_F32 / TQ_F16. */
+int tq_qjl_quantize(const tq_quantizer* q, const void* r_dev, int32_t dtype, int64_t n,
+                    uint8_t* out_bits_dev, float* out_norm_dev, void* stream);
+/* QJL.dequantize (turboquant/qjl.py:96-134): shrinkage * sqrt(pi/2)/sqrt(d) * ||r|| * S^T z. */
+int tq_qjl_dequantize(const tq_quantizer* q, const uint8_t* bits_dev, const float* rnorm_dev,
+                      float shrinkage, int64_t n, void* out_dev, int32_t out_dtype, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Paged compressed cache.  New surface: the reference's KVCacheCompressor
+ * (turboquant/kv_cache.py:69-165) only has bulk compress/decompress; its docstring names a
+ * streaming compress_token (kv_cache.py:65-66) that is never defined.  One layer's cache is a
+ * byte pool of `num_pages` pages; page p, KV head h starts at p*page_stride + h*head_stride and
+ * holds `page_tokens` tokens as consecutive arrays (offsets in the layout struct):
+ *   K indices [page_tokens][d*bits/8] | K scale f32[page_tokens] | (K QJL bits [page_tokens][d/8]
+ *   | K residual scale f32[page_tokens]) | V indices | V scale
+ * q8_0 tensors hold int8 [page_tokens][d] | fp16 scales [page_tokens][d/32].
+ * ------------------------------------------------------------------------------------------ */
+typedef struct tq_cache_layout {
+  int32_t d, page_tokens, num_kv_heads, k_format, v_format;
+  int32_t k_idx_bytes, v_idx_bytes;       /* per token                                         */
+  int32_t k_idx_off, k_scale_off, k_qjl_off, k_rscale_off, v_idx_off, v_scale_off;
+  int32_t record_bytes;                   /* one (page, head) record, multiple of 128          */
+  int64_t head_stride, page_stride;       /* bytes                                             */
+} tq_cache_layout;
+
+/* Fills every field from (d, page_tokens, num_kv_heads, k_format, v_format); d must be 128 and
+ * page_tokens a multiple of 32 in 32..256. */
+int tq_cache_layout_init(tq_cache_layout* layout, int32_t d, int32_t page_tokens, int32_t num_kv_heads,
+                         int32_t k_format, int32_t v_format);
+
+/* Quantize-on-append: k_dev, v_dev are [n_tokens][num_kv_heads][d] (dtype TQ_F32/TQ_F16/TQ_BF16),
+ * slot_dev[t] = page*page_tokens + offset of token t (negative: skip the token).
+ * kq / vq hold the constants of the K and V tensors (ignored for q8_0 tensors, may be NULL). */
+int tq_cache_append(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cache_layout* layout,
+                    uint8_t* pool_dev, const void* k_dev, const void* v_dev, int32_t dtype,
+                    int64_t n_tokens, const int64_t* slot_dev, void* stream);
+
+/* Stores rows that were quantized elsewhere (tq_quantize with a dense-mode quantizer, whose
+ * kernel does not address pages) into the records of a paged cache: which = 0 writes the K
+ * arrays, 1 the V arrays.  packed_dev [n_tokens][num_kv_heads][idx_bytes], scale_dev
+ * [n_tokens][num_kv_heads] (the out_scale of tq_quantize); PROD formats also take the sign sketch
+ * [n_tokens][num_kv_heads][d/8] and residual scales = ||r|| * sqrt(pi/2)/sqrt(d).  Same new
+ * surface as tq_cache_append (the reference has no paged cache). */
+int tq_cache_store(const tq_cache_layout* layout, uint8_t* pool_dev, int32_t which,
+                   const uint8_t* packed_dev, const float* scale_dev, const uint8_t* qjl_dev,
+                   const float* rscale_dev, int64_t n_tokens, const int64_t* slot_dev, void* stream);
+
+/* Scratch for tq_decode_attn (split partials + rotated queries), bytes; 256-byte aligned buffer. */
+int64_t tq_decode_workspace_bytes(int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
+                                  int32_t max_pages_per_seq);
+/* After a synchronisation: 0 if the last tq_decode_attn that used this workspace finished cleanly,
+ * 1 if a bounded wait inside the kernel gave up (results invalid). Copies 4 bytes to the host. */
+int tq_decode_status_sync(const void* workspace_dev, int64_t workspace_bytes, int32_t* status_out);
+
+/* Decode attention straight off the packed cache: for every sequence b and query head h,
+ * softmax(q k^T * scale) v over the first seq_lens[b] cached tokens of KV head
+ * h / (num_q_heads/num_kv_heads), with k and v the dequantized cache contents -- the
+ * dequantize-then-attend computation of the reference's tests (tests/test_kv_cache.py:73-89,
+ * 128-131) without materialising the dequantized cache.  Queries are rotated once by the K
+ * rotation (and projected by S for PROD formats), scores are taken against centroid values, V is
+ * accumulated in its rotated space and un-rotated once per output row.
+ *   q_dev [batch][num_q_heads][d] (TQ_F16/TQ_BF16/TQ_F32); out_dev same shape, out_dtype likewise
+ *   block_table_dev [batch][max_pages_per_seq] int32 page numbers; seq_lens_dev [batch] int32
+ *   scale <= 0 selects 1/sqrt(d). */
+int tq_decode_attn(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cache_layout* layout,
+                   const uint8_t* pool_dev, const int32_t* block_table_dev, int32_t max_pages_per_seq,
+                   const int32_t* seq_lens_dev, const void* q_dev, int32_t q_dtype, int32_t batch,
+                   int32_t num_q_heads, float scale, void* workspace_dev, int64_t workspace_bytes,
+                   void* out_dev, int32_t out_dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TQ_B200_H */

@@ -1,0 +1,252 @@
+"""CUDA quantize / dequantize against the golden fixtures and the NumPy oracle (through the C ABI)."""
+import numpy as np
+import pytest
+
+from oracle import tq_oracle as o
+from tests.helpers import D, check_indices, wht_dense
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def tq():
+    import turboquant_plus_b200 as pkg
+    return pkg
+
+
+def _rot(g_const, mode, seed):
+    return g_const[f"rot_{seed}"] if mode == "dense" else wht_dense(g_const, seed)
+
+
+@pytest.mark.parametrize("mode", ["dense", "wht"])
+@pytest.mark.parametrize("b", [2, 3, 4])
+def test_polar_golden(tq, g_const, g_polar, mode, b):
+    x = g_polar["x"]
+    q = tq.TurboQuantMSE(D, b, seed=42, rotation=mode)
+    assert np.array_equal(q.polar_quant.rotation, _rot(g_const, mode, 42))
+    assert np.array_equal(q.polar_quant.centroids, g_const[f"centroids_b{b}"])
+    idx, nrm = q.quantize(x)
+    tag = f"{mode}_b{b}"
+    ref_idx, ref_nrm = g_polar[f"{tag}_idx"], g_polar[f"{tag}_norms"]
+    assert idx.dtype == np.int64 and nrm.dtype == np.float32
+    _, _, y = o.polar_quantize(x, q.polar_quant.rotation, q.polar_quant.centroids, return_rotated=True)
+    mism, band = check_indices(idx, ref_idx, y, q.polar_quant.centroids)
+    print(f"{tag}: {mism} index mismatches, {band} coordinates inside the boundary band, of {idx.size}")
+    if mode == "dense":
+        assert mism == 0
+    # norms within 1e-6 relative; row 6 has squares in the fp32 subnormal range, where the reference's own
+    # fp32 sum of squares is only good to ~1e-3
+    ok = np.ones(len(x), bool)
+    ok[6] = False
+    assert np.allclose(nrm[ok], ref_nrm[ok], rtol=1e-6, atol=0)
+    assert np.allclose(nrm[6], ref_nrm[6], rtol=2e-2)
+    assert nrm[5] == 0.0
+    if mode == "dense":
+        assert np.array_equal(nrm[ok], ref_nrm[ok])          # NumPy's pairwise fp32 summation reproduced
+    # packed stream = the reference's pack_indices of the same indices
+    import torch
+    out = q.polar_quant.quantize_device(torch.as_tensor(x).cuda(), packed=True, want_scale=True)
+    assert np.array_equal(out["packed"].cpu().numpy().ravel(), o.pack_idx(idx, b))
+    if mism == 0:
+        assert np.array_equal(out["packed"].cpu().numpy().ravel(), g_polar[f"{tag}_packed"])
+    cn = np.linalg.norm(q.polar_quant.centroids[idx], axis=1)
+    assert np.allclose(out["scale"].cpu().numpy()[ok], (nrm / np.where(cn > 1e-10, cn, 1))[ok], rtol=2e-6)
+    # dequantize (from the reference's indices, so that near-boundary flips do not enter)
+    deq = q.dequantize(ref_idx.astype(np.int64), ref_nrm)
+    ref = g_polar[f"{tag}_deq"]
+    tol = 1e-12 if mode == "dense" else 2e-6
+    scale = np.maximum(np.abs(ref).max(axis=1, keepdims=True), 1e-300)
+    assert (np.abs(deq - ref) / scale).max() < tol
+    qn = tq.TurboQuantMSE(D, b, seed=42, rotation=mode, norm_correction=False)
+    deq = qn.dequantize(ref_idx.astype(np.int64), ref_nrm)
+    assert (np.abs(deq - g_polar[f"{tag}_deq_nonc"]) / scale).max() < tol
+    # packed dequantize path
+    dq = q.polar_quant.dequantize_device(out["norm"], packed=out["packed"]).cpu().numpy()
+    assert (np.abs(dq - q.dequantize(idx, nrm)) / scale).max() < 1e-6
+
+
+def test_single_vector_convention(tq, g_polar):
+    q = tq.PolarQuant(D, 3, seed=42)
+    i1, n1 = q.quantize(g_polar["x"][0])
+    assert i1.shape == (D,) and np.shape(n1) == ()
+    assert np.array_equal(i1, g_polar["single_idx"]) and n1 == g_polar["single_norm"]
+    x1 = q.dequantize(i1, n1)
+    assert x1.shape == (D,) and np.abs(x1 - g_polar["single_deq"]).max() < 1e-12 * np.abs(x1).max()
+
+
+@pytest.mark.parametrize("mode", ["dense", "wht"])
+@pytest.mark.parametrize("b", [2, 3, 4])
+def test_prod_golden(tq, g_const, g_prod, mode, b):
+    x = g_prod["x"]
+    t = tq.TurboQuant(D, b, seed=42, rotation=mode)
+    assert np.array_equal(t.qjl.S, g_const["qjl_1042"] if mode == "dense" else wht_dense(g_const, 1042))
+    c = t.quantize(x)
+    tag = f"{mode}_b{b}"
+    cb = t.polar_quant.centroids
+    _, _, y = o.polar_quantize(x, t.polar_quant.rotation, cb, return_rotated=True)
+    mism, _ = check_indices(c.mse_indices, g_prod[f"{tag}_idx"], y, cb)
+    assert c.qjl_signs.dtype == np.int8 and set(np.unique(c.qjl_signs)) <= {-1, 1}
+    ref_signs = o.unpack_signs(g_prod[f"{tag}_signs"], D)
+    rows_ok = (c.mse_indices == g_prod[f"{tag}_idx"]).all(axis=1)
+    rows_ok[6] = False            # subnormal squares, see test_polar_golden
+    flips = (c.qjl_signs != ref_signs)[rows_ok]
+    # a sign may differ only where the projected residual is within rounding of zero
+    _, _, res = o.polar_residual(x, t.polar_quant.rotation, cb)
+    proj = (t.qjl.S @ res.T).T
+    rel = np.abs(proj) / np.maximum(np.linalg.norm(res, axis=1, keepdims=True), 1e-300)
+    assert (rel[rows_ok][flips] < 1e-5).all()
+    print(f"{tag}: {mism} index mismatches, {int(flips.sum())} sign flips near zero of {flips.size}")
+    if mode == "dense":
+        assert flips.sum() == 0
+    assert (c.qjl_signs[5] == 1).all() and c.residual_norms[5] == 0.0
+    assert np.allclose(c.residual_norms[rows_ok], g_prod[f"{tag}_rnorms"][rows_ok], rtol=1e-5 if mode == "wht" else 1e-6)
+    ref_code = o.ProdCode(g_prod[f"{tag}_idx"].astype(np.int64), g_prod[f"{tag}_norms"], ref_signs,
+                          g_prod[f"{tag}_rnorms"], b)
+    import dataclasses
+    cv = tq.CompressedVector(**dataclasses.asdict(ref_code))
+    ref = g_prod[f"{tag}_deq"]
+    scale = np.maximum(np.abs(ref).max(axis=1, keepdims=True), 1e-300)
+    tol = 1e-7 if mode == "dense" else 3e-6      # norms travel as fp32
+    assert (np.abs(t.dequantize(cv) - ref) / scale).max() < tol
+    assert (np.abs(t.dequantize(cv, shrinkage=2 / np.pi) - g_prod[f"{tag}_deq_shrink"]) / scale).max() < tol
+    assert t.compressed_size_bits(100) == 100 * (128 * b + 32)
+
+
+def test_qjl_golden(tq, g_const, g_qjl):
+    qj = tq.QJL(D, seed=123)
+    assert np.array_equal(qj.S, g_const["qjl_123"])
+    z, n = qj.quantize(g_qjl["r"])
+    assert np.array_equal(o.pack_signs(z), g_qjl["signs"])
+    assert np.allclose(n, g_qjl["norms"], rtol=1e-7) and n[4] == 0 and (z[4] == 1).all()
+    assert np.abs(qj.dequantize(z, g_qjl["norms"]) - g_qjl["deq"]).max() < 1e-7 * np.abs(g_qjl["deq"]).max()
+    assert np.abs(qj.dequantize(z, g_qjl["norms"], shrinkage=0.5) - g_qjl["deq_shrink"]).max() < 1e-7
+    z1, n1 = qj.quantize(g_qjl["r"][0])
+    assert z1.shape == (D,) and np.shape(n1) == ()
+
+
+def test_primitives_golden(tq, g_prim, g_const):
+    from turboquant_plus_b200 import codebook, rotation, utils
+    p = g_prim
+    assert np.array_equal(rotation.fast_walsh_hadamard_transform(p["fwht_in"]), p["fwht_out"])
+    s1, s2 = p["fast_s1"], p["fast_s2"]
+    assert np.array_equal(rotation.apply_fast_rotation(p["fast_x"], s1, s2, 128), p["fast_y"])
+    assert np.array_equal(rotation.apply_fast_rotation_transpose(p["fast_x"], s1, s2, 128), p["fast_yT"])
+    assert np.array_equal(rotation.apply_fast_rotation_batch(p["fast_xb"], s1, s2, 128), p["fast_yb"])
+    with pytest.raises(ValueError):
+        rotation.fast_walsh_hadamard_transform(np.ones(12))
+    assert np.array_equal(codebook.nearest_centroid_indices(p["nci_vals"], g_const["centroids_b3"]).astype(np.uint8),
+                          p["nci_idx"])
+    c2 = g_const["centroids_b2"]
+    assert list(codebook.nearest_centroid_indices(o.boundaries(c2), c2)) == [0, 1, 2]      # ties go down
+    assert np.array_equal(utils.pack_bits(p["bits_in"]), p["bits_packed"])
+    assert np.array_equal(utils.pack_bits(p["bits_in1"]), p["bits_packed1"])
+    assert np.array_equal(utils.unpack_bits(p["bits_packed"], 21), p["bits_unpacked"])
+    for b in (1, 2, 3, 4, 6):
+        idx = p["idx_in"] % (1 << b)
+        packed = utils.pack_indices(idx, b)
+        assert np.array_equal(packed, p[f"idx_packed_b{b}"])
+        if b <= 4:
+            assert np.array_equal(utils.unpack_indices(packed, b, idx.size), idx.ravel())
+    with pytest.raises(ValueError):
+        utils.pack_indices(p["idx_in"], 9)
+    assert utils.pack_indices(np.zeros((0, 128), np.uint8), 3).size == 0      # empty input
+
+
+@pytest.mark.parametrize("mode", ["wht", "dense"])
+def test_config0_full_size(tq, mode):
+    """65,536 synthetic key vectors (N(0,1) x lognormal scale, 4 outlier channels x10, seed 0), b = 2, 3, 4:
+    indices against the oracle, MSE and inner-product distortion against 4,096 N(0,1) queries."""
+    x = o.synth_keys(65536, seed=0)
+    qv = np.random.default_rng(1).standard_normal((4096, D))
+    for b in (2, 3, 4):
+        q = tq.TurboQuantMSE(D, b, seed=42, rotation=mode)
+        rot, cb = q.polar_quant.rotation, q.polar_quant.centroids
+        ref_idx, ref_nrm, y = o.polar_quantize(x, rot, cb, return_rotated=True)
+        idx, nrm = q.quantize(x)
+        mism, band = check_indices(idx, ref_idx, y, cb)
+        assert np.allclose(nrm, ref_nrm, rtol=1e-6, atol=0)
+        xh = q.dequantize(idx, nrm)
+        xr = o.polar_dequantize(ref_idx, ref_nrm, rot, cb)
+        mse, mse_ref = np.mean((x - xh) ** 2), np.mean((x - xr) ** 2)
+        ip = np.mean((qv @ (x[:4096] - xh[:4096]).T) ** 2)
+        ip_ref = np.mean((qv @ (x[:4096] - xr[:4096]).T) ** 2)
+        print(f"{mode} turbo{b}: {mism} index mismatches / {band} in band of {idx.size}; "
+              f"MSE {mse:.6f} (oracle {mse_ref:.6f}); IP distortion {ip:.5f} (oracle {ip_ref:.5f})")
+        assert abs(mse / mse_ref - 1) < 1e-4 and abs(ip / ip_ref - 1) < 1e-3
+        if mode == "dense":
+            assert mism == 0
+    # prod, 3 bits, on a slice (the oracle needs three fp64 GEMMs per vector)
+    xs = x[:16384]
+    t = tq.TurboQuant(D, 3, seed=42, rotation=mode)
+    c = t.quantize(xs)
+    ref = o.prod_quantize(xs, t.polar_quant.rotation, t.polar_quant.centroids, t.qjl.S, 3)
+    rows = (c.mse_indices == ref.mse_indices).all(axis=1)
+    flips = int((c.qjl_signs != ref.qjl_signs)[rows].sum())
+    print(f"{mode} prod3: {int((~rows).sum())} rows with an index mismatch, {flips} sign flips of {rows.sum() * D}")
+    assert (~rows).sum() <= 8 and flips <= 32
+    assert np.allclose(c.residual_norms[rows], ref.residual_norms[rows], rtol=2e-5)
+
+
+def test_reference_style_behaviour(tq):
+    """Cases the reference's own tests pin (tests/test_polar_quant.py, test_turbo4.py, test_turboquant.py):
+    batch equals single, determinism, zero vector, odd head dimensions, MSE bound, bad bit width."""
+    rng = np.random.default_rng(7)
+    for d in (64, 96, 128, 200):
+        q = tq.PolarQuant(d, 3, seed=42)
+        xb = rng.standard_normal((6, d))
+        ib, nb = q.quantize(xb)
+        for r in range(6):
+            i1, n1 = q.quantize(xb[r])
+            assert np.array_equal(i1, ib[r]) and n1 == nb[r]
+        assert np.array_equal(q.quantize(xb)[0], ib)
+        i0, n0 = q.quantize(np.zeros(d))
+        assert n0 == 0.0 and np.abs(q.dequantize(i0, n0)).max() == 0.0
+        u = xb / np.linalg.norm(xb, axis=1, keepdims=True)
+        uh = q.dequantize(*q.quantize(u))
+        assert np.mean(np.sum((u - uh) ** 2, axis=1)) < 3 * 0.03       # paper bound for 3 bits, 3x slack
+    with pytest.raises(ValueError):
+        tq.TurboQuant(128, 1)
+    t = tq.TurboQuant(64, 3, seed=1)
+    xb = rng.standard_normal((5, 64))
+    c = t.quantize(xb)
+    assert c.mse_indices.shape == (5, 64) and c.mse_indices.max() < 4 and c.bit_width == 3
+    c1 = t.quantize(xb[2])
+    assert np.array_equal(c1.mse_indices, c.mse_indices[2]) and np.array_equal(c1.qjl_signs, c.qjl_signs[2])
+    assert np.allclose(t.dequantize(c1), t.dequantize(c)[2])
+
+
+def test_kv_compressor_matches_reference(tq, g_kv):
+    comp = tq.KVCacheCompressor(D, k_bits=3, v_bits=3, seed=42)
+    cc = comp.compress(g_kv["k"], g_kv["v"])
+    assert (cc.num_layers, cc.num_heads, cc.seq_len, cc.head_dim, cc.k_bit_width, cc.v_bit_width) == (1, 2, 200, D, 3, 3)
+    assert len(cc.k_compressed) == 1 and len(cc.k_compressed[0]) == 2 and cc.v_indices[0][1].shape == (200, D)
+    kh, vh = comp.decompress(cc)
+    assert kh.shape == g_kv["k"].shape
+    assert np.abs(kh - g_kv["dense_prod_k_hat"]).max() < 2e-5 * np.abs(kh).max()
+    assert np.abs(vh - g_kv["dense_prod_v_hat"]).max() < 2e-5 * np.abs(vh).max()
+    st = comp.memory_stats(1024, 32, 32)
+    assert [st[k] for k in sorted(st)] == list(g_kv["stats_vals"])
+    with pytest.raises(AssertionError):
+        comp.compress(np.zeros((1, 1, 4, 64)), np.zeros((1, 1, 4, 64)))
+
+
+def test_input_dtypes_and_errors(tq):
+    import torch
+    x = o.synth_keys(1000, seed=5)
+    q = tq.PolarQuant(D, 3, seed=42, rotation="wht")
+    a = q.quantize_device(torch.as_tensor(x).cuda(), packed=True)
+    h = q.quantize_device(torch.as_tensor(x).cuda().half().float(), packed=True)
+    h16 = q.quantize_device(torch.as_tensor(x).cuda().half(), packed=True)
+    assert torch.equal(h["packed"], h16["packed"]) and torch.equal(h["norm"], h16["norm"])
+    b16 = q.quantize_device(torch.as_tensor(x).cuda().bfloat16(), packed=True)
+    b32 = q.quantize_device(torch.as_tensor(x).cuda().bfloat16().float(), packed=True)
+    assert torch.equal(b16["packed"], b32["packed"])
+    assert a["packed"].shape == (1000, 48)
+    with pytest.raises(ValueError):
+        q.quantize(np.zeros((3, 64)))
+    with pytest.raises(ValueError):
+        tq.PolarQuant(96, 3, rotation="wht")
+    # n not a multiple of the 4 vectors a warp handles
+    for n in (1, 2, 3, 5, 33):
+        r = q.quantize_device(torch.as_tensor(x[:n]).cuda(), packed=True)
+        assert torch.equal(r["packed"], a["packed"][:n]) and torch.equal(r["norm"], a["norm"][:n])

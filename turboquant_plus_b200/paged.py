@@ -1,0 +1,152 @@
+"""Paged compressed KV cache: quantize-on-append and decode attention straight off the packed pages.
+
+New surface (the reference's KVCacheCompressor only has bulk compress / decompress; the streaming
+``compress_token`` its docstring names, turboquant/kv_cache.py:65-66, is never defined).  One object is
+one layer's cache; K and V formats are chosen per layer:
+
+    "turbo2" | "turbo3" | "turbo4"   b-bit PolarQuant, MSE-only (TurboQuantMSE), fp32 scale per vector
+    "prod2"  | "prod3"  | "prod4"    (b-1)-bit PolarQuant + 1-bit QJL sketch (TurboQuant), K only
+    "q8_0"                            int8 with an fp16 scale per 32 values
+
+The attention computed is the reference tests' dequantize-then-attend
+(tests/test_kv_cache.py:73-89): softmax(q k_hat^T / sqrt(d)) v_hat, per sequence and query head.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import numpy as np
+
+from . import _native as nv
+from .polar_quant import PolarQuant
+from .turboquant import TurboQuant
+
+
+def _fmt_bits(fmt: str) -> int:
+    return int(fmt[-1])
+
+
+class PagedKVCache:
+    def __init__(self, head_dim: int, num_kv_heads: int, num_pages: int, page_tokens: int = 128,
+                 k_format: str = "turbo3", v_format: str = "turbo3", seed: int = 42,
+                 norm_correction: bool = True, rotation: str = "wht", device=None,
+                 k_quantizer=None, v_quantizer=None):
+        torch = nv.require_cuda()
+        if k_format not in nv.FORMATS or v_format not in nv.FORMATS:
+            raise ValueError(f"unknown cache format {k_format!r} / {v_format!r}")
+        if v_format.startswith("prod"):
+            raise ValueError("V is stored MSE-only (turboN) or q8_0; the QJL sketch is a K format")
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.head_dim, self.num_kv_heads, self.num_pages, self.page_tokens = head_dim, num_kv_heads, num_pages, page_tokens
+        self.k_format, self.v_format = k_format, v_format
+        self.layout = nv.CacheLayout()
+        nv.call("tq_cache_layout_init", C.byref(self.layout), head_dim, page_tokens, num_kv_heads,
+                nv.FORMATS[k_format], nv.FORMATS[v_format])
+        # K uses the compressor's seed, V seed + 500, QJL seed + 1000 (turboquant/kv_cache.py:89-96,
+        # turboquant/turboquant.py:77)
+        if k_quantizer is None and k_format != "q8_0":
+            if k_format.startswith("prod"):
+                k_quantizer = TurboQuant(head_dim, _fmt_bits(k_format), seed=seed, norm_correction=norm_correction,
+                                         rotation=rotation, device=self.device)
+            else:
+                k_quantizer = PolarQuant(head_dim, _fmt_bits(k_format), seed=seed, norm_correction=norm_correction,
+                                         rotation=rotation, device=self.device)
+        if v_quantizer is None and v_format != "q8_0":
+            v_quantizer = PolarQuant(head_dim, _fmt_bits(v_format), seed=seed + 500, norm_correction=norm_correction,
+                                     rotation=rotation, device=self.device)
+        self.k_quantizer, self.v_quantizer = k_quantizer, v_quantizer
+        self.pool = torch.zeros((num_pages, num_kv_heads, self.layout.record_bytes), dtype=torch.uint8,
+                                device=self.device)
+        self._ws = None
+        self._dummy = None
+
+    # bytes one cached token of one KV head occupies (K + V), the figure roofline arithmetic uses
+    @property
+    def bytes_per_token(self) -> int:
+        L = self.layout
+        def tensor(fmt, idx_bytes):
+            if fmt == "q8_0":
+                return idx_bytes + (self.head_dim // 32) * 2
+            return idx_bytes + 4 + ((self.head_dim // 8 + 4) if fmt.startswith("prod") else 0)
+        return tensor(self.k_format, L.k_idx_bytes) + tensor(self.v_format, L.v_idx_bytes)
+
+    def _handle(self, quantizer):
+        if quantizer is None:
+            return self._placeholder().handle
+        return quantizer._native(self.device).handle
+
+    def _placeholder(self):
+        """q8_0 tensors need no codebook; the attention entry point still takes the rotation, which for
+        q8_0 is the identity."""
+        if self._dummy is None:
+            self._dummy = nv.Quantizer(self.head_dim, 1, nv.ROT_DENSE, False, np.array([-1.0, 1.0]),
+                                       rot=np.eye(self.head_dim), device=self.device)
+        return self._dummy
+
+    def append(self, k, v, slot_mapping):
+        """k, v: (n_tokens, num_kv_heads, head_dim) CUDA tensors (fp16, bf16 or fp32);
+        slot_mapping: (n_tokens,) int64, page * page_tokens + offset, negative = skip."""
+        torch = nv.require_cuda()
+        k, v = k.contiguous(), v.contiguous()
+        n = k.shape[0]
+        assert k.shape == v.shape == (n, self.num_kv_heads, self.head_dim)
+        assert k.dtype == v.dtype
+        slots = slot_mapping.to(device=self.device, dtype=torch.int64).contiguous()
+        wht_ok = all(q is None or q._native(self.device).rotation == nv.ROT_WHT
+                     for q in (self.k_quantizer, self.v_quantizer))
+        with torch.cuda.device(self.device):
+            if wht_ok:
+                nv.call("tq_cache_append", self._handle(self.k_quantizer) if self.k_quantizer else None,
+                        self._handle(self.v_quantizer) if self.v_quantizer else None, C.byref(self.layout),
+                        nv.ptr(self.pool), nv.ptr(k), nv.ptr(v), nv.torch_dtype_code(k.dtype), n, nv.ptr(slots),
+                        nv.stream_ptr())
+                return
+            # dense-rotation quantizers: quantize into rows, then scatter the rows into the pages
+            for which, (x, quant, fmt) in enumerate(((k, self.k_quantizer, self.k_format),
+                                                     (v, self.v_quantizer, self.v_format))):
+                rows = x.reshape(n * self.num_kv_heads, self.head_dim)
+                if fmt == "q8_0":
+                    raise nv.TQError("mixing q8_0 with dense-rotation quantizers in one cache is not built")
+                if rows.dtype == torch.bfloat16:
+                    rows = rows.float()
+                out = quant.quantize_device(rows, packed=True, want_scale=True)
+                qjl = rscale = None
+                if fmt.startswith("prod"):
+                    qjl = out["qjl"]
+                    rscale = out["rnorm"] * (math.sqrt(math.pi / 2) / math.sqrt(self.head_dim))
+                nv.call("tq_cache_store", C.byref(self.layout), nv.ptr(self.pool), which, nv.ptr(out["packed"]),
+                        nv.ptr(out["scale"]), nv.ptr(qjl), nv.ptr(rscale), n, nv.ptr(slots), nv.stream_ptr())
+
+    def workspace(self, batch: int, num_q_heads: int, max_pages: int):
+        torch = nv.require_cuda()
+        need = nv.load().tq_decode_workspace_bytes(batch, num_q_heads, self.num_kv_heads, max_pages)
+        nv.check(int(need))
+        if self._ws is None or self._ws.numel() < need:
+            self._ws = torch.empty((int(need),), dtype=torch.uint8, device=self.device)
+        return self._ws
+
+    def attend(self, q, block_table, seq_lens, scale=None, out=None, workspace=None):
+        """q: (batch, num_q_heads, head_dim) CUDA tensor; block_table: (batch, max_pages) int32 page
+        numbers; seq_lens: (batch,) int32.  Returns (batch, num_q_heads, head_dim) in q's dtype."""
+        torch = nv.require_cuda()
+        q = q.contiguous()
+        bsz, hq, d = q.shape
+        assert d == self.head_dim
+        bt = block_table.to(device=self.device, dtype=torch.int32).contiguous()
+        sl = seq_lens.to(device=self.device, dtype=torch.int32).contiguous()
+        ws = self.workspace(bsz, hq, bt.shape[1]) if workspace is None else workspace
+        if out is None:
+            out = torch.empty_like(q)
+        with torch.cuda.device(self.device):
+            nv.call("tq_decode_attn", self._handle(self.k_quantizer), self._handle(self.v_quantizer),
+                    C.byref(self.layout), nv.ptr(self.pool), nv.ptr(bt), bt.shape[1], nv.ptr(sl), nv.ptr(q),
+                    nv.torch_dtype_code(q.dtype), bsz, hq, float(scale) if scale else 0.0, nv.ptr(ws), ws.numel(),
+                    nv.ptr(out), nv.torch_dtype_code(out.dtype), nv.stream_ptr())
+        return out
+
+    def kernel_status(self) -> int:
+        """0 after a clean decode; 1 if a bounded wait inside the kernel gave up (synchronises)."""
+        st = C.c_int32(0)
+        nv.call("tq_decode_status_sync", nv.ptr(self._ws), self._ws.numel(), C.byref(st))
+        return st.value
