@@ -1,0 +1,335 @@
+"""Benchmark of the TurboQuant+ hot path on B200: decode attention over a turbo3-compressed KV cache.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (N = 1): single-layer decode attention, Llama-3-8B shaped -- 32 query / 8 KV heads, d = 128,
+batch 1, context 32,768, K and V stored as turbo3 (3-bit PolarQuant, fp32 scale: 52 B per vector), fp16
+queries.  One cache is 27.3 MB and would sit in the 126 MB L2, so a step is one decode-attention pass over
+each of LAYERS distinct layer caches of that shape (1.09 GB of packed cache per step, larger than L2).
+Synthetic data: keys N(0,1) x lognormal(0, 0.5) per vector with 4 outlier channels x10 and a RoPE-style
+rotation by position, values N(0,1), generated on the device from a fixed seed and written through the
+quantize-on-append kernel.
+
+value  = KV-tokens/s (one KV-token = one cached position of one KV head, its K and its V vector), whole job,
+         cache resident in HBM, launches replayed from a CUDA graph, timed with CUDA events.
+e2e    = the same metric through LayeredKVCache.decode_step with host buffers: every step copies the
+         queries and the new token's K/V rows from pinned host memory, appends (quantizes) them, attends,
+         and copies the outputs back.
+With N > 1 ranks each rank owns its own sequence (batch sharding, no collective on the data path): weak scaling.
+
+--impl reference times the reference's algorithm for this path on the host cores: dequantize the whole
+compressed cache, then NumPy softmax attention (the reference's dequantize-then-attend), through the NumPy
+port under oracle/ (the reference itself is a Python package that is not present on the GPU box).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+D, HQ, HKV, CTX, PT = 128, 32, 8, 32768, 128
+LAYERS = 40
+BYTES_PER_KV_TOKEN = 104          # turbo3 K (48 + 4) + turbo3 V (48 + 4)
+METRIC = "turbo3_decode_attn_kv_tokens_per_s"
+UNIT = "KV-tokens/s"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-i", str(index), "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [s.strip() for s in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        # the busiest half of the samples is "under load"
+        load = sorted(sm)[len(sm) // 2:] if sm else []
+        return {"sm_mhz": statistics.median(load) if load else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU arm: the reference's algorithm (dequantize the cache, then softmax attention) in NumPy
+# ----------------------------------------------------------------------------------------------
+def cpu_reference_run(steps: int, warmup: int, heads: int = HKV):
+    """One step = one layer of the workload: for each of `heads` KV heads, dequantize 32,768 K and V vectors
+    (3-bit PolarQuant, WHT-equivalent dense rotation, fp64 as in the reference) and attend with 4 query heads."""
+    from oracle import tq_oracle as o
+    try:
+        from threadpoolctl import threadpool_info
+        cores = max([p.get("num_threads", 1) for p in threadpool_info()] or [1])
+    except Exception:
+        cores = os.cpu_count() or 1
+    rng = np.random.default_rng(0)
+    a1, a2, _ = o.wht_signs(D, np.random.default_rng(42))
+    b1, b2, _ = o.wht_signs(D, np.random.default_rng(542))
+    rk, rv, c = o.wht_as_dense(a1, a2), o.wht_as_dense(b1, b2), o.centroids(3, D)
+    k = o.rope_rotate(o.synth_keys(CTX, seed=0), np.arange(CTX)).astype(np.float32)
+    v = rng.standard_normal((CTX, D)).astype(np.float32)
+    ki, kn = o.polar_quantize(k, rk, c)
+    vi, vn = o.polar_quantize(v, rv, c)
+    q = rng.standard_normal((HQ // HKV, D)).astype(np.float16).astype(np.float64)
+
+    def step():
+        for _ in range(heads):
+            kh = o.polar_dequantize(ki, kn, rk, c)
+            vh = o.polar_dequantize(vi, vn, rv, c)
+            o.attend_one(q, kh, vh)
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    return {"value": CTX * heads / dt, "ms_per_step": dt * 1e3, "cores": int(cores),
+            "sample": f"{heads} KV heads x {CTX} tokens of one layer per step (dequantize K and V, then attend "
+                      f"with {HQ // HKV} query heads each), {steps} steps"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    r = cpu_reference_run(max(1, min(args.steps, 20)), 1)
+    line = {"metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f64", "data": "synthetic", "impl": "reference",
+            "config": {"workload": "decode attention, 32q/8kv heads, d=128, batch 1, ctx 32768, turbo3 K+V "
+                                   "(reference algorithm: dequantize the cache, then NumPy attention)"},
+            "cpu_baseline": {"value": r["value"], "unit": UNIT, "cores": r["cores"], "kind": "port",
+                             "sample": r["sample"]},
+            "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------------
+def synth_layer(torch, gen, dev, n, seed_shift):
+    """(n, HKV, D) fp16 keys and values on the device, distributions as in the module docstring."""
+    k = torch.randn((n, HKV, D), generator=gen, device=dev)
+    k *= torch.exp(0.5 * torch.randn((n, HKV, 1), generator=gen, device=dev))
+    ch = torch.randperm(D, generator=gen, device=dev)[:4]
+    k[:, :, ch] *= 10.0
+    pos = torch.arange(n, device=dev, dtype=torch.float32)[:, None]
+    inv = 10000.0 ** (-torch.arange(0, D, 2, device=dev, dtype=torch.float32) / D)
+    ang = pos * inv[None, :]
+    cs, sn = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    ke, ko = k[..., 0::2].clone(), k[..., 1::2].clone()
+    k[..., 0::2] = ke * cs - ko * sn
+    k[..., 1::2] = ke * sn + ko * cs
+    v = torch.randn((n, HKV, D), generator=gen, device=dev)
+    return k.half(), v.half()
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    import turboquant_plus_b200 as tq
+    from turboquant_plus_b200.layered import LayeredKVCache
+
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1234 + rank)
+    pages_per_seq = CTX // PT + 1                      # one spare page for the tokens appended by the e2e leg
+    cache = LayeredKVCache(LAYERS, D, HKV, pages_per_seq, PT, ("turbo3", "turbo3"), seed=42, device=dev)
+    bt = torch.randperm(pages_per_seq, generator=gen, device=dev).to(torch.int32)[None, :]
+    pos = torch.arange(CTX, device=dev)
+    slots = bt[0, pos // PT].to(torch.int64) * PT + pos % PT
+
+    # ---- fill the caches through quantize-on-append, timing it (quantize vectors/s) ----
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    q_ms = []
+    for layer in range(LAYERS):
+        k, v = synth_layer(torch, gen, dev, CTX, layer)
+        torch.cuda.synchronize(dev)
+        ev[0].record()
+        cache.append(layer, k, v, slots)
+        ev[1].record()
+        torch.cuda.synchronize(dev)
+        q_ms.append(ev[0].elapsed_time(ev[1]))
+        del k, v
+    append_ms = statistics.median(q_ms[3:])
+    vec_per_s = 2 * CTX * HKV / (append_ms * 1e-3)
+    append_bytes = 2 * CTX * HKV * (D * 2 + 52)        # fp16 in, 52 B out per vector
+    seq_lens = torch.full((1,), CTX, dtype=torch.int32, device=dev)
+    q = torch.randn((LAYERS, 1, HQ, D), generator=gen, device=dev).half()
+    out = torch.empty_like(q)
+    ws = cache.layers[0].workspace(1, HQ, pages_per_seq)
+
+    def one_step(phases=7):
+        for i, layer in enumerate(cache.layers):
+            layer.attend(q[i], bt, seq_lens, out=out[i], workspace=ws, phases=phases)
+
+    one_step()
+    torch.cuda.synchronize(dev)
+    assert cache.layers[-1].kernel_status(ws) == 0, "a bounded wait in the decode kernel gave up"
+    graphs = {}
+    for ph in (7, 2):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            one_step(ph)
+        graphs[ph] = g
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def timed(graph, steps, warmup):
+        for _ in range(warmup):
+            graph.replay()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            graph.replay()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms_step = timed(graphs[7], args.steps, args.warmup)
+    ms_kernel_step = timed(graphs[2], args.steps, args.warmup)
+    clocks = sampler.stop() if sampler else None
+
+    # ---- end to end: host buffers in, host buffers out, one graph replay per step ----
+    st = cache.prepare_decode(1, HQ, bt, seq_lens)
+    qh = torch.randn((LAYERS, 1, HQ, D)).half().pin_memory()
+    kh = torch.randn((LAYERS, 1, HKV, D)).half().pin_memory()
+    vh = torch.randn((LAYERS, 1, HKV, D)).half().pin_memory()
+    oh = torch.empty((LAYERS, 1, HQ, D), dtype=torch.float16).pin_memory()
+    e2e_steps = min(args.steps, PT - 8 - args.warmup)
+    for _ in range(args.warmup):
+        cache.decode_step(qh, kh, vh, oh)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        cache.decode_step(qh, kh, vh, oh)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_ms /= e2e_steps
+    assert torch.isfinite(oh.float()).all()
+
+    if rank == 0:
+        peak, peak_src = peaks()
+        tokens_step = LAYERS * CTX * HKV * world
+        value = tokens_step / (ms_step * 1e-3)
+        kernel_s = ms_kernel_step * 1e-3 / LAYERS
+        achieved = CTX * HKV * BYTES_PER_KV_TOKEN / kernel_s / 1e9
+        cpu = cpu_reference_run(10, 1) if world == 1 else None
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16 tensor-core products, f32 accumulate and softmax", "data": "synthetic",
+            "config": {"workload": f"decode attention, 32q/8kv heads, d=128, batch 1 per GPU, ctx {CTX}, turbo3 K+V, "
+                                   f"fp16 queries; step = {LAYERS} distinct layer caches (1.09 GB packed > L2)",
+                       "l2": "inputs larger than L2", "page_tokens": PT, "layers_per_step": LAYERS,
+                       "parallelism": f"batch-sharded x{world}, no collective"},
+            "kv_tokens_per_s_per_gpu": value / world,
+            "hbm_gbs_algorithmic": value / world * BYTES_PER_KV_TOKEN / 1e9,
+            "frac_of_8tbs": value / world * BYTES_PER_KV_TOKEN / 8e12,
+            "quantize_vectors_per_s": vec_per_s,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": f"{peak_src} copy bandwidth", "traffic": None,
+                         "kernel": "k_decode_attn<3,3>", "us_per_launch": kernel_s * 1e6,
+                         "bytes_per_launch": CTX * HKV * BYTES_PER_KV_TOKEN},
+            "roofline_quantize": {"bound": "hbm", "kernel": "k_quantize_wht<half,3> x2 (K and V append)",
+                                  "achieved": append_bytes / (append_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                                  "frac": append_bytes / (append_ms * 1e-3) / 1e9 / peak,
+                                  "bytes_per_vector": D * 2 + 52},
+            "e2e": {"value": LAYERS * CTX * HKV * world / (e2e_ms * 1e-3), "unit": UNIT,
+                    "ms_per_step": e2e_ms, "steps": e2e_steps,
+                    "h2d_bytes_per_step": int(qh.numel() + kh.numel() + vh.numel()) * 2,
+                    "d2h_bytes_per_step": int(oh.numel()) * 2},
+            "gpu_launches": LAYERS * 3,
+            "clocks": clocks,
+        }
+        if cpu:
+            line["cpu_baseline"] = {"value": cpu["value"], "unit": UNIT, "cores": cpu["cores"], "kind": "port",
+                                    "sample": cpu["sample"]}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -209,6 +209,17 @@ int tq_decode_attn(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cach
                    int32_t num_q_heads, float scale, void* workspace_dev, int64_t workspace_bytes,
                    void* out_dev, int32_t out_dtype, void* stream);
 
+/* tq_decode_attn with its three launches selectable: phases bit 0 = rotate the queries into the
+ * workspace, bit 1 = the split attention kernel, bit 2 = merge the splits and un-rotate into out.
+ * 7 is tq_decode_attn.  Lets a caller re-run the attention kernel alone (timing, or many layers
+ * that share one rotated query); bits must be run in order against the same workspace. */
+int tq_decode_attn_phases(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cache_layout* layout,
+                          const uint8_t* pool_dev, const int32_t* block_table_dev,
+                          int32_t max_pages_per_seq, const int32_t* seq_lens_dev, const void* q_dev,
+                          int32_t q_dtype, int32_t batch, int32_t num_q_heads, float scale,
+                          void* workspace_dev, int64_t workspace_bytes, void* out_dev, int32_t out_dtype,
+                          int32_t phases, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

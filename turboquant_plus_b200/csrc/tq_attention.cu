@@ -551,6 +551,16 @@ extern "C" int tq_decode_attn(const tq_quantizer* kq, const tq_quantizer* vq, co
                               const int32_t* seq_lens_dev, const void* q_dev, int32_t q_dtype, int32_t batch,
                               int32_t num_q_heads, float scale, void* workspace_dev, int64_t workspace_bytes,
                               void* out_dev, int32_t out_dtype, void* stream) {
+  return tq_decode_attn_phases(kq, vq, L, pool_dev, block_table_dev, max_pages_per_seq, seq_lens_dev, q_dev, q_dtype,
+                               batch, num_q_heads, scale, workspace_dev, workspace_bytes, out_dev, out_dtype, 7, stream);
+}
+
+extern "C" int tq_decode_attn_phases(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cache_layout* L,
+                                     const uint8_t* pool_dev, const int32_t* block_table_dev,
+                                     int32_t max_pages_per_seq, const int32_t* seq_lens_dev, const void* q_dev,
+                                     int32_t q_dtype, int32_t batch, int32_t num_q_heads, float scale,
+                                     void* workspace_dev, int64_t workspace_bytes, void* out_dev, int32_t out_dtype,
+                                     int32_t phases, void* stream) {
   TQ_REQUIRE(kq && vq && L, TQ_ERR_INVALID, "tq_decode_attn: quantizers or layout missing");
   TQ_REQUIRE(batch >= 0 && num_q_heads >= 1 && max_pages_per_seq >= 1, TQ_ERR_INVALID, "bad sizes");
   if (batch == 0) return TQ_OK;
@@ -585,17 +595,20 @@ extern "C" int tq_decode_attn(const tq_quantizer* kq, const tq_quantizer* vq, co
 #define TQ_PREP(T)                                                                                                  \
   k_prepare_queries<T><<<pgrid, 128, 0, st>>>((const T*)q_dev, rows, qscale, k_dense, kq->rot32_t, kq->fast, 0,     \
                                               kq->s32_t, qrot, qproj, status)
-  switch (q_dtype) {
-    case TQ_F16: TQ_PREP(__half); break;
-    case TQ_BF16: TQ_PREP(__nv_bfloat16); break;
-    case TQ_F32: TQ_PREP(float); break;
-    default:
-      tq_set_error("queries must be fp16, bf16 or fp32, got dtype %d", q_dtype);
-      return TQ_ERR_UNSUPPORTED;
+  int rc = TQ_OK;
+  if (phases & 1) {
+    switch (q_dtype) {
+      case TQ_F16: TQ_PREP(__half); break;
+      case TQ_BF16: TQ_PREP(__nv_bfloat16); break;
+      case TQ_F32: TQ_PREP(float); break;
+      default:
+        tq_set_error("queries must be fp16, bf16 or fp32, got dtype %d", q_dtype);
+        return TQ_ERR_UNSUPPORTED;
+    }
+    rc = tq_launch_check("k_prepare_queries");
+    if (rc != TQ_OK) return rc;
   }
 #undef TQ_PREP
-  int rc = tq_launch_check("k_prepare_queries");
-  if (rc != TQ_OK) return rc;
 
   AttnParams P;
   memset(&P, 0, sizeof(P));
@@ -617,10 +630,13 @@ extern "C" int tq_decode_attn(const tq_quantizer* kq, const tq_quantizer* vq, co
   P.L = *L;
 #define TQ_ATT(K, V) \
   if (kb == K && vb == V) rc = launch_attn<K, V>(P, kq->fast, vq->fast, st);
-  rc = TQ_ERR_UNSUPPORTED;
-  TQ_ATT(2, 2) TQ_ATT(2, 3) TQ_ATT(2, 4) TQ_ATT(3, 2) TQ_ATT(3, 3) TQ_ATT(3, 4) TQ_ATT(4, 2) TQ_ATT(4, 3) TQ_ATT(4, 4)
+  if (phases & 2) {
+    rc = TQ_ERR_UNSUPPORTED;
+    TQ_ATT(2, 2) TQ_ATT(2, 3) TQ_ATT(2, 4) TQ_ATT(3, 2) TQ_ATT(3, 3) TQ_ATT(3, 4) TQ_ATT(4, 2) TQ_ATT(4, 3) TQ_ATT(4, 4)
+    if (rc != TQ_OK) return rc;
+  }
 #undef TQ_ATT
-  if (rc != TQ_OK) return rc;
+  if (!(phases & 4)) return TQ_OK;
 
 #define TQ_COMB(T)                                                                                             \
   k_decode_combine<T><<<(unsigned)rows, 128, 0, st>>>(P.part_o, P.part_ml, seq_lens_dev, num_q_heads,          \

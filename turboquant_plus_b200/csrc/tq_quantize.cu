@@ -260,38 +260,33 @@ int tq_quantize_wht_launch(const TqFast& f, const void* x, int32_t dtype, int64_
 // NumPy's pairwise float summation (what np.linalg.norm(x, axis=1) runs for each contiguous row):
 // fewer than 8 terms are added in order, up to 128 terms use 8 interleaved accumulators combined
 // as ((r0+r1)+(r2+r3))+((r4+r5)+(r6+r7)), longer rows are split in halves (a multiple of 8).
+// The square and the add are kept as separately rounded operations (no FMA contraction), as on the host.
+__device__ __forceinline__ float tq_add_rn(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ double tq_add_rn(double a, double b) { return __dadd_rn(a, b); }
+__device__ __forceinline__ float tq_sq_rn(float a) { return __fmul_rn(a, a); }
+__device__ __forceinline__ double tq_sq_rn(double a) { return __dmul_rn(a, a); }
+
 template <typename A>
 __device__ A tq_pairwise_sq(const double* xs, int stride, int n) {
   if (n < 8) {
-    A r = (A)0;  // NumPy starts from the first element; adding it to +0 first is the same value
-    for (int i = 0; i < n; ++i) {
-      A t = (A)xs[(size_t)i * stride];
-      r = r + t * t;
-    }
+    A r = (A)0;  // adding the first term to +0 gives the first term
+    for (int i = 0; i < n; ++i) r = tq_add_rn(r, tq_sq_rn((A)xs[(size_t)i * stride]));
     return r;
   }
   if (n <= 128) {
     A r[8];
-    for (int j = 0; j < 8; ++j) {
-      A t = (A)xs[(size_t)j * stride];
-      r[j] = t * t;
-    }
+    for (int j = 0; j < 8; ++j) r[j] = tq_sq_rn((A)xs[(size_t)j * stride]);
     int i = 8;
     for (; i < n - (n % 8); i += 8)
-      for (int j = 0; j < 8; ++j) {
-        A t = (A)xs[(size_t)(i + j) * stride];
-        r[j] = r[j] + t * t;
-      }
-    A res = ((r[0] + r[1]) + (r[2] + r[3])) + ((r[4] + r[5]) + (r[6] + r[7]));
-    for (; i < n; ++i) {
-      A t = (A)xs[(size_t)i * stride];
-      res = res + t * t;
-    }
+      for (int j = 0; j < 8; ++j) r[j] = tq_add_rn(r[j], tq_sq_rn((A)xs[(size_t)(i + j) * stride]));
+    A res = tq_add_rn(tq_add_rn(tq_add_rn(r[0], r[1]), tq_add_rn(r[2], r[3])),
+                      tq_add_rn(tq_add_rn(r[4], r[5]), tq_add_rn(r[6], r[7])));
+    for (; i < n; ++i) res = tq_add_rn(res, tq_sq_rn((A)xs[(size_t)i * stride]));
     return res;
   }
   int n2 = n / 2;
   n2 -= n2 % 8;
-  return tq_pairwise_sq<A>(xs, stride, n2) + tq_pairwise_sq<A>(xs + (size_t)n2 * stride, stride, n - n2);
+  return tq_add_rn(tq_pairwise_sq<A>(xs, stride, n2), tq_pairwise_sq<A>(xs + (size_t)n2 * stride, stride, n - n2));
 }
 
 template <typename T> __device__ __forceinline__ double tq_to_double(T v);
@@ -329,9 +324,17 @@ __global__ void __launch_bounds__(128) k_quantize_dense(const TqDenseArgs a, con
   __syncthreads();
   if (tid < TV) {
     // the reference takes the norm in the input's own precision (fp32 input -> fp32 arithmetic)
+    // Same shape as NumPy's add.reduce (first term + pairwise sum of the rest).  SIMD builds of NumPy
+    // order the partial sums differently, so the norm agrees to an ulp or two, not bit for bit.
     double nrm;
-    if (WIDE) nrm = sqrt(tq_pairwise_sq<double>(xs + tid, TV, d));
-    else nrm = (double)sqrtf(tq_pairwise_sq<float>(xs + tid, TV, d));
+    if (WIDE) {
+      const double s0 = tq_sq_rn(xs[tid]);
+      nrm = sqrt(d > 1 ? tq_add_rn(s0, tq_pairwise_sq<double>(xs + TV + tid, TV, d - 1)) : s0);
+    } else {
+      const float x0 = (float)xs[tid];
+      const float s0 = tq_sq_rn(x0);
+      nrm = (double)sqrtf(d > 1 ? tq_add_rn(s0, tq_pairwise_sq<float>(xs + TV + tid, TV, d - 1)) : s0);
+    }
     s_norm[tid] = nrm;
     s_normf[tid] = (float)nrm;
     s_red[tid] = 0.0;

@@ -1,0 +1,105 @@
+"""A stack of per-layer paged caches with a per-layer (K format, V format) table, and a decode step
+that takes host buffers: copy in, quantize-on-append + attention for every layer (one CUDA graph),
+copy out.  Covers asymmetric K/V formats and boundary layers kept at higher precision
+(the reference's layer-aware policy: docs/papers/layer-aware-v-compression.md:25-28).
+"""
+from __future__ import annotations
+
+from . import _native as nv
+from .paged import PagedKVCache
+
+
+def boundary_format_table(num_layers: int, inner=("q8_0", "turbo2"), boundary=("q8_0", "q8_0"), keep: int = 2):
+    """First and last ``keep`` layers use ``boundary``, the rest ``inner``."""
+    return [boundary if (i < keep or i >= num_layers - keep) else inner for i in range(num_layers)]
+
+
+class LayeredKVCache:
+    def __init__(self, num_layers: int, head_dim: int, num_kv_heads: int, num_pages: int, page_tokens: int = 128,
+                 formats=("turbo3", "turbo3"), seed: int = 42, norm_correction: bool = True,
+                 rotation: str = "wht", device=None):
+        if isinstance(formats[0], str):
+            formats = [tuple(formats)] * num_layers
+        assert len(formats) == num_layers
+        self.formats = [tuple(f) for f in formats]
+        self.layers = []
+        shared = {}
+        for kf, vf in self.formats:
+            donor = shared.get((kf, vf))
+            layer = PagedKVCache(head_dim, num_kv_heads, num_pages, page_tokens, kf, vf, seed=seed,
+                                 norm_correction=norm_correction, rotation=rotation, device=device,
+                                 k_quantizer=donor.k_quantizer if donor else None,
+                                 v_quantizer=donor.v_quantizer if donor else None)
+            shared.setdefault((kf, vf), layer)
+            self.layers.append(layer)
+        self.device = self.layers[0].device
+        self.num_layers, self.head_dim, self.num_kv_heads = num_layers, head_dim, num_kv_heads
+        self.page_tokens = page_tokens
+        self._step = None
+
+    def bytes_per_token_all_layers(self) -> int:
+        return sum(layer.bytes_per_token for layer in self.layers)
+
+    def append(self, layer: int, k, v, slot_mapping):
+        self.layers[layer].append(k, v, slot_mapping)
+
+    def attend(self, layer: int, q, block_table, seq_lens, **kw):
+        return self.layers[layer].attend(q, block_table, seq_lens, **kw)
+
+    # ------------------------------------------------------------------------------------------
+    def prepare_decode(self, batch: int, num_q_heads: int, block_table, seq_lens, dtype=None):
+        """Allocates the static device buffers of a decode step and captures the per-layer launches
+        (append one token per sequence, attend) into one CUDA graph.  ``block_table`` must already hold
+        a page for position seq_lens[b] of every sequence."""
+        torch = nv.require_cuda()
+        dtype = dtype or torch.float16
+        dev, L, d = self.device, self.num_layers, self.head_dim
+        st = {
+            "q": torch.zeros((L, batch, num_q_heads, d), dtype=dtype, device=dev),
+            "k": torch.zeros((L, batch, self.num_kv_heads, d), dtype=dtype, device=dev),
+            "v": torch.zeros((L, batch, self.num_kv_heads, d), dtype=dtype, device=dev),
+            "out": torch.zeros((L, batch, num_q_heads, d), dtype=dtype, device=dev),
+            "bt": block_table.to(device=dev, dtype=torch.int32).contiguous(),
+            "len": seq_lens.to(device=dev, dtype=torch.int32).clone(),
+            "slots": torch.zeros((batch,), dtype=torch.int64, device=dev),
+            "rows": torch.arange(batch, device=dev),
+        }
+        ws = self.layers[0].workspace(batch, num_q_heads, st["bt"].shape[1])
+
+        def body():
+            pos = st["len"].to(torch.int64)
+            page = st["bt"][st["rows"], pos // self.page_tokens].to(torch.int64)
+            st["slots"].copy_(page * self.page_tokens + pos % self.page_tokens)
+            st["len"].add_(1)
+            for i, layer in enumerate(self.layers):
+                layer.append(st["k"][i], st["v"][i], st["slots"])
+                layer.attend(st["q"][i], st["bt"], st["len"], out=st["out"][i], workspace=ws)
+
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):      # warm-up outside capture (sets kernel attributes, fills caches)
+            saved = st["len"].clone()
+            body()
+            st["len"].copy_(saved)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            body()
+        st["len"].copy_(saved)
+        st["graph"] = graph
+        self._step = st
+        return st
+
+    def decode_step(self, q_host, k_host, v_host, out_host):
+        """One decode step from host buffers (pinned tensors shaped like the static device buffers):
+        H2D of the step's queries and new K/V rows, the captured graph, D2H of the outputs."""
+        torch = nv.require_cuda()
+        st = self._step
+        st["q"].copy_(q_host, non_blocking=True)
+        st["k"].copy_(k_host, non_blocking=True)
+        st["v"].copy_(v_host, non_blocking=True)
+        st["graph"].replay()
+        out_host.copy_(st["out"], non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        return out_host

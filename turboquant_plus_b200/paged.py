@@ -126,7 +126,7 @@ class PagedKVCache:
             self._ws = torch.empty((int(need),), dtype=torch.uint8, device=self.device)
         return self._ws
 
-    def attend(self, q, block_table, seq_lens, scale=None, out=None, workspace=None):
+    def attend(self, q, block_table, seq_lens, scale=None, out=None, workspace=None, phases=7):
         """q: (batch, num_q_heads, head_dim) CUDA tensor; block_table: (batch, max_pages) int32 page
         numbers; seq_lens: (batch,) int32.  Returns (batch, num_q_heads, head_dim) in q's dtype."""
         torch = nv.require_cuda()
@@ -139,14 +139,17 @@ class PagedKVCache:
         if out is None:
             out = torch.empty_like(q)
         with torch.cuda.device(self.device):
-            nv.call("tq_decode_attn", self._handle(self.k_quantizer), self._handle(self.v_quantizer),
+            nv.call("tq_decode_attn_phases", self._handle(self.k_quantizer), self._handle(self.v_quantizer),
                     C.byref(self.layout), nv.ptr(self.pool), nv.ptr(bt), bt.shape[1], nv.ptr(sl), nv.ptr(q),
                     nv.torch_dtype_code(q.dtype), bsz, hq, float(scale) if scale else 0.0, nv.ptr(ws), ws.numel(),
-                    nv.ptr(out), nv.torch_dtype_code(out.dtype), nv.stream_ptr())
+                    nv.ptr(out), nv.torch_dtype_code(out.dtype), int(phases), nv.stream_ptr())
         return out
 
-    def kernel_status(self) -> int:
+    def kernel_status(self, workspace=None) -> int:
         """0 after a clean decode; 1 if a bounded wait inside the kernel gave up (synchronises)."""
+        ws = self._ws if workspace is None else workspace
+        if ws is None:
+            return 0
         st = C.c_int32(0)
-        nv.call("tq_decode_status_sync", nv.ptr(self._ws), self._ws.numel(), C.byref(st))
+        nv.call("tq_decode_status_sync", nv.ptr(ws), ws.numel(), C.byref(st))
         return st.value
