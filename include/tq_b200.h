@@ -220,6 +220,39 @@ int tq_decode_attn_phases(const tq_quantizer* kq, const tq_quantizer* vq, const 
                           void* workspace_dev, int64_t workspace_bytes, void* out_dev, int32_t out_dtype,
                           int32_t phases, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * tq_decode_attn_static: tq_decode_attn for callers that cannot allocate device memory.
+ * (No counterpart in the reference, which has neither an attention kernel nor device memory.)
+ *
+ * Who this is for: code that holds device pointers to its inputs and outputs but has no way to
+ * obtain a scratch buffer -- a plugin loaded into a serving process whose memory pool already owns
+ * all of HBM, a loop that cannot afford the device-wide synchronisation cudaMalloc brings, or a
+ * foreign-language host that binds this header and owns no allocator.  Instead of a
+ * caller-provided workspace, the split partials and rotated queries go to an array compiled into
+ * the library: TQ_DECODE_STATIC_SCRATCH_BYTES (8 MiB) per GPU that loads the library, held until
+ * the process exits.  The call itself allocates and frees nothing.
+ *
+ *   - Shapes whose scratch need (tq_decode_workspace_bytes) exceeds 8 MiB are refused with
+ *     TQ_ERR_TOO_LARGE and a message naming both numbers; nothing is launched.  Batch 1 with
+ *     32 query heads over 256 pages needs about 0.7 MB; batch 256 with 32 heads does not fit.
+ *   - The first call on each device looks up the array's device address (one
+ *     cudaGetSymbolAddress, with that device current).  Make that first call before any stream
+ *     capture begins on the device.
+ *   - All calls on a device share the one array, and it keeps whatever the previous call left.
+ *     The kernels do not depend on old contents (the status word is reset by the first kernel of
+ *     every call, every partial that is read was written in the same call), but two calls that
+ *     overlap on the GPU -- different streams, or different host threads -- race on it.  Issue
+ *     calls that use this entry point on one stream per device, or order them with events.
+ *   - Arguments and results are those of tq_decode_attn without workspace_dev/workspace_bytes;
+ *     the outputs are bit-identical to tq_decode_attn on the same inputs.
+ * ------------------------------------------------------------------------------------------ */
+#define TQ_DECODE_STATIC_SCRATCH_BYTES (8 * 1024 * 1024)
+int tq_decode_attn_static(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cache_layout* layout,
+                          const uint8_t* pool_dev, const int32_t* block_table_dev,
+                          int32_t max_pages_per_seq, const int32_t* seq_lens_dev, const void* q_dev,
+                          int32_t q_dtype, int32_t batch, int32_t num_q_heads, float scale,
+                          void* out_dev, int32_t out_dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -653,3 +653,68 @@ extern "C" int tq_decode_attn_phases(const tq_quantizer* kq, const tq_quantizer*
 #undef TQ_COMB
   return tq_launch_check("k_decode_combine");
 }
+
+// ------------------------------------------------------------------------------------------
+// Decode attention for callers that may not allocate device memory.
+//
+// The split partials and rotated queries of tq_decode_attn normally live in a buffer the caller
+// allocates.  Some callers cannot do that: a plugin that runs inside another runtime which has
+// already handed every byte of HBM to its own pool, a latency-bound serving loop in which
+// cudaMalloc's implicit device-wide synchronisation is not acceptable, or a host language binding
+// that has raw pointers to inputs and outputs but no allocator of its own.  For them the scratch is
+// this fixed array, part of the library image: every GPU that loads the library holds
+// TQ_STATIC_SCRATCH_BYTES of it until the process exits.
+//
+// In host code `g_static_scratch` is only a handle for the symbol, not an address the GPU can use;
+// the device address comes from cudaGetSymbolAddress, looked up once per device below.
+// ------------------------------------------------------------------------------------------
+#include <mutex>
+
+#define TQ_STATIC_SCRATCH_BYTES TQ_DECODE_STATIC_SCRATCH_BYTES  // 8 MiB, stated in tq_b200.h
+#define TQ_STATIC_MAX_DEVICES 64
+
+static __device__ __align__(256) unsigned char g_static_scratch[TQ_STATIC_SCRATCH_BYTES];
+static void* g_static_scratch_addr[TQ_STATIC_MAX_DEVICES];  // device address of the array, per device
+static std::mutex g_static_scratch_mutex;
+
+// Device address of g_static_scratch on the current device (set-up on the first call per device).
+static int static_scratch_for_current_device(void** out) {
+  int dev = -1;
+  TQ_CUDA(cudaGetDevice(&dev));
+  TQ_REQUIRE(dev >= 0 && dev < TQ_STATIC_MAX_DEVICES, TQ_ERR_UNSUPPORTED, "device ordinal %d beyond %d", dev,
+             TQ_STATIC_MAX_DEVICES);
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void**)&p, g_static_scratch);
+    if (e != cudaSuccess) return tq_cuda_fail(e, "cudaGetSymbolAddress(g_static_scratch)");
+    TQ_REQUIRE(p != nullptr && tq_aligned(p, 256), TQ_ERR_CUDA, "static scratch has no usable device address");
+    g_static_scratch_addr[dev] = p;
+  }
+  *out = g_static_scratch_addr[dev];
+  return TQ_OK;
+}
+
+extern "C" int tq_decode_attn_static(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cache_layout* L,
+                                     const uint8_t* pool_dev, const int32_t* block_table_dev,
+                                     int32_t max_pages_per_seq, const int32_t* seq_lens_dev, const void* q_dev,
+                                     int32_t q_dtype, int32_t batch, int32_t num_q_heads, float scale, void* out_dev,
+                                     int32_t out_dtype, void* stream) {
+  TQ_REQUIRE(L, TQ_ERR_INVALID, "tq_decode_attn_static: layout missing");
+  TQ_REQUIRE(batch >= 0 && num_q_heads >= 1 && max_pages_per_seq >= 1, TQ_ERR_INVALID, "bad sizes");
+  if (batch == 0) return TQ_OK;
+  const int64_t need = tq_decode_workspace_bytes(batch, num_q_heads, L->num_kv_heads, max_pages_per_seq);
+  TQ_REQUIRE(need > 0, TQ_ERR_INVALID, "bad sizes");
+  TQ_REQUIRE(need <= TQ_STATIC_SCRATCH_BYTES, TQ_ERR_TOO_LARGE,
+             "tq_decode_attn_static: this shape needs %lld bytes of scratch, the built-in array holds %d "
+             "(batch %d x %d query heads x %d pages); use tq_decode_attn with a caller-owned workspace",
+             (long long)need, TQ_STATIC_SCRATCH_BYTES, batch, num_q_heads, max_pages_per_seq);
+  void* scratch = nullptr;
+  int rc = static_scratch_for_current_device(&scratch);
+  if (rc != TQ_OK) return rc;
+  // Nothing in the scratch has to start at zero: the query kernel resets the status word, and every
+  // partial that the merge kernel reads is written by the attention kernel of the same call.
+  return tq_decode_attn_phases(kq, vq, L, pool_dev, block_table_dev, max_pages_per_seq, seq_lens_dev, q_dev, q_dtype,
+                               batch, num_q_heads, scale, scratch, TQ_STATIC_SCRATCH_BYTES, out_dev, out_dtype, 7,
+                               stream);
+}
