@@ -189,6 +189,10 @@ int tq_cache_store(const tq_cache_layout* layout, uint8_t* pool_dev, int32_t whi
 /* Scratch for tq_decode_attn (split partials + rotated queries), bytes; 256-byte aligned buffer. */
 int64_t tq_decode_workspace_bytes(int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
                                   int32_t max_pages_per_seq);
+/* A workspace must be initialised once after it is allocated (or be zero-filled): its last 256 KB hold
+ * the per-(sequence, KV head) tickets with which the last split to finish elects itself to merge the
+ * others, and a status word.  Every call leaves the tickets at zero again.  Enqueues one memset. */
+int tq_decode_workspace_init(void* workspace_dev, int64_t workspace_bytes, void* stream);
 /* After a synchronisation: 0 if the last tq_decode_attn that used this workspace finished cleanly,
  * 1 if a bounded wait inside the kernel gave up (results invalid). Copies 4 bytes to the host. */
 int tq_decode_status_sync(const void* workspace_dev, int64_t workspace_bytes, int32_t* status_out);
@@ -209,10 +213,11 @@ int tq_decode_attn(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cach
                    int32_t num_q_heads, float scale, void* workspace_dev, int64_t workspace_bytes,
                    void* out_dev, int32_t out_dtype, void* stream);
 
-/* tq_decode_attn with its three launches selectable: phases bit 0 = rotate the queries into the
- * workspace, bit 1 = the split attention kernel, bit 2 = merge the splits and un-rotate into out.
- * 7 is tq_decode_attn.  Lets a caller re-run the attention kernel alone (timing, or many layers
- * that share one rotated query); bits must be run in order against the same workspace. */
+/* tq_decode_attn with its launches selectable: phases bit 0 = the dense-rotation query kernel (only
+ * launched when the K quantizer has a dense rotation; sign-WHT rotations are applied inside the
+ * attention kernel), bit 1 = the attention kernel (split attention, merge by the last split to finish,
+ * un-rotation).  3 is tq_decode_attn.  Lets a caller re-run the attention kernel alone (timing, or
+ * many layers that share one rotated query); bits run in order against the same workspace. */
 int tq_decode_attn_phases(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cache_layout* layout,
                           const uint8_t* pool_dev, const int32_t* block_table_dev,
                           int32_t max_pages_per_seq, const int32_t* seq_lens_dev, const void* q_dev,

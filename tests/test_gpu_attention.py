@@ -49,27 +49,32 @@ def oracle_attention(cache, ks, vs, q, seq_lens):
 
 
 @pytest.mark.parametrize("mode", ["wht", "dense"])
-def test_attention_golden(tq, g_kv, mode):
-    """Fixture produced by the reference: compress -> decompress -> softmax(q k^T / sqrt d) v."""
+@pytest.mark.parametrize("kk", ["mse", "prod"])
+def test_attention_golden(tq, g_kv, mode, kk):
+    """Fixture produced by the reference: compress -> decompress -> softmax(q k^T / sqrt d) v.
+    kk = "prod": K through TurboQuant (2-bit PolarQuant + QJL), exactly KVCacheCompressor(k_bits=3)."""
     import torch
     k, v, q = g_kv["k"], g_kv["v"], g_kv["q"]          # (1, 2, 200, 128) x2, (8, 128) fp16
-    cache = tq.PagedKVCache(D, 2, num_pages=7, k_format="turbo3", v_format="turbo3", seed=42, rotation=mode)
+    cache = tq.PagedKVCache(D, 2, num_pages=7, k_format="turbo3" if kk == "mse" else "prod3", v_format="turbo3",
+                            seed=42, rotation=mode)
     ks = [np.ascontiguousarray(k[0].transpose(1, 0, 2))]
     vs = [np.ascontiguousarray(v[0].transpose(1, 0, 2))]
     bt = fill_cache(cache, ks, vs, [200], np.random.default_rng(0))
     out = cache.attend(torch.as_tensor(q[None]).cuda(), bt, torch.tensor([200]))
     assert cache.kernel_status() == 0
-    err = max_rel(out[0].float().cpu().numpy(), g_kv[f"{mode}_mse_out"])
-    print(f"{mode} turbo3/turbo3 vs reference fixture: max-rel {err:.2e}")
+    err = max_rel(out[0].float().cpu().numpy(), g_kv[f"{mode}_{kk}_out"])
+    print(f"{mode} {cache.k_format}/turbo3 vs reference fixture: max-rel {err:.2e}")
     assert err < TOL + 1e-3          # fp16 output rounding of the fixture comparison (4.9e-4) included
     out32 = cache.attend(torch.as_tensor(q[None]).cuda().float(), bt, torch.tensor([200]))
-    err = max_rel(out32[0].cpu().numpy(), g_kv[f"{mode}_mse_out"])
+    err = max_rel(out32[0].cpu().numpy(), g_kv[f"{mode}_{kk}_out"])
     print(f"   fp32 output: max-rel {err:.2e}")
     assert err < TOL
 
 
 @pytest.mark.parametrize("kf,vf", [("turbo3", "turbo3"), ("turbo2", "turbo2"), ("turbo4", "turbo4"),
-                                   ("turbo4", "turbo2"), ("turbo2", "turbo3"), ("turbo3", "turbo4")])
+                                   ("turbo4", "turbo2"), ("turbo2", "turbo3"), ("turbo3", "turbo4"),
+                                   ("q8_0", "turbo2"), ("q8_0", "q8_0"), ("q8_0", "turbo4"),
+                                   ("prod3", "turbo3"), ("prod2", "turbo2"), ("prod4", "turbo4"), ("prod3", "turbo2")])
 def test_ragged_paged_batch(tq, kf, vf):
     """Ragged lengths (1, page edges, several pages), shuffled pages, 4 query heads per KV head."""
     import torch
@@ -168,3 +173,46 @@ def test_append_matches_bulk_quantize(tq):
             assert rec[L.v_scale_off + within * 4: L.v_scale_off + within * 4 + 4].view(np.float32)[0] == \
                 vq["scale"][row].item()
     assert cache.bytes_per_token == 104
+
+
+def test_q8_0_and_prod_records_match_oracle(tq):
+    """Bytes written by quantize-on-append for q8_0 (against the restated block rule) and PROD (sign sketch and
+    residual scale against the oracle)."""
+    import torch
+    rng = np.random.default_rng(9)
+    hkv, n = 2, 200
+    cache = tq.PagedKVCache(D, hkv, num_pages=2, k_format="q8_0", v_format="q8_0")
+    k = o.synth_keys(n * hkv, seed=4).reshape(n, hkv, D)
+    k[3] = 0
+    v = rng.standard_normal((n, hkv, D)).astype(np.float32)
+    slots = torch.arange(n, dtype=torch.int64)
+    cache.append(torch.as_tensor(k).cuda(), torch.as_tensor(v).cuda(), slots)
+    pool, L = cache.pool.cpu().numpy(), cache.layout
+    for name, x, io, so in (("k", k, L.k_idx_off, L.k_scale_off), ("v", v, L.v_idx_off, L.v_scale_off)):
+        q_ref, s_ref = o.q8_0_quantize(x.reshape(-1, D))
+        for t in (0, 3, 127, 128, 199):
+            page, w = divmod(t, 128)
+            for h in range(hkv):
+                rec = pool[page, h]
+                assert np.array_equal(rec[io + w * 128: io + w * 128 + 128].view(np.int8), q_ref[t * hkv + h]), name
+                assert np.array_equal(rec[so + w * 8: so + w * 8 + 8].view(np.float16), s_ref[t * hkv + h]), name
+    assert cache.bytes_per_token == 272
+    cache = tq.PagedKVCache(D, hkv, num_pages=2, k_format="prod3", v_format="turbo3", seed=42)
+    cache.append(torch.as_tensor(k).cuda(), torch.as_tensor(v).cuda(), slots)
+    pool, L = cache.pool.cpu().numpy(), cache.layout
+    kq = cache.k_quantizer
+    code = o.prod_quantize(k.reshape(-1, D), kq.polar_quant.rotation, kq.polar_quant.centroids, kq.qjl.S, 3)
+    bits_ref = o.pack_signs(code.qjl_signs)
+    flips = 0
+    for t in range(n):
+        page, w = divmod(t, 128)
+        for h in range(hkv):
+            rec, row = pool[page, h], t * hkv + h
+            got_idx = rec[L.k_idx_off + w * 32: L.k_idx_off + w * 32 + 32]
+            if not np.array_equal(got_idx, o.pack_idx(code.mse_indices[row], 2)):
+                continue                                   # a near-boundary index moves the residual
+            flips += int(np.unpackbits(rec[L.k_qjl_off + w * 16: L.k_qjl_off + w * 16 + 16] ^ bits_ref[row]).sum())
+            rs = rec[L.k_rscale_off + w * 4: L.k_rscale_off + w * 4 + 4].view(np.float32)[0]
+            assert abs(rs - code.residual_norms[row] * o.QJL_CONST / np.sqrt(D)) <= 2e-5 * abs(rs) + 1e-30
+    assert flips <= 4
+    assert cache.bytes_per_token == 108

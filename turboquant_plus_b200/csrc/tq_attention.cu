@@ -1,19 +1,26 @@
-// Decode attention straight off the packed paged cache, and quantize-on-append.
+// Decode attention straight off the packed paged cache.
 //
-//   k_prepare_queries  rotates each query once by the K rotation (and projects it by the QJL matrix
-//                      for PROD formats), folds in softmax scale * log2(e) and the fp16 LUT factor.
-//   k_decode_attn      grid (split, kv head, sequence).  A CTA walks its range of pages; each page
-//                      record (packed K | K scales | packed V | V scales) is brought into shared memory
-//                      with one bulk async copy (cp.async.bulk + mbarrier, 3 stages).  Eight warps
-//                      take 16 tokens each per page: pairs of packed indices are turned into fp16
-//                      centroid pairs through a lane-replicated (bank-conflict-free) table, fed to
-//                      mma.sync.m16n8k16 as the A operand (tokens on M, the <= 8 query heads of the
-//                      GQA group on N), softmax is kept online in the log2 domain, the probabilities
-//                      are transposed in registers (movmatrix) and multiply V^T tiles dequantized the
-//                      same way.  tcgen05 is deliberately not used here: with 4..8 query rows the
-//                      work per byte is tiny and the cost is the dequantization ALU, not the MMA.
-//   k_decode_combine   merges the split partials (deterministic order) and rotates the output back
-//                      from V's rotated space.
+//   k_decode_attn<KK,VK>  grid (split, kv head, sequence), 256 threads, 2 CTAs per SM.
+//     prologue  the CTA's <= 8 query heads are rotated by the K rotation (one warp per head: sign,
+//               128-point Walsh-Hadamard in registers + shuffles, sign) and, for PROD keys, projected by
+//               the QJL sign-WHT; scale * log2(e) and the fp16 table factor are folded in.  Dense
+//               rotations are applied by k_prepare_queries beforehand instead.
+//     main loop the CTA walks its range of pages; each (page, head) record (packed K | K scales |
+//               [sign sketch | residual scales] | packed V | V scales) arrives in shared memory through one
+//               bulk async copy (cp.async.bulk + mbarrier, 3 stages, bounded waits).  Eight warps take 16
+//               tokens each: 2b-bit index *pairs* become fp16 centroid pairs through a lane-replicated
+//               (bank-conflict-free) table whose address is one shift + one logic op, and feed
+//               mma.sync.m16n8k16 as the A operand (tokens on M, query heads of the GQA group on N, query
+//               split into hi+lo fp16).  q8_0 operands are int8 -> fp16 by byte permute + one subtract.
+//               Softmax is online in the log2 domain; probabilities * V scale are transposed in registers
+//               (movmatrix) and multiply V^T tiles dequantized the same way; O stays in V's rotated space.
+//     epilogue  the CTA stores its split partial; the last CTA of a (sequence, kv head) to finish -- a
+//               ticket taken with one atomicAdd, nobody waits -- merges the splits in fixed order, rotates
+//               back (WHT per warp, or dense) and writes the output.  One launch per call in WHT mode.
+//   tcgen05 is deliberately not used here: with 4..8 query rows the MMA work is a few percent of the tensor
+//   pipe; the cost is forming the operands.
+#include <mutex>
+
 #include "tq_internal.cuh"
 
 namespace {
@@ -22,7 +29,9 @@ constexpr int ATT_THREADS = 256;
 constexpr int ATT_WARPS = 8;
 constexpr int ATT_STAGES = 3;
 constexpr int MAX_G = 8;  // query heads per KV head handled by one N=8 MMA tile
-constexpr uint32_t WAIT_TRIES = 1u << 22;
+constexpr long long WAIT_CYCLES = 1LL << 30;  // ~0.5 s at the SM clock: upper bound of any single wait
+constexpr int MAX_TICKETS = 65536;                    // (sequence, kv head) pairs per call
+constexpr size_t TAIL_BYTES = (size_t)MAX_TICKETS * 4 + 256;  // tickets + status word at the end of a workspace
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -47,15 +56,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after WAIT_TRIES polls and reports it instead of spinning forever.
+// Bounded wait: polls until the phase completes or WAIT_CYCLES SM clocks have passed, then gives up and
+// reports it instead of spinning forever.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < WAIT_TRIES; ++i)
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (clock64() - t0 < WAIT_CYCLES)
     if (mbar_try_wait(bar, parity)) return true;
   return false;
 }
 
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
+  // volatile on purpose: a warp-collective instruction must not be sunk into, or speculated out of,
+  // code that only some lanes execute
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -74,153 +88,372 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
 }
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  // not volatile: the tables are constant while the main loop runs, so loads may be hoisted and batched
+  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("sub.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
 
 struct AttnParams {
   const uint8_t* pool;
   const int32_t* block_table;
   const int32_t* seq_lens;
-  const float* qrot;   // [B][Hq][128]  K-rotated, pre-scaled queries
-  const float* qproj;  // [B][Hq][128]  S-projected queries (PROD), pre-scaled
+  const void* q;       // raw queries [B][Hq][128] (q_dtype), used when the rotation is applied in the prologue
+  const float* qrot;   // [B][Hq][128] rotated, pre-scaled queries (dense rotations only)
+  const float* qproj;  // [B][Hq][128] S-projected queries (dense PROD only)
   float* part_o;       // [B][Hq][S][128]
   float* part_ml;      // [B][Hq][S][2]
+  int32_t* tickets;    // [B*Hkv], zero between calls
   int32_t* status;
+  void* out;           // [B][Hq][128] (out_dtype)
+  const float* v_rot;  // dense V rotation, row-major fp32 (nullptr: sign-WHT or identity)
+  float qscale;        // softmax scale * log2(e)
+  int32_t q_dtype, out_dtype;
+  int32_t k_pre;       // 1: queries come rotated from qrot/qproj
+  int32_t k_ident, v_ident;  // identity rotation (q8_0 tensors)
   int32_t max_pages, batch, hq, hkv, group, chunk_pages, num_splits;
+  int32_t stages;      // 2 or 3 page records in flight per CTA
   tq_cache_layout L;
 };
 
-// Pair table: entry (ia << BITS | ib) holds half2(alpha*c[ia], alpha*c[ib]).  Tables of <= 64 entries
-// are replicated per lane (word index = entry*32 + lane) so that every lookup hits its own bank.
+// ---- kinds ------------------------------------------------------------------------------------
+// KK / VK: 2,3,4 = turbo bits; 8 = q8_0; 18,19,20 = PROD with 1,2,3 PolarQuant bits + sign sketch.
+template <int KIND> struct Kind {
+  static constexpr bool Q8 = KIND == 8;
+  static constexpr bool PROD = KIND >= 18;
+  static constexpr int BITS = Q8 ? 0 : (PROD ? KIND - 17 : KIND);
+};
+
+// Pair table: entry (ia << BITS | ib) holds half2(alpha*c[ia], alpha*c[ib]).  Tables of <= 64 entries are
+// replicated per lane (byte address = entry*128 + lane*4) so that every lookup hits its own bank; the table is
+// aligned to its size so that the address is (field bits) | (lane base).
 template <int BITS> struct PairLut {
-  static constexpr int ENTRIES = 1 << (2 * BITS);
+  static constexpr int ENTRIES = BITS ? (1 << (2 * BITS)) : 0;
   static constexpr bool REPL = ENTRIES <= 64;
-  static constexpr int WORDS = REPL ? ENTRIES * 32 : ENTRIES;
-  static __device__ __forceinline__ void fill(uint32_t* lut, const TqFast& f, int tid, int nthreads) {
-    for (int i = tid; i < WORDS; i += nthreads) {
-      const int e = REPL ? (i >> 5) : i;
-      const uint32_t lo = f.cent16[e >> BITS], hi = f.cent16[e & ((1 << BITS) - 1)];
-      lut[i] = lo | (hi << 16);
-    }
+  static constexpr int SHIFT = REPL ? 7 : 2;
+  static constexpr int BYTES = BITS ? ENTRIES << SHIFT : 0;
+};
+
+template <int BITS>
+__device__ __forceinline__ void lut_fill(uint8_t* lut, const uint16_t* c16, int tid) {
+  using T = PairLut<BITS>;
+  uint32_t* w = reinterpret_cast<uint32_t*>(lut);
+  for (int i = tid; i < T::BYTES / 4; i += ATT_THREADS) {
+    const int e = T::REPL ? (i >> 5) : i;
+    w[i] = (uint32_t)c16[e >> BITS] | ((uint32_t)c16[e & ((1 << BITS) - 1)] << 16);
   }
-  static __device__ __forceinline__ uint32_t get(const uint32_t* lut, uint32_t field, int lane) {
-    return REPL ? lut[field * 32 + lane] : lut[field];
+}
+
+// (field p of width FB bits, counted from the most significant end of a big-endian word array) << SH
+template <int FB, int SH, int NW>
+__device__ __forceinline__ uint32_t field_off(const uint32_t (&w)[NW], int p) {
+  constexpr uint32_t MASK = ((1u << FB) - 1) << SH;
+  const int start = p * FB, k = start >> 5, o = start & 31;
+  if (o + FB <= 32) {
+    const int sr = 32 - FB - o;
+    const uint32_t v = sr > SH ? (w[k] >> (sr - SH)) : (sr < SH ? (w[k] << (SH - sr)) : w[k]);
+    return v & MASK;
+  }
+  const uint32_t v = __funnelshift_l(w[k + 1 < NW ? k + 1 : k], w[k], o);
+  return (v >> (32 - FB - SH)) & MASK;
+}
+
+__device__ __forceinline__ float load_q(const void* q, int dtype, size_t i) {
+  if (dtype == TQ_F16) return __half2float(reinterpret_cast<const __half*>(q)[i]);
+  if (dtype == TQ_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(q)[i]);
+  return reinterpret_cast<const float*>(q)[i];
+}
+__device__ __forceinline__ void store_out(void* out, int dtype, size_t i, float v) {
+  if (dtype == TQ_F16) reinterpret_cast<__half*>(out)[i] = __float2half_rn(v);
+  else if (dtype == TQ_BF16) reinterpret_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(v);
+  else reinterpret_cast<float*>(out)[i] = v;
+}
+
+// 128-point sign * Walsh-Hadamard of one vector held by a warp: lane l has elements 4l..4l+3.
+// y = post (H/sqrt d) pre x, signs as bit masks (bit e set => -1).
+__device__ __forceinline__ void warp_wht128(float (&x)[4], const uint32_t (&pre)[4], const uint32_t (&post)[4], int lane) {
+  const uint32_t pb = (pre[lane >> 3] >> ((lane & 7) * 4)) & 0xfu, qb = (post[lane >> 3] >> ((lane & 7) * 4)) & 0xfu;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) x[k] = ((pb >> k) & 1u) ? -x[k] : x[k];
+  float a = x[0] + x[1], b = x[0] - x[1], c = x[2] + x[3], d = x[2] - x[3];
+  x[0] = a + c; x[1] = b + d; x[2] = a - c; x[3] = b - d;
+#pragma unroll
+  for (int bit = 1; bit < 32; bit <<= 1) {
+    const float sgn = (lane & bit) ? -1.0f : 1.0f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) x[k] = fmaf(sgn, x[k], __shfl_xor_sync(0xffffffffu, x[k], bit));
+  }
+#pragma unroll
+  for (int k = 0; k < 4; ++k) x[k] = (((qb >> k) & 1u) ? -x[k] : x[k]) * TQ_RSQRT_D;
+}
+
+// shared-memory carve-up, identical on host and device
+template <int KK, int VK> struct SmemPlan {
+  static constexpr int LK = PairLut<Kind<KK>::BITS>::BYTES;
+  static constexpr int LV = PairLut<Kind<VK>::BITS>::BYTES;
+  static constexpr int LS = Kind<KK>::PROD ? PairLut<1>::BYTES : 0;
+  static constexpr int ALIGN = (LK > LV ? LK : LV) > 512 ? (LK > LV ? LK : LV) : 512;  // largest table
+  // order tables by size so that each stays aligned to its own size
+  static constexpr int OFF_BIG = 0;
+  static constexpr int OFF_SMALL = LK > LV ? LK : LV;
+  static constexpr int OFF_K = LK >= LV ? OFF_BIG : OFF_SMALL;
+  static constexpr int OFF_V = LK >= LV ? OFF_SMALL : OFF_BIG;
+  static constexpr int OFF_S = LK + LV;
+  static constexpr int OFF_Q = ((OFF_S + LS + 127) / 128) * 128;  // float qbuf[2][8][128]
+  static constexpr int OFF_BAR = OFF_Q + 2 * MAX_G * TQ_D * 4;
+  static constexpr int OFF_PL = OFF_BAR + 128;  // PROD: lo halves of the projected-query fragments, uint2[8][32]
+  static constexpr int OFF_STAGE = OFF_PL + (Kind<KK>::PROD ? 2048 : 0);
+  static size_t bytes(int record_bytes, int nstages) {
+    const size_t stages = (size_t)nstages * record_bytes;
+    const size_t merge = (size_t)ATT_WARPS * MAX_G * (TQ_D + 2) * 4;
+    return (size_t)ALIGN + OFF_STAGE + (stages > merge ? stages : merge);
   }
 };
 
-// field p (2*BITS bits wide, counted from the most significant end) of a big-endian word array
-template <int BITS, int NW>
-__device__ __forceinline__ uint32_t be_field(const uint32_t (&w)[NW], int p) {
-  constexpr int FB = 2 * BITS;
-  const int start = p * FB, k = start >> 5, o = start & 31;
-  if (o + FB <= 32) return (w[k] >> (32 - FB - o)) & ((1u << FB) - 1);
-  return __funnelshift_l(w[k + 1 < NW ? k + 1 : k], w[k], o) >> (32 - FB);
-}
-
-template <int KB, int VB>
+template <int KK, int VK>
 __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn(const AttnParams P, const TqFast fk, const TqFast fv) {
-  extern __shared__ __align__(128) uint8_t smem[];
+  using KT = Kind<KK>;
+  using VT = Kind<VK>;
+  using SP = SmemPlan<KK, VK>;
+  constexpr int KB = KT::BITS, VB = VT::BITS;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
   const int seq_len = P.seq_lens[b];
   const int PT = P.L.page_tokens;
   const int n_pages = (seq_len + PT - 1) / PT;
   const int page_lo = split * P.chunk_pages;
+  const size_t row0 = (size_t)b * P.hq + (size_t)kvh * P.group;  // first query / output row of this CTA
+  if (n_pages == 0 && split == 0) {  // empty sequence: zeros
+    for (int e = tid; e < P.group * TQ_D; e += ATT_THREADS) store_out(P.out, P.out_dtype, row0 * TQ_D + e, 0.f);
+    return;
+  }
   if (page_lo >= n_pages) return;
   const int page_hi = min(n_pages, page_lo + P.chunk_pages);
   const int np = page_hi - page_lo;
+  const int ns = (n_pages + P.chunk_pages - 1) / P.chunk_pages;  // splits of this sequence that run
 
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  // align the carve-up to the largest table
+  const uint32_t raw = smem_u32(smem_raw);
+  uint8_t* sm = smem_raw + (((raw + SP::ALIGN - 1) & ~(uint32_t)(SP::ALIGN - 1)) - raw);
+  float* qbuf = reinterpret_cast<float*>(sm + SP::OFF_Q);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + SP::OFF_BAR);
+  volatile int* s_flags = reinterpret_cast<volatile int*>(sm + SP::OFF_BAR + 64);  // [0] wait failed, [1] this CTA merges
+  uint8_t* stage0 = sm + SP::OFF_STAGE;
   const uint32_t rec = (uint32_t)P.L.record_bytes;
-  uint8_t* stage0 = smem;
-  uint32_t* lutk = reinterpret_cast<uint32_t*>(smem + (size_t)ATT_STAGES * rec);
-  uint32_t* lutv = lutk + PairLut<KB>::WORDS;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(lutv + PairLut<VB>::WORDS);
-  __shared__ int s_fail;
-
-  if (tid == 0) {
-    for (int s = 0; s < ATT_STAGES; ++s) mbar_init(&bars[s], 1);
-    s_fail = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  PairLut<KB>::fill(lutk, fk, tid, ATT_THREADS);
-  PairLut<VB>::fill(lutv, fv, tid, ATT_THREADS);
-  __syncthreads();
+  const int NS = P.stages;
 
   const int32_t* bt = P.block_table + (size_t)b * P.max_pages;
   auto issue = [&](int i) {
     const int64_t page = bt[page_lo + i];
     const uint8_t* src = P.pool + page * P.L.page_stride + (int64_t)kvh * P.L.head_stride;
-    uint64_t* bar = &bars[i % ATT_STAGES];
+    uint64_t* bar = &bars[i % NS];
     mbar_expect_tx(bar, rec);
-    bulk_g2s(stage0 + (size_t)(i % ATT_STAGES) * rec, src, rec, bar);
+    bulk_g2s(stage0 + (size_t)(i % NS) * rec, src, rec, bar);
   };
   if (tid == 0) {
+    for (int s = 0; s < ATT_STAGES; ++s) mbar_init(&bars[s], 1);
+    s_flags[0] = 0;
+    s_flags[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     issue(0);
-    if (np > 1) issue(1);
+    if (NS > 2 && np > 1) issue(1);
   }
+  if constexpr (KB > 0) lut_fill<KB>(sm + SP::OFF_K, fk.cent16, tid);
+  if constexpr (VB > 0) lut_fill<VB>(sm + SP::OFF_V, fv.cent16, tid);
+  if (KT::PROD) {
+    uint32_t* w = reinterpret_cast<uint32_t*>(sm + SP::OFF_S);
+    for (int i = tid; i < PairLut<1>::BYTES / 4; i += ATT_THREADS) {
+      const int e = i >> 5;  // (bit_a << 1) | bit_b, bit 1 => +1.0
+      w[i] = ((e & 2) ? 0x3C00u : 0xBC00u) | (((e & 1) ? 0x3C00u : 0xBC00u) << 16);
+    }
+  }
+  // ---- prologue: rotated / projected queries into qbuf[0] (K rotation) and qbuf[1] (QJL projection) ----
+  if (warp < P.group) {
+    float x[4], y[4];
+    const size_t row = row0 + warp;
+    if (P.k_pre) {
+      const float4 v = *reinterpret_cast<const float4*>(P.qrot + row * TQ_D + 4 * lane);
+      x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+      if (KT::PROD) {
+        const float4 u = *reinterpret_cast<const float4*>(P.qproj + row * TQ_D + 4 * lane);
+        y[0] = u.x; y[1] = u.y; y[2] = u.z; y[3] = u.w;
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) x[k] = y[k] = load_q(P.q, P.q_dtype, row * TQ_D + 4 * lane + k);
+      if (!P.k_ident) {
+        warp_wht128(x, fk.s1, fk.s2, lane);
+        if (KT::PROD) warp_wht128(y, fk.j1, fk.j2, lane);
+      }
+      const float sk = P.qscale / (KT::Q8 ? 1.0f : fk.lut_alpha);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        x[k] *= sk;
+        y[k] *= P.qscale;
+      }
+    }
+    *reinterpret_cast<float4*>(qbuf + warp * TQ_D + 4 * lane) = make_float4(x[0], x[1], x[2], x[3]);
+    if (KT::PROD) *reinterpret_cast<float4*>(qbuf + (MAX_G + warp) * TQ_D + 4 * lane) = make_float4(y[0], y[1], y[2], y[3]);
+  }
+  __syncthreads();
 
-  // query fragments (B operand): head g, dims 32t + 4j + {0,1} and {2,3}; hi/lo fp16 split
-  uint32_t qh[8][2], ql[8][2];
+  // query fragments (B operand) of head g, hi/lo fp16 split
+  uint32_t qh[8][2], ql[8][2], ph[KT::PROD ? 8 : 1][2];
   {
     const bool hv = g < P.group;
-    const float* qp = P.qrot + ((size_t)b * P.hq + (size_t)kvh * P.group + (hv ? g : 0)) * TQ_D + 32 * t;
+    const float* qp = qbuf + (hv ? g : 0) * TQ_D;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      float4 v = hv ? *reinterpret_cast<const float4*>(qp + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
+      // dims this thread supplies in k-step j: 32t + 4j .. +3 (packed formats), or, for q8_0 keys, the
+      // thread's 8 dims of block j/2: 32(j/2) + 8t + 4(j%2) .. +3
+      const int dq = KT::Q8 ? 32 * (j >> 1) + 8 * t + 4 * (j & 1) : 32 * t + 4 * j;
+      float4 v = hv ? *reinterpret_cast<const float4*>(qp + dq) : make_float4(0.f, 0.f, 0.f, 0.f);
       const __half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
       const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
       qh[j][0] = *reinterpret_cast<const uint32_t*>(&h0);
       qh[j][1] = *reinterpret_cast<const uint32_t*>(&h1);
       ql[j][0] = pack_h2(v.x - f0.x, v.y - f0.y);
       ql[j][1] = pack_h2(v.z - f1.x, v.w - f1.y);
+      if constexpr (KT::PROD) {
+        float4 u = hv ? *reinterpret_cast<const float4*>(qp + MAX_G * TQ_D + dq) : make_float4(0.f, 0.f, 0.f, 0.f);
+        const __half2 e0 = __floats2half2_rn(u.x, u.y), e1 = __floats2half2_rn(u.z, u.w);
+        const float2 r0 = __half22float2(e0), r1 = __half22float2(e1);
+        ph[j][0] = *reinterpret_cast<const uint32_t*>(&e0);
+        ph[j][1] = *reinterpret_cast<const uint32_t*>(&e1);
+        // the lo halves live in shared memory (registers are spent on qh, ql, ph and the O accumulators);
+        // a fragment depends on the lane only, so warp 0 writes it for everybody
+        if (warp == 0)
+          reinterpret_cast<uint2*>(sm + SP::OFF_PL)[j * 32 + lane] =
+              make_uint2(pack_h2(u.x - r0.x, u.y - r0.y), pack_h2(u.z - r1.x, u.w - r1.y));
+      }
     }
   }
+  if constexpr (KT::PROD) __syncthreads();
+  const uint32_t lk_base = smem_u32(sm + SP::OFF_K) + (PairLut<KB>::REPL ? lane * 4 : 0);
+  const uint32_t lv_base = smem_u32(sm + SP::OFF_V) + (PairLut<VB>::REPL ? lane * 4 : 0);
+  const uint32_t ls_base = smem_u32(sm + SP::OFF_S) + lane * 4;
 
   float o[8][4];
 #pragma unroll
   for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
-  constexpr int KIDXB = 16 * KB, VIDXB = 16 * VB;
-  constexpr int KW = KB;  // 32-bit words per thread chunk (32 dims * KB bits / 32)
+  constexpr int KIDXB = KT::Q8 ? TQ_D : 16 * KB;  // K bytes per token
+  constexpr int VIDXB = VT::Q8 ? TQ_D : 16 * VB;
+  constexpr int KW = KT::Q8 ? 8 : KB;             // 32-bit words per thread chunk (32 dims)
   const int tiles_per_page = PT / 16;
 
   for (int i = 0; i < np; ++i) {
-    if (tid == 0 && i + 2 < np) issue(i + 2);
-    if (!mbar_wait_bounded(&bars[i % ATT_STAGES], (uint32_t)((i / ATT_STAGES) & 1))) s_fail = 1;
-    const uint8_t* st = stage0 + (size_t)(i % ATT_STAGES) * rec;
+    if (tid == 0 && i + NS - 1 < np) issue(i + NS - 1);
+    // once a wait has given up the CTA stops waiting (and stops trusting the data): it only drains
+    if (!s_flags[0] && !mbar_wait_bounded(&bars[i % NS], (uint32_t)((i / NS) & 1))) s_flags[0] = 1;
+    const uint8_t* st = stage0 + (size_t)(i % NS) * rec;
     const int valid = min(PT, seq_len - (page_lo + i) * PT);  // tokens of this page that exist
 
     for (int tile = warp; tile < tiles_per_page; tile += ATT_WARPS) {
       const int tb = tile * 16;
       if (tb >= valid) break;
+      const bool ok0 = tb + g < valid, ok1 = tb + g + 8 < valid;
       // ---------------- S = K_tile (16 tokens x 128) . q^T ----------------
       float s[4] = {0.f, 0.f, 0.f, 0.f};
       {
         uint32_t w0[KW], w1[KW];
         const uint32_t* p0 = reinterpret_cast<const uint32_t*>(st + P.L.k_idx_off + (tb + g) * KIDXB + t * (KIDXB / 4));
         const uint32_t* p1 = p0 + 8 * (KIDXB / 4);
+        if constexpr (KT::Q8) {
+          // int8 -> fp16 exactly: (b ^ 0x80) | 0x6400 is 1024 + (b + 128); subtract 1152.  A 32-value block has
+          // one scale, so k-steps 2b and 2b+1 cover block b (thread t supplies its dims 8t..8t+7) and the
+          // block's partial scores are scaled in fp32 afterwards -- the operands carry no rounding.
+          const uint8_t* q0 = st + P.L.k_idx_off + (tb + g) * TQ_D + 8 * t;
+          const uint8_t* q1 = q0 + 8 * TQ_D;
+          const uint2 sc0 = *reinterpret_cast<const uint2*>(st + P.L.k_scale_off + (tb + g) * 8);
+          const uint2 sc1 = *reinterpret_cast<const uint2*>(st + P.L.k_scale_off + (tb + g + 8) * 8);
+          const uint32_t scw0[2] = {sc0.x, sc0.y}, scw1[2] = {sc1.x, sc1.y};
 #pragma unroll
-        for (int k = 0; k < KW; ++k) {
-          w0[k] = __byte_perm(p0[k], 0, 0x0123);
-          w1[k] = __byte_perm(p1[k], 0, 0x0123);
-        }
+          for (int blk = 0; blk < 4; ++blk) {
+            const uint2 u0 = *reinterpret_cast<const uint2*>(q0 + 32 * blk);
+            const uint2 u1 = *reinterpret_cast<const uint2*>(q1 + 32 * blk);
+            const uint32_t x0[2] = {u0.x ^ 0x80808080u, u0.y ^ 0x80808080u};
+            const uint32_t x1[2] = {u1.x ^ 0x80808080u, u1.y ^ 0x80808080u};
+            float sb[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t a0 = PairLut<KB>::get(lutk, be_field<KB, KW>(w0, 2 * j), lane);
-          const uint32_t a1 = PairLut<KB>::get(lutk, be_field<KB, KW>(w1, 2 * j), lane);
-          const uint32_t a2 = PairLut<KB>::get(lutk, be_field<KB, KW>(w0, 2 * j + 1), lane);
-          const uint32_t a3 = PairLut<KB>::get(lutk, be_field<KB, KW>(w1, 2 * j + 1), lane);
-          mma16816(s, a0, a1, a2, a3, qh[j][0], qh[j][1]);
-          mma16816(s, a0, a1, a2, a3, ql[j][0], ql[j][1]);
+            for (int h2 = 0; h2 < 2; ++h2) {
+              const int j = 2 * blk + h2;
+              const uint32_t a0 = hsub2_u32(__byte_perm(x0[h2], 0x64646464u, 0x4140), 0x64806480u);
+              const uint32_t a2 = hsub2_u32(__byte_perm(x0[h2], 0x64646464u, 0x4342), 0x64806480u);
+              const uint32_t a1 = hsub2_u32(__byte_perm(x1[h2], 0x64646464u, 0x4140), 0x64806480u);
+              const uint32_t a3 = hsub2_u32(__byte_perm(x1[h2], 0x64646464u, 0x4342), 0x64806480u);
+              mma16816(sb, a0, a1, a2, a3, qh[j][0], qh[j][1]);
+              mma16816(sb, a0, a1, a2, a3, ql[j][0], ql[j][1]);
+            }
+            const __half2 hs0 = *reinterpret_cast<const __half2*>(&scw0[blk >> 1]);
+            const __half2 hs1 = *reinterpret_cast<const __half2*>(&scw1[blk >> 1]);
+            const float f0 = (blk & 1) ? __high2float(hs0) : __low2float(hs0);
+            const float f1 = (blk & 1) ? __high2float(hs1) : __low2float(hs1);
+            s[0] = fmaf(sb[0], f0, s[0]); s[1] = fmaf(sb[1], f0, s[1]);
+            s[2] = fmaf(sb[2], f1, s[2]); s[3] = fmaf(sb[3], f1, s[3]);
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < KW; ++k) {
+            w0[k] = __byte_perm(p0[k], 0, 0x0123);
+            w1[k] = __byte_perm(p1[k], 0, 0x0123);
+          }
+          constexpr int SH = PairLut<KB>::SHIFT;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t a0 = lds32(field_off<2 * KB, SH, KW>(w0, 2 * j) | lk_base);
+            const uint32_t a1 = lds32(field_off<2 * KB, SH, KW>(w1, 2 * j) | lk_base);
+            const uint32_t a2 = lds32(field_off<2 * KB, SH, KW>(w0, 2 * j + 1) | lk_base);
+            const uint32_t a3 = lds32(field_off<2 * KB, SH, KW>(w1, 2 * j + 1) | lk_base);
+            mma16816(s, a0, a1, a2, a3, qh[j][0], qh[j][1]);
+            mma16816(s, a0, a1, a2, a3, ql[j][0], ql[j][1]);
+          }
         }
       }
-      const float* ksc = reinterpret_cast<const float*>(st + P.L.k_scale_off);
-      const float* vsc = reinterpret_cast<const float*>(st + P.L.v_scale_off);
-      const bool ok0 = tb + g < valid, ok1 = tb + g + 8 < valid;
-      const float ks0 = ksc[tb + g], ks1 = ksc[tb + g + 8];
-      s[0] = ok0 ? s[0] * ks0 : -INFINITY;
-      s[1] = ok0 ? s[1] * ks0 : -INFINITY;
-      s[2] = ok1 ? s[2] * ks1 : -INFINITY;
-      s[3] = ok1 ? s[3] * ks1 : -INFINITY;
+      if (!KT::Q8) {
+        const float* ksc = reinterpret_cast<const float*>(st + P.L.k_scale_off);
+        const float ks0 = ksc[tb + g], ks1 = ksc[tb + g + 8];
+        s[0] *= ks0; s[1] *= ks0; s[2] *= ks1; s[3] *= ks1;
+      }
+      if constexpr (KT::PROD) {
+        // + sqrt(pi/2)/sqrt(d) * ||r|| * <S q, z>: the sign sketch as +-1 fp16 operands
+        float s2[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t z0[1], z1[1];
+        const uint32_t* pz = reinterpret_cast<const uint32_t*>(st + P.L.k_qjl_off + (tb + g) * 16 + t * 4);
+        z0[0] = __byte_perm(pz[0], 0, 0x0123);
+        z1[0] = __byte_perm(pz[8 * 4], 0, 0x0123);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t a0 = lds32(field_off<2, 7, 1>(z0, 2 * j) | ls_base);
+          const uint32_t a1 = lds32(field_off<2, 7, 1>(z1, 2 * j) | ls_base);
+          const uint32_t a2 = lds32(field_off<2, 7, 1>(z0, 2 * j + 1) | ls_base);
+          const uint32_t a3 = lds32(field_off<2, 7, 1>(z1, 2 * j + 1) | ls_base);
+          mma16816(s2, a0, a1, a2, a3, ph[j][0], ph[j][1]);
+          const uint2 lo = reinterpret_cast<const uint2*>(sm + SP::OFF_PL)[j * 32 + lane];
+          mma16816(s2, a0, a1, a2, a3, lo.x, lo.y);
+        }
+        const float* rsc = reinterpret_cast<const float*>(st + P.L.k_rscale_off);
+        const float r0 = rsc[tb + g], r1 = rsc[tb + g + 8];
+        s[0] = fmaf(s2[0], r0, s[0]); s[1] = fmaf(s2[1], r0, s[1]);
+        s[2] = fmaf(s2[2], r1, s[2]); s[3] = fmaf(s2[3], r1, s[3]);
+      }
+      s[0] = ok0 ? s[0] : -INFINITY;
+      s[1] = ok0 ? s[1] : -INFINITY;
+      s[2] = ok1 ? s[2] : -INFINITY;
+      s[3] = ok1 ? s[3] : -INFINITY;
       // ---------------- online softmax (log2 domain), heads 2t and 2t+1 ----------------
       float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
 #pragma unroll
@@ -242,36 +475,67 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn(const AttnParams
           o[j][0] *= r0; o[j][1] *= r1; o[j][2] *= r0; o[j][3] *= r1;
         }
       }
-      // probabilities * V scale, as fp16, transposed into the B-operand layout (tokens on K)
-      const float vs0 = ok0 ? vsc[tb + g] : 0.f, vs1 = ok1 ? vsc[tb + g + 8] : 0.f;
+      // probabilities (* V scale), as fp16, transposed into the B-operand layout (tokens on K)
+      float vs0 = 1.0f, vs1 = 1.0f;
+      if (!VT::Q8) {
+        const float* vsc = reinterpret_cast<const float*>(st + P.L.v_scale_off);
+        vs0 = ok0 ? vsc[tb + g] : 0.f;
+        vs1 = ok1 ? vsc[tb + g + 8] : 0.f;
+      }
       const uint32_t pb0 = movmatrix_trans(pack_h2(p00 * vs0, p01 * vs0));
       const uint32_t pb1 = movmatrix_trans(pack_h2(p10 * vs1, p11 * vs1));
       // ---------------- O^T += V_tile^T . P^T ----------------
-      {
-        uint32_t h[4][8];  // half2 (dim 16g+2jj, dim 16g+2jj+1) for tokens tb + {2t, 2t+1, 2t+8, 2t+9}
+      // thread (g, t): dims 16g .. 16g+15 of tokens tb + {2t, 2t+1, 2t+8, 2t+9}
+      if constexpr (VT::Q8) {
+        uint32_t x[4][4], sc2[2];
+        const uint16_t* vsc = reinterpret_cast<const uint16_t*>(st + P.L.v_scale_off);
+        uint32_t scl[4];
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int tok = tb + 2 * t + (q4 & 1) + (q4 >> 1) * 8;
+          const uint4 v = *reinterpret_cast<const uint4*>(st + P.L.v_idx_off + tok * TQ_D + g * 16);
+          x[q4][0] = v.x ^ 0x80808080u; x[q4][1] = v.y ^ 0x80808080u;
+          x[q4][2] = v.z ^ 0x80808080u; x[q4][3] = v.w ^ 0x80808080u;
+          scl[q4] = tok < valid ? vsc[tok * 4 + (g >> 1)] : 0u;  // a stale scale must not meet p = 0
+        }
+        sc2[0] = scl[0] | (scl[1] << 16);
+        sc2[1] = scl[2] | (scl[3] << 16);
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          const uint32_t sel = (jj & 1) ? 0x4342 : 0x4140;
+          const uint32_t h0 = hsub2_u32(__byte_perm(x[0][jj >> 1], 0x64646464u, sel), 0x64806480u);
+          const uint32_t h1 = hsub2_u32(__byte_perm(x[1][jj >> 1], 0x64646464u, sel), 0x64806480u);
+          const uint32_t h2 = hsub2_u32(__byte_perm(x[2][jj >> 1], 0x64646464u, sel), 0x64806480u);
+          const uint32_t h3 = hsub2_u32(__byte_perm(x[3][jj >> 1], 0x64646464u, sel), 0x64806480u);
+          const uint32_t a0 = hmul2_u32(__byte_perm(h0, h1, 0x5410), sc2[0]);
+          const uint32_t a1 = hmul2_u32(__byte_perm(h0, h1, 0x7632), sc2[0]);
+          const uint32_t a2 = hmul2_u32(__byte_perm(h2, h3, 0x5410), sc2[1]);
+          const uint32_t a3 = hmul2_u32(__byte_perm(h2, h3, 0x7632), sc2[1]);
+          mma16816(o[jj], a0, a1, a2, a3, pb0, pb1);
+        }
+      } else {
+        uint32_t h[4][8];  // half2 (dim 16g+2jj, dim 16g+2jj+1) per token
+        constexpr int SH = PairLut<VB>::SHIFT;
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
           const int tok = tb + 2 * t + (q4 & 1) + (q4 >> 1) * 8;
           const uint8_t* pv = st + P.L.v_idx_off + tok * VIDXB + g * (2 * VB);
           uint32_t w[2];
-          if (VB == 3) {
-            const uint16_t* ph = reinterpret_cast<const uint16_t*>(pv);
-            const uint32_t a = ph[0], bb = ph[1], c = ph[2];
+          if constexpr (VB == 3) {
+            const uint16_t* phw = reinterpret_cast<const uint16_t*>(pv);
+            const uint32_t a = phw[0], bb = phw[1], c = phw[2];
             w[0] = __byte_perm(a, bb, 0x0145);
             w[1] = __byte_perm(c, 0, 0x0144);
-          } else if (VB == 2) {
+          } else if constexpr (VB == 2) {
             w[0] = __byte_perm(*reinterpret_cast<const uint32_t*>(pv), 0, 0x0123);
             w[1] = 0;
-          } else if (VB == 4) {
+          } else {
             const uint2 v2 = *reinterpret_cast<const uint2*>(pv);
             w[0] = __byte_perm(v2.x, 0, 0x0123);
             w[1] = __byte_perm(v2.y, 0, 0x0123);
-          } else {  // VB == 1
-            w[0] = __byte_perm((uint32_t)*reinterpret_cast<const uint16_t*>(pv), 0, 0x0144);
-            w[1] = 0;
           }
 #pragma unroll
-          for (int jj = 0; jj < 8; ++jj) h[q4][jj] = PairLut<VB>::get(lutv, be_field<VB, 2>(w, jj), lane);
+          for (int jj = 0; jj < 8; ++jj) h[q4][jj] = lds32(field_off<2 * VB, SH, 2>(w, jj) | lv_base);
         }
 #pragma unroll
         for (int jj = 0; jj < 8; ++jj) {
@@ -293,8 +557,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn(const AttnParams
     l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], sh);
     l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], sh);
   }
-  float* so = reinterpret_cast<float*>(smem);            // [warp][head 8][dim 128]
-  float* sml = so + ATT_WARPS * MAX_G * TQ_D;            // [warp][head 8][2]
+  float* so = reinterpret_cast<float*>(stage0);   // [warp][head 8][dim 128]
+  float* sml = so + ATT_WARPS * MAX_G * TQ_D;     // [warp][head 8][2]
 #pragma unroll
   for (int jj = 0; jj < 8; ++jj) {
     const int d0 = 16 * g + 2 * jj;
@@ -316,112 +580,120 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn(const AttnParams
     float M = -INFINITY;
 #pragma unroll
     for (int w = 0; w < ATT_WARPS; ++w) M = fmaxf(M, sml[(w * MAX_G + head) * 2]);
-    float acc = 0.f, L = 0.f;
+    float acc = 0.f, Lsum = 0.f;
 #pragma unroll
     for (int w = 0; w < ATT_WARPS; ++w) {
       const float mw = sml[(w * MAX_G + head) * 2];
       const float f = mw == -INFINITY ? 0.f : fast_exp2(mw - M);
       acc = fmaf(so[((size_t)w * MAX_G + head) * TQ_D + dim], f, acc);
-      L = fmaf(sml[(w * MAX_G + head) * 2 + 1], f, L);
+      Lsum = fmaf(sml[(w * MAX_G + head) * 2 + 1], f, Lsum);
     }
-    const size_t slot = ((size_t)b * P.hq + (size_t)kvh * P.group + head) * P.num_splits + split;
+    const size_t slot = (row0 + head) * P.num_splits + split;
     P.part_o[slot * TQ_D + dim] = acc;
     if (dim == 0) {
       P.part_ml[slot * 2] = M;
-      P.part_ml[slot * 2 + 1] = L;
+      P.part_ml[slot * 2 + 1] = Lsum;
     }
   }
-  if (tid == 0 && s_fail) atomicExch(P.status, 1);
+  // ---------------- ticket: the last CTA of this (sequence, kv head) merges the splits ----------------
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    if (s_flags[0]) atomicExch(P.status, 1);
+    const int prev = atomicAdd(&P.tickets[b * P.hkv + kvh], 1);
+    if (prev == ns - 1) {
+      P.tickets[b * P.hkv + kvh] = 0;  // leave the counter at zero for the next call
+      s_flags[1] = 1;
+    }
+  }
+  __syncthreads();
+  if (!s_flags[1]) return;
+  __threadfence();
+  // (m, l) of every split -> shared memory; per head one warp finds the max and the weights 2^(m_s - M)
+  float* sw = reinterpret_cast<float*>(stage0);      // [head][ns] weights
+  float* sl = sw + MAX_G * ns;                       // [head] 1 / (sum_s l_s w_s)
+  for (int e = tid; e < P.group * ns; e += ATT_THREADS) {
+    const int head = e / ns, s_i = e - head * ns;
+    sw[head * ns + s_i] = __ldcg(P.part_ml + ((row0 + head) * P.num_splits + s_i) * 2);
+  }
+  __syncthreads();
+  if (warp < P.group) {
+    float M = -INFINITY;
+    for (int s_i = lane; s_i < ns; s_i += 32) M = fmaxf(M, sw[warp * ns + s_i]);
+#pragma unroll
+    for (int sh = 16; sh > 0; sh >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, sh));
+    float Lsum = 0.f;
+    for (int s_i = lane; s_i < ns; s_i += 32) {
+      const float f = exp2f(sw[warp * ns + s_i] - M);
+      sw[warp * ns + s_i] = f;
+      Lsum = fmaf(__ldcg(P.part_ml + ((row0 + warp) * P.num_splits + s_i) * 2 + 1), f, Lsum);
+    }
+#pragma unroll
+    for (int sh = 16; sh > 0; sh >>= 1) Lsum += __shfl_xor_sync(0xffffffffu, Lsum, sh);
+    if (lane == 0) sl[warp] = 1.0f / (Lsum * (VT::Q8 ? 1.0f : fv.lut_alpha));
+  }
+  __syncthreads();
+  for (int e = tid; e < P.group * TQ_D; e += ATT_THREADS) {
+    const int head = e >> 7, dim = e & 127;
+    const float* po = P.part_o + (row0 + head) * P.num_splits * TQ_D + dim;
+    const float* wv = sw + head * ns;
+    float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+    int s_i = 0;
+    for (; s_i + 4 <= ns; s_i += 4) {  // four independent loads in flight; summation order is fixed
+      const float a = __ldcg(po + (size_t)s_i * TQ_D), bq = __ldcg(po + (size_t)(s_i + 1) * TQ_D);
+      const float c = __ldcg(po + (size_t)(s_i + 2) * TQ_D), dq = __ldcg(po + (size_t)(s_i + 3) * TQ_D);
+      acc0 = fmaf(a, wv[s_i], acc0);
+      acc1 = fmaf(bq, wv[s_i + 1], acc1);
+      acc2 = fmaf(c, wv[s_i + 2], acc2);
+      acc3 = fmaf(dq, wv[s_i + 3], acc3);
+    }
+    for (; s_i < ns; ++s_i) acc0 = fmaf(__ldcg(po + (size_t)s_i * TQ_D), wv[s_i], acc0);
+    // attention output in V's rotated space
+    qbuf[head * TQ_D + dim] = ((acc0 + acc1) + (acc2 + acc3)) * sl[head];
+  }
+  __syncthreads();
+  if (P.v_rot) {  // dense rotation: x = R^T y
+    for (int e = tid; e < P.group * TQ_D; e += ATT_THREADS) {
+      const int head = e >> 7, j = e & 127;
+      float x = 0.f;
+#pragma unroll 8
+      for (int k = 0; k < TQ_D; ++k) x = fmaf(__ldg(P.v_rot + k * TQ_D + j), qbuf[head * TQ_D + k], x);
+      store_out(P.out, P.out_dtype, (row0 + head) * TQ_D + j, x);
+    }
+  } else if (warp < P.group) {
+    float x[4];
+    const float4 v = *reinterpret_cast<const float4*>(qbuf + warp * TQ_D + 4 * lane);
+    x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+    if (!P.v_ident) warp_wht128(x, fv.s2, fv.s1, lane);  // R^T = D1 (H/sqrt d) D2
+#pragma unroll
+    for (int k = 0; k < 4; ++k) store_out(P.out, P.out_dtype, (row0 + warp) * TQ_D + 4 * lane + k, x[k]);
+  }
 }
 
 // ------------------------------------------------------------------------------------------
-// 128-point sign*WHT of a vector held in shared memory by a 128-thread block
-__device__ __forceinline__ float wht128_block(float v, float* buf, int j) {
-  buf[j] = v;
-  __syncthreads();
-#pragma unroll
-  for (int h = 1; h < TQ_D; h <<= 1) {
-    const float a = buf[j], bb = buf[j ^ h];
-    __syncthreads();
-    buf[j] = (j & h) ? bb - a : a + bb;
-    __syncthreads();
-  }
-  return buf[j] * TQ_RSQRT_D;
-}
-
-__device__ __forceinline__ float sign_of(const uint32_t (&m)[4], int j) { return ((m[j >> 5] >> (j & 31)) & 1u) ? -1.f : 1.f; }
-
+// dense rotations of the queries (the d x d matrix is too large to apply once per CTA)
 template <typename Tq>
 __global__ void __launch_bounds__(128) k_prepare_queries(const Tq* __restrict__ q, int64_t rows, float qscale,
-                                                         int k_dense, const float* __restrict__ rot_t,
-                                                         const TqFast fk, int prod, const float* __restrict__ s_t,
-                                                         float* __restrict__ qrot, float* __restrict__ qproj,
-                                                         int32_t* status) {
-  __shared__ float xs[TQ_D], buf[TQ_D];
+                                                         const float* __restrict__ rot_t, float alpha, int prod,
+                                                         const float* __restrict__ s_t, float* __restrict__ qrot,
+                                                         float* __restrict__ qproj) {
+  __shared__ float xs[TQ_D];
   const int j = threadIdx.x;
-  if (blockIdx.x == 0 && j == 0) *status = 0;
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
-    const float x = (float)q[row * TQ_D + j];
-    xs[j] = x;
+    xs[j] = (float)q[row * TQ_D + j];
     __syncthreads();
-    float y;
-    if (k_dense) {
-      y = 0.f;
+    float y = 0.f;
 #pragma unroll 8
-      for (int k = 0; k < TQ_D; ++k) y = fmaf(__ldg(rot_t + k * TQ_D + j), xs[k], y);  // (R x)_j
-    } else {
-      y = wht128_block(x * sign_of(fk.s1, j), buf, j) * sign_of(fk.s2, j);
-    }
-    qrot[row * TQ_D + j] = y * (qscale / fk.lut_alpha);
+    for (int k = 0; k < TQ_D; ++k) y = fmaf(__ldg(rot_t + k * TQ_D + j), xs[k], y);  // (R x)_j
+    qrot[row * TQ_D + j] = y * (qscale / alpha);
     if (prod) {
-      float z;
-      if (k_dense) {
-        z = 0.f;
+      float z = 0.f;
 #pragma unroll 8
-        for (int k = 0; k < TQ_D; ++k) z = fmaf(__ldg(s_t + k * TQ_D + j), xs[k], z);  // (S x)_j
-      } else {
-        __syncthreads();
-        z = wht128_block(x * sign_of(fk.j1, j), buf, j) * sign_of(fk.j2, j);
-      }
+      for (int k = 0; k < TQ_D; ++k) z = fmaf(__ldg(s_t + k * TQ_D + j), xs[k], z);  // (S x)_j
       qproj[row * TQ_D + j] = z * qscale;
     }
     __syncthreads();
   }
-}
-
-template <typename To>
-__global__ void __launch_bounds__(128) k_decode_combine(const float* __restrict__ part_o,
-                                                        const float* __restrict__ part_ml,
-                                                        const int32_t* __restrict__ seq_lens, int hq, int num_splits,
-                                                        int chunk_pages, int page_tokens, int v_dense,
-                                                        const float* __restrict__ rot, const TqFast fv,
-                                                        To* __restrict__ out) {
-  __shared__ float ys[TQ_D], buf[TQ_D];
-  const int j = threadIdx.x;
-  const int64_t row = blockIdx.x;
-  const int b = (int)(row / hq);
-  const int n_pages = (seq_lens[b] + page_tokens - 1) / page_tokens;
-  const int ns = (n_pages + chunk_pages - 1) / chunk_pages;
-  float M = -INFINITY;
-  for (int s = 0; s < ns; ++s) M = fmaxf(M, part_ml[(row * num_splits + s) * 2]);
-  float acc = 0.f, L = 0.f;
-  for (int s = 0; s < ns; ++s) {
-    const float f = exp2f(part_ml[(row * num_splits + s) * 2] - M);
-    acc = fmaf(part_o[(row * num_splits + s) * TQ_D + j], f, acc);
-    L = fmaf(part_ml[(row * num_splits + s) * 2 + 1], f, L);
-  }
-  const float y = ns > 0 ? acc / (L * fv.lut_alpha) : 0.f;  // attention output in V's rotated space
-  float x;
-  if (v_dense) {
-    ys[j] = y;
-    __syncthreads();
-    x = 0.f;
-#pragma unroll 8
-    for (int k = 0; k < TQ_D; ++k) x = fmaf(__ldg(rot + k * TQ_D + j), ys[k], x);  // (R^T y)_j
-  } else {
-    x = wht128_block(y * sign_of(fv.s2, j), buf, j) * sign_of(fv.s1, j);  // D1 (H/sqrt d) D2 y
-  }
-  out[row * TQ_D + j] = (To)x;
 }
 
 struct SplitPlan {
@@ -445,7 +717,7 @@ SplitPlan plan_splits(int batch, int hkv, int max_pages) {
 }
 
 struct WsLayout {
-  size_t qrot, qproj, part_o, part_ml, status, total;
+  size_t qrot, qproj, part_o, part_ml, total;
 };
 
 WsLayout ws_layout(int batch, int hq, int num_splits) {
@@ -461,24 +733,31 @@ WsLayout ws_layout(int batch, int hq, int num_splits) {
   w.qproj = take(rows * TQ_D * 4);
   w.part_o = take(rows * num_splits * TQ_D * 4);
   w.part_ml = take(rows * num_splits * 2 * 4);
-  w.status = take(256);
-  w.total = off;
+  w.total = off + TAIL_BYTES;  // tickets and the status word live at the very end of the caller's buffer
   return w;
 }
 
-int fmt_bits(int fmt) { return (fmt >= TQ_FMT_TURBO2 && fmt <= TQ_FMT_TURBO4) ? fmt : 0; }
-
-template <int KB, int VB>
+template <int KK, int VK>
 int launch_attn(const AttnParams& P, const TqFast& fk, const TqFast& fv, cudaStream_t st) {
-  const size_t smem = (size_t)ATT_STAGES * P.L.record_bytes + (size_t)(PairLut<KB>::WORDS + PairLut<VB>::WORDS) * 4 + 64;
-  const size_t merge = (size_t)ATT_WARPS * MAX_G * (TQ_D + 2) * 4;
-  const size_t need = smem > merge ? smem : merge;
-  TQ_REQUIRE(need <= 227 * 1024, TQ_ERR_TOO_LARGE, "page record of %d bytes does not fit the shared-memory pipeline",
+  const size_t need = SmemPlan<KK, VK>::bytes(P.L.record_bytes, P.stages);
+  TQ_REQUIRE(need <= 113 * 1024, TQ_ERR_TOO_LARGE, "page record of %d bytes does not fit the shared-memory pipeline",
              P.L.record_bytes);
-  TQ_CUDA(cudaFuncSetAttribute(k_decode_attn<KB, VB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need));
+  static thread_local int configured_dev = -1;  // per instantiation
+  int dev = 0;
+  TQ_CUDA(cudaGetDevice(&dev));
+  if (configured_dev != dev) {
+    TQ_CUDA(cudaFuncSetAttribute(k_decode_attn<KK, VK>, cudaFuncAttributeMaxDynamicSharedMemorySize, 113 * 1024));
+    configured_dev = dev;
+  }
   dim3 grid(P.num_splits, P.hkv, P.batch);
-  k_decode_attn<KB, VB><<<grid, ATT_THREADS, need, st>>>(P, fk, fv);
+  k_decode_attn<KK, VK><<<grid, ATT_THREADS, need, st>>>(P, fk, fv);
   return tq_launch_check("k_decode_attn");
+}
+
+bool fmt_ok(int fmt, bool is_k) {
+  if (fmt >= TQ_FMT_TURBO2 && fmt <= TQ_FMT_TURBO4) return true;
+  if (fmt == TQ_FMT_Q8_0) return true;
+  return is_k && fmt >= TQ_FMT_PROD2 && fmt <= TQ_FMT_PROD4;
 }
 
 }  // namespace
@@ -490,59 +769,16 @@ extern "C" int64_t tq_decode_workspace_bytes(int32_t batch, int32_t num_q_heads,
   return (int64_t)ws_layout(batch, num_q_heads, p.num_splits).total;
 }
 
-extern "C" int tq_decode_status_sync(const void* workspace_dev, int64_t workspace_bytes, int32_t* status_out) {
-  TQ_REQUIRE(workspace_dev && status_out && workspace_bytes >= 256, TQ_ERR_INVALID, "bad workspace");
-  TQ_CUDA(cudaMemcpy(status_out, (const uint8_t*)workspace_dev + workspace_bytes - 256, 4, cudaMemcpyDeviceToHost));
+extern "C" int tq_decode_workspace_init(void* workspace_dev, int64_t workspace_bytes, void* stream) {
+  TQ_REQUIRE(workspace_dev && workspace_bytes >= (int64_t)TAIL_BYTES, TQ_ERR_INVALID,
+             "workspace must hold at least %lld bytes", (long long)TAIL_BYTES);
+  TQ_CUDA(cudaMemsetAsync((uint8_t*)workspace_dev + workspace_bytes - TAIL_BYTES, 0, TAIL_BYTES, (cudaStream_t)stream));
   return TQ_OK;
 }
 
-extern "C" int tq_cache_append(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cache_layout* L,
-                               uint8_t* pool_dev, const void* k_dev, const void* v_dev, int32_t dtype, int64_t n_tokens,
-                               const int64_t* slot_dev, void* stream) {
-  TQ_REQUIRE(L && pool_dev, TQ_ERR_INVALID, "tq_cache_append: layout or pool missing");
-  TQ_REQUIRE(n_tokens >= 0, TQ_ERR_INVALID, "n_tokens must be >= 0");
-  if (n_tokens == 0) return TQ_OK;
-  TQ_REQUIRE(k_dev && v_dev && slot_dev, TQ_ERR_INVALID, "tq_cache_append: k, v or slot mapping missing");
-  TQ_REQUIRE(tq_aligned(pool_dev, 128), TQ_ERR_ALIGN, "cache pool must be 128-byte aligned");
-  cudaStream_t st = (cudaStream_t)stream;
-  const int H = L->num_kv_heads;
-  for (int which = 0; which < 2; ++which) {
-    const int fmt = which == 0 ? L->k_format : L->v_format;
-    const tq_quantizer* q = which == 0 ? kq : vq;
-    const void* x = which == 0 ? k_dev : v_dev;
-    const int idx_off = which == 0 ? L->k_idx_off : L->v_idx_off;
-    const int sc_off = which == 0 ? L->k_scale_off : L->v_scale_off;
-    if (fmt == TQ_FMT_Q8_0) {
-      int rc = tq_q8_0_append_launch(x, dtype, n_tokens, H, pool_dev + idx_off, pool_dev + sc_off, slot_dev,
-                                     L->page_tokens, L->page_stride, L->head_stride, st);
-      if (rc != TQ_OK) return rc;
-      continue;
-    }
-    const bool prod = fmt >= TQ_FMT_PROD2;
-    const int bits = prod ? fmt - 17 : fmt;
-    TQ_REQUIRE(q, TQ_ERR_INVALID, "tq_cache_append: quantizer missing for a turbo/prod tensor");
-    TQ_REQUIRE(q->d == TQ_D && q->bits == bits, TQ_ERR_INVALID,
-               "quantizer (d=%d, bits=%d) does not match cache format %d", q->d, q->bits, fmt);
-    TQ_REQUIRE(!prod || q->qjl, TQ_ERR_INVALID, "PROD cache format needs a quantizer with a QJL stage");
-    TQ_REQUIRE(q->rotation == TQ_ROT_WHT, TQ_ERR_UNSUPPORTED,
-               "quantize-on-append is built for WHT-mode quantizers (dense mode: quantize, then tq_cache_store)");
-    TqQuantDst dst;
-    memset(&dst, 0, sizeof(dst));
-    dst.idx = pool_dev + idx_off;
-    dst.scale = reinterpret_cast<float*>(pool_dev + sc_off);
-    if (prod) {
-      dst.qjl = pool_dev + L->k_qjl_off;
-      dst.rnorm = reinterpret_cast<float*>(pool_dev + L->k_rscale_off);
-      dst.rscale_const = 1;
-    }
-    dst.slots = slot_dev;
-    dst.page_stride = L->page_stride;
-    dst.head_stride = L->head_stride;
-    dst.page_tokens = L->page_tokens;
-    dst.heads = H;
-    int rc = tq_quantize_wht_launch(q->fast, x, dtype, TQ_D, n_tokens * H, dst, prod, st);
-    if (rc != TQ_OK) return rc;
-  }
+extern "C" int tq_decode_status_sync(const void* workspace_dev, int64_t workspace_bytes, int32_t* status_out) {
+  TQ_REQUIRE(workspace_dev && status_out && workspace_bytes >= 256, TQ_ERR_INVALID, "bad workspace");
+  TQ_CUDA(cudaMemcpy(status_out, (const uint8_t*)workspace_dev + workspace_bytes - 256, 4, cudaMemcpyDeviceToHost));
   return TQ_OK;
 }
 
@@ -552,7 +788,7 @@ extern "C" int tq_decode_attn(const tq_quantizer* kq, const tq_quantizer* vq, co
                               int32_t num_q_heads, float scale, void* workspace_dev, int64_t workspace_bytes,
                               void* out_dev, int32_t out_dtype, void* stream) {
   return tq_decode_attn_phases(kq, vq, L, pool_dev, block_table_dev, max_pages_per_seq, seq_lens_dev, q_dev, q_dtype,
-                               batch, num_q_heads, scale, workspace_dev, workspace_bytes, out_dev, out_dtype, 7, stream);
+                               batch, num_q_heads, scale, workspace_dev, workspace_bytes, out_dev, out_dtype, 3, stream);
 }
 
 extern "C" int tq_decode_attn_phases(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cache_layout* L,
@@ -561,65 +797,84 @@ extern "C" int tq_decode_attn_phases(const tq_quantizer* kq, const tq_quantizer*
                                      int32_t q_dtype, int32_t batch, int32_t num_q_heads, float scale,
                                      void* workspace_dev, int64_t workspace_bytes, void* out_dev, int32_t out_dtype,
                                      int32_t phases, void* stream) {
-  TQ_REQUIRE(kq && vq && L, TQ_ERR_INVALID, "tq_decode_attn: quantizers or layout missing");
+  TQ_REQUIRE(L, TQ_ERR_INVALID, "tq_decode_attn: layout missing");
   TQ_REQUIRE(batch >= 0 && num_q_heads >= 1 && max_pages_per_seq >= 1, TQ_ERR_INVALID, "bad sizes");
   if (batch == 0) return TQ_OK;
   TQ_REQUIRE(pool_dev && block_table_dev && seq_lens_dev && q_dev && out_dev && workspace_dev, TQ_ERR_INVALID,
              "tq_decode_attn: null buffer");
-  TQ_REQUIRE(L->d == TQ_D && kq->d == TQ_D && vq->d == TQ_D, TQ_ERR_UNSUPPORTED, "decode attention is built for d == 128");
+  TQ_REQUIRE(L->d == TQ_D, TQ_ERR_UNSUPPORTED, "decode attention is built for d == 128");
+  TQ_REQUIRE(fmt_ok(L->k_format, true) && fmt_ok(L->v_format, false), TQ_ERR_UNSUPPORTED,
+             "decode attention: K format %d / V format %d unknown", L->k_format, L->v_format);
+  const bool k_q8 = L->k_format == TQ_FMT_Q8_0, v_q8 = L->v_format == TQ_FMT_Q8_0;
+  const bool k_prod = L->k_format >= TQ_FMT_PROD2;
+  TQ_REQUIRE(k_q8 || kq, TQ_ERR_INVALID, "tq_decode_attn: K quantizer missing");
+  TQ_REQUIRE(v_q8 || vq, TQ_ERR_INVALID, "tq_decode_attn: V quantizer missing");
   TQ_REQUIRE(num_q_heads % L->num_kv_heads == 0, TQ_ERR_INVALID, "num_q_heads must be a multiple of num_kv_heads");
   const int group = num_q_heads / L->num_kv_heads;
   TQ_REQUIRE(group <= MAX_G, TQ_ERR_UNSUPPORTED, "at most %d query heads per KV head, got %d", MAX_G, group);
-  TQ_REQUIRE(batch <= 65535 && L->num_kv_heads <= 65535, TQ_ERR_TOO_LARGE, "batch and KV heads are grid dimensions (<= 65535)");
+  TQ_REQUIRE(batch <= 65535 && L->num_kv_heads <= 65535 && (int64_t)batch * L->num_kv_heads <= MAX_TICKETS,
+             TQ_ERR_TOO_LARGE, "batch x KV heads beyond %d", MAX_TICKETS);
   TQ_REQUIRE(tq_aligned(pool_dev, 128) && tq_aligned(workspace_dev, 256) && tq_aligned(q_dev, 16) && tq_aligned(out_dev, 16),
              TQ_ERR_ALIGN, "pool (128), workspace (256), q and out (16) must be aligned");
-  const int kb = fmt_bits(L->k_format), vb = fmt_bits(L->v_format);
-  TQ_REQUIRE(kb && vb, TQ_ERR_UNSUPPORTED, "decode attention: K format %d / V format %d not built yet", L->k_format,
-             L->v_format);
-  TQ_REQUIRE(kq->bits == kb && vq->bits == vb, TQ_ERR_INVALID, "quantizer bit widths do not match the cache formats");
+  TQ_REQUIRE(workspace_bytes % 256 == 0, TQ_ERR_ALIGN, "workspace size must be a multiple of 256 bytes");
+  TQ_REQUIRE(q_dtype == TQ_F16 || q_dtype == TQ_BF16 || q_dtype == TQ_F32, TQ_ERR_UNSUPPORTED,
+             "queries must be fp16, bf16 or fp32, got dtype %d", q_dtype);
+  TQ_REQUIRE(out_dtype == TQ_F16 || out_dtype == TQ_BF16 || out_dtype == TQ_F32, TQ_ERR_UNSUPPORTED,
+             "output must be fp16, bf16 or fp32, got dtype %d", out_dtype);
+  if (!k_q8) {
+    const int kb = k_prod ? L->k_format - 17 : L->k_format;
+    TQ_REQUIRE(kq->d == TQ_D && kq->bits == kb, TQ_ERR_INVALID, "K quantizer bit width does not match the cache format");
+    TQ_REQUIRE(!k_prod || kq->qjl, TQ_ERR_INVALID, "PROD cache format needs a K quantizer with a QJL stage");
+  }
+  if (!v_q8) TQ_REQUIRE(vq->d == TQ_D && vq->bits == L->v_format, TQ_ERR_INVALID,
+                        "V quantizer bit width does not match the cache format");
   const SplitPlan plan = plan_splits(batch, L->num_kv_heads, max_pages_per_seq);
   const WsLayout w = ws_layout(batch, num_q_heads, plan.num_splits);
   TQ_REQUIRE((int64_t)w.total <= workspace_bytes, TQ_ERR_TOO_LARGE, "workspace of %lld bytes is smaller than the %lld needed",
              (long long)workspace_bytes, (long long)w.total);
   cudaStream_t st = (cudaStream_t)stream;
   uint8_t* ws = (uint8_t*)workspace_dev;
-  // the status word sits in the last 256 bytes of the caller's buffer
-  int32_t* status = reinterpret_cast<int32_t*>(ws + workspace_bytes - 256);
   if (scale <= 0.f) scale = TQ_RSQRT_D;
   const float qscale = scale * 1.4426950408889634f;
   const int64_t rows = (int64_t)batch * num_q_heads;
-  const int pgrid = (int)(rows < 4096 ? rows : 4096);
-  const int k_dense = kq->rotation == TQ_ROT_DENSE, v_dense = vq->rotation == TQ_ROT_DENSE;
+  const bool k_dense = !k_q8 && kq->rotation == TQ_ROT_DENSE, v_dense = !v_q8 && vq->rotation == TQ_ROT_DENSE;
   float* qrot = reinterpret_cast<float*>(ws + w.qrot);
   float* qproj = reinterpret_cast<float*>(ws + w.qproj);
-#define TQ_PREP(T)                                                                                                  \
-  k_prepare_queries<T><<<pgrid, 128, 0, st>>>((const T*)q_dev, rows, qscale, k_dense, kq->rot32_t, kq->fast, 0,     \
-                                              kq->s32_t, qrot, qproj, status)
   int rc = TQ_OK;
-  if (phases & 1) {
-    switch (q_dtype) {
-      case TQ_F16: TQ_PREP(__half); break;
-      case TQ_BF16: TQ_PREP(__nv_bfloat16); break;
-      case TQ_F32: TQ_PREP(float); break;
-      default:
-        tq_set_error("queries must be fp16, bf16 or fp32, got dtype %d", q_dtype);
-        return TQ_ERR_UNSUPPORTED;
-    }
+  if ((phases & 1) && k_dense) {
+    const int pgrid = (int)(rows < 4096 ? rows : 4096);
+#define TQ_PREP(T)                                                                                              \
+  k_prepare_queries<T><<<pgrid, 128, 0, st>>>((const T*)q_dev, rows, qscale, kq->rot32_t, kq->fast.lut_alpha,   \
+                                              k_prod ? 1 : 0, kq->s32_t, qrot, qproj)
+    if (q_dtype == TQ_F16) TQ_PREP(__half);
+    else if (q_dtype == TQ_BF16) TQ_PREP(__nv_bfloat16);
+    else TQ_PREP(float);
+#undef TQ_PREP
     rc = tq_launch_check("k_prepare_queries");
     if (rc != TQ_OK) return rc;
   }
-#undef TQ_PREP
+  if (!(phases & 2)) return TQ_OK;
 
   AttnParams P;
   memset(&P, 0, sizeof(P));
   P.pool = pool_dev;
   P.block_table = block_table_dev;
   P.seq_lens = seq_lens_dev;
+  P.q = q_dev;
   P.qrot = qrot;
   P.qproj = qproj;
   P.part_o = reinterpret_cast<float*>(ws + w.part_o);
   P.part_ml = reinterpret_cast<float*>(ws + w.part_ml);
-  P.status = status;
+  P.tickets = reinterpret_cast<int32_t*>(ws + workspace_bytes - TAIL_BYTES);
+  P.status = reinterpret_cast<int32_t*>(ws + workspace_bytes - 256);
+  P.out = out_dev;
+  P.v_rot = v_dense ? vq->rot32 : nullptr;
+  P.qscale = qscale;
+  P.q_dtype = q_dtype;
+  P.out_dtype = out_dtype;
+  P.k_pre = k_dense ? 1 : 0;
+  P.k_ident = k_q8 ? 1 : 0;
+  P.v_ident = v_q8 ? 1 : 0;
   P.max_pages = max_pages_per_seq;
   P.batch = batch;
   P.hq = num_q_heads;
@@ -627,31 +882,22 @@ extern "C" int tq_decode_attn_phases(const tq_quantizer* kq, const tq_quantizer*
   P.group = group;
   P.chunk_pages = plan.chunk_pages;
   P.num_splits = plan.num_splits;
+  P.stages = L->record_bytes > 24 * 1024 ? 2 : 3;
   P.L = *L;
+  TqFast none;
+  memset(&none, 0, sizeof(none));
+  none.lut_alpha = 1.0f;
+  const TqFast& fk = k_q8 ? none : kq->fast;
+  const TqFast& fv = v_q8 ? none : vq->fast;
+  rc = TQ_ERR_UNSUPPORTED;
+  tq_set_error("decode attention: K format %d with V format %d is not instantiated", L->k_format, L->v_format);
 #define TQ_ATT(K, V) \
-  if (kb == K && vb == V) rc = launch_attn<K, V>(P, kq->fast, vq->fast, st);
-  if (phases & 2) {
-    rc = TQ_ERR_UNSUPPORTED;
-    TQ_ATT(2, 2) TQ_ATT(2, 3) TQ_ATT(2, 4) TQ_ATT(3, 2) TQ_ATT(3, 3) TQ_ATT(3, 4) TQ_ATT(4, 2) TQ_ATT(4, 3) TQ_ATT(4, 4)
-    if (rc != TQ_OK) return rc;
-  }
+  if (L->k_format == K && L->v_format == V) rc = launch_attn<K, V>(P, fk, fv, st);
+  TQ_ATT(2, 2) TQ_ATT(2, 3) TQ_ATT(2, 4) TQ_ATT(3, 2) TQ_ATT(3, 3) TQ_ATT(3, 4) TQ_ATT(4, 2) TQ_ATT(4, 3) TQ_ATT(4, 4)
+  TQ_ATT(8, 2) TQ_ATT(8, 3) TQ_ATT(8, 4) TQ_ATT(8, 8)
+  TQ_ATT(18, 2) TQ_ATT(18, 3) TQ_ATT(19, 2) TQ_ATT(19, 3) TQ_ATT(19, 4) TQ_ATT(20, 3) TQ_ATT(20, 4)
 #undef TQ_ATT
-  if (!(phases & 4)) return TQ_OK;
-
-#define TQ_COMB(T)                                                                                             \
-  k_decode_combine<T><<<(unsigned)rows, 128, 0, st>>>(P.part_o, P.part_ml, seq_lens_dev, num_q_heads,          \
-                                                      plan.num_splits, plan.chunk_pages, L->page_tokens, v_dense, \
-                                                      vq->rot32, vq->fast, (T*)out_dev)
-  switch (out_dtype) {
-    case TQ_F16: TQ_COMB(__half); break;
-    case TQ_BF16: TQ_COMB(__nv_bfloat16); break;
-    case TQ_F32: TQ_COMB(float); break;
-    default:
-      tq_set_error("output must be fp16, bf16 or fp32, got dtype %d", out_dtype);
-      return TQ_ERR_UNSUPPORTED;
-  }
-#undef TQ_COMB
-  return tq_launch_check("k_decode_combine");
+  return rc;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -668,8 +914,6 @@ extern "C" int tq_decode_attn_phases(const tq_quantizer* kq, const tq_quantizer*
 // In host code `g_static_scratch` is only a handle for the symbol, not an address the GPU can use;
 // the device address comes from cudaGetSymbolAddress, looked up once per device below.
 // ------------------------------------------------------------------------------------------
-#include <mutex>
-
 #define TQ_STATIC_SCRATCH_BYTES TQ_DECODE_STATIC_SCRATCH_BYTES  // 8 MiB, stated in tq_b200.h
 #define TQ_STATIC_MAX_DEVICES 64
 
@@ -712,9 +956,10 @@ extern "C" int tq_decode_attn_static(const tq_quantizer* kq, const tq_quantizer*
   void* scratch = nullptr;
   int rc = static_scratch_for_current_device(&scratch);
   if (rc != TQ_OK) return rc;
-  // Nothing in the scratch has to start at zero: the query kernel resets the status word, and every
-  // partial that the merge kernel reads is written by the attention kernel of the same call.
+  // What must start at zero: the ticket counters at the end of the array.  The array is zero when the
+  // library is loaded, and every call leaves its counters at zero again (the CTA that takes the last
+  // ticket resets it), so nothing is cleared here.  Partials are written before they are read.
   return tq_decode_attn_phases(kq, vq, L, pool_dev, block_table_dev, max_pages_per_seq, seq_lens_dev, q_dev, q_dtype,
-                               batch, num_q_heads, scale, scratch, TQ_STATIC_SCRATCH_BYTES, out_dev, out_dtype, 7,
+                               batch, num_q_heads, scale, scratch, TQ_STATIC_SCRATCH_BYTES, out_dev, out_dtype, 3,
                                stream);
 }

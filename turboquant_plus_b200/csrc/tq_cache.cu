@@ -1,0 +1,52 @@
+// Quantize-on-append into the paged cache (dispatch over the per-tensor formats).
+#include "tq_internal.cuh"
+
+extern "C" int tq_cache_append(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cache_layout* L,
+                               uint8_t* pool_dev, const void* k_dev, const void* v_dev, int32_t dtype, int64_t n_tokens,
+                               const int64_t* slot_dev, void* stream) {
+  TQ_REQUIRE(L && pool_dev, TQ_ERR_INVALID, "tq_cache_append: layout or pool missing");
+  TQ_REQUIRE(n_tokens >= 0, TQ_ERR_INVALID, "n_tokens must be >= 0");
+  if (n_tokens == 0) return TQ_OK;
+  TQ_REQUIRE(k_dev && v_dev && slot_dev, TQ_ERR_INVALID, "tq_cache_append: k, v or slot mapping missing");
+  TQ_REQUIRE(tq_aligned(pool_dev, 128), TQ_ERR_ALIGN, "cache pool must be 128-byte aligned");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int H = L->num_kv_heads;
+  for (int which = 0; which < 2; ++which) {
+    const int fmt = which == 0 ? L->k_format : L->v_format;
+    const tq_quantizer* q = which == 0 ? kq : vq;
+    const void* x = which == 0 ? k_dev : v_dev;
+    const int idx_off = which == 0 ? L->k_idx_off : L->v_idx_off;
+    const int sc_off = which == 0 ? L->k_scale_off : L->v_scale_off;
+    if (fmt == TQ_FMT_Q8_0) {
+      int rc = tq_q8_0_append_launch(x, dtype, n_tokens, H, pool_dev + idx_off, pool_dev + sc_off, slot_dev,
+                                     L->page_tokens, L->page_stride, L->head_stride, st);
+      if (rc != TQ_OK) return rc;
+      continue;
+    }
+    const bool prod = fmt >= TQ_FMT_PROD2;
+    const int bits = prod ? fmt - 17 : fmt;
+    TQ_REQUIRE(q, TQ_ERR_INVALID, "tq_cache_append: quantizer missing for a turbo/prod tensor");
+    TQ_REQUIRE(q->d == TQ_D && q->bits == bits, TQ_ERR_INVALID,
+               "quantizer (d=%d, bits=%d) does not match cache format %d", q->d, q->bits, fmt);
+    TQ_REQUIRE(!prod || q->qjl, TQ_ERR_INVALID, "PROD cache format needs a quantizer with a QJL stage");
+    TQ_REQUIRE(q->rotation == TQ_ROT_WHT, TQ_ERR_UNSUPPORTED,
+               "quantize-on-append is built for WHT-mode quantizers (dense mode: quantize, then tq_cache_store)");
+    TqQuantDst dst;
+    memset(&dst, 0, sizeof(dst));
+    dst.idx = pool_dev + idx_off;
+    dst.scale = reinterpret_cast<float*>(pool_dev + sc_off);
+    if (prod) {
+      dst.qjl = pool_dev + L->k_qjl_off;
+      dst.rnorm = reinterpret_cast<float*>(pool_dev + L->k_rscale_off);
+      dst.rscale_const = 1;
+    }
+    dst.slots = slot_dev;
+    dst.page_stride = L->page_stride;
+    dst.head_stride = L->head_stride;
+    dst.page_tokens = L->page_tokens;
+    dst.heads = H;
+    int rc = tq_quantize_wht_launch(q->fast, x, dtype, TQ_D, n_tokens * H, dst, prod, st);
+    if (rc != TQ_OK) return rc;
+  }
+  return TQ_OK;
+}

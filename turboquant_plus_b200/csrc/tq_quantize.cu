@@ -12,19 +12,46 @@
 
 // ------------------------------------------------------------------------------------------
 // d = 128, WHT rotation
+//
+// The integer ALU pipe of an SM runs at half the FP32 rate, so everything that can be phrased as fp32
+// arithmetic is: sign flips are multiplications by +-1, threshold tests produce 0.0f / 1.0f that are summed,
+// the index is assembled as a float, and eight 3-bit indices are packed by an exact fp32 Horner sum
+// (< 2^24) that is turned into an integer once per group.
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint8_t* tq_dst_ptr(uint8_t* base, const TqQuantDst& dst, int64_t v, int32_t elem_bytes,
                                                bool& ok) {
   if (dst.page_tokens == 0) return base + v * elem_bytes;
-  const int64_t tok = v / dst.heads;
-  const int32_t head = (int32_t)(v - tok * dst.heads);
+  // 32-bit arithmetic whenever the numbers allow it (64-bit division costs ~100 instructions)
+  int64_t tok;
+  int32_t head;
+  if (v < 0x7fffffffLL) {
+    const uint32_t v32 = (uint32_t)v, h32 = (uint32_t)dst.heads;
+    const uint32_t t32 = v32 / h32;
+    tok = t32;
+    head = (int32_t)(v32 - t32 * h32);
+  } else {
+    tok = v / dst.heads;
+    head = (int32_t)(v - tok * dst.heads);
+  }
   const int64_t slot = dst.slots ? dst.slots[tok] : tok;
   if (slot < 0) {
     ok = false;
     return base;
   }
-  const int64_t page = slot / dst.page_tokens;
-  const int32_t within = (int32_t)(slot - page * dst.page_tokens);
+  int64_t page;
+  int32_t within;
+  if ((dst.page_tokens & (dst.page_tokens - 1)) == 0) {
+    const int sh = 31 - __clz(dst.page_tokens);
+    page = slot >> sh;
+    within = (int32_t)(slot & (dst.page_tokens - 1));
+  } else if (slot < 0x7fffffffLL) {
+    const uint32_t pg = (uint32_t)slot / (uint32_t)dst.page_tokens;
+    page = pg;
+    within = (int32_t)((uint32_t)slot - pg * (uint32_t)dst.page_tokens);
+  } else {
+    page = slot / dst.page_tokens;
+    within = (int32_t)(slot - page * dst.page_tokens);
+  }
   return base + page * dst.page_stride + head * dst.head_stride + (int64_t)within * elem_bytes;
 }
 
@@ -32,12 +59,21 @@ template <typename Tin, int BITS, bool SYM, bool QJL>
 __global__ void __launch_bounds__(256) k_quantize_wht(const TqFast f, const Tin* __restrict__ x, int64_t ld, int64_t n,
                                                       const TqQuantDst dst) {
   constexpr int NC = 1 << BITS, HALF = NC / 2;
-  constexpr int IDXB = 16 * BITS;  // packed bytes per vector
+  constexpr int IDXB = 16 * BITS;              // packed bytes per vector
+  constexpr int GS = BITS == 4 ? 4 : 8;        // indices per fp32 Horner group (GS * BITS <= 24 bits)
+  constexpr int NG = 16 / GS;
+  constexpr float RADIX = (float)(1 << BITS);
   __shared__ __align__(16) uint8_t st_idx[8][4][IDXB];
   __shared__ __align__(16) uint8_t st_q[8][4][16];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, sub = lane & 7, vi = lane >> 3;
   const uint32_t b1 = tq_lane_bits16(f.s1, sub), b2 = tq_lane_bits16(f.s2, sub);
   const bool need_c = QJL || (dst.scale != nullptr && f.norm_correction);
+  float sg1[16], sg2[16];
+#pragma unroll
+  for (int k = 0; k < 16; ++k) {
+    sg1[k] = ((b1 >> k) & 1u) ? -1.0f : 1.0f;
+    sg2[k] = ((b2 >> k) & 1u) ? -1.0f : 1.0f;
+  }
 
   for (int64_t base = ((int64_t)blockIdx.x * 8 + warp) * 4; base < n; base += (int64_t)gridDim.x * 32) {
     const int64_t v = base + vi;
@@ -56,48 +92,51 @@ __global__ void __launch_bounds__(256) k_quantize_wht(const TqFast f, const Tin*
     const float nrm = sqrtf(ss);
     const float safe = nrm > 0.f ? nrm : 1.0f;  // turboquant/polar_quant.py:74
 #pragma unroll
-    for (int k = 0; k < 16; ++k) u[k] = tq_flip(u[k], b1, k);
+    for (int k = 0; k < 16; ++k) u[k] *= sg1[k];
     tq_wht16_regs(u);
     tq_wht128_lanes(u, sub);
-#pragma unroll
-    for (int k = 0; k < 16; ++k) u[k] = tq_flip(u[k], b2, k);
-    // u = y * safe * sqrt(d) with y the rotated unit vector; compare against scaled boundaries
+    // u * sg2 = y * safe * sqrt(d) with y the rotated unit vector; compare against scaled boundaries
     const float ts = safe * TQ_SQRT_D;
     float T[NC - 1];
 #pragma unroll
     for (int j = 0; j < NC - 1; ++j) T[j] = f.bnd[j] * ts;
 
-    uint32_t idx[16];
     float c[16];
     float cc = 0.f;
+    float wf[NG];
+#pragma unroll
+    for (int gq = 0; gq < NG; ++gq) wf[gq] = 0.f;
 #pragma unroll
     for (int k = 0; k < 16; ++k) {
+      u[k] *= sg2[k];
+      float idxf, cm;
       if (SYM) {
+        // magnitude level m = #positive boundaries below |u|, sign from the centre boundary
         const float a = fabsf(u[k]);
-        int m = 0;
-        float cm = f.cent[HALF];
+        float m = 0.f;
+        cm = f.cent[HALF];
 #pragma unroll
         for (int j = 1; j < HALF; ++j) {
-          const bool p = a > T[HALF - 1 + j];
-          m += p ? 1 : 0;
-          if (need_c) cm = p ? f.cent[HALF + j] : cm;
+          const float p = a > T[HALF - 1 + j] ? 1.0f : 0.0f;
+          m += p;
+          if (need_c) cm = fmaf(p, f.cent[HALF + j] - f.cent[HALF + j - 1], cm);
         }
-        const bool pos = u[k] > T[HALF - 1];
-        idx[k] = pos ? (HALF + m) : (HALF - 1 - m);
-        c[k] = pos ? cm : -cm;
+        const float sgn = u[k] > T[HALF - 1] ? 1.0f : -1.0f;
+        idxf = fmaf(sgn, m + 0.5f, (float)HALF - 0.5f);  // HALF + m or HALF - 1 - m
+        cm *= sgn;
       } else {
-        int m = 0;
-        float cm = f.cent[0];
+        idxf = 0.f;
+        cm = f.cent[0];
 #pragma unroll
         for (int j = 0; j < NC - 1; ++j) {
-          const bool p = u[k] > T[j];
-          m += p ? 1 : 0;
-          if (need_c) cm = p ? f.cent[j + 1] : cm;
+          const float p = u[k] > T[j] ? 1.0f : 0.0f;
+          idxf += p;
+          if (need_c) cm = fmaf(p, f.cent[j + 1] - f.cent[j], cm);
         }
-        idx[k] = m;
-        c[k] = cm;
       }
-      if (need_c) cc = fmaf(c[k], c[k], cc);
+      c[k] = cm;
+      if (need_c) cc = fmaf(cm, cm, cc);
+      wf[k / GS] = fmaf(wf[k / GS], RADIX, idxf);  // exact: below 2^24
     }
     float invn = 1.0f;
     if (need_c) {
@@ -108,13 +147,17 @@ __global__ void __launch_bounds__(256) k_quantize_wht(const TqFast f, const Tin*
         invn = 1.0f / cn;
       }
     }
-
-    // pack 16 indices MSB first: two groups of 8 -> BITS bytes each
-    uint32_t w0 = 0, w1 = 0;
+    // integers out of the Horner sums (exact: the sums are whole numbers below 2^24)
+    uint32_t wi[NG];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      w0 = (w0 << BITS) | idx[k];
-      w1 = (w1 << BITS) | idx[8 + k];
+    for (int gq = 0; gq < NG; ++gq) wi[gq] = __float2uint_rn(wf[gq]);
+    uint32_t w0, w1;  // 8 indices each, MSB first
+    if (BITS == 4) {
+      w0 = (wi[0] << 16) | wi[1 % NG];
+      w1 = (wi[2 % NG] << 16) | wi[3 % NG];
+    } else {
+      w0 = wi[0];
+      w1 = wi[1 % NG];
     }
     if (dst.idx) {
       uint8_t* s = &st_idx[warp][vi][sub * 2 * BITS];
@@ -125,12 +168,14 @@ __global__ void __launch_bounds__(256) k_quantize_wht(const TqFast f, const Tin*
       }
     }
     if (dst.idx_u8 && ok) {
-      uint4 o;
-      o.x = idx[0] | (idx[1] << 8) | (idx[2] << 16) | (idx[3] << 24);
-      o.y = idx[4] | (idx[5] << 8) | (idx[6] << 16) | (idx[7] << 24);
-      o.z = idx[8] | (idx[9] << 8) | (idx[10] << 16) | (idx[11] << 24);
-      o.w = idx[12] | (idx[13] << 8) | (idx[14] << 16) | (idx[15] << 24);
-      *reinterpret_cast<uint4*>(dst.idx_u8 + v * TQ_D + sub * 16) = o;
+      uint32_t o4[4] = {0, 0, 0, 0};
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        const uint32_t wsrc = k < 8 ? w0 : w1;
+        const uint32_t id = (wsrc >> (BITS * (7 - (k & 7)))) & ((1u << BITS) - 1);
+        o4[k >> 2] |= id << (8 * (k & 3));
+      }
+      *reinterpret_cast<uint4*>(dst.idx_u8 + v * TQ_D + sub * 16) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
     }
 
     float rn = 0.f;
@@ -149,7 +194,7 @@ __global__ void __launch_bounds__(256) k_quantize_wht(const TqFast f, const Tin*
       const uint32_t m12 = b1 ^ tq_lane_bits16(f.j1, sub);
       const uint32_t bj2 = tq_lane_bits16(f.j2, sub);
 #pragma unroll
-      for (int k = 0; k < 16; ++k) u[k] = tq_flip(u[k], b2, k);
+      for (int k = 0; k < 16; ++k) u[k] *= sg2[k];
       tq_wht16_regs(u);
       tq_wht128_lanes(u, sub);
 #pragma unroll

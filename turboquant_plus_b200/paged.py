@@ -123,7 +123,8 @@ class PagedKVCache:
         need = nv.load().tq_decode_workspace_bytes(batch, num_q_heads, self.num_kv_heads, max_pages)
         nv.check(int(need))
         if self._ws is None or self._ws.numel() < need:
-            self._ws = torch.empty((int(need),), dtype=torch.uint8, device=self.device)
+            # zero-filled: the ticket counters at the end of a workspace must start at zero
+            self._ws = torch.zeros((int(need),), dtype=torch.uint8, device=self.device)
         return self._ws
 
     def attend(self, q, block_table, seq_lens, scale=None, out=None, workspace=None, phases=7):
