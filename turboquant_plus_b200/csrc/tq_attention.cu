@@ -148,10 +148,17 @@ template <int BITS> struct PairLut {
 template <int BITS>
 __device__ __forceinline__ void lut_fill(uint8_t* lut, const uint16_t* c16, int tid) {
   using T = PairLut<BITS>;
-  uint32_t* w = reinterpret_cast<uint32_t*>(lut);
-  for (int i = tid; i < T::BYTES / 4; i += ATT_THREADS) {
-    const int e = T::REPL ? (i >> 5) : i;
-    w[i] = (uint32_t)c16[e >> BITS] | ((uint32_t)c16[e & ((1 << BITS) - 1)] << 16);
+  if (T::REPL) {
+    // entry e occupies 128 bytes (one word per lane): eight 16-byte stores of the same value
+    for (int i = tid; i < T::ENTRIES * 8; i += ATT_THREADS) {
+      const int e = i >> 3;
+      const uint32_t v = (uint32_t)c16[e >> BITS] | ((uint32_t)c16[e & ((1 << BITS) - 1)] << 16);
+      reinterpret_cast<uint4*>(lut)[i] = make_uint4(v, v, v, v);
+    }
+  } else {
+    uint32_t* w = reinterpret_cast<uint32_t*>(lut);
+    for (int e = tid; e < T::ENTRIES; e += ATT_THREADS)
+      w[e] = (uint32_t)c16[e >> BITS] | ((uint32_t)c16[e & ((1 << BITS) - 1)] << 16);
   }
 }
 
@@ -609,47 +616,62 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn(const AttnParams
   __syncthreads();
   if (!s_flags[1]) return;
   __threadfence();
-  // (m, l) of every split -> shared memory; per head one warp finds the max and the weights 2^(m_s - M)
-  float* sw = reinterpret_cast<float*>(stage0);      // [head][ns] weights
-  float* sl = sw + MAX_G * ns;                       // [head] 1 / (sum_s l_s w_s)
-  for (int e = tid; e < P.group * ns; e += ATT_THREADS) {
-    const int head = e / ns, s_i = e - head * ns;
-    sw[head * ns + s_i] = __ldcg(P.part_ml + ((row0 + head) * P.num_splits + s_i) * 2);
-  }
-  __syncthreads();
-  if (warp < P.group) {
-    float M = -INFINITY;
-    for (int s_i = lane; s_i < ns; s_i += 32) M = fmaxf(M, sw[warp * ns + s_i]);
+  // Warp w folds splits w, w+8, w+16, ... of every head (eight independent 16-byte loads per lane in flight,
+  // online rescaling inside the warp), then the eight warp results are folded in fixed order.
+  float* red = reinterpret_cast<float*>(stage0);          // [warp][head][128]
+  float* redm = red + ATT_WARPS * MAX_G * TQ_D;           // [warp][head][2] = (max, sum)
+  for (int head = 0; head < P.group; ++head) {
+    const size_t base = (row0 + head) * P.num_splits;
+    float M = -INFINITY, Lsum = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = warp; s0 < ns; s0 += 8 * ATT_WARPS) {
+      float2 ml[8];
+      float4 ov[8];
 #pragma unroll
-    for (int sh = 16; sh > 0; sh >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, sh));
-    float Lsum = 0.f;
-    for (int s_i = lane; s_i < ns; s_i += 32) {
-      const float f = exp2f(sw[warp * ns + s_i] - M);
-      sw[warp * ns + s_i] = f;
-      Lsum = fmaf(__ldcg(P.part_ml + ((row0 + warp) * P.num_splits + s_i) * 2 + 1), f, Lsum);
+      for (int u = 0; u < 8; ++u) {
+        const int s_i = s0 + ATT_WARPS * u;
+        const bool have = s_i < ns;
+        ml[u] = have ? __ldcg(reinterpret_cast<const float2*>(P.part_ml) + base + s_i) : make_float2(-INFINITY, 0.f);
+        ov[u] = have ? __ldcg(reinterpret_cast<const float4*>(P.part_o + (base + s_i) * TQ_D) + lane)
+                     : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      float Mn = M;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) Mn = fmaxf(Mn, ml[u].x);   // finite: split s0 exists
+      const float r = exp2f(M - Mn);
+      acc.x *= r; acc.y *= r; acc.z *= r; acc.w *= r;
+      Lsum *= r;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float f = exp2f(ml[u].x - Mn);
+        acc.x = fmaf(ov[u].x, f, acc.x); acc.y = fmaf(ov[u].y, f, acc.y);
+        acc.z = fmaf(ov[u].z, f, acc.z); acc.w = fmaf(ov[u].w, f, acc.w);
+        Lsum = fmaf(ml[u].y, f, Lsum);
+      }
+      M = Mn;
     }
-#pragma unroll
-    for (int sh = 16; sh > 0; sh >>= 1) Lsum += __shfl_xor_sync(0xffffffffu, Lsum, sh);
-    if (lane == 0) sl[warp] = 1.0f / (Lsum * (VT::Q8 ? 1.0f : fv.lut_alpha));
+    reinterpret_cast<float4*>(red + ((size_t)warp * MAX_G + head) * TQ_D)[lane] = acc;
+    if (lane == 0) {
+      redm[(warp * MAX_G + head) * 2] = M;
+      redm[(warp * MAX_G + head) * 2 + 1] = Lsum;
+    }
   }
   __syncthreads();
   for (int e = tid; e < P.group * TQ_D; e += ATT_THREADS) {
     const int head = e >> 7, dim = e & 127;
-    const float* po = P.part_o + (row0 + head) * P.num_splits * TQ_D + dim;
-    const float* wv = sw + head * ns;
-    float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
-    int s_i = 0;
-    for (; s_i + 4 <= ns; s_i += 4) {  // four independent loads in flight; summation order is fixed
-      const float a = __ldcg(po + (size_t)s_i * TQ_D), bq = __ldcg(po + (size_t)(s_i + 1) * TQ_D);
-      const float c = __ldcg(po + (size_t)(s_i + 2) * TQ_D), dq = __ldcg(po + (size_t)(s_i + 3) * TQ_D);
-      acc0 = fmaf(a, wv[s_i], acc0);
-      acc1 = fmaf(bq, wv[s_i + 1], acc1);
-      acc2 = fmaf(c, wv[s_i + 2], acc2);
-      acc3 = fmaf(dq, wv[s_i + 3], acc3);
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; ++w) M = fmaxf(M, redm[(w * MAX_G + head) * 2]);
+    float acc = 0.f, Lsum = 0.f;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; ++w) {
+      const float mw = redm[(w * MAX_G + head) * 2];
+      const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+      acc = fmaf(red[((size_t)w * MAX_G + head) * TQ_D + dim], f, acc);
+      Lsum = fmaf(redm[(w * MAX_G + head) * 2 + 1], f, Lsum);
     }
-    for (; s_i < ns; ++s_i) acc0 = fmaf(__ldcg(po + (size_t)s_i * TQ_D), wv[s_i], acc0);
     // attention output in V's rotated space
-    qbuf[head * TQ_D + dim] = ((acc0 + acc1) + (acc2 + acc3)) * sl[head];
+    qbuf[head * TQ_D + dim] = acc / (Lsum * (VT::Q8 ? 1.0f : fv.lut_alpha));
   }
   __syncthreads();
   if (P.v_rot) {  // dense rotation: x = R^T y

@@ -68,11 +68,22 @@ __global__ void __launch_bounds__(256) k_quantize_wht(const TqFast f, const Tin*
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, sub = lane & 7, vi = lane >> 3;
   const uint32_t b1 = tq_lane_bits16(f.s1, sub), b2 = tq_lane_bits16(f.s2, sub);
   const bool need_c = QJL || (dst.scale != nullptr && f.norm_correction);
-  float sg1[16], sg2[16];
+  // sign1 as +-1.0f factors, pinned in registers (opaque to the compiler, or it recomputes them from the
+  // bit mask for every vector on the half-rate integer pipe)
+  float sg1[16];
 #pragma unroll
   for (int k = 0; k < 16; ++k) {
     sg1[k] = ((b1 >> k) & 1u) ? -1.0f : 1.0f;
-    sg2[k] = ((b2 >> k) & 1u) ? -1.0f : 1.0f;
+    asm volatile("" : "+f"(sg1[k]));
+  }
+  // sign2 never touches the values when the codebook is symmetric: negating a coordinate mirrors its index
+  // (i -> 2^b - 1 - i), which is an XOR of the packed word with a per-lane constant.  (A coordinate exactly on a
+  // boundary then takes the upper instead of the lower index on mirrored lanes.)
+  uint32_t flip0 = 0, flip1 = 0;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    if ((b2 >> k) & 1u) flip0 |= ((1u << BITS) - 1) << (BITS * (7 - k));
+    if ((b2 >> (8 + k)) & 1u) flip1 |= ((1u << BITS) - 1) << (BITS * (7 - k));
   }
 
   for (int64_t base = ((int64_t)blockIdx.x * 8 + warp) * 4; base < n; base += (int64_t)gridDim.x * 32) {
@@ -95,7 +106,7 @@ __global__ void __launch_bounds__(256) k_quantize_wht(const TqFast f, const Tin*
     for (int k = 0; k < 16; ++k) u[k] *= sg1[k];
     tq_wht16_regs(u);
     tq_wht128_lanes(u, sub);
-    // u * sg2 = y * safe * sqrt(d) with y the rotated unit vector; compare against scaled boundaries
+    // sg2 * u = y * safe * sqrt(d) with y the rotated unit vector; compare against scaled boundaries
     const float ts = safe * TQ_SQRT_D;
     float T[NC - 1];
 #pragma unroll
@@ -108,7 +119,7 @@ __global__ void __launch_bounds__(256) k_quantize_wht(const TqFast f, const Tin*
     for (int gq = 0; gq < NG; ++gq) wf[gq] = 0.f;
 #pragma unroll
     for (int k = 0; k < 16; ++k) {
-      u[k] *= sg2[k];
+      if (!SYM) u[k] = tq_flip(u[k], b2, k);
       float idxf, cm;
       if (SYM) {
         // magnitude level m = #positive boundaries below |u|, sign from the centre boundary
@@ -159,6 +170,10 @@ __global__ void __launch_bounds__(256) k_quantize_wht(const TqFast f, const Tin*
       w0 = wi[0];
       w1 = wi[1 % NG];
     }
+    if (SYM && nrm > 0.f) {  // a zero vector keeps the index of the value 0 on every lane
+      w0 ^= flip0;
+      w1 ^= flip1;
+    }
     if (dst.idx) {
       uint8_t* s = &st_idx[warp][vi][sub * 2 * BITS];
 #pragma unroll
@@ -193,8 +208,10 @@ __global__ void __launch_bounds__(256) k_quantize_wht(const TqFast f, const Tin*
       // r ~ D1 H D2 E, then S r ~ J2 H J1 r  (positive factors dropped: only signs are kept)
       const uint32_t m12 = b1 ^ tq_lane_bits16(f.j1, sub);
       const uint32_t bj2 = tq_lane_bits16(f.j2, sub);
+      if (!SYM) {  // symmetric codebooks never applied sign2, so there is nothing to undo
 #pragma unroll
-      for (int k = 0; k < 16; ++k) u[k] *= sg2[k];
+        for (int k = 0; k < 16; ++k) u[k] = tq_flip(u[k], b2, k);
+      }
       tq_wht16_regs(u);
       tq_wht128_lanes(u, sub);
 #pragma unroll
