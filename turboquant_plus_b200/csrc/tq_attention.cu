@@ -616,20 +616,24 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn(const AttnParams
   __syncthreads();
   if (!s_flags[1]) return;
   __threadfence();
-  // Warp w folds splits w, w+8, w+16, ... of every head (eight independent 16-byte loads per lane in flight,
-  // online rescaling inside the warp), then the eight warp results are folded in fixed order.
-  float* red = reinterpret_cast<float*>(stage0);          // [warp][head][128]
-  float* redm = red + ATT_WARPS * MAX_G * TQ_D;           // [warp][head][2] = (max, sum)
-  for (int head = 0; head < P.group; ++head) {
+  // The eight warps share the heads: with `group` heads, wph = 8 / group warps work on each head and warp
+  // (part, head) folds splits part, part + wph, ... (ten independent 16-byte loads per lane in flight, online
+  // rescaling inside the warp); then the wph results per head are folded in fixed order.
+  float* red = reinterpret_cast<float*>(stage0);          // [warp][128]
+  float* redm = red + ATT_WARPS * TQ_D;                   // [warp][2] = (max, sum)
+  const int wph = ATT_WARPS / P.group;                    // >= 1 because group <= 8
+  if (warp < wph * P.group) {
+    const int head = warp % P.group, part = warp / P.group;
     const size_t base = (row0 + head) * P.num_splits;
     float M = -INFINITY, Lsum = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s0 = warp; s0 < ns; s0 += 8 * ATT_WARPS) {
-      float2 ml[8];
-      float4 ov[8];
+    constexpr int NB = 10;
+    for (int s0 = part; s0 < ns; s0 += NB * wph) {
+      float2 ml[NB];
+      float4 ov[NB];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int s_i = s0 + ATT_WARPS * u;
+      for (int u = 0; u < NB; ++u) {
+        const int s_i = s0 + wph * u;
         const bool have = s_i < ns;
         ml[u] = have ? __ldcg(reinterpret_cast<const float2*>(P.part_ml) + base + s_i) : make_float2(-INFINITY, 0.f);
         ov[u] = have ? __ldcg(reinterpret_cast<const float4*>(P.part_o + (base + s_i) * TQ_D) + lane)
@@ -637,12 +641,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn(const AttnParams
       }
       float Mn = M;
 #pragma unroll
-      for (int u = 0; u < 8; ++u) Mn = fmaxf(Mn, ml[u].x);   // finite: split s0 exists
+      for (int u = 0; u < NB; ++u) Mn = fmaxf(Mn, ml[u].x);   // finite: split s0 exists
       const float r = exp2f(M - Mn);
       acc.x *= r; acc.y *= r; acc.z *= r; acc.w *= r;
       Lsum *= r;
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
+      for (int u = 0; u < NB; ++u) {
         const float f = exp2f(ml[u].x - Mn);
         acc.x = fmaf(ov[u].x, f, acc.x); acc.y = fmaf(ov[u].y, f, acc.y);
         acc.z = fmaf(ov[u].z, f, acc.z); acc.w = fmaf(ov[u].w, f, acc.w);
@@ -650,25 +654,24 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn(const AttnParams
       }
       M = Mn;
     }
-    reinterpret_cast<float4*>(red + ((size_t)warp * MAX_G + head) * TQ_D)[lane] = acc;
+    reinterpret_cast<float4*>(red + (size_t)warp * TQ_D)[lane] = acc;
     if (lane == 0) {
-      redm[(warp * MAX_G + head) * 2] = M;
-      redm[(warp * MAX_G + head) * 2 + 1] = Lsum;
+      redm[warp * 2] = M;
+      redm[warp * 2 + 1] = Lsum;
     }
   }
   __syncthreads();
   for (int e = tid; e < P.group * TQ_D; e += ATT_THREADS) {
     const int head = e >> 7, dim = e & 127;
     float M = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < ATT_WARPS; ++w) M = fmaxf(M, redm[(w * MAX_G + head) * 2]);
+    for (int pt = 0; pt < wph; ++pt) M = fmaxf(M, redm[(pt * P.group + head) * 2]);
     float acc = 0.f, Lsum = 0.f;
-#pragma unroll
-    for (int w = 0; w < ATT_WARPS; ++w) {
-      const float mw = redm[(w * MAX_G + head) * 2];
+    for (int pt = 0; pt < wph; ++pt) {
+      const int w = pt * P.group + head;
+      const float mw = redm[w * 2];
       const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
-      acc = fmaf(red[((size_t)w * MAX_G + head) * TQ_D + dim], f, acc);
-      Lsum = fmaf(redm[(w * MAX_G + head) * 2 + 1], f, Lsum);
+      acc = fmaf(red[(size_t)w * TQ_D + dim], f, acc);
+      Lsum = fmaf(redm[w * 2 + 1], f, Lsum);
     }
     // attention output in V's rotated space
     qbuf[head * TQ_D + dim] = acc / (Lsum * (VT::Q8 ? 1.0f : fv.lut_alpha));

@@ -24,7 +24,11 @@ __device__ __forceinline__ uint8_t* tq_dst_ptr(uint8_t* base, const TqQuantDst& 
   // 32-bit arithmetic whenever the numbers allow it (64-bit division costs ~100 instructions)
   int64_t tok;
   int32_t head;
-  if (v < 0x7fffffffLL) {
+  if ((dst.heads & (dst.heads - 1)) == 0) {
+    const int sh = 31 - __clz(dst.heads);
+    tok = v >> sh;
+    head = (int32_t)(v & (dst.heads - 1));
+  } else if (v < 0x7fffffffLL) {
     const uint32_t v32 = (uint32_t)v, h32 = (uint32_t)dst.heads;
     const uint32_t t32 = v32 / h32;
     tok = t32;
@@ -106,11 +110,18 @@ __global__ void __launch_bounds__(256) k_quantize_wht(const TqFast f, const Tin*
     for (int k = 0; k < 16; ++k) u[k] *= sg1[k];
     tq_wht16_regs(u);
     tq_wht128_lanes(u, sub);
-    // sg2 * u = y * safe * sqrt(d) with y the rotated unit vector; compare against scaled boundaries
+    // sg2 * u = y * safe * sqrt(d) with y the rotated unit vector.
+    // Magnitude threshold tests on the FP32 pipe: step(a > b) = sat(sat(a * BIGS - b * BIG) * 2^16) with BIG = 2^40 and
+    // BIGS = BIG / (safe * sqrt d).  The inner FMA is exact up to one rounding, so it is positive exactly when
+    // a * BIGS > b * BIG, and a positive result is at least 2^-10 (operands near 2^37 carry 48 exact product
+    // bits; 2^-12 for the smallest 4-bit boundary), which the second saturating multiply turns into 1.  Compared with testing a > b * safe * sqrt d
+    // this moves a decision only for coordinates within a few 1e-8 relative of a boundary.
     const float ts = safe * TQ_SQRT_D;
-    float T[NC - 1];
+    constexpr float BIG = 1099511627776.0f;  // 2^40
+    const float bigs = BIG / ts;
+    float NB[NC - 1];                        // -b_j * BIG
 #pragma unroll
-    for (int j = 0; j < NC - 1; ++j) T[j] = f.bnd[j] * ts;
+    for (int j = 0; j < NC - 1; ++j) NB[j] = -f.bnd[j] * BIG;
 
     float c[16];
     float cc = 0.f;
@@ -128,11 +139,12 @@ __global__ void __launch_bounds__(256) k_quantize_wht(const TqFast f, const Tin*
         cm = f.cent[HALF];
 #pragma unroll
         for (int j = 1; j < HALF; ++j) {
-          const float p = a > T[HALF - 1 + j] ? 1.0f : 0.0f;
+          const float p = __saturatef(__saturatef(fmaf(a, bigs, NB[HALF - 1 + j])) * 65536.0f);
           m += p;
           if (need_c) cm = fmaf(p, f.cent[HALF + j] - f.cent[HALF + j - 1], cm);
         }
-        const float sgn = u[k] > T[HALF - 1] ? 1.0f : -1.0f;
+        // the centre boundary is (almost) zero, where the 2^-10 argument does not hold: plain comparison
+        const float sgn = u[k] > f.bnd[HALF - 1] * ts ? 1.0f : -1.0f;
         idxf = fmaf(sgn, m + 0.5f, (float)HALF - 0.5f);  // HALF + m or HALF - 1 - m
         cm *= sgn;
       } else {
@@ -140,7 +152,7 @@ __global__ void __launch_bounds__(256) k_quantize_wht(const TqFast f, const Tin*
         cm = f.cent[0];
 #pragma unroll
         for (int j = 0; j < NC - 1; ++j) {
-          const float p = u[k] > T[j] ? 1.0f : 0.0f;
+          const float p = u[k] > f.bnd[j] * ts ? 1.0f : 0.0f;  // arbitrary codebook: plain comparisons
           idxf += p;
           if (need_c) cm = fmaf(p, f.cent[j + 1] - f.cent[j], cm);
         }
