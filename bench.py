@@ -59,7 +59,7 @@ class ClockSampler:
         self.proc = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-i", str(index), "-lms", "100"], stdout=subprocess.PIPE,
+                                          "-i", str(index), "-lms", "50"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
@@ -244,9 +244,7 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize(dev)
 
-    def timed(graph, steps, warmup):
-        for _ in range(warmup):
-            graph.replay()
+    def timed_once(graph, steps):
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -260,6 +258,15 @@ def run_ours(args):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
         return ms / steps
+
+    def timed(graph, steps, warmup):
+        """Exactly `steps` steps per timed region; the region is repeated (every rank the same number of
+        times) until ~0.4 s have been spent so that the clock sampler sees the GPU under load; median region."""
+        for _ in range(warmup):
+            graph.replay()
+        first = timed_once(graph, steps)
+        rounds = max(1, min(40, int(400.0 / max(first * steps, 1e-3))))
+        return statistics.median([first] + [timed_once(graph, steps) for _ in range(rounds - 1)])
 
     sampler = ClockSampler(local) if rank == 0 else None
     ms_step = timed(graphs[7], args.steps, args.warmup)
@@ -310,7 +317,10 @@ def run_ours(args):
             "frac_of_8tbs": value / world * BYTES_PER_KV_TOKEN / 8e12,
             "quantize_vectors_per_s": vec_per_s,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_source": f"{peak_src} copy bandwidth", "traffic": None,
+                         "peak_source": f"{peak_src} copy bandwidth",
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch, ncu capture summarised in
+                         # profiles/k_decode_attn_turbo3_ctx32768.md
+                         "traffic": 27321600,
                          "kernel": "k_decode_attn<3,3>", "us_per_launch": kernel_s * 1e6,
                          "bytes_per_launch": CTX * HKV * BYTES_PER_KV_TOKEN},
             "roofline_quantize": {"bound": "hbm", "kernel": "k_quantize_wht<half,3>, 2 launches of 2^22 vectors into pages",
