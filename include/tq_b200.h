@@ -225,6 +225,21 @@ int tq_decode_attn_phases(const tq_quantizer* kq, const tq_quantizer* vq, const 
                           void* workspace_dev, int64_t workspace_bytes, void* out_dev, int32_t out_dtype,
                           int32_t phases, void* stream);
 
+/* Chunked-prefill attention over the packed cache on the tcgen05 tensor cores: a chunk of
+ * `chunk_tokens` new tokens per sequence, whose K/V rows have already been appended, attends
+ * causally to the cache: query i of sequence b sits at position kv_lens[b] - chunk_tokens + i and
+ * sees the cached tokens 0 .. that position.  Per (sequence, query, head) this is again the
+ * reference tests' dequantize-then-attend (tests/test_kv_cache.py:73-89) restricted to the visible
+ * prefix; the reference has no chunked or masked variant of its own.
+ *   q_dev, out_dev [batch][chunk_tokens][num_q_heads][d]; K and V formats turbo2/3/4; 128-token pages.
+ *   workspace_dev: at least 256 bytes, 256-byte aligned, zero-filled once; its last word is the
+ *   status word read by tq_decode_status_sync (1 = a bounded wait inside the kernel gave up). */
+int tq_prefill_attn(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cache_layout* layout,
+                    const uint8_t* pool_dev, const int32_t* block_table_dev, int32_t max_pages_per_seq,
+                    const int32_t* kv_lens_dev, const void* q_dev, int32_t q_dtype, int32_t batch,
+                    int32_t chunk_tokens, int32_t num_q_heads, float scale, void* workspace_dev,
+                    int64_t workspace_bytes, void* out_dev, int32_t out_dtype, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * tq_decode_attn_static: tq_decode_attn for callers that cannot allocate device memory.
  * (No counterpart in the reference, which has neither an attention kernel nor device memory.)

@@ -424,6 +424,24 @@ def attend_gqa(q, k_hat, v_hat, seq_lens=None, scale=None):
     return out
 
 
+def attend_chunk_gqa(q, k_hat, v_hat, kv_lens, scale=None):
+    """Causal chunked prefill: q (B, Tq, Hq, d) holds the last Tq tokens of each sequence; query i of sequence b
+    sits at position kv_lens[b] - Tq + i and attends to cached positions 0 .. that position (attend_one on the
+    visible prefix).  The mask and the chunking are not in the reference -- parity unpinned for those aspects."""
+    bsz, tq, hq, d = q.shape
+    g = hq // k_hat.shape[1]
+    out = np.zeros((bsz, tq, hq, d))
+    for b in range(bsz):
+        for i in range(tq):
+            n = int(kv_lens[b]) - tq + i + 1
+            if n <= 0:
+                continue
+            for h in range(hq):
+                out[b, i, h] = attend_one(q[b, i, h][None].astype(np.float64), k_hat[b, h // g, :n],
+                                          v_hat[b, h // g, :n], scale)[0]
+    return out
+
+
 # --------------------------------------------------------------------------
 # q8_0 (not in the reference: parity unpinned)
 # --------------------------------------------------------------------------

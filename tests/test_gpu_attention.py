@@ -216,3 +216,38 @@ def test_q8_0_and_prod_records_match_oracle(tq):
             assert abs(rs - code.residual_norms[row] * o.QJL_CONST / np.sqrt(D)) <= 2e-5 * abs(rs) + 1e-30
     assert flips <= 4
     assert cache.bytes_per_token == 108
+
+
+@pytest.mark.parametrize("kf,vf,mode", [("turbo3", "turbo3", "wht"), ("turbo4", "turbo2", "wht"), ("turbo2", "turbo2", "wht"),
+                                        ("turbo3", "turbo3", "dense")])
+def test_prefill_chunk_tcgen05(tq, kf, vf, mode):
+    """Causal chunked prefill (tcgen05 kernel) against dequantize-then-attend on the visible prefix: ragged
+    lengths, a chunk that starts the sequence, a chunk that crosses page edges, 8 query heads per KV head."""
+    import torch
+    rng = np.random.default_rng(23)
+    hkv, g, tq_len = 2, 8, 24
+    kv_lens = [24, 128, 129, 400, 1000]          # first: the chunk is the whole sequence
+    cache = tq.PagedKVCache(D, hkv, num_pages=24, k_format=kf, v_format=vf, seed=42, rotation=mode)
+    ks = [np.stack([o.rope_rotate(o.synth_keys(n, seed=9 * b + h), np.arange(n)) for h in range(hkv)], axis=1)
+          for b, n in enumerate(kv_lens)]
+    vs = [rng.standard_normal((n, hkv, D)).astype(np.float32) for n in kv_lens]
+    bt = fill_cache(cache, ks, vs, kv_lens, rng)
+    q = rng.standard_normal((len(kv_lens), tq_len, hkv * g, D)).astype(np.float16)
+    out = cache.prefill_attend(torch.as_tensor(q).cuda().float(), bt, torch.tensor(kv_lens)).cpu().numpy()
+    assert cache.kernel_status() == 0
+    ctx = max(kv_lens)
+    kh = np.zeros((len(kv_lens), hkv, ctx, D))
+    vh = np.zeros((len(kv_lens), hkv, ctx, D))
+    for b, n in enumerate(kv_lens):
+        for h in range(hkv):
+            kh[b, h, :n] = oracle_roundtrip(cache, ks[b][:, h], "k")
+            vh[b, h, :n] = oracle_roundtrip(cache, vs[b][:, h], "v")
+    ref = o.attend_chunk_gqa(q.astype(np.float64), kh, vh, kv_lens)
+    err = max_rel(out.reshape(-1, D), ref.reshape(-1, D))
+    print(f"prefill {kf}/{vf} {mode}: max-rel {err:.2e}")
+    assert err < TOL
+    # the last query of a chunk sees the whole cache: same answer as decode attention for that token
+    dec = cache.attend(torch.as_tensor(q[:, -1]).cuda().float(), bt, torch.tensor(kv_lens)).cpu().numpy()
+    assert max_rel(out[:, -1], dec) < TOL
+    out2 = cache.prefill_attend(torch.as_tensor(q).cuda().float(), bt, torch.tensor(kv_lens)).cpu().numpy()
+    assert np.array_equal(out, out2)

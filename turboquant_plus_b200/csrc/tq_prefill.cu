@@ -1,0 +1,561 @@
+// Chunked-prefill attention over the packed paged cache on the 5th-generation tensor cores (tcgen05).
+//
+// One CTA = 128 threads = 128 rows of (query token, query head) pairs that share a KV head; thread r owns row r,
+// which is also lane r of tensor memory.  Per 128-token page:
+//   1. the packed page record arrives by one bulk async copy (two stages, prefetch one page ahead);
+//   2. all threads dequantize the K indices (2b-bit pairs -> fp16 centroid pairs through a lane-replicated
+//      table) into a K-major, unswizzled tcgen05 operand tile in shared memory;
+//   3. one thread issues S = Q K^T: 16 x tcgen05.mma (M128 N128 K16; fp16 hi and lo halves of Q), A = the rotated queries that live in
+//      tensor memory for the whole kernel, accumulator in tensor memory; while it runs everybody dequantizes V
+//      into an MN-major operand tile;
+//   4. every thread reads its S row back (tcgen05.ld), applies the per-token K scale and the causal mask, keeps
+//      the online softmax state in registers, and stores P * (V scale) as packed fp16 over the first half of
+//      the S columns (tcgen05.st) -- P is the A operand of the second product straight from tensor memory;
+//   5. O_page = P V: 2 x 8 tcgen05.mma (two N=64 halves, one after the other); each half is read back and
+//      added to the fp32 accumulator row held in registers (rescaled when the running max moved).
+// Tensor-memory budget: 256 columns per CTA = Q hi 64 | Q lo 64 | S 128 (P overlays its first 64, one O half at
+// a time its last 64), so two CTAs fit the 512 columns of an SM.  Every wait is bounded in time; a CTA that gives up
+// sets the status word, stops issuing work and still frees its tensor memory.
+#include "tq_internal.cuh"
+
+namespace {
+
+constexpr int PF_THREADS = 128;
+constexpr int PF_ROWS = 128;
+constexpr long long PF_WAIT_CYCLES = 1LL << 30;
+
+__device__ __forceinline__ uint32_t sptr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ bool pf_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(sptr(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool pf_wait(uint64_t* bar, uint32_t parity) {
+  if (pf_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (clock64() - t0 < PF_WAIT_CYCLES)
+    if (pf_try_wait(bar, parity)) return true;
+  return false;
+}
+
+// shared-memory matrix descriptor, no swizzle: start address, leading-dimension and stride byte offsets (16-byte
+// units), descriptor version 1.  K-major operand: LBO = distance between 8-element K chunks, SBO = distance
+// between 8-row groups.  MN-major operand: LBO = distance between 8-row K groups, SBO = between 8-element N chunks.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+  return (uint64_t)((addr >> 4) & 0x3fff) | ((uint64_t)((lbo >> 4) & 0x3fff) << 16) |
+         ((uint64_t)((sbo >> 4) & 0x3fff) << 32) | ((uint64_t)1 << 46);
+}
+// instruction descriptor, kind::f16: fp32 accumulator, fp16 A and B, A K-major, B major as given, N, M
+__device__ __forceinline__ uint32_t umma_idesc(int m, int n, bool b_mn_major) {
+  return (1u << 4) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+               ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(sptr(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(addr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t addr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(addr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
+}
+__device__ __forceinline__ float pf_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pf_pack(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t pf_lds(uint32_t addr) {
+  uint32_t v;
+  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+
+// 128-point sign * Walsh-Hadamard of a row held by one thread: y = post (H/sqrt d) pre x
+__device__ __forceinline__ void row_wht128(float (&x)[TQ_D], const uint32_t (&pre)[4], const uint32_t (&post)[4]) {
+#pragma unroll
+  for (int e = 0; e < TQ_D; ++e) x[e] = ((pre[e >> 5] >> (e & 31)) & 1u) ? -x[e] : x[e];
+#pragma unroll
+  for (int h = 1; h < TQ_D; h <<= 1) {
+#pragma unroll
+    for (int i = 0; i < TQ_D; ++i) {
+      if ((i & h) == 0) {
+        const float a = x[i], b = x[i + h];
+        x[i] = a + b;
+        x[i + h] = a - b;
+      }
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < TQ_D; ++e) x[e] = (((post[e >> 5] >> (e & 31)) & 1u) ? -x[e] : x[e]) * TQ_RSQRT_D;
+}
+
+struct PrefillParams {
+  const uint8_t* pool;
+  const int32_t* block_table;
+  const int32_t* kv_lens;   // cached tokens per sequence, the chunk's own tokens included
+  const void* q;            // [B][Tq][Hq][128]
+  void* out;                // same shape
+  const float* k_rot_t;     // dense K rotation transposed (R x)_j = sum_k rot_t[k][j] x_k, or nullptr
+  const float* v_rot;       // dense V rotation row-major (R^T y)_j = sum_k rot[k][j] y_k, or nullptr
+  int32_t* status;
+  float qscale;             // softmax scale * log2(e)
+  int32_t q_dtype, out_dtype;
+  int32_t max_pages, batch, tq, hq, hkv, group;
+  tq_cache_layout L;
+};
+
+template <int BITS> struct PfLut {
+  static constexpr int ENTRIES = 1 << (2 * BITS);
+  static constexpr bool REPL = ENTRIES <= 64;
+  static constexpr int SHIFT = REPL ? 7 : 2;
+  static constexpr int BYTES = ENTRIES << SHIFT;
+};
+
+template <int BITS>
+__device__ __forceinline__ void pf_lut_fill(uint8_t* lut, const uint16_t* c16, int tid) {
+  using T = PfLut<BITS>;
+  if (T::REPL) {
+    for (int i = tid; i < T::ENTRIES * 8; i += PF_THREADS) {
+      const int e = i >> 3;
+      const uint32_t v = (uint32_t)c16[e >> BITS] | ((uint32_t)c16[e & ((1 << BITS) - 1)] << 16);
+      reinterpret_cast<uint4*>(lut)[i] = make_uint4(v, v, v, v);
+    }
+  } else {
+    uint32_t* w = reinterpret_cast<uint32_t*>(lut);
+    for (int e = tid; e < T::ENTRIES; e += PF_THREADS)
+      w[e] = (uint32_t)c16[e >> BITS] | ((uint32_t)c16[e & ((1 << BITS) - 1)] << 16);
+  }
+}
+
+// One token's packed indices (16*BITS bytes at `src`) -> 128 fp16 values written as sixteen 16-byte rows of the
+// operand tile: chunk c (dims 8c..8c+7) goes to tile + c*128 (+ the token's row offset, already in `dst`).
+template <int BITS>
+__device__ __forceinline__ void pf_dequant_token(const uint8_t* src, uint8_t* dst, uint32_t lut_base) {
+  constexpr int SH = PfLut<BITS>::SHIFT;
+  constexpr uint32_t MASK = ((1u << (2 * BITS)) - 1) << SH;
+  constexpr int NW = 4 * BITS;  // 32-bit words per token
+  const uint4* s4 = reinterpret_cast<const uint4*>(src);
+  uint32_t w[NW];
+#pragma unroll
+  for (int i = 0; i < BITS; ++i) {
+    const uint4 v = s4[i];
+    w[4 * i] = __byte_perm(v.x, 0, 0x0123);
+    w[4 * i + 1] = __byte_perm(v.y, 0, 0x0123);
+    w[4 * i + 2] = __byte_perm(v.z, 0, 0x0123);
+    w[4 * i + 3] = __byte_perm(v.w, 0, 0x0123);
+  }
+#pragma unroll
+  for (int c = 0; c < 16; ++c) {
+    uint32_t o4[4];
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const int start = (4 * c + p) * 2 * BITS, k = start >> 5, o = start & 31;
+      uint32_t f;
+      if (o + 2 * BITS <= 32) {
+        const int sr = 32 - 2 * BITS - o;
+        f = sr > SH ? (w[k] >> (sr - SH)) : (sr < SH ? (w[k] << (SH - sr)) : w[k]);
+      } else {
+        f = __funnelshift_l(w[k + 1 < NW ? k + 1 : k], w[k], o) >> (32 - 2 * BITS - SH);
+      }
+      o4[p] = pf_lds((f & MASK) + lut_base);
+    }
+    *reinterpret_cast<uint4*>(dst + c * 128) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+  }
+}
+
+
+template <int KB, int VB> struct PfSmem {
+  static constexpr int LK = PfLut<KB>::BYTES, LV = PfLut<VB>::BYTES;
+  static constexpr int ALIGN = 128;                     // table addresses are formed by addition here
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = LK;
+  static constexpr int OFF_BAR = LK + LV;               // 4 mbarriers, tensor-memory base, flags
+  static constexpr int OFF_KT = OFF_BAR + 128;          // K operand tile, 128 tokens x 128 dims fp16
+  static constexpr int OFF_VT = OFF_KT + 32768;         // V operand tile
+  static constexpr int OFF_ST = OFF_VT + 32768;         // two page records
+  static size_t bytes(int record_bytes) { return (size_t)ALIGN + OFF_ST + 2 * (size_t)record_bytes; }
+};
+
+template <int KB, int VB>
+__global__ void __launch_bounds__(PF_THREADS, 2) k_prefill_attn(const PrefillParams P, const TqFast fk, const TqFast fv) {
+  using SP = PfSmem<KB, VB>;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  const int rb = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int PT = P.L.page_tokens;  // 128 (checked on the host)
+  const int kv_len = P.kv_lens[b];
+  const int nrows = P.tq * P.group;
+  const int row = rb * PF_ROWS + tid;  // row = query index * group + head within the group
+  const bool row_ok = row < nrows;
+  const int qi = row_ok ? row / P.group : 0, hl = row_ok ? row - qi * P.group : 0;
+  const int pos = row_ok ? kv_len - P.tq + qi : -1;  // last cache position this row attends to
+  const int last_row = min(nrows, (rb + 1) * PF_ROWS) - 1;
+  const int pos_max = kv_len - P.tq + last_row / P.group;
+  const int np = min(P.max_pages, pos_max >= 0 ? pos_max / PT + 1 : 0);  // never walk past the block table
+
+  const uint32_t raw = sptr(smem_raw);
+  uint8_t* sm = smem_raw + (((raw + SP::ALIGN - 1) & ~(uint32_t)(SP::ALIGN - 1)) - raw);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + SP::OFF_BAR);   // [0],[1] page stages, [2] S ready, [3] O ready
+  uint32_t* tbase = reinterpret_cast<uint32_t*>(sm + SP::OFF_BAR + 64);
+  volatile int* fail = reinterpret_cast<volatile int*>(sm + SP::OFF_BAR + 72);
+  uint8_t* ktile = sm + SP::OFF_KT;
+  uint8_t* vtile = sm + SP::OFF_VT;
+  uint8_t* stage0 = sm + SP::OFF_ST;
+  const uint32_t rec = (uint32_t)P.L.record_bytes;
+  const int32_t* bt = P.block_table + (size_t)b * P.max_pages;
+
+  auto issue = [&](int i) {
+    const int64_t page = bt[i];
+    const uint8_t* src = P.pool + page * P.L.page_stride + (int64_t)kvh * P.L.head_stride;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(sptr(&bars[i & 1])), "r"(rec) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     sptr(stage0 + (size_t)(i & 1) * rec)), "l"(src), "r"(rec), "r"(sptr(&bars[i & 1])) : "memory");
+  };
+  if (tid == 0) {
+    for (int i = 0; i < 4; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sptr(&bars[i])) : "memory");
+    *fail = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (np > 0) issue(0);
+  }
+  if (warp == 0) {  // tensor memory: 256 columns
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sptr(tbase)), "r"(256u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  pf_lut_fill<KB>(sm + SP::OFF_K, fk.cent16, tid);
+  pf_lut_fill<VB>(sm + SP::OFF_V, fv.cent16, tid);
+
+  // ---- prologue: this row's query, rotated by the K rotation, scaled, as packed fp16 into tensor memory ----
+  float o[TQ_D];
+  {
+    const size_t qoff = (((size_t)b * P.tq + qi) * P.hq + (size_t)kvh * P.group + hl) * TQ_D;
+#pragma unroll
+    for (int e = 0; e < TQ_D; e += 4) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (row_ok) {
+        if (P.q_dtype == TQ_F32) {
+          v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(P.q) + qoff + e);
+        } else if (P.q_dtype == TQ_F16) {
+          const uint2 w = *reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(P.q) + qoff + e);
+          const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
+          const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
+          v = make_float4(a.x, a.y, c.x, c.y);
+        } else {
+          const uint2 w = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(P.q) + qoff + e);
+          const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w.x));
+          const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w.y));
+          v = make_float4(a.x, a.y, c.x, c.y);
+        }
+      }
+      o[e] = v.x; o[e + 1] = v.y; o[e + 2] = v.z; o[e + 3] = v.w;
+    }
+    if (P.k_rot_t) {
+      // dense rotation: stage the rows transposed in the (still unused) operand tiles, then y = R x per thread
+      float* xs = reinterpret_cast<float*>(ktile);  // [k][row], 64 KB = both tiles
+#pragma unroll
+      for (int k = 0; k < TQ_D; ++k) xs[k * PF_ROWS + tid] = o[k];
+#pragma unroll
+      for (int j = 0; j < TQ_D; ++j) o[j] = 0.f;
+      for (int k = 0; k < TQ_D; ++k) {
+        const float xv = xs[k * PF_ROWS + tid];
+        const float4* rr = reinterpret_cast<const float4*>(P.k_rot_t + (size_t)k * TQ_D);
+#pragma unroll
+        for (int j = 0; j < TQ_D; j += 4) {
+          const float4 r4 = __ldg(rr + (j >> 2));
+          o[j] = fmaf(r4.x, xv, o[j]); o[j + 1] = fmaf(r4.y, xv, o[j + 1]);
+          o[j + 2] = fmaf(r4.z, xv, o[j + 2]); o[j + 3] = fmaf(r4.w, xv, o[j + 3]);
+        }
+      }
+    } else {
+      row_wht128(o, fk.s1, fk.s2);
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();  // tensor-memory base address visible; dense staging buffer free again
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tm = *tbase + ((uint32_t)(warp * 32) << 16);  // this warp's 32 lanes
+  // columns: Q hi 0..63 | Q lo 64..127 | S 128..255; P overlays S 128..191; one O half at a time in 192..255
+  const uint32_t TQc = 0, TQLc = 64, TSc = 128, TPc = 128, TOc = 192;
+  {
+    // fp16 hi + lo halves of the scaled query: two accumulating products keep the query at ~fp32 accuracy
+    const float sk = P.qscale / fk.lut_alpha;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t u[16], ul[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float a = o[32 * c + 2 * j] * sk, bq = o[32 * c + 2 * j + 1] * sk;
+        const __half2 h = __floats2half2_rn(a, bq);
+        const float2 hf = __half22float2(h);
+        u[j] = *reinterpret_cast<const uint32_t*>(&h);
+        ul[j] = pf_pack(a - hf.x, bq - hf.y);
+      }
+      tmem_st16(tm + TQc + 16 * c, u);
+      tmem_st16(tm + TQLc + 16 * c, ul);
+    }
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+  }
+#pragma unroll
+  for (int j = 0; j < TQ_D; ++j) o[j] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;
+  const uint32_t lk_base = sptr(sm + SP::OFF_K) + (PfLut<KB>::REPL ? lane * 4 : 0);
+  const uint32_t lv_base = sptr(sm + SP::OFF_V) + (PfLut<VB>::REPL ? lane * 4 : 0);
+  const uint32_t tile_row = (uint32_t)(tid >> 3) * 2048 + (uint32_t)(tid & 7) * 16;  // token tid inside an operand tile
+  const uint32_t idesc_s = umma_idesc(128, 128, false), idesc_o = umma_idesc(128, 64, true);
+
+  for (int i = 0; i < np; ++i) {
+    if (tid == 0 && i + 1 < np) issue(i + 1);
+    if (!*fail && !pf_wait(&bars[i & 1], (uint32_t)((i >> 1) & 1))) *fail = 1;
+    const uint8_t* st = stage0 + (size_t)(i & 1) * rec;
+    // ---- K indices of token `tid` -> K-major operand tile ----
+    pf_dequant_token<KB>(st + P.L.k_idx_off + tid * (16 * KB), ktile + tile_row, lk_base);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (*fail) break;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (tid == 0) {
+      // S[128 rows x 128 tokens] = Q (tensor memory) . K^T: eight K=16 steps
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint64_t kd = umma_desc(sptr(ktile) + ks * 256, 128, 2048);
+        umma_ts(*tbase + TSc, *tbase + TQc + ks * 8, kd, idesc_s, ks > 0);
+        umma_ts(*tbase + TSc, *tbase + TQLc + ks * 8, kd, idesc_s, 1);
+      }
+      umma_commit(&bars[2]);
+    }
+    // ---- meanwhile: V indices of token `tid` -> MN-major operand tile (same physical layout) ----
+    pf_dequant_token<VB>(st + P.L.v_idx_off + tid * (16 * VB), vtile + tile_row, lv_base);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (!pf_wait(&bars[2], (uint32_t)(i & 1))) *fail = 1;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    // ---- softmax over this page for row `tid` ----
+    const float* ksc = reinterpret_cast<const float*>(st + P.L.k_scale_off);
+    const float* vsc = reinterpret_cast<const float*>(st + P.L.v_scale_off);
+    const int t0 = i * PT;
+    float mx = -INFINITY;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t v[32];
+      tmem_ld32(tm + TSc + 32 * c, v);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int t = 32 * c + j;
+        const float sv = __uint_as_float(v[j]) * ksc[t];
+        mx = fmaxf(mx, (t0 + t <= pos) ? sv : -INFINITY);
+      }
+    }
+    const float m_new = fmaxf(m_run, mx);
+    const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row that has seen nothing yet
+    const float resc = pf_exp2(m_run - m_use);
+    m_run = m_new;
+    l_run *= resc;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t v[32], u[16];
+      tmem_ld32(tm + TSc + 32 * c, v);
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        const int t = 32 * c + j;
+        const bool s0 = t0 + t <= pos, s1 = t0 + t + 1 <= pos;
+        const float p0 = s0 ? pf_exp2(__uint_as_float(v[j]) * ksc[t] - m_use) : 0.f;
+        const float p1 = s1 ? pf_exp2(__uint_as_float(v[j + 1]) * ksc[t + 1] - m_use) : 0.f;
+        l_run += p0 + p1;
+        u[j >> 1] = pf_pack(s0 ? p0 * vsc[t] : 0.f, s1 ? p1 * vsc[t + 1] : 0.f);
+      }
+      tmem_st16(tm + TPc + 16 * c, u);  // P chunk c overlays S columns that have been consumed
+    }
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    if (resc != 1.0f) {
+#pragma unroll
+      for (int j = 0; j < TQ_D; ++j) o[j] *= resc;
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (*fail) break;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    // O_page[128 rows x 128 dims] = P (tensor memory) . V in two N=64 halves through the same 64 columns
+#pragma unroll 1
+    for (int h = 0; h < 2; ++h) {
+      if (tid == 0) {
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ts(*tbase + TOc, *tbase + TPc + ks * 8, umma_desc(sptr(vtile) + h * 1024 + ks * 4096, 2048, 128),
+                  idesc_o, ks > 0);
+        umma_commit(&bars[3]);
+      }
+      if (!pf_wait(&bars[3], (uint32_t)((2 * i + h) & 1))) *fail = 1;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (h == 0) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[32];
+          tmem_ld32(tm + TOc + 32 * c, v);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[32 * c + j] += __uint_as_float(v[j]);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[32];
+          tmem_ld32(tm + TOc + 32 * c, v);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[64 + 32 * c + j] += __uint_as_float(v[j]);
+        }
+      }
+      if (h == 0) {  // everybody has read half 0 before half 1 overwrites the columns
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();  // operand tiles, the page record and the S / O columns are free again
+    if (*fail) break;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  }
+  const bool failed = *fail != 0;
+  if (failed) {  // a prefetched page may still be on its way: give it the same bounded time before leaving
+    for (int st_i = 0; st_i < 2; ++st_i) pf_wait(&bars[st_i], 0), pf_wait(&bars[st_i], 1);
+  }
+  // ---- epilogue: normalise, rotate back, store; then free the tensor memory ----
+  if (!failed) {
+    const float inv = l_run > 0.f ? 1.0f / (l_run * fv.lut_alpha) : 0.f;
+#pragma unroll
+    for (int j = 0; j < TQ_D; ++j) o[j] *= inv;
+    if (P.v_rot) {
+      float* ys = reinterpret_cast<float*>(ktile);  // [k][row]
+#pragma unroll
+      for (int k = 0; k < TQ_D; ++k) ys[k * PF_ROWS + tid] = o[k];
+#pragma unroll
+      for (int j = 0; j < TQ_D; ++j) o[j] = 0.f;
+      for (int k = 0; k < TQ_D; ++k) {
+        const float yv = ys[k * PF_ROWS + tid];
+        const float4* rr = reinterpret_cast<const float4*>(P.v_rot + (size_t)k * TQ_D);
+#pragma unroll
+        for (int j = 0; j < TQ_D; j += 4) {
+          const float4 r4 = __ldg(rr + (j >> 2));
+          o[j] = fmaf(r4.x, yv, o[j]); o[j + 1] = fmaf(r4.y, yv, o[j + 1]);
+          o[j + 2] = fmaf(r4.z, yv, o[j + 2]); o[j + 3] = fmaf(r4.w, yv, o[j + 3]);
+        }
+      }
+    } else {
+      row_wht128(o, fv.s2, fv.s1);  // R^T = D1 (H/sqrt d) D2
+    }
+    if (row_ok) {
+      const size_t ooff = (((size_t)b * P.tq + qi) * P.hq + (size_t)kvh * P.group + hl) * TQ_D;
+      if (P.out_dtype == TQ_F32) {
+        float4* op = reinterpret_cast<float4*>(reinterpret_cast<float*>(P.out) + ooff);
+#pragma unroll
+        for (int j = 0; j < TQ_D; j += 4) op[j >> 2] = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+      } else if (P.out_dtype == TQ_F16) {
+        uint2* op = reinterpret_cast<uint2*>(reinterpret_cast<__half*>(P.out) + ooff);
+#pragma unroll
+        for (int j = 0; j < TQ_D; j += 4) op[j >> 2] = make_uint2(pf_pack(o[j], o[j + 1]), pf_pack(o[j + 2], o[j + 3]));
+      } else {
+        __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(P.out) + ooff;
+#pragma unroll
+        for (int j = 0; j < TQ_D; ++j) op[j] = __float2bfloat16_rn(o[j]);
+      }
+    }
+  } else if (tid == 0) {
+    atomicExch(P.status, 1);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(*tbase), "r"(256u) : "memory");
+}
+
+}  // namespace
+
+template <int KB, int VB>
+static int launch_prefill(const PrefillParams& P, const TqFast& fk, const TqFast& fv, cudaStream_t st) {
+  const size_t need = PfSmem<KB, VB>::bytes(P.L.record_bytes);
+  TQ_REQUIRE(need <= 113 * 1024, TQ_ERR_TOO_LARGE, "page record of %d bytes does not fit the prefill pipeline",
+             P.L.record_bytes);
+  static thread_local int configured_dev = -1;
+  int dev = 0;
+  TQ_CUDA(cudaGetDevice(&dev));
+  if (configured_dev != dev) {
+    TQ_CUDA(cudaFuncSetAttribute(k_prefill_attn<KB, VB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 113 * 1024));
+    configured_dev = dev;
+  }
+  const int nrows = P.tq * P.group;
+  dim3 grid((nrows + PF_ROWS - 1) / PF_ROWS, P.hkv, P.batch);
+  k_prefill_attn<KB, VB><<<grid, PF_THREADS, need, st>>>(P, fk, fv);
+  return tq_launch_check("k_prefill_attn");
+}
+
+extern "C" int tq_prefill_attn(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cache_layout* L,
+                               const uint8_t* pool_dev, const int32_t* block_table_dev, int32_t max_pages_per_seq,
+                               const int32_t* kv_lens_dev, const void* q_dev, int32_t q_dtype, int32_t batch,
+                               int32_t chunk_tokens, int32_t num_q_heads, float scale, void* workspace_dev,
+                               int64_t workspace_bytes, void* out_dev, int32_t out_dtype, void* stream) {
+  TQ_REQUIRE(kq && vq && L, TQ_ERR_INVALID, "tq_prefill_attn: quantizers or layout missing");
+  TQ_REQUIRE(batch >= 0 && chunk_tokens >= 1 && num_q_heads >= 1 && max_pages_per_seq >= 1, TQ_ERR_INVALID, "bad sizes");
+  if (batch == 0) return TQ_OK;
+  TQ_REQUIRE(pool_dev && block_table_dev && kv_lens_dev && q_dev && out_dev && workspace_dev, TQ_ERR_INVALID,
+             "tq_prefill_attn: null buffer");
+  TQ_REQUIRE(workspace_bytes >= 256 && workspace_bytes % 256 == 0 && tq_aligned(workspace_dev, 256), TQ_ERR_ALIGN,
+             "workspace must be 256-byte aligned and at least 256 bytes");
+  TQ_REQUIRE(L->d == TQ_D && L->page_tokens == 128, TQ_ERR_UNSUPPORTED,
+             "prefill attention is built for d == 128 and 128-token pages");
+  TQ_REQUIRE(L->k_format >= TQ_FMT_TURBO2 && L->k_format <= TQ_FMT_TURBO4 && L->v_format >= TQ_FMT_TURBO2 &&
+                 L->v_format <= TQ_FMT_TURBO4,
+             TQ_ERR_UNSUPPORTED, "prefill attention is built for turbo2/3/4 K and V, got %d / %d", L->k_format, L->v_format);
+  TQ_REQUIRE(kq->d == TQ_D && vq->d == TQ_D && kq->bits == L->k_format && vq->bits == L->v_format, TQ_ERR_INVALID,
+             "quantizer bit widths do not match the cache formats");
+  TQ_REQUIRE(num_q_heads % L->num_kv_heads == 0, TQ_ERR_INVALID, "num_q_heads must be a multiple of num_kv_heads");
+  TQ_REQUIRE(q_dtype == TQ_F16 || q_dtype == TQ_BF16 || q_dtype == TQ_F32, TQ_ERR_UNSUPPORTED, "bad query dtype %d", q_dtype);
+  TQ_REQUIRE(out_dtype == TQ_F16 || out_dtype == TQ_BF16 || out_dtype == TQ_F32, TQ_ERR_UNSUPPORTED, "bad output dtype %d", out_dtype);
+  TQ_REQUIRE(tq_aligned(pool_dev, 128) && tq_aligned(q_dev, 16) && tq_aligned(out_dev, 16), TQ_ERR_ALIGN,
+             "pool (128), q and out (16) must be aligned");
+  TQ_REQUIRE(batch <= 65535 && L->num_kv_heads <= 65535, TQ_ERR_TOO_LARGE, "batch and KV heads are grid dimensions");
+  PrefillParams P;
+  memset(&P, 0, sizeof(P));
+  P.pool = pool_dev;
+  P.block_table = block_table_dev;
+  P.kv_lens = kv_lens_dev;
+  P.q = q_dev;
+  P.out = out_dev;
+  P.k_rot_t = kq->rotation == TQ_ROT_DENSE ? kq->rot32_t : nullptr;
+  P.v_rot = vq->rotation == TQ_ROT_DENSE ? vq->rot32 : nullptr;
+  P.status = reinterpret_cast<int32_t*>((uint8_t*)workspace_dev + workspace_bytes - 256);
+  if (scale <= 0.f) scale = TQ_RSQRT_D;
+  P.qscale = scale * 1.4426950408889634f;
+  P.q_dtype = q_dtype;
+  P.out_dtype = out_dtype;
+  P.max_pages = max_pages_per_seq;
+  P.batch = batch;
+  P.tq = chunk_tokens;
+  P.hq = num_q_heads;
+  P.hkv = L->num_kv_heads;
+  P.group = num_q_heads / L->num_kv_heads;
+  P.L = *L;
+  cudaStream_t st = (cudaStream_t)stream;
+  int rc = TQ_ERR_UNSUPPORTED;
+#define TQ_PF(K, V) \
+  if (L->k_format == K && L->v_format == V) rc = launch_prefill<K, V>(P, kq->fast, vq->fast, st);
+  TQ_PF(2, 2) TQ_PF(3, 3) TQ_PF(4, 4) TQ_PF(3, 2) TQ_PF(4, 2) TQ_PF(4, 3)
+#undef TQ_PF
+  if (rc == TQ_ERR_UNSUPPORTED) tq_set_error("prefill attention: K format %d with V format %d is not instantiated", L->k_format, L->v_format);
+  return rc;
+}

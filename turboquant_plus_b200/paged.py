@@ -146,6 +146,27 @@ class PagedKVCache:
                     nv.ptr(out), nv.torch_dtype_code(out.dtype), int(phases), nv.stream_ptr())
         return out
 
+    def prefill_attend(self, q, block_table, kv_lens, scale=None, out=None, workspace=None):
+        """Chunked prefill on the tcgen05 tensor cores.  q: (batch, chunk_tokens, num_q_heads, head_dim) CUDA
+        tensor of a chunk whose K/V rows are already in the cache; kv_lens: (batch,) cached tokens including
+        the chunk.  Query i of a sequence sees cached positions 0 .. kv_len - chunk_tokens + i.  Formats:
+        turbo2/3/4 K and V."""
+        torch = nv.require_cuda()
+        q = q.contiguous()
+        bsz, tq, hq, d = q.shape
+        assert d == self.head_dim
+        bt = block_table.to(device=self.device, dtype=torch.int32).contiguous()
+        kl = kv_lens.to(device=self.device, dtype=torch.int32).contiguous()
+        ws = self.workspace(bsz, hq, bt.shape[1]) if workspace is None else workspace
+        if out is None:
+            out = torch.empty_like(q)
+        with torch.cuda.device(self.device):
+            nv.call("tq_prefill_attn", self._handle(self.k_quantizer), self._handle(self.v_quantizer),
+                    C.byref(self.layout), nv.ptr(self.pool), nv.ptr(bt), bt.shape[1], nv.ptr(kl), nv.ptr(q),
+                    nv.torch_dtype_code(q.dtype), bsz, tq, hq, float(scale) if scale else 0.0, nv.ptr(ws), ws.numel(),
+                    nv.ptr(out), nv.torch_dtype_code(out.dtype), nv.stream_ptr())
+        return out
+
     def kernel_status(self, workspace=None) -> int:
         """0 after a clean decode; 1 if a bounded wait inside the kernel gave up (synchronises)."""
         ws = self._ws if workspace is None else workspace
