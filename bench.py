@@ -50,6 +50,44 @@ def peaks():
     return 6650.0, "fallback"
 
 
+def tensor_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["bf16_tflops"]), "measured cuBLAS bf16 burst"
+    return 1590.0, "fallback"
+
+
+def prefill_probe(torch, tq, dev, gen):
+    """Chunked prefill (tcgen05 kernel), Llama-3-70B head shape: one 128-query chunk x 64 query heads / 8 KV heads
+    over a 16,384-token turbo3 cache of one layer.  FLOPs counted: the two contractions over the visible prefix."""
+    hq, hkv, tq_len, n = 64, 8, 128, 16384
+    cache = tq.PagedKVCache(D, hkv, n // PT, PT, "turbo3", "turbo3", seed=42, device=dev)
+    k, v = synth_layer(torch, gen, dev, n, 0)
+    cache.append(k, v, torch.arange(n, device=dev))
+    bt = torch.arange(n // PT, device=dev, dtype=torch.int32)[None]
+    kv_len = torch.tensor([n], dtype=torch.int32, device=dev)
+    q = torch.randn((1, tq_len, hq, D), generator=gen, device=dev).half()
+    out = torch.empty_like(q)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    times = []
+    for _ in range(6):
+        torch.cuda.synchronize(dev)
+        ev[0].record()
+        cache.prefill_attend(q, bt, kv_len, out=out)
+        ev[1].record()
+        torch.cuda.synchronize(dev)
+        times.append(ev[0].elapsed_time(ev[1]))
+    assert cache.kernel_status() == 0 and torch.isfinite(out.float()).all()
+    ms = statistics.median(times[2:])
+    visible = sum(n - tq_len + i + 1 for i in range(tq_len))       # cached positions seen by the chunk's queries
+    flops = 2 * 2 * hq * D * visible
+    peak, src = tensor_peak()
+    return {"bound": "tensor", "kernel": "k_prefill_attn<3,3> (tcgen05)", "achieved": flops / (ms * 1e-3) / 1e12,
+            "peak": peak, "unit": "TFLOP/s", "frac": flops / (ms * 1e-3) / 1e12 / peak, "peak_source": src,
+            "ms": ms, "ctas": (tq_len * hq // hkv // 128) * hkv,
+            "workload": f"{tq_len}-query chunk, {hq}q/{hkv}kv heads, ctx {n}, turbo3 K+V, one layer"}
+
+
 class ClockSampler:
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -297,6 +335,7 @@ def run_ours(args):
     e2e_ms /= e2e_steps
     assert torch.isfinite(oh.float()).all()
 
+    pre = prefill_probe(torch, tq, dev, gen) if rank == 0 else None
     if rank == 0:
         peak, peak_src = peaks()
         tokens_step = LAYERS * CTX * HKV * world
@@ -332,7 +371,8 @@ def run_ours(args):
                     "ms_per_step": e2e_ms, "steps": e2e_steps,
                     "h2d_bytes_per_step": int(qh.numel() + kh.numel() + vh.numel()) * 2,
                     "d2h_bytes_per_step": int(oh.numel()) * 2},
-            "gpu_launches": LAYERS * 3,
+            "roofline_prefill": pre,
+            "gpu_launches": LAYERS,
             "clocks": clocks,
         }
         if cpu:

@@ -232,8 +232,13 @@ int tq_decode_attn_phases(const tq_quantizer* kq, const tq_quantizer* vq, const 
  * reference tests' dequantize-then-attend (tests/test_kv_cache.py:73-89) restricted to the visible
  * prefix; the reference has no chunked or masked variant of its own.
  *   q_dev, out_dev [batch][chunk_tokens][num_q_heads][d]; K and V formats turbo2/3/4; 128-token pages.
- *   workspace_dev: at least 256 bytes, 256-byte aligned, zero-filled once; its last word is the
- *   status word read by tq_decode_status_sync (1 = a bounded wait inside the kernel gave up). */
+ *   The page range of a row block is split over several CTAs when the grid would otherwise not fill
+ *   the GPU; the last split to finish folds the partials (ticket, as in tq_decode_attn).
+ *   workspace_dev: tq_prefill_workspace_bytes(...) bytes, 256-byte aligned, initialised once with
+ *   tq_decode_workspace_init (or zero-filled); same tail layout as the decode workspace, so one
+ *   buffer of the larger size serves both; tq_decode_status_sync reads its status word. */
+int64_t tq_prefill_workspace_bytes(int32_t batch, int32_t chunk_tokens, int32_t num_q_heads,
+                                   int32_t num_kv_heads, int32_t max_pages_per_seq);
 int tq_prefill_attn(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cache_layout* layout,
                     const uint8_t* pool_dev, const int32_t* block_table_dev, int32_t max_pages_per_seq,
                     const int32_t* kv_lens_dev, const void* q_dev, int32_t q_dtype, int32_t batch,

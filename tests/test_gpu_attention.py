@@ -251,3 +251,33 @@ def test_prefill_chunk_tcgen05(tq, kf, vf, mode):
     assert max_rel(out[:, -1], dec) < TOL
     out2 = cache.prefill_attend(torch.as_tensor(q).cuda().float(), bt, torch.tensor(kv_lens)).cpu().numpy()
     assert np.array_equal(out, out2)
+
+
+def test_prefill_split_pages(tq):
+    """Long contexts: the page range of a row block is split over several CTAs and folded by the last one."""
+    import torch
+    rng = np.random.default_rng(29)
+    hkv, g, tq_len = 2, 8, 40
+    kv_lens = [4096, 3000]
+    cache = tq.PagedKVCache(D, hkv, num_pages=64, seed=42)
+    ks = [np.stack([o.rope_rotate(o.synth_keys(n, seed=11 * b + h), np.arange(n)) for h in range(hkv)], axis=1)
+          for b, n in enumerate(kv_lens)]
+    vs = [rng.standard_normal((n, hkv, D)).astype(np.float32) for n in kv_lens]
+    bt = fill_cache(cache, ks, vs, kv_lens, rng)
+    from turboquant_plus_b200 import _native as nv
+    assert nv.load().tq_prefill_workspace_bytes(2, tq_len, hkv * g, hkv, bt.shape[1]) > 4 * 128 * 130 * 4
+    q = rng.standard_normal((2, tq_len, hkv * g, D)).astype(np.float16)
+    out = cache.prefill_attend(torch.as_tensor(q).cuda(), bt, torch.tensor(kv_lens))
+    assert cache.kernel_status() == 0 and out.dtype == torch.float16
+    kh = np.zeros((2, hkv, 4096, D))
+    vh = np.zeros((2, hkv, 4096, D))
+    for b, n in enumerate(kv_lens):
+        for h in range(hkv):
+            kh[b, h, :n] = oracle_roundtrip(cache, ks[b][:, h], "k")
+            vh[b, h, :n] = oracle_roundtrip(cache, vs[b][:, h], "v")
+    ref = o.attend_chunk_gqa(q.astype(np.float64), kh, vh, kv_lens)
+    err = max_rel(out.float().cpu().numpy().reshape(-1, D), ref.reshape(-1, D))
+    print(f"prefill with split pages: max-rel {err:.2e}")
+    assert err < TOL + 1e-3          # fp16 output rounding included
+    out2 = cache.prefill_attend(torch.as_tensor(q).cuda(), bt, torch.tensor(kv_lens))
+    assert torch.equal(out, out2)

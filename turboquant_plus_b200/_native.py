@@ -72,6 +72,7 @@ SIGNATURES = {
                                  _P, _I64, _P, _I32, _P]),
     "tq_decode_attn_phases": (C.c_int, [_P, _P, C.POINTER(CacheLayout), _P, _P, _I32, _P, _P, _I32, _I32, _I32,
                                         _F, _P, _I64, _P, _I32, _I32, _P]),
+    "tq_prefill_workspace_bytes": (C.c_int64, [_I32, _I32, _I32, _I32, _I32]),
     "tq_prefill_attn": (C.c_int, [_P, _P, C.POINTER(CacheLayout), _P, _P, _I32, _P, _P, _I32, _I32, _I32, _I32,
                                   _F, _P, _I64, _P, _I32, _P]),
     "tq_decode_attn_static": (C.c_int, [_P, _P, C.POINTER(CacheLayout), _P, _P, _I32, _P, _P, _I32, _I32, _I32,

@@ -120,6 +120,11 @@ struct PrefillParams {
   float qscale;             // softmax scale * log2(e)
   int32_t q_dtype, out_dtype;
   int32_t max_pages, batch, tq, hq, hkv, group;
+  // split of the page range over several CTAs (flash-decoding style), merged by the last CTA to finish
+  float* part_o;            // [slot][128 rows][128]
+  float* part_ml;           // [slot][128 rows][2]
+  int32_t* tickets;         // [(b * hkv + kvh) * row_blocks + rb], zero between calls
+  int32_t chunk_pages, num_splits, row_blocks;
   tq_cache_layout L;
 };
 
@@ -199,7 +204,7 @@ template <int KB, int VB>
 __global__ void __launch_bounds__(PF_THREADS, 2) k_prefill_attn(const PrefillParams P, const TqFast fk, const TqFast fv) {
   using SP = PfSmem<KB, VB>;
   extern __shared__ __align__(128) uint8_t smem_raw[];
-  const int rb = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int rb = blockIdx.x / P.num_splits, split = blockIdx.x - rb * P.num_splits, kvh = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int PT = P.L.page_tokens;  // 128 (checked on the host)
   const int kv_len = P.kv_lens[b];
@@ -210,7 +215,11 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_prefill_attn(const PrefillPar
   const int pos = row_ok ? kv_len - P.tq + qi : -1;  // last cache position this row attends to
   const int last_row = min(nrows, (rb + 1) * PF_ROWS) - 1;
   const int pos_max = kv_len - P.tq + last_row / P.group;
-  const int np = min(P.max_pages, pos_max >= 0 ? pos_max / PT + 1 : 0);  // never walk past the block table
+  const int np_all = min(P.max_pages, pos_max >= 0 ? pos_max / PT + 1 : 0);  // never walk past the block table
+  const int ns = np_all > 0 ? (np_all + P.chunk_pages - 1) / P.chunk_pages : 1;  // splits that have pages (>= 1)
+  if (split >= ns) return;                       // nothing to do, and no tensor memory taken yet
+  const int page_lo = split * P.chunk_pages;
+  const int np = max(0, min(np_all, page_lo + P.chunk_pages) - page_lo);
 
   const uint32_t raw = sptr(smem_raw);
   uint8_t* sm = smem_raw + (((raw + SP::ALIGN - 1) & ~(uint32_t)(SP::ALIGN - 1)) - raw);
@@ -224,7 +233,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_prefill_attn(const PrefillPar
   const int32_t* bt = P.block_table + (size_t)b * P.max_pages;
 
   auto issue = [&](int i) {
-    const int64_t page = bt[i];
+    const int64_t page = bt[page_lo + i];
     const uint8_t* src = P.pool + page * P.L.page_stride + (int64_t)kvh * P.L.head_stride;
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(sptr(&bars[i & 1])), "r"(rec) : "memory");
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
@@ -350,7 +359,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_prefill_attn(const PrefillPar
     // ---- softmax over this page for row `tid` ----
     const float* ksc = reinterpret_cast<const float*>(st + P.L.k_scale_off);
     const float* vsc = reinterpret_cast<const float*>(st + P.L.v_scale_off);
-    const int t0 = i * PT;
+    const int t0 = (page_lo + i) * PT;
     float mx = -INFINITY;
 #pragma unroll 1
     for (int c = 0; c < 4; ++c) {
@@ -436,8 +445,59 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_prefill_attn(const PrefillPar
   if (failed) {  // a prefetched page may still be on its way: give it the same bounded time before leaving
     for (int st_i = 0; st_i < 2; ++st_i) pf_wait(&bars[st_i], 0), pf_wait(&bars[st_i], 1);
   }
-  // ---- epilogue: normalise, rotate back, store; then free the tensor memory ----
-  if (!failed) {
+  // every tensor-core operation of this CTA has completed: give the tensor memory back before the epilogue
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(*tbase), "r"(256u) : "memory");
+  if (failed) {
+    if (tid == 0) atomicExch(P.status, 1);
+    return;
+  }
+  if (ns > 1) {
+    // ---- split partial out; the last split of this row block to finish folds them (fixed order) ----
+    const size_t slot0 = (((size_t)b * P.hkv + kvh) * P.row_blocks + rb) * P.num_splits;
+    {
+      float4* po = reinterpret_cast<float4*>(P.part_o + ((slot0 + split) * PF_ROWS + tid) * TQ_D);
+#pragma unroll
+      for (int j = 0; j < TQ_D; j += 4) po[j >> 2] = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+      reinterpret_cast<float2*>(P.part_ml)[(slot0 + split) * PF_ROWS + tid] = make_float2(m_run, l_run);
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      int* tk = P.tickets + ((size_t)b * P.hkv + kvh) * P.row_blocks + rb;
+      const int prev = atomicAdd(tk, 1);
+      int last = 0;
+      if (prev == ns - 1) {
+        *tk = 0;  // zero again for the next call
+        last = 1;
+      }
+      *fail = last;  // reuse the flag word as "this CTA merges"
+    }
+    __syncthreads();
+    if (!*fail) return;
+    __threadfence();
+    float M = -INFINITY;
+    for (int s_i = 0; s_i < ns; ++s_i)
+      M = fmaxf(M, __ldcg(reinterpret_cast<const float2*>(P.part_ml) + (slot0 + s_i) * PF_ROWS + tid).x);
+#pragma unroll
+    for (int j = 0; j < TQ_D; ++j) o[j] = 0.f;
+    l_run = 0.f;
+    for (int s_i = 0; s_i < ns; ++s_i) {
+      const float2 ml = __ldcg(reinterpret_cast<const float2*>(P.part_ml) + (slot0 + s_i) * PF_ROWS + tid);
+      const float f = ml.x == -INFINITY ? 0.f : exp2f(ml.x - M);
+      l_run = fmaf(ml.y, f, l_run);
+      const float4* po = reinterpret_cast<const float4*>(P.part_o + ((slot0 + s_i) * PF_ROWS + tid) * TQ_D);
+#pragma unroll
+      for (int j = 0; j < TQ_D; j += 4) {
+        const float4 v = __ldcg(po + (j >> 2));
+        o[j] = fmaf(v.x, f, o[j]); o[j + 1] = fmaf(v.y, f, o[j + 1]);
+        o[j + 2] = fmaf(v.z, f, o[j + 2]); o[j + 3] = fmaf(v.w, f, o[j + 3]);
+      }
+    }
+  }
+  // ---- epilogue: normalise, rotate back, store ----
+  {
     const float inv = l_run > 0.f ? 1.0f / (l_run * fv.lut_alpha) : 0.f;
 #pragma unroll
     for (int j = 0; j < TQ_D; ++j) o[j] *= inv;
@@ -476,12 +536,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_prefill_attn(const PrefillPar
         for (int j = 0; j < TQ_D; ++j) op[j] = __float2bfloat16_rn(o[j]);
       }
     }
-  } else if (tid == 0) {
-    atomicExch(P.status, 1);
   }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(*tbase), "r"(256u) : "memory");
 }
 
 }  // namespace
@@ -498,10 +553,42 @@ static int launch_prefill(const PrefillParams& P, const TqFast& fk, const TqFast
     TQ_CUDA(cudaFuncSetAttribute(k_prefill_attn<KB, VB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 113 * 1024));
     configured_dev = dev;
   }
-  const int nrows = P.tq * P.group;
-  dim3 grid((nrows + PF_ROWS - 1) / PF_ROWS, P.hkv, P.batch);
+  dim3 grid(P.row_blocks * P.num_splits, P.hkv, P.batch);
   k_prefill_attn<KB, VB><<<grid, PF_THREADS, need, st>>>(P, fk, fv);
   return tq_launch_check("k_prefill_attn");
+}
+
+struct PfPlan {
+  int row_blocks, chunk_pages, num_splits;
+  size_t part_o, part_ml, total;
+};
+static const size_t PF_TAIL = 65536 * 4 + 256;  // tickets + status word, at the end of the workspace
+
+static PfPlan pf_plan(int batch, int chunk_tokens, int hq, int hkv, int max_pages) {
+  PfPlan p;
+  p.row_blocks = (chunk_tokens * (hq / hkv) + PF_ROWS - 1) / PF_ROWS;
+  const long base = (long)p.row_blocks * hkv * batch;
+  const int slots = 2 * tq_num_sms();
+  int s = (int)((slots + base - 1) / base);
+  const int cap = max_pages / 8 > 1 ? max_pages / 8 : 1;  // at least eight pages per split
+  if (s > cap) s = cap;
+  if (s < 1) s = 1;
+  p.chunk_pages = (max_pages + s - 1) / s;
+  p.num_splits = (max_pages + p.chunk_pages - 1) / p.chunk_pages;
+  const size_t slots_total = (size_t)base * p.num_splits;
+  p.part_o = 0;
+  p.part_ml = slots_total * PF_ROWS * TQ_D * 4;
+  p.total = p.part_ml + slots_total * PF_ROWS * 2 * 4 + PF_TAIL;
+  p.total = (p.total + 255) & ~(size_t)255;
+  return p;
+}
+
+extern "C" int64_t tq_prefill_workspace_bytes(int32_t batch, int32_t chunk_tokens, int32_t num_q_heads,
+                                              int32_t num_kv_heads, int32_t max_pages_per_seq) {
+  if (batch < 1 || chunk_tokens < 1 || num_q_heads < 1 || num_kv_heads < 1 || max_pages_per_seq < 1 ||
+      num_q_heads % num_kv_heads)
+    return TQ_ERR_INVALID;
+  return (int64_t)pf_plan(batch, chunk_tokens, num_q_heads, num_kv_heads, max_pages_per_seq).total;
 }
 
 extern "C" int tq_prefill_attn(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cache_layout* L,
@@ -514,8 +601,8 @@ extern "C" int tq_prefill_attn(const tq_quantizer* kq, const tq_quantizer* vq, c
   if (batch == 0) return TQ_OK;
   TQ_REQUIRE(pool_dev && block_table_dev && kv_lens_dev && q_dev && out_dev && workspace_dev, TQ_ERR_INVALID,
              "tq_prefill_attn: null buffer");
-  TQ_REQUIRE(workspace_bytes >= 256 && workspace_bytes % 256 == 0 && tq_aligned(workspace_dev, 256), TQ_ERR_ALIGN,
-             "workspace must be 256-byte aligned and at least 256 bytes");
+  TQ_REQUIRE(workspace_bytes % 256 == 0 && tq_aligned(workspace_dev, 256), TQ_ERR_ALIGN,
+             "workspace must be 256-byte aligned and a multiple of 256 bytes");
   TQ_REQUIRE(L->d == TQ_D && L->page_tokens == 128, TQ_ERR_UNSUPPORTED,
              "prefill attention is built for d == 128 and 128-token pages");
   TQ_REQUIRE(L->k_format >= TQ_FMT_TURBO2 && L->k_format <= TQ_FMT_TURBO4 && L->v_format >= TQ_FMT_TURBO2 &&
@@ -549,6 +636,18 @@ extern "C" int tq_prefill_attn(const tq_quantizer* kq, const tq_quantizer* vq, c
   P.hq = num_q_heads;
   P.hkv = L->num_kv_heads;
   P.group = num_q_heads / L->num_kv_heads;
+  const PfPlan plan = pf_plan(batch, chunk_tokens, num_q_heads, L->num_kv_heads, max_pages_per_seq);
+  TQ_REQUIRE((int64_t)plan.total <= workspace_bytes, TQ_ERR_TOO_LARGE,
+             "prefill workspace of %lld bytes is smaller than the %lld needed (tq_prefill_workspace_bytes)",
+             (long long)workspace_bytes, (long long)plan.total);
+  TQ_REQUIRE((int64_t)batch * L->num_kv_heads * plan.row_blocks <= 65536, TQ_ERR_TOO_LARGE,
+             "batch x KV heads x row blocks beyond 65536");
+  P.part_o = reinterpret_cast<float*>((uint8_t*)workspace_dev + plan.part_o);
+  P.part_ml = reinterpret_cast<float*>((uint8_t*)workspace_dev + plan.part_ml);
+  P.tickets = reinterpret_cast<int32_t*>((uint8_t*)workspace_dev + workspace_bytes - PF_TAIL);
+  P.chunk_pages = plan.chunk_pages;
+  P.num_splits = plan.num_splits;
+  P.row_blocks = plan.row_blocks;
   P.L = *L;
   cudaStream_t st = (cudaStream_t)stream;
   int rc = TQ_ERR_UNSUPPORTED;

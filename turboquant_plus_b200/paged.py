@@ -157,7 +157,14 @@ class PagedKVCache:
         assert d == self.head_dim
         bt = block_table.to(device=self.device, dtype=torch.int32).contiguous()
         kl = kv_lens.to(device=self.device, dtype=torch.int32).contiguous()
-        ws = self.workspace(bsz, hq, bt.shape[1]) if workspace is None else workspace
+        if workspace is None:
+            need = int(nv.load().tq_prefill_workspace_bytes(bsz, tq, hq, self.num_kv_heads, bt.shape[1]))
+            nv.check(need)
+            if self._ws is None or self._ws.numel() < need:
+                self._ws = torch.zeros((need,), dtype=torch.uint8, device=self.device)
+            ws = self._ws
+        else:
+            ws = workspace
         if out is None:
             out = torch.empty_like(q)
         with torch.cuda.device(self.device):
