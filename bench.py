@@ -384,16 +384,126 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+
+# ----------------------------------------------------------------------------------------------
+# Other decode workloads of the benchmark family (not the headline line): --workload config2 | config4
+# ----------------------------------------------------------------------------------------------
+OTHER_WORKLOADS = {
+    "config2": "config2: 32 layers, 32q/8kv heads, d128, batch 16, ctx 8192, K q8_0 + V turbo2, layers 0,1,30,31 q8_0/q8_0",
+    "config4": "config4: 2 layers, 32q/8kv heads, d128, batch 256, ragged ctx uniform in [1024, 32768], K prod3 + V turbo3, "
+               "shuffled block table",
+}
+
+
+def run_other_workload(args):
+    """config2: 32 layers, batch 16, ctx 8,192, K q8_0, V turbo2 (layers 0,1,30,31 q8_0/q8_0), sharded by KV head.
+    config4: batch 256, ragged contexts uniform in [1,024, 32,768], K prod3 (2-bit PolarQuant + QJL), V turbo3,
+    2 layers, sequences sharded over the ranks balanced by cached tokens."""
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    from turboquant_plus_b200.layered import LayeredKVCache, boundary_format_table
+    from turboquant_plus_b200 import sharding
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(99 + rank)
+    if args.workload == "config2":
+        layers, hkv, hq = 32, HKV // world, HQ // world
+        lens = [8192] * 16
+        formats = boundary_format_table(layers, ("q8_0", "turbo2"), ("q8_0", "q8_0"), keep=2)
+        par = f"KV heads sharded x{world}"
+    else:
+        layers, hkv, hq = 2, HKV, HQ
+        all_lens = np.random.default_rng(4).integers(1024, 32769, size=256).tolist()
+        lens = [all_lens[i] for i in sharding.shard_batch_by_tokens(all_lens, world)[rank]]
+        formats = [("prod3", "turbo3")] * layers
+        par = f"sequences sharded x{world}, balanced by tokens"
+    n_pages = [(n + PT - 1) // PT for n in lens]
+    cache = LayeredKVCache(layers, D, hkv, sum(n_pages), PT, formats, seed=42, device=dev)
+    bt = torch.zeros((len(lens), max(n_pages)), dtype=torch.int32, device=dev)
+    perm = torch.randperm(sum(n_pages), generator=gen, device=dev).to(torch.int32)
+    off = 0
+    for b, npg in enumerate(n_pages):
+        bt[b, :npg] = perm[off:off + npg]
+        off += npg
+    for layer in range(layers):
+        for b, n in enumerate(lens):
+            k = torch.randn((n, hkv, D), generator=gen, device=dev)
+            k *= torch.exp(0.5 * torch.randn((n, hkv, 1), generator=gen, device=dev))
+            v = torch.randn((n, hkv, D), generator=gen, device=dev)
+            pos = torch.arange(n, device=dev)
+            cache.append(layer, k.half(), v.half(), bt[b, pos // PT].to(torch.int64) * PT + pos % PT)
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device=dev)
+    q = torch.randn((layers, len(lens), hq, D), generator=gen, device=dev).half()
+    out = torch.empty_like(q)
+    ws = cache.layers[0].workspace(len(lens), hq, bt.shape[1])
+
+    def one_step():
+        for i, layer in enumerate(cache.layers):
+            layer.attend(q[i], bt, seq_lens, out=out[i], workspace=ws)
+
+    one_step()
+    torch.cuda.synchronize(dev)
+    assert cache.layers[0].kernel_status(ws) == 0 and torch.isfinite(out.float()).all()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        one_step()
+    for _ in range(args.warmup):
+        g.replay()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        g.replay()
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1) / args.steps
+    tokens = float(sum(lens)) * hkv * layers
+    nbytes = float(sum(lens)) * hkv * sum(layer.bytes_per_token for layer in cache.layers)
+    if world > 1:
+        t = torch.tensor([ms, tokens, nbytes], device=dev, dtype=torch.float64)
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        ms, tokens, nbytes = float(tmax[0]), float(t[1]), float(t[2])
+    if rank == 0:
+        peak, src = peaks()
+        print(json.dumps({
+            "metric": "decode_attn_kv_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16 tensor-core products, f32 accumulate and softmax",
+            "data": "synthetic",
+            "config": {"workload": OTHER_WORKLOADS[args.workload],
+                       "parallelism": par, "l2": "inputs larger than L2"},
+            "hbm_gbs_algorithmic": nbytes / (ms * 1e-3) / 1e9, "frac_of_measured_hbm": nbytes / (ms * 1e-3) / 1e9 / peak / world,
+            "peak_source": src, "gpu_launches": layers}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="config1", choices=["config1", "config2", "config4"],
+                    help="config1 is the headline workload; the others print a line of the same shape")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload != "config1":
+        run_other_workload(args)
     else:
         run_ours(args)
 
