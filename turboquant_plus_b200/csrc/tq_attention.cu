@@ -105,6 +105,30 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
   return d;
 }
 
+// Optional per-CTA phase stamps (debug builds with -DTQ_PHASE_TIMING): globaltimer at kernel entry, main-loop
+// entry, main-loop exit, partial written, kernel exit.
+#ifdef TQ_PHASE_TIMING
+__device__ unsigned long long g_phase_log[8192 * 16];
+__device__ __forceinline__ void phase_stamp(int slot) {
+  if (threadIdx.x == 0) {
+    unsigned long long tns;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tns));
+    const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    if (cta < 8192) {
+      g_phase_log[cta * 16 + slot] = tns;
+      if (slot == 0) {
+        unsigned smid;
+        asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+        g_phase_log[cta * 16 + 15] = smid;
+      }
+    }
+  }
+}
+#define PHASE_STAMP(s) phase_stamp(s)
+#else
+#define PHASE_STAMP(s)
+#endif
+
 struct AttnParams {
   const uint8_t* pool;
   const int32_t* block_table;
@@ -146,18 +170,18 @@ template <int BITS> struct PairLut {
 };
 
 template <int BITS>
-__device__ __forceinline__ void lut_fill(uint8_t* lut, const uint16_t* c16, int tid) {
+__device__ __forceinline__ void lut_fill(uint8_t* lut, const uint16_t* c16, int tid, int nthreads = ATT_THREADS) {
   using T = PairLut<BITS>;
   if (T::REPL) {
     // entry e occupies 128 bytes (one word per lane): eight 16-byte stores of the same value
-    for (int i = tid; i < T::ENTRIES * 8; i += ATT_THREADS) {
+    for (int i = tid; i < T::ENTRIES * 8; i += nthreads) {
       const int e = i >> 3;
       const uint32_t v = (uint32_t)c16[e >> BITS] | ((uint32_t)c16[e & ((1 << BITS) - 1)] << 16);
       reinterpret_cast<uint4*>(lut)[i] = make_uint4(v, v, v, v);
     }
   } else {
     uint32_t* w = reinterpret_cast<uint32_t*>(lut);
-    for (int e = tid; e < T::ENTRIES; e += ATT_THREADS)
+    for (int e = tid; e < T::ENTRIES; e += nthreads)
       w[e] = (uint32_t)c16[e >> BITS] | ((uint32_t)c16[e & ((1 << BITS) - 1)] << 16);
   }
 }
@@ -205,6 +229,123 @@ __device__ __forceinline__ void warp_wht128(float (&x)[4], const uint32_t (&pre)
   for (int k = 0; k < 4; ++k) x[k] = (((qb >> k) & 1u) ? -x[k] : x[k]) * TQ_RSQRT_D;
 }
 
+// Fold of the split partials of one head by one warp (see finish_splits).  A round covers 64 splits: lane j
+// fetches (max, sum) of splits s0 + j and s0 + 32 + j, twenty 16-byte loads per lane go out before anything
+// waits, the warp agrees on the maximum, then the rows are accumulated in split order.
+template <int HALVES, bool V_Q8>
+__device__ __forceinline__ void fold_splits(const AttnParams& P, float v_alpha, float* qbuf, size_t row0, int ns) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (warp >= HALVES * P.group) return;
+  const int head = warp % P.group, half = warp / P.group;
+  constexpr int ROW_LANES = 32 / HALVES;
+  const int chunk = lane & (ROW_LANES - 1), parity = lane / ROW_LANES;
+  const int col4 = half * 16 + chunk;                      // 16-byte column of the 128-float row
+  const size_t base = (row0 + head) * P.num_splits;
+  const float4* rows = reinterpret_cast<const float4*>(P.part_o + base * TQ_D) + col4;
+  float M = -INFINITY, Lsum = 0.f;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  constexpr int NB = 20, BATCHES = (64 + HALVES * NB - 1) / (HALVES * NB);
+  for (int s0 = 0; s0 < ns; s0 += 64) {
+    float4 ov[NB];
+#pragma unroll
+    for (int u = 0; u < NB; ++u) {
+      const int j = HALVES * u + parity;                   // split s0 + j
+      ov[u] = s0 + j < ns ? __ldcg(rows + (size_t)(s0 + j) * (TQ_D / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    const float2* mlp = reinterpret_cast<const float2*>(P.part_ml) + base + s0 + lane;
+    const float2 ml0 = s0 + lane < ns ? __ldcg(mlp) : make_float2(-INFINITY, 0.f);
+    const float2 ml1 = s0 + 32 + lane < ns ? __ldcg(mlp + 32) : make_float2(-INFINITY, 0.f);
+    float Mn = fmaxf(ml0.x, ml1.x);
+#pragma unroll
+    for (int sh = 1; sh < 32; sh <<= 1) Mn = fmaxf(Mn, __shfl_xor_sync(0xffffffffu, Mn, sh));
+    Mn = fmaxf(Mn, M);                                     // finite: split s0 exists
+    const float r = fast_exp2(M - Mn);
+    const float f0 = fast_exp2(ml0.x - Mn), f1 = fast_exp2(ml1.x - Mn);  // 0 for the lanes without a split
+    float lf = fmaf(ml0.y, f0, ml1.y * f1);
+#pragma unroll
+    for (int sh = 1; sh < 32; sh <<= 1) lf += __shfl_xor_sync(0xffffffffu, lf, sh);
+    Lsum = fmaf(Lsum, r, lf);
+    acc.x *= r; acc.y *= r; acc.z *= r; acc.w *= r;
+    M = Mn;
+#pragma unroll
+    for (int k = 0; k < BATCHES; ++k) {
+      if (k > 0) {
+        if (s0 + HALVES * NB * k >= ns) break;
+#pragma unroll
+        for (int u = 0; u < NB; ++u) {
+          const int j = HALVES * (NB * k + u) + parity;
+          ov[u] = (j < 64 && s0 + j < ns) ? __ldcg(rows + (size_t)(s0 + j) * (TQ_D / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < NB; ++u) {
+        const int jb = HALVES * (NB * k + u);              // lane-independent part of the split number
+        if (jb >= 64) break;
+        const float fu = __shfl_sync(0xffffffffu, jb < 32 ? f0 : f1, (jb + parity) & 31);
+        acc.x = fmaf(ov[u].x, fu, acc.x); acc.y = fmaf(ov[u].y, fu, acc.y);
+        acc.z = fmaf(ov[u].z, fu, acc.z); acc.w = fmaf(ov[u].w, fu, acc.w);
+      }
+    }
+  }
+  if (HALVES == 2) {
+    acc.x += __shfl_xor_sync(0xffffffffu, acc.x, 16); acc.y += __shfl_xor_sync(0xffffffffu, acc.y, 16);
+    acc.z += __shfl_xor_sync(0xffffffffu, acc.z, 16); acc.w += __shfl_xor_sync(0xffffffffu, acc.w, 16);
+  }
+  PHASE_STAMP(12);
+  // attention output in V's rotated space
+  const float inv = 1.0f / (Lsum * (V_Q8 ? 1.0f : v_alpha));
+  if (parity == 0)
+    reinterpret_cast<float4*>(qbuf + head * TQ_D)[col4] = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+}
+
+// Tail shared by the decode kernels, entered by the whole CTA after its split partial has been written:
+// take a ticket; the last CTA of a (sequence, kv head) folds all splits in a fixed order, un-rotates and stores.
+// One thread publishes the CTA's writes (the block barrier orders the other threads' stores before its
+// release), so the rest of the CTA does not execute a device-wide fence.
+template <bool V_Q8>
+__device__ __forceinline__ void finish_splits(const AttnParams& P, const uint32_t (&vs1)[4], const uint32_t (&vs2)[4],
+                                              float v_alpha, float* qbuf, uint8_t* stage0, volatile int* s_flags,
+                                              size_t row0, int ns, int b, int kvh) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  __syncthreads();
+  if (tid == 0) {
+    if (s_flags[0]) atomicExch(P.status, 1);
+    __threadfence();
+    const int prev = atomicAdd(&P.tickets[b * P.hkv + kvh], 1);
+    if (prev == ns - 1) {
+      P.tickets[b * P.hkv + kvh] = 0;  // leave the counter at zero for the next call
+      s_flags[1] = 1;
+      __threadfence();
+    }
+  }
+  __syncthreads();
+  PHASE_STAMP(3);
+  if (!s_flags[1]) return;
+  // Warp (half, head) folds the splits of one head.  With at most four heads there are two warps per head and each
+  // takes 64 of the 128 dims: lanes 0..15 then read even splits, lanes 16..31 odd ones (16 bytes each), and one
+  // lane exchange joins the two at the end; with more heads a warp takes the whole row and every split.
+  if (2 * P.group <= ATT_WARPS) fold_splits<2, V_Q8>(P, v_alpha, qbuf, row0, ns);
+  else fold_splits<1, V_Q8>(P, v_alpha, qbuf, row0, ns);
+  __syncthreads();
+  PHASE_STAMP(13);
+  if (P.v_rot) {  // dense rotation: x = R^T y
+    for (int e = tid; e < P.group * TQ_D; e += ATT_THREADS) {
+      const int head = e >> 7, j = e & 127;
+      float x = 0.f;
+#pragma unroll 8
+      for (int k = 0; k < TQ_D; ++k) x = fmaf(__ldg(P.v_rot + k * TQ_D + j), qbuf[head * TQ_D + k], x);
+      store_out(P.out, P.out_dtype, (row0 + head) * TQ_D + j, x);
+    }
+  } else if (warp < P.group) {
+    float x[4];
+    const float4 v = *reinterpret_cast<const float4*>(qbuf + warp * TQ_D + 4 * lane);
+    x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+    if (!P.v_ident) warp_wht128(x, vs2, vs1, lane);  // R^T = D1 (H/sqrt d) D2
+#pragma unroll
+    for (int k = 0; k < 4; ++k) store_out(P.out, P.out_dtype, (row0 + warp) * TQ_D + 4 * lane + k, x[k]);
+  }
+}
+
 // shared-memory carve-up, identical on host and device
 template <int KK, int VK> struct SmemPlan {
   static constexpr int LK = PairLut<Kind<KK>::BITS>::BYTES;
@@ -237,6 +378,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn(const AttnParams
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  PHASE_STAMP(0);
   const int seq_len = P.seq_lens[b];
   const int PT = P.L.page_tokens;
   const int n_pages = (seq_len + PT - 1) / PT;
@@ -286,6 +428,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn(const AttnParams
       w[i] = ((e & 2) ? 0x3C00u : 0xBC00u) | (((e & 1) ? 0x3C00u : 0xBC00u) << 16);
     }
   }
+  PHASE_STAMP(5);
   // ---- prologue: rotated / projected queries into qbuf[0] (K rotation) and qbuf[1] (QJL projection) ----
   if (warp < P.group) {
     float x[4], y[4];
@@ -314,7 +457,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn(const AttnParams
     *reinterpret_cast<float4*>(qbuf + warp * TQ_D + 4 * lane) = make_float4(x[0], x[1], x[2], x[3]);
     if (KT::PROD) *reinterpret_cast<float4*>(qbuf + (MAX_G + warp) * TQ_D + 4 * lane) = make_float4(y[0], y[1], y[2], y[3]);
   }
+  PHASE_STAMP(6);
   __syncthreads();
+  PHASE_STAMP(7);
 
   // query fragments (B operand) of head g, hi/lo fp16 split
   uint32_t qh[8][2], ql[8][2], ph[KT::PROD ? 8 : 1][2];
@@ -352,6 +497,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn(const AttnParams
   const uint32_t lv_base = smem_u32(sm + SP::OFF_V) + (PairLut<VB>::REPL ? lane * 4 : 0);
   const uint32_t ls_base = smem_u32(sm + SP::OFF_S) + lane * 4;
 
+  PHASE_STAMP(1);
   float o[8][4];
 #pragma unroll
   for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
@@ -557,6 +703,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn(const AttnParams
     __syncthreads();  // every warp is done with this stage before it is refilled
   }
 
+  PHASE_STAMP(2);
   // ---------------- merge the eight warps, write the split partial ----------------
   // l is still per thread (tokens g and g+8 only): sum over the 8 lanes that share t
 #pragma unroll
@@ -602,97 +749,329 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn(const AttnParams
       P.part_ml[slot * 2 + 1] = Lsum;
     }
   }
-  // ---------------- ticket: the last CTA of this (sequence, kv head) merges the splits ----------------
-  __threadfence();
+  finish_splits<VT::Q8>(P, fv.s1, fv.s2, fv.lut_alpha, qbuf, stage0, s_flags, row0, ns, b, kvh);
+  PHASE_STAMP(4);
+}
+
+// ------------------------------------------------------------------------------------------
+// Decode attention, PolarQuant K and V, at most four query heads per KV head (the GQA shape of every decode
+// workload this library is measured on).  Same pipeline and the same split / ticket protocol as k_decode_attn;
+// what changes is how the 8 columns of the MMA tiles are spent:
+//   * S = K q^T: columns 0..3 carry the fp16 "hi" halves of the four query heads, columns 4..7 the "lo" halves,
+//     so one m16n8k16 per 16 dims instead of two; the halves meet through one lane exchange (lane ^ 2), after
+//     which thread (g, t) owns one token (g + 8 (t >> 1)) and two heads (2 (t & 1), + 1).
+//   * O^T += V^T P^T: a k-slot pair is (token, dim parity) instead of (token, token'), column n is
+//     (head n >> 1, parity n & 1), and the P operand is p on the matching parity, 0 on the other.  A pair-table
+//     word (two dims of one token) is then an A-operand register as it comes: no re-pairing permutes, 32 dims per
+//     MMA, and O takes 16 accumulator registers per thread: o[blk] = head t, dims 16 g + 4 blk .. + 3.
+//   * the running maxima are only reduced across the warp when some score exceeds them.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void load_q4(const void* q, int dtype, size_t i, float (&x)[4]) {
+  if (dtype == TQ_F16) {
+    const uint2 u = *reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(q) + i);
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+    x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+  } else if (dtype == TQ_BF16) {
+    const uint2 u = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(q) + i);
+    x[0] = __uint_as_float(u.x << 16); x[1] = __uint_as_float(u.x & 0xffff0000u);
+    x[2] = __uint_as_float(u.y << 16); x[3] = __uint_as_float(u.y & 0xffff0000u);
+  } else {
+    const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(q) + i);
+    x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+  }
+}
+
+// What the kernel needs of a quantizer, packed into 80 bytes so that the whole parameter block is six 64-byte
+// lines: parameters live in the constant bank, every line misses once per launch, and the misses of one warp
+// are serial.  The warps therefore touch one line each before anything else happens.
+struct AttnQuant {
+  uint32_t s1[4], s2[4];
+  uint16_t cent16[16];
+  float alpha;
+  uint32_t pad[3];
+};
+static_assert(sizeof(AttnQuant) == 80, "AttnQuant layout");
+
+constexpr int G4_HEADS = 4;
+constexpr int G4_HSTRIDE = TQ_D + 4;  // floats between heads in the warp-merge buffer: 16-byte stores stay conflict-free
+
+template <int KB, int VB>
+__global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_constant__ AttnParams P, const __grid_constant__ AttnQuant fk,
+                                                                    const __grid_constant__ AttnQuant fv) {
+  using SP = SmemPlan<KB, VB>;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  PHASE_STAMP(0);
+  {  // one parameter line per warp, all misses in flight together
+    const uint32_t* pp = reinterpret_cast<const uint32_t*>(&P);
+    uint32_t touch;
+    if (warp < 4) touch = pp[min(16 * warp, (int)(sizeof(AttnParams) / 4) - 1)];
+    else if (warp < 6) touch = warp == 4 ? fk.s1[0] : fk.pad[2];
+    else touch = warp == 6 ? fv.s1[0] : fv.pad[2];
+    asm volatile("" ::"r"(touch));
+  }
+  PHASE_STAMP(14);
+  const int PT = P.L.page_tokens;
+  const int page_lo = split * P.chunk_pages;
+  const size_t row0 = (size_t)b * P.hq + (size_t)kvh * P.group;
+  const int32_t* bt = P.block_table + (size_t)b * P.max_pages;
+  const uint32_t raw = smem_u32(smem_raw);
+  uint8_t* sm = smem_raw + (((raw + SP::ALIGN - 1) & ~(uint32_t)(SP::ALIGN - 1)) - raw);
+  float* qbuf = reinterpret_cast<float*>(sm + SP::OFF_Q);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + SP::OFF_BAR);
+  volatile int* s_flags = reinterpret_cast<volatile int*>(sm + SP::OFF_BAR + 64);
+  uint8_t* stage0 = sm + SP::OFF_STAGE;
+  const uint32_t rec = (uint32_t)P.L.record_bytes;
+  const int NS = P.stages;
+  constexpr int PRODUCER = ATT_THREADS - 32;  // lane 0 of the last warp issues every bulk copy
+
+  auto issue = [&](int i, int64_t page) {
+    const uint8_t* src = P.pool + page * P.L.page_stride + (int64_t)kvh * P.L.head_stride;
+    uint64_t* bar = &bars[i % NS];
+    mbar_expect_tx(bar, rec);
+    bulk_g2s(stage0 + (size_t)(i % NS) * rec, src, rec, bar);
+  };
+
+  // The warps take different roles so that their global-load latencies (and their instruction fetches, which are
+  // cold in every launch) overlap: the producer sends the first pages on their way as early as it can, the first
+  // `group` warps rotate one query head each, the others fill the pair tables.
+  const int seq_len = P.seq_lens[b];
+  int pg_ahead = 0;  // producer: block-table entry of the page issued in the next iteration
+  float x[4] = {0.f, 0.f, 0.f, 0.f};
+  if (tid == PRODUCER) {
+    int pg_next[ATT_STAGES];
+#pragma unroll
+    for (int i = 0; i < ATT_STAGES; ++i) pg_next[i] = bt[min(page_lo + i, P.max_pages - 1)];
+    for (int s = 0; s < ATT_STAGES; ++s) mbar_init(&bars[s], 1);
+    s_flags[0] = 0;
+    s_flags[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const int my_pages = min((seq_len + PT - 1) / PT, page_lo + P.chunk_pages) - page_lo;
+    if (my_pages > 0) {
+      issue(0, pg_next[0]);
+      if (NS > 2) {
+        if (my_pages > 1) issue(1, pg_next[1]);
+        pg_ahead = pg_next[2];
+      } else {
+        pg_ahead = pg_next[1];
+      }
+    }
+  } else if (warp < P.group) {
+    if (P.k_pre) load_q4(P.qrot, TQ_F32, (row0 + warp) * TQ_D + 4 * lane, x);
+    else load_q4(P.q, P.q_dtype, (row0 + warp) * TQ_D + 4 * lane, x);
+    if (!P.k_pre) {
+      warp_wht128(x, fk.s1, fk.s2, lane);
+      const float sk = P.qscale / fk.alpha;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) x[k] *= sk;
+    }
+    // 16-byte chunk c = 8 t + j of head h sits at 8 t + (j ^ (t + 4 (h & 1))): the fragment reads below (fixed j,
+    // all t and h) then touch every bank group instead of one
+    const int tq = lane >> 3, jq = lane & 7;
+    *reinterpret_cast<float4*>(qbuf + warp * TQ_D + 4 * (8 * tq + (jq ^ (tq + 4 * (warp & 1))))) =
+        make_float4(x[0], x[1], x[2], x[3]);
+  }
+  __syncwarp();
+  if (warp >= P.group) {
+    const int ft = tid - 32 * P.group, fn = ATT_THREADS - 32 * P.group;
+    lut_fill<KB>(sm + SP::OFF_K, fk.cent16, ft, fn);
+    lut_fill<VB>(sm + SP::OFF_V, fv.cent16, ft, fn);
+  }
+  PHASE_STAMP(5);
+  const int n_pages = (seq_len + PT - 1) / PT;
+  if (n_pages == 0 && split == 0) {
+    for (int e = tid; e < P.group * TQ_D; e += ATT_THREADS) store_out(P.out, P.out_dtype, row0 * TQ_D + e, 0.f);
+    return;
+  }
+  if (page_lo >= n_pages) return;
+  const int np = min(n_pages, page_lo + P.chunk_pages) - page_lo;
+  const int ns = (n_pages + P.chunk_pages - 1) / P.chunk_pages;
+  PHASE_STAMP(6);
   __syncthreads();
-  if (tid == 0) {
-    if (s_flags[0]) atomicExch(P.status, 1);
-    const int prev = atomicAdd(&P.tickets[b * P.hkv + kvh], 1);
-    if (prev == ns - 1) {
-      P.tickets[b * P.hkv + kvh] = 0;  // leave the counter at zero for the next call
-      s_flags[1] = 1;
+  PHASE_STAMP(7);
+
+  // B operand of S = K q^T: column g is head g & 3, hi half for g < 4, lo half otherwise
+  uint32_t qf[8][2];
+  {
+    const int head = g & 3;
+    const bool hv = head < P.group, lo = g >= 4;
+    const float* qp = qbuf + (hv ? head : 0) * TQ_D + 32 * t;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float4 v = hv ? *reinterpret_cast<const float4*>(qp + 4 * (j ^ (t + 4 * (head & 1)))) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const __half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
+      const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+      qf[j][0] = lo ? pack_h2(v.x - f0.x, v.y - f0.y) : *reinterpret_cast<const uint32_t*>(&h0);
+      qf[j][1] = lo ? pack_h2(v.z - f1.x, v.w - f1.y) : *reinterpret_cast<const uint32_t*>(&h1);
     }
   }
-  __syncthreads();
-  if (!s_flags[1]) return;
-  __threadfence();
-  // The eight warps share the heads: with `group` heads, wph = 8 / group warps work on each head and warp
-  // (part, head) folds splits part, part + wph, ... (ten independent 16-byte loads per lane in flight, online
-  // rescaling inside the warp); then the wph results per head are folded in fixed order.
-  float* red = reinterpret_cast<float*>(stage0);          // [warp][128]
-  float* redm = red + ATT_WARPS * TQ_D;                   // [warp][2] = (max, sum)
-  const int wph = ATT_WARPS / P.group;                    // >= 1 because group <= 8
-  if (warp < wph * P.group) {
-    const int head = warp % P.group, part = warp / P.group;
-    const size_t base = (row0 + head) * P.num_splits;
-    float M = -INFINITY, Lsum = 0.f;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    constexpr int NB = 10;
-    for (int s0 = part; s0 < ns; s0 += NB * wph) {
-      float2 ml[NB];
-      float4 ov[NB];
+  const uint32_t lk_base = smem_u32(sm + SP::OFF_K) + (PairLut<KB>::REPL ? lane * 4 : 0);
+  const uint32_t lv_base = smem_u32(sm + SP::OFF_V) + (PairLut<VB>::REPL ? lane * 4 : 0);
+  // P operand: this thread's column is (head g >> 1, parity g & 1); the owner of p[token][head] is lane
+  // 4 (token & 7) + 2 (token >> 3) + (head >> 1), half (head & 1) of its packed pair
+  const int src0 = 16 * (t & 1) + 2 * (t >> 1) + (g >> 2);            // token 4t; token 4t + i is 4 i lanes further
+  const uint32_t psel = ((g >> 1) & 1) ? ((g & 1) ? 0x3244u : 0x4432u) : ((g & 1) ? 0x1044u : 0x4410u);
+  const int rsrc = (lane & ~3) | (t >> 1);                             // a lane that tracks head t's running maximum
+  const bool upper = t >= 2;                                           // keeps token g + 8 after the exchange
+
+  PHASE_STAMP(1);
+  float o[4][4];
 #pragma unroll
-      for (int u = 0; u < NB; ++u) {
-        const int s_i = s0 + wph * u;
-        const bool have = s_i < ns;
-        ml[u] = have ? __ldcg(reinterpret_cast<const float2*>(P.part_ml) + base + s_i) : make_float2(-INFINITY, 0.f);
-        ov[u] = have ? __ldcg(reinterpret_cast<const float4*>(P.part_o + (base + s_i) * TQ_D) + lane)
-                     : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-      float Mn = M;
-#pragma unroll
-      for (int u = 0; u < NB; ++u) Mn = fmaxf(Mn, ml[u].x);   // finite: split s0 exists
-      const float r = exp2f(M - Mn);
-      acc.x *= r; acc.y *= r; acc.z *= r; acc.w *= r;
-      Lsum *= r;
-#pragma unroll
-      for (int u = 0; u < NB; ++u) {
-        const float f = exp2f(ml[u].x - Mn);
-        acc.x = fmaf(ov[u].x, f, acc.x); acc.y = fmaf(ov[u].y, f, acc.y);
-        acc.z = fmaf(ov[u].z, f, acc.z); acc.w = fmaf(ov[u].w, f, acc.w);
-        Lsum = fmaf(ml[u].y, f, Lsum);
-      }
-      M = Mn;
+  for (int j = 0; j < 4; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+  constexpr int KIDXB = 16 * KB, VIDXB = 16 * VB, KW = KB;
+  const int tiles_per_page = PT / 16;
+
+  for (int i = 0; i < np; ++i) {
+    if (tid == PRODUCER && i + NS - 1 < np) {
+      issue(i + NS - 1, pg_ahead);
+      pg_ahead = bt[min(page_lo + i + NS, P.max_pages - 1)];
     }
-    reinterpret_cast<float4*>(red + (size_t)warp * TQ_D)[lane] = acc;
-    if (lane == 0) {
-      redm[warp * 2] = M;
-      redm[warp * 2 + 1] = Lsum;
+    if (!s_flags[0] && !mbar_wait_bounded(&bars[i % NS], (uint32_t)((i / NS) & 1))) s_flags[0] = 1;
+    const uint8_t* st = stage0 + (size_t)(i % NS) * rec;
+    const int valid = min(PT, seq_len - (page_lo + i) * PT);
+
+    for (int tile = warp; tile < tiles_per_page; tile += ATT_WARPS) {
+      const int tb = tile * 16;
+      if (tb >= valid) break;
+      // ---------------- S = K_tile (16 tokens x 128) . [q_hi | q_lo] ----------------
+      float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+      {
+        uint32_t w0[KW], w1[KW];
+        const uint32_t* p0 = reinterpret_cast<const uint32_t*>(st + P.L.k_idx_off + (tb + g) * KIDXB + t * (KIDXB / 4));
+        const uint32_t* p1 = p0 + 8 * (KIDXB / 4);
+#pragma unroll
+        for (int k = 0; k < KW; ++k) {
+          w0[k] = __byte_perm(p0[k], 0, 0x0123);
+          w1[k] = __byte_perm(p1[k], 0, 0x0123);
+        }
+        constexpr int SH = PairLut<KB>::SHIFT;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t a0 = lds32(field_off<2 * KB, SH, KW>(w0, 2 * j) | lk_base);
+          const uint32_t a1 = lds32(field_off<2 * KB, SH, KW>(w1, 2 * j) | lk_base);
+          const uint32_t a2 = lds32(field_off<2 * KB, SH, KW>(w0, 2 * j + 1) | lk_base);
+          const uint32_t a3 = lds32(field_off<2 * KB, SH, KW>(w1, 2 * j + 1) | lk_base);
+          if (j & 1) mma16816(sb, a0, a1, a2, a3, qf[j][0], qf[j][1]);
+          else mma16816(sa, a0, a1, a2, a3, qf[j][0], qf[j][1]);
+        }
+      }
+      // hi + lo: the partner lane (t ^ 2) holds the other half of the same heads
+      const float give0 = upper ? sa[0] + sb[0] : sa[2] + sb[2], give1 = upper ? sa[1] + sb[1] : sa[3] + sb[3];
+      const float keep0 = upper ? sa[2] + sb[2] : sa[0] + sb[0], keep1 = upper ? sa[3] + sb[3] : sa[1] + sb[1];
+      const int tok = tb + g + (upper ? 8 : 0);
+      const bool ok = tok < valid;
+      const float ks = reinterpret_cast<const float*>(st + P.L.k_scale_off)[tok];
+      float sc0 = (keep0 + __shfl_xor_sync(0xffffffffu, give0, 2)) * ks;
+      float sc1 = (keep1 + __shfl_xor_sync(0xffffffffu, give1, 2)) * ks;
+      sc0 = ok ? sc0 : -INFINITY;
+      sc1 = ok ? sc1 : -INFINITY;
+      // ---------------- online softmax (log2 domain), heads 2(t&1) and 2(t&1)+1 ----------------
+      if (__any_sync(0xffffffffu, (sc0 > m0) || (sc1 > m1))) {
+        float mx0 = sc0, mx1 = sc1;
+#pragma unroll
+        for (int sh = 2; sh < 32; sh <<= 1) {
+          mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
+          mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, sh));
+        }
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);  // finite: token tb is valid
+        const float r0 = fast_exp2(m0 - mn0), r1 = fast_exp2(m1 - mn1);
+        m0 = mn0;
+        m1 = mn1;
+        l0 *= r0;
+        l1 *= r1;
+        const float ra = __shfl_sync(0xffffffffu, r0, rsrc), rb = __shfl_sync(0xffffffffu, r1, rsrc);
+        const float r = (t & 1) ? rb : ra;                        // O of this thread belongs to head t
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          o[j][0] *= r; o[j][1] *= r; o[j][2] *= r; o[j][3] *= r;
+        }
+      }
+      const float p0 = fast_exp2(sc0 - m0), p1 = fast_exp2(sc1 - m1);
+      l0 += p0;
+      l1 += p1;
+      const float vs = ok ? reinterpret_cast<const float*>(st + P.L.v_scale_off)[tok] : 0.f;
+      const uint32_t hp = pack_h2(p0 * vs, p1 * vs);
+      uint32_t pb[4];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) pb[q4] = __byte_perm(__shfl_sync(0xffffffffu, hp, src0 + 4 * q4), 0, psel);
+      // ---------------- O^T += V_tile^T . P^T : tokens tb + 4t .. 4t+3, dims 16g .. 16g+15 ----------------
+      uint32_t h[4][8];
+      constexpr int SHV = PairLut<VB>::SHIFT;
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const uint8_t* pv = st + P.L.v_idx_off + (tb + 4 * t + q4) * VIDXB + g * (2 * VB);
+        uint32_t w[2];
+        if constexpr (VB == 3) {
+          const uint16_t* phw = reinterpret_cast<const uint16_t*>(pv);
+          const uint32_t a = phw[0], bb = phw[1], c = phw[2];
+          w[0] = __byte_perm(a, bb, 0x0145);
+          w[1] = __byte_perm(c, 0, 0x0144);
+        } else if constexpr (VB == 2) {
+          w[0] = __byte_perm(*reinterpret_cast<const uint32_t*>(pv), 0, 0x0123);
+          w[1] = 0;
+        } else {
+          const uint2 v2 = *reinterpret_cast<const uint2*>(pv);
+          w[0] = __byte_perm(v2.x, 0, 0x0123);
+          w[1] = __byte_perm(v2.y, 0, 0x0123);
+        }
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) h[q4][jj] = lds32(field_off<2 * VB, SHV, 2>(w, jj) | lv_base);
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+#pragma unroll
+        for (int blk = 0; blk < 4; ++blk)
+          mma16816(o[blk], h[2 * u][2 * blk], h[2 * u][2 * blk + 1], h[2 * u + 1][2 * blk], h[2 * u + 1][2 * blk + 1],
+                   pb[2 * u], pb[2 * u + 1]);
+      }
     }
+    __syncthreads();  // every warp is done with this stage before it is refilled
+  }
+
+  PHASE_STAMP(2);
+  // ---------------- merge the eight warps, write the split partial ----------------
+#pragma unroll
+  for (int sh = 2; sh < 32; sh <<= 1) {
+    l0 += __shfl_xor_sync(0xffffffffu, l0, sh);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, sh);
+  }
+  float* so = reinterpret_cast<float*>(stage0);                    // [warp][head 4][G4_HSTRIDE]
+  float* sml = so + ATT_WARPS * G4_HEADS * G4_HSTRIDE;             // [warp][head 4][2]
+#pragma unroll
+  for (int blk = 0; blk < 4; ++blk)
+    *reinterpret_cast<float4*>(so + (size_t)(warp * G4_HEADS + t) * G4_HSTRIDE + 16 * g + 4 * blk) =
+        make_float4(o[blk][0], o[blk][1], o[blk][2], o[blk][3]);
+  if (g == 0 && t < 2) {
+    *reinterpret_cast<float4*>(sml + (warp * G4_HEADS + 2 * t) * 2) = make_float4(m0, l0, m1, l1);
   }
   __syncthreads();
   for (int e = tid; e < P.group * TQ_D; e += ATT_THREADS) {
     const int head = e >> 7, dim = e & 127;
     float M = -INFINITY;
-    for (int pt = 0; pt < wph; ++pt) M = fmaxf(M, redm[(pt * P.group + head) * 2]);
-    float acc = 0.f, Lsum = 0.f;
-    for (int pt = 0; pt < wph; ++pt) {
-      const int w = pt * P.group + head;
-      const float mw = redm[w * 2];
-      const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
-      acc = fmaf(red[(size_t)w * TQ_D + dim], f, acc);
-      Lsum = fmaf(redm[w * 2 + 1], f, Lsum);
-    }
-    // attention output in V's rotated space
-    qbuf[head * TQ_D + dim] = acc / (Lsum * (VT::Q8 ? 1.0f : fv.lut_alpha));
-  }
-  __syncthreads();
-  if (P.v_rot) {  // dense rotation: x = R^T y
-    for (int e = tid; e < P.group * TQ_D; e += ATT_THREADS) {
-      const int head = e >> 7, j = e & 127;
-      float x = 0.f;
-#pragma unroll 8
-      for (int k = 0; k < TQ_D; ++k) x = fmaf(__ldg(P.v_rot + k * TQ_D + j), qbuf[head * TQ_D + k], x);
-      store_out(P.out, P.out_dtype, (row0 + head) * TQ_D + j, x);
-    }
-  } else if (warp < P.group) {
-    float x[4];
-    const float4 v = *reinterpret_cast<const float4*>(qbuf + warp * TQ_D + 4 * lane);
-    x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
-    if (!P.v_ident) warp_wht128(x, fv.s2, fv.s1, lane);  // R^T = D1 (H/sqrt d) D2
 #pragma unroll
-    for (int k = 0; k < 4; ++k) store_out(P.out, P.out_dtype, (row0 + warp) * TQ_D + 4 * lane + k, x[k]);
+    for (int w = 0; w < ATT_WARPS; ++w) M = fmaxf(M, sml[(w * G4_HEADS + head) * 2]);
+    float acc = 0.f, Lsum = 0.f;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; ++w) {
+      const float mw = sml[(w * G4_HEADS + head) * 2];
+      const float f = mw == -INFINITY ? 0.f : fast_exp2(mw - M);
+      acc = fmaf(so[(size_t)(w * G4_HEADS + head) * G4_HSTRIDE + dim], f, acc);
+      Lsum = fmaf(sml[(w * G4_HEADS + head) * 2 + 1], f, Lsum);
+    }
+    const size_t slot = (row0 + head) * P.num_splits + split;
+    P.part_o[slot * TQ_D + dim] = acc;
+    if (dim == 0) {
+      P.part_ml[slot * 2] = M;
+      P.part_ml[slot * 2 + 1] = Lsum;
+    }
   }
+  PHASE_STAMP(11);
+  finish_splits<false>(P, fv.s1, fv.s2, fv.alpha, qbuf, stage0, s_flags, row0, ns, b, kvh);
+  PHASE_STAMP(4);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -779,6 +1158,28 @@ int launch_attn(const AttnParams& P, const TqFast& fk, const TqFast& fv, cudaStr
   return tq_launch_check("k_decode_attn");
 }
 
+template <int KB, int VB>
+int launch_attn_g4(const AttnParams& P, const TqFast& fk, const TqFast& fv, cudaStream_t st) {
+  const size_t need = SmemPlan<KB, VB>::bytes(P.L.record_bytes, P.stages);
+  TQ_REQUIRE(need <= 113 * 1024, TQ_ERR_TOO_LARGE, "page record of %d bytes does not fit the shared-memory pipeline",
+             P.L.record_bytes);
+  static thread_local int configured_dev = -1;  // per instantiation
+  int dev = 0;
+  TQ_CUDA(cudaGetDevice(&dev));
+  if (configured_dev != dev) {
+    TQ_CUDA(cudaFuncSetAttribute(k_decode_attn_g4<KB, VB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 113 * 1024));
+    configured_dev = dev;
+  }
+  dim3 grid(P.num_splits, P.hkv, P.batch);
+  AttnQuant ak, av;
+  memset(&ak, 0, sizeof(ak));
+  memset(&av, 0, sizeof(av));
+  memcpy(ak.s1, fk.s1, 16); memcpy(ak.s2, fk.s2, 16); memcpy(ak.cent16, fk.cent16, 32); ak.alpha = fk.lut_alpha;
+  memcpy(av.s1, fv.s1, 16); memcpy(av.s2, fv.s2, 16); memcpy(av.cent16, fv.cent16, 32); av.alpha = fv.lut_alpha;
+  k_decode_attn_g4<KB, VB><<<grid, ATT_THREADS, need, st>>>(P, ak, av);
+  return tq_launch_check("k_decode_attn_g4");
+}
+
 bool fmt_ok(int fmt, bool is_k) {
   if (fmt >= TQ_FMT_TURBO2 && fmt <= TQ_FMT_TURBO4) return true;
   if (fmt == TQ_FMT_Q8_0) return true;
@@ -786,6 +1187,12 @@ bool fmt_ok(int fmt, bool is_k) {
 }
 
 }  // namespace
+
+#ifdef TQ_PHASE_TIMING
+extern "C" int tq_debug_phase_log(void* host_out, long long bytes) {
+  return cudaMemcpyFromSymbol(host_out, g_phase_log, (size_t)bytes) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 extern "C" int64_t tq_decode_workspace_bytes(int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
                                              int32_t max_pages_per_seq) {
@@ -916,6 +1323,14 @@ extern "C" int tq_decode_attn_phases(const tq_quantizer* kq, const tq_quantizer*
   const TqFast& fv = v_q8 ? none : vq->fast;
   rc = TQ_ERR_UNSUPPORTED;
   tq_set_error("decode attention: K format %d with V format %d is not instantiated", L->k_format, L->v_format);
+  // PolarQuant K and V with at most four query heads per KV head take the kernel specialised for that shape
+  const bool g4 = group <= G4_HEADS && !k_q8 && !v_q8 && !k_prod;
+#define TQ_ATT_G4(K, V) \
+  if (g4 && L->k_format == K && L->v_format == V) rc = launch_attn_g4<K, V>(P, fk, fv, st);
+  TQ_ATT_G4(2, 2) TQ_ATT_G4(2, 3) TQ_ATT_G4(2, 4) TQ_ATT_G4(3, 2) TQ_ATT_G4(3, 3) TQ_ATT_G4(3, 4) TQ_ATT_G4(4, 2)
+  TQ_ATT_G4(4, 3) TQ_ATT_G4(4, 4)
+#undef TQ_ATT_G4
+  if (g4) return rc;
 #define TQ_ATT(K, V) \
   if (L->k_format == K && L->v_format == V) rc = launch_attn<K, V>(P, fk, fv, st);
   TQ_ATT(2, 2) TQ_ATT(2, 3) TQ_ATT(2, 4) TQ_ATT(3, 2) TQ_ATT(3, 3) TQ_ATT(3, 4) TQ_ATT(4, 2) TQ_ATT(4, 3) TQ_ATT(4, 4)
