@@ -66,6 +66,12 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   return false;
 }
 
+// Barrier `id` over one 256-thread group.  id 0 with a 256-thread CTA is the block barrier; a 512-thread CTA runs
+// two independent groups on ids 1 and 2.
+__device__ __forceinline__ void group_sync(int id) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(ATT_THREADS) : "memory");
+}
+
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
   // volatile on purpose: a warp-collective instruction must not be sunk into, or speculated out of,
@@ -110,10 +116,11 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
 #ifdef TQ_PHASE_TIMING
 __device__ unsigned long long g_phase_log[8192 * 16];
 __device__ __forceinline__ void phase_stamp(int slot) {
-  if (threadIdx.x == 0) {
+  if ((threadIdx.x & 255) == 0) {
     unsigned long long tns;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tns));
-    const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    const int per = blockDim.x >> 8;  // 256-thread groups per CTA, each stamps its own row
+    const int cta = blockIdx.x * per + (threadIdx.x >> 8) + gridDim.x * per * (blockIdx.y + gridDim.y * blockIdx.z);
     if (cta < 8192) {
       g_phase_log[cta * 16 + slot] = tns;
       if (slot == 0) {
@@ -196,8 +203,10 @@ __device__ __forceinline__ uint32_t field_off(const uint32_t (&w)[NW], int p) {
     const uint32_t v = sr > SH ? (w[k] >> (sr - SH)) : (sr < SH ? (w[k] << (SH - sr)) : w[k]);
     return v & MASK;
   }
-  const uint32_t v = __funnelshift_l(w[k + 1 < NW ? k + 1 : k], w[k], o);
-  return (v >> (32 - FB - SH)) & MASK;
+  // the field straddles words k and k+1: in the 64-bit value (w[k] : w[k+1]) it sits 64 - o - FB bits above the
+  // low end, so one funnel shift by sr puts it at bit SH.  o > 32 - FB gives sr < 32 - SH: the 5-bit count is exact.
+  const int sr = 64 - o - FB - SH;
+  return __funnelshift_r(w[k + 1 < NW ? k + 1 : k], w[k], sr) & MASK;
 }
 
 __device__ __forceinline__ float load_q(const void* q, int dtype, size_t i) {
@@ -233,8 +242,8 @@ __device__ __forceinline__ void warp_wht128(float (&x)[4], const uint32_t (&pre)
 // fetches (max, sum) of splits s0 + j and s0 + 32 + j, twenty 16-byte loads per lane go out before anything
 // waits, the warp agrees on the maximum, then the rows are accumulated in split order.
 template <int HALVES, bool V_Q8>
-__device__ __forceinline__ void fold_splits(const AttnParams& P, float v_alpha, float* qbuf, size_t row0, int ns) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+__device__ __forceinline__ void fold_splits(const AttnParams& P, float v_alpha, float* qbuf, size_t row0, int ns, int warp) {
+  const int lane = threadIdx.x & 31;
   if (warp >= HALVES * P.group) return;
   const int head = warp % P.group, half = warp / P.group;
   constexpr int ROW_LANES = 32 / HALVES;
@@ -305,9 +314,9 @@ __device__ __forceinline__ void fold_splits(const AttnParams& P, float v_alpha, 
 template <bool V_Q8>
 __device__ __forceinline__ void finish_splits(const AttnParams& P, const uint32_t (&vs1)[4], const uint32_t (&vs2)[4],
                                               float v_alpha, float* qbuf, uint8_t* stage0, volatile int* s_flags,
-                                              size_t row0, int ns, int b, int kvh) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  __syncthreads();
+                                              size_t row0, int ns, int b, int kvh, int tid = threadIdx.x, int bar_id = 0) {
+  const int lane = tid & 31, warp = tid >> 5;
+  group_sync(bar_id);
   if (tid == 0) {
     if (s_flags[0]) atomicExch(P.status, 1);
     __threadfence();
@@ -318,15 +327,15 @@ __device__ __forceinline__ void finish_splits(const AttnParams& P, const uint32_
       __threadfence();
     }
   }
-  __syncthreads();
+  group_sync(bar_id);
   PHASE_STAMP(3);
   if (!s_flags[1]) return;
   // Warp (half, head) folds the splits of one head.  With at most four heads there are two warps per head and each
   // takes 64 of the 128 dims: lanes 0..15 then read even splits, lanes 16..31 odd ones (16 bytes each), and one
   // lane exchange joins the two at the end; with more heads a warp takes the whole row and every split.
-  if (2 * P.group <= ATT_WARPS) fold_splits<2, V_Q8>(P, v_alpha, qbuf, row0, ns);
-  else fold_splits<1, V_Q8>(P, v_alpha, qbuf, row0, ns);
-  __syncthreads();
+  if (2 * P.group <= ATT_WARPS) fold_splits<2, V_Q8>(P, v_alpha, qbuf, row0, ns, warp);
+  else fold_splits<1, V_Q8>(P, v_alpha, qbuf, row0, ns, warp);
+  group_sync(bar_id);
   PHASE_STAMP(13);
   if (P.v_rot) {  // dense rotation: x = R^T y
     for (int e = tid; e < P.group * TQ_D; e += ATT_THREADS) {
@@ -796,13 +805,33 @@ static_assert(sizeof(AttnQuant) == 80, "AttnQuant layout");
 constexpr int G4_HEADS = 4;
 constexpr int G4_HSTRIDE = TQ_D + 4;  // floats between heads in the warp-merge buffer: 16-byte stores stay conflict-free
 
+// One CTA per SM runs TWO independent 256-thread groups (own split, own pipeline, own barrier), sharing only the
+// pair tables.  Two separate 256-thread CTAs on one SM did the same work, but the warp schedulers favoured the
+// CTA that arrived first: it finished its pages in 9.7 us, its neighbour in 12.6 us, and the SM idled at half
+// occupancy in between.  Warps of one CTA have the same age and progress together.
+constexpr int G4_THREADS = 2 * ATT_THREADS;
+
+// bytes of one group's private shared memory: query buffer, barriers, pipeline stages (or the warp-merge buffer)
 template <int KB, int VB>
-__global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_constant__ AttnParams P, const __grid_constant__ AttnQuant fk,
+constexpr size_t g4_group_bytes(int record_bytes, int nstages) {
+  using SP = SmemPlan<KB, VB>;
+  const size_t stages = (size_t)nstages * record_bytes;
+  const size_t merge = (size_t)ATT_WARPS * G4_HEADS * (TQ_D + 4 + 2) * 4;
+  return (((size_t)(SP::OFF_STAGE - SP::OFF_Q) + (stages > merge ? stages : merge)) + 127) / 128 * 128;
+}
+
+template <int KB, int VB>
+__global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_constant__ AttnParams P, const __grid_constant__ AttnQuant fk,
                                                                     const __grid_constant__ AttnQuant fv) {
   using SP = SmemPlan<KB, VB>;
   extern __shared__ __align__(128) uint8_t smem_raw[];
-  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int grp = threadIdx.x >> 8;              // which of the CTA's two groups
+  // groups are numbered (kv head, split) so that an odd number of splits does not leave half a CTA empty
+  const int gidx = 2 * blockIdx.x + grp, b = blockIdx.y;
+  const bool exists = gidx < P.num_splits * P.hkv;
+  const int kvh = exists ? gidx / P.num_splits : 0, split = exists ? gidx % P.num_splits : P.num_splits;
+  const int tid = threadIdx.x & 255, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int bar_id = 1 + grp;
   PHASE_STAMP(0);
   {  // one parameter line per warp, all misses in flight together
     const uint32_t* pp = reinterpret_cast<const uint32_t*>(&P);
@@ -819,12 +848,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_
   const int32_t* bt = P.block_table + (size_t)b * P.max_pages;
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* sm = smem_raw + (((raw + SP::ALIGN - 1) & ~(uint32_t)(SP::ALIGN - 1)) - raw);
-  float* qbuf = reinterpret_cast<float*>(sm + SP::OFF_Q);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + SP::OFF_BAR);
-  volatile int* s_flags = reinterpret_cast<volatile int*>(sm + SP::OFF_BAR + 64);
-  uint8_t* stage0 = sm + SP::OFF_STAGE;
   const uint32_t rec = (uint32_t)P.L.record_bytes;
   const int NS = P.stages;
+  uint8_t* smg = sm + (size_t)grp * g4_group_bytes<KB, VB>(rec, NS);   // this group's private part
+  float* qbuf = reinterpret_cast<float*>(smg + SP::OFF_Q);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smg + SP::OFF_BAR);
+  volatile int* s_flags = reinterpret_cast<volatile int*>(smg + SP::OFF_BAR + 64);
+  uint8_t* stage0 = smg + SP::OFF_STAGE;
   constexpr int PRODUCER = ATT_THREADS - 32;  // lane 0 of the last warp issues every bulk copy
 
   auto issue = [&](int i, int64_t page) {
@@ -875,21 +905,19 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_
   }
   __syncwarp();
   if (warp >= P.group) {
-    const int ft = tid - 32 * P.group, fn = ATT_THREADS - 32 * P.group;
-    lut_fill<KB>(sm + SP::OFF_K, fk.cent16, ft, fn);
-    lut_fill<VB>(sm + SP::OFF_V, fv.cent16, ft, fn);
+    const int fh = ATT_THREADS - 32 * P.group;   // table-filling threads per group; both groups share the work
+    lut_fill<KB>(sm + SP::OFF_K, fk.cent16, grp * fh + tid - 32 * P.group, 2 * fh);
+    lut_fill<VB>(sm + SP::OFF_V, fv.cent16, grp * fh + tid - 32 * P.group, 2 * fh);
   }
   PHASE_STAMP(5);
   const int n_pages = (seq_len + PT - 1) / PT;
-  if (n_pages == 0 && split == 0) {
+  if (n_pages == 0 && split == 0)  // empty sequence: zeros (split 0 exists for every kv head)
     for (int e = tid; e < P.group * TQ_D; e += ATT_THREADS) store_out(P.out, P.out_dtype, row0 * TQ_D + e, 0.f);
-    return;
-  }
-  if (page_lo >= n_pages) return;
   const int np = min(n_pages, page_lo + P.chunk_pages) - page_lo;
   const int ns = (n_pages + P.chunk_pages - 1) / P.chunk_pages;
   PHASE_STAMP(6);
-  __syncthreads();
+  __syncthreads();               // the only CTA-wide barrier: tables, query buffers and mbarriers are ready
+  if (np <= 0) return;           // this group has no pages (its split lies beyond the sequence)
   PHASE_STAMP(7);
 
   // B operand of S = K q^T: column g is head g & 3, hi half for g < 4, lo half otherwise
@@ -923,7 +951,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
   constexpr int KIDXB = 16 * KB, VIDXB = 16 * VB, KW = KB;
+  constexpr float MAX_SLACK = 4.0f;
   const int tiles_per_page = PT / 16;
+  // byte offsets inside a page record that do not depend on the tile
+  const uint32_t k_off = P.L.k_idx_off + g * KIDXB + t * (KIDXB / 4);
+  const uint32_t v_off = P.L.v_idx_off + 4 * t * VIDXB + g * (2 * VB);
+  const uint32_t ks_off = P.L.k_scale_off + 4 * (g + (upper ? 8 : 0));
+  const uint32_t vs_off = P.L.v_scale_off + 4 * (g + (upper ? 8 : 0));
 
   for (int i = 0; i < np; ++i) {
     if (tid == PRODUCER && i + NS - 1 < np) {
@@ -941,7 +975,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_
       float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
       {
         uint32_t w0[KW], w1[KW];
-        const uint32_t* p0 = reinterpret_cast<const uint32_t*>(st + P.L.k_idx_off + (tb + g) * KIDXB + t * (KIDXB / 4));
+        const uint32_t* p0 = reinterpret_cast<const uint32_t*>(st + k_off + tb * KIDXB);
         const uint32_t* p1 = p0 + 8 * (KIDXB / 4);
 #pragma unroll
         for (int k = 0; k < KW; ++k) {
@@ -964,13 +998,16 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_
       const float keep0 = upper ? sa[2] + sb[2] : sa[0] + sb[0], keep1 = upper ? sa[3] + sb[3] : sa[1] + sb[1];
       const int tok = tb + g + (upper ? 8 : 0);
       const bool ok = tok < valid;
-      const float ks = reinterpret_cast<const float*>(st + P.L.k_scale_off)[tok];
+      const float ks = *reinterpret_cast<const float*>(st + ks_off + 4 * tb);
       float sc0 = (keep0 + __shfl_xor_sync(0xffffffffu, give0, 2)) * ks;
       float sc1 = (keep1 + __shfl_xor_sync(0xffffffffu, give1, 2)) * ks;
       sc0 = ok ? sc0 : -INFINITY;
       sc1 = ok ? sc1 : -INFINITY;
       // ---------------- online softmax (log2 domain), heads 2(t&1) and 2(t&1)+1 ----------------
-      if (__any_sync(0xffffffffu, (sc0 > m0) || (sc1 > m1))) {
+      // The running maxima move only when a score exceeds them by more than 2^MAX_SLACK: probabilities then stay
+      // below 2^MAX_SLACK (far inside fp16 and fp32 range) and almost every tile skips the warp reduction and the
+      // rescaling of O.  The normalised result is the same up to rounding.
+      if (__any_sync(0xffffffffu, (sc0 > m0 + MAX_SLACK) || (sc1 > m1 + MAX_SLACK))) {
         float mx0 = sc0, mx1 = sc1;
 #pragma unroll
         for (int sh = 2; sh < 32; sh <<= 1) {
@@ -993,7 +1030,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_
       const float p0 = fast_exp2(sc0 - m0), p1 = fast_exp2(sc1 - m1);
       l0 += p0;
       l1 += p1;
-      const float vs = ok ? reinterpret_cast<const float*>(st + P.L.v_scale_off)[tok] : 0.f;
+      const float vs = ok ? *reinterpret_cast<const float*>(st + vs_off + 4 * tb) : 0.f;
       const uint32_t hp = pack_h2(p0 * vs, p1 * vs);
       uint32_t pb[4];
 #pragma unroll
@@ -1003,7 +1040,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_
       constexpr int SHV = PairLut<VB>::SHIFT;
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
-        const uint8_t* pv = st + P.L.v_idx_off + (tb + 4 * t + q4) * VIDXB + g * (2 * VB);
+        const uint8_t* pv = st + v_off + tb * VIDXB + q4 * VIDXB;
         uint32_t w[2];
         if constexpr (VB == 3) {
           const uint16_t* phw = reinterpret_cast<const uint16_t*>(pv);
@@ -1029,7 +1066,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_
                    pb[2 * u], pb[2 * u + 1]);
       }
     }
-    __syncthreads();  // every warp is done with this stage before it is refilled
+    group_sync(bar_id);  // every warp of the group is done with this stage before it is refilled
   }
 
   PHASE_STAMP(2);
@@ -1048,7 +1085,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_
   if (g == 0 && t < 2) {
     *reinterpret_cast<float4*>(sml + (warp * G4_HEADS + 2 * t) * 2) = make_float4(m0, l0, m1, l1);
   }
-  __syncthreads();
+  group_sync(bar_id);
   for (int e = tid; e < P.group * TQ_D; e += ATT_THREADS) {
     const int head = e >> 7, dim = e & 127;
     float M = -INFINITY;
@@ -1070,7 +1107,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_
     }
   }
   PHASE_STAMP(11);
-  finish_splits<false>(P, fv.s1, fv.s2, fv.alpha, qbuf, stage0, s_flags, row0, ns, b, kvh);
+  finish_splits<false>(P, fv.s1, fv.s2, fv.alpha, qbuf, stage0, s_flags, row0, ns, b, kvh, tid, bar_id);
   PHASE_STAMP(4);
 }
 
@@ -1160,23 +1197,25 @@ int launch_attn(const AttnParams& P, const TqFast& fk, const TqFast& fv, cudaStr
 
 template <int KB, int VB>
 int launch_attn_g4(const AttnParams& P, const TqFast& fk, const TqFast& fv, cudaStream_t st) {
-  const size_t need = SmemPlan<KB, VB>::bytes(P.L.record_bytes, P.stages);
-  TQ_REQUIRE(need <= 113 * 1024, TQ_ERR_TOO_LARGE, "page record of %d bytes does not fit the shared-memory pipeline",
+  using SP = SmemPlan<KB, VB>;
+  const size_t need = (size_t)SP::ALIGN + SP::OFF_Q + 2 * g4_group_bytes<KB, VB>(P.L.record_bytes, P.stages);
+  constexpr size_t LIMIT = 220 * 1024;  // one CTA per SM
+  TQ_REQUIRE(need <= LIMIT, TQ_ERR_TOO_LARGE, "page record of %d bytes does not fit the shared-memory pipeline",
              P.L.record_bytes);
   static thread_local int configured_dev = -1;  // per instantiation
   int dev = 0;
   TQ_CUDA(cudaGetDevice(&dev));
   if (configured_dev != dev) {
-    TQ_CUDA(cudaFuncSetAttribute(k_decode_attn_g4<KB, VB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 113 * 1024));
+    TQ_CUDA(cudaFuncSetAttribute(k_decode_attn_g4<KB, VB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)LIMIT));
     configured_dev = dev;
   }
-  dim3 grid(P.num_splits, P.hkv, P.batch);
   AttnQuant ak, av;
   memset(&ak, 0, sizeof(ak));
   memset(&av, 0, sizeof(av));
   memcpy(ak.s1, fk.s1, 16); memcpy(ak.s2, fk.s2, 16); memcpy(ak.cent16, fk.cent16, 32); ak.alpha = fk.lut_alpha;
   memcpy(av.s1, fv.s1, 16); memcpy(av.s2, fv.s2, 16); memcpy(av.cent16, fv.cent16, 32); av.alpha = fv.lut_alpha;
-  k_decode_attn_g4<KB, VB><<<grid, ATT_THREADS, need, st>>>(P, ak, av);
+  dim3 grid((P.num_splits * P.hkv + 1) / 2, P.batch);
+  k_decode_attn_g4<KB, VB><<<grid, G4_THREADS, need, st>>>(P, ak, av);
   return tq_launch_check("k_decode_attn_g4");
 }
 
