@@ -265,7 +265,7 @@ def run_ours(args):
 
     def one_step(phases=7):
         for i, layer in enumerate(cache.layers):
-            layer.attend(q[i], bt, seq_lens, out=out[i], workspace=ws, phases=phases)
+            layer.attend(q[i], bt, seq_lens, out=out[i], workspace=ws, phases=phases, overlap=True)
 
     one_step()
     torch.cuda.synchronize(dev)
@@ -445,7 +445,7 @@ def run_other_workload(args):
 
     def one_step():
         for i, layer in enumerate(cache.layers):
-            layer.attend(q[i], bt, seq_lens, out=out[i], workspace=ws)
+            layer.attend(q[i], bt, seq_lens, out=out[i], workspace=ws, overlap=True)
 
     one_step()
     torch.cuda.synchronize(dev)

@@ -217,7 +217,13 @@ int tq_decode_attn(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cach
  * launched when the K quantizer has a dense rotation; sign-WHT rotations are applied inside the
  * attention kernel), bit 1 = the attention kernel (split attention, merge by the last split to finish,
  * un-rotation).  3 is tq_decode_attn.  Lets a caller re-run the attention kernel alone (timing, or
- * many layers that share one rotated query); bits run in order against the same workspace. */
+ * many layers that share one rotated query); bits run in order against the same workspace.
+ * TQ_DECODE_OVERLAP (bit 3) launches the attention kernel with programmatic stream serialization:
+ * it may start while the preceding kernel of the stream is still running, and until that kernel has
+ * completed it only reads the cache pages, the block table and the sequence lengths (queries are read,
+ * the workspace and the output written, afterwards).  Set it when the preceding kernel does not write
+ * those three -- e.g. the attention call of another layer -- or never signals early completion. */
+#define TQ_DECODE_OVERLAP 8
 int tq_decode_attn_phases(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cache_layout* layout,
                           const uint8_t* pool_dev, const int32_t* block_table_dev,
                           int32_t max_pages_per_seq, const int32_t* seq_lens_dev, const void* q_dev,

@@ -155,6 +155,7 @@ struct AttnParams {
   int32_t k_ident, v_ident;  // identity rotation (q8_0 tensors)
   int32_t max_pages, batch, hq, hkv, group, chunk_pages, num_splits;
   int32_t stages;      // 2 or 3 page records in flight per CTA
+  int32_t overlap;     // launched with programmatic stream serialization: see TQ_DECODE_OVERLAP
   tq_cache_layout L;
 };
 
@@ -842,6 +843,12 @@ __global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_c
     asm volatile("" ::"r"(touch));
   }
   PHASE_STAMP(14);
+  // Programmatic dependent launch: let the next kernel in the stream start its own prologue as soon as SMs free
+  // up.  Everything this kernel does before griddepcontrol.wait below reads only the cache, the block table and
+  // the sequence lengths; queries are read, and the workspace and the output written, after the wait, i.e.
+  // after the preceding kernel has completed and its writes are visible.  Both instructions do nothing in a
+  // launch without the attribute.
+  if (P.overlap) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int PT = P.L.page_tokens;
   const int page_lo = split * P.chunk_pages;
   const size_t row0 = (size_t)b * P.hq + (size_t)kvh * P.group;
@@ -889,6 +896,7 @@ __global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_c
       }
     }
   } else if (warp < P.group) {
+    if (P.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (P.k_pre) load_q4(P.qrot, TQ_F32, (row0 + warp) * TQ_D + 4 * lane, x);
     else load_q4(P.q, P.q_dtype, (row0 + warp) * TQ_D + 4 * lane, x);
     if (!P.k_pre) {
@@ -910,6 +918,8 @@ __global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_c
     lut_fill<VB>(sm + SP::OFF_V, fv.cent16, grp * fh + tid - 32 * P.group, 2 * fh);
   }
   PHASE_STAMP(5);
+  // every thread waits before it can touch the workspace or the output (the query warps already have)
+  if (P.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
   const int n_pages = (seq_len + PT - 1) / PT;
   if (n_pages == 0 && split == 0)  // empty sequence: zeros (split 0 exists for every kv head)
     for (int e = tid; e < P.group * TQ_D; e += ATT_THREADS) store_out(P.out, P.out_dtype, row0 * TQ_D + e, 0.f);
@@ -1214,8 +1224,18 @@ int launch_attn_g4(const AttnParams& P, const TqFast& fk, const TqFast& fv, cuda
   memset(&av, 0, sizeof(av));
   memcpy(ak.s1, fk.s1, 16); memcpy(ak.s2, fk.s2, 16); memcpy(ak.cent16, fk.cent16, 32); ak.alpha = fk.lut_alpha;
   memcpy(av.s1, fv.s1, 16); memcpy(av.s2, fv.s2, 16); memcpy(av.cent16, fv.cent16, 32); av.alpha = fv.lut_alpha;
-  dim3 grid((P.num_splits * P.hkv + 1) / 2, P.batch);
-  k_decode_attn_g4<KB, VB><<<grid, G4_THREADS, need, st>>>(P, ak, av);
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((P.num_splits * P.hkv + 1) / 2, P.batch);
+  cfg.blockDim = dim3(G4_THREADS);
+  cfg.dynamicSmemBytes = need;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = P.overlap ? 1 : 0;
+  TQ_CUDA(cudaLaunchKernelEx(&cfg, k_decode_attn_g4<KB, VB>, P, ak, av));
   return tq_launch_check("k_decode_attn_g4");
 }
 
@@ -1354,6 +1374,7 @@ extern "C" int tq_decode_attn_phases(const tq_quantizer* kq, const tq_quantizer*
   P.chunk_pages = plan.chunk_pages;
   P.num_splits = plan.num_splits;
   P.stages = L->record_bytes > 24 * 1024 ? 2 : 3;
+  P.overlap = (phases & TQ_DECODE_OVERLAP) ? 1 : 0;
   P.L = *L;
   TqFast none;
   memset(&none, 0, sizeof(none));

@@ -73,7 +73,9 @@ class LayeredKVCache:
             st["len"].add_(1)
             for i, layer in enumerate(self.layers):
                 layer.append(st["k"][i], st["v"][i], st["slots"])
-                layer.attend(st["q"][i], st["bt"], st["len"], out=st["out"][i], workspace=ws)
+                # the preceding kernel is this layer's append (it completes before its dependents start) or,
+                # across layers, another attention call: neither writes what this kernel reads early
+                layer.attend(st["q"][i], st["bt"], st["len"], out=st["out"][i], workspace=ws, overlap=True)
 
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))

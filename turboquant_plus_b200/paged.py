@@ -127,9 +127,16 @@ class PagedKVCache:
             self._ws = torch.zeros((int(need),), dtype=torch.uint8, device=self.device)
         return self._ws
 
-    def attend(self, q, block_table, seq_lens, scale=None, out=None, workspace=None, phases=7):
+    def attend(self, q, block_table, seq_lens, scale=None, out=None, workspace=None, phases=7, overlap=False):
         """q: (batch, num_q_heads, head_dim) CUDA tensor; block_table: (batch, max_pages) int32 page
-        numbers; seq_lens: (batch,) int32.  Returns (batch, num_q_heads, head_dim) in q's dtype."""
+        numbers; seq_lens: (batch,) int32.  Returns (batch, num_q_heads, head_dim) in q's dtype.
+
+        overlap=True lets the kernel start while the preceding kernel of the stream is still running; until
+        that kernel has completed it only reads cache pages, the block table and the sequence lengths.  Use it
+        when the preceding kernel does not write those (another layer's attention, an append kernel that does
+        not signal early completion)."""
+        if overlap:
+            phases = int(phases) | nv.DECODE_OVERLAP
         torch = nv.require_cuda()
         q = q.contiguous()
         bsz, hq, d = q.shape
