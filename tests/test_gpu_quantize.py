@@ -231,10 +231,14 @@ def test_input_dtypes_and_errors(tq):
     a = q.quantize_device(torch.as_tensor(x).cuda(), packed=True)
     h = q.quantize_device(torch.as_tensor(x).cuda().half().float(), packed=True)
     h16 = q.quantize_device(torch.as_tensor(x).cuda().half(), packed=True)
-    assert torch.equal(h["packed"], h16["packed"]) and torch.equal(h["norm"], h16["norm"])
     b16 = q.quantize_device(torch.as_tensor(x).cuda().bfloat16(), packed=True)
     b32 = q.quantize_device(torch.as_tensor(x).cuda().bfloat16().float(), packed=True)
-    assert torch.equal(b16["packed"], b32["packed"])
+    # 16-bit inputs run the Hadamard transform on the tensor cores, fp32 inputs in registers: the same values
+    # up to fp32 rounding, so indices may differ only for coordinates that sit on a decision boundary
+    for lo, hi in ((h, h16), (b32, b16)):
+        differ = (lo["packed"] != hi["packed"]).any(dim=1).sum().item()
+        assert differ <= 2, differ
+        torch.testing.assert_close(lo["norm"], hi["norm"], rtol=1e-6, atol=0)
     assert a["packed"].shape == (1000, 48)
     with pytest.raises(ValueError):
         q.quantize(np.zeros((3, 64)))

@@ -810,7 +810,8 @@ constexpr int G4_HSTRIDE = TQ_D + 4;  // floats between heads in the warp-merge 
 // pair tables.  Two separate 256-thread CTAs on one SM did the same work, but the warp schedulers favoured the
 // CTA that arrived first: it finished its pages in 9.7 us, its neighbour in 12.6 us, and the SM idled at half
 // occupancy in between.  Warps of one CTA have the same age and progress together.
-constexpr int G4_THREADS = 2 * ATT_THREADS;
+constexpr int G4_GROUPS = 2;
+constexpr int G4_THREADS = G4_GROUPS * ATT_THREADS;
 
 // bytes of one group's private shared memory: query buffer, barriers, pipeline stages (or the warp-merge buffer)
 template <int KB, int VB>
@@ -828,7 +829,7 @@ __global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_c
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const int grp = threadIdx.x >> 8;              // which of the CTA's two groups
   // groups are numbered (kv head, split) so that an odd number of splits does not leave half a CTA empty
-  const int gidx = 2 * blockIdx.x + grp, b = blockIdx.y;
+  const int gidx = G4_GROUPS * blockIdx.x + grp, b = blockIdx.y;
   const bool exists = gidx < P.num_splits * P.hkv;
   const int kvh = exists ? gidx / P.num_splits : 0, split = exists ? gidx % P.num_splits : P.num_splits;
   const int tid = threadIdx.x & 255, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
@@ -914,8 +915,8 @@ __global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_c
   __syncwarp();
   if (warp >= P.group) {
     const int fh = ATT_THREADS - 32 * P.group;   // table-filling threads per group; both groups share the work
-    lut_fill<KB>(sm + SP::OFF_K, fk.cent16, grp * fh + tid - 32 * P.group, 2 * fh);
-    lut_fill<VB>(sm + SP::OFF_V, fv.cent16, grp * fh + tid - 32 * P.group, 2 * fh);
+    lut_fill<KB>(sm + SP::OFF_K, fk.cent16, grp * fh + tid - 32 * P.group, G4_GROUPS * fh);
+    lut_fill<VB>(sm + SP::OFF_V, fv.cent16, grp * fh + tid - 32 * P.group, G4_GROUPS * fh);
   }
   PHASE_STAMP(5);
   // every thread waits before it can touch the workspace or the output (the query warps already have)
@@ -1208,7 +1209,7 @@ int launch_attn(const AttnParams& P, const TqFast& fk, const TqFast& fv, cudaStr
 template <int KB, int VB>
 int launch_attn_g4(const AttnParams& P, const TqFast& fk, const TqFast& fv, cudaStream_t st) {
   using SP = SmemPlan<KB, VB>;
-  const size_t need = (size_t)SP::ALIGN + SP::OFF_Q + 2 * g4_group_bytes<KB, VB>(P.L.record_bytes, P.stages);
+  const size_t need = (size_t)SP::ALIGN + SP::OFF_Q + G4_GROUPS * g4_group_bytes<KB, VB>(P.L.record_bytes, P.stages);
   constexpr size_t LIMIT = 220 * 1024;  // one CTA per SM
   TQ_REQUIRE(need <= LIMIT, TQ_ERR_TOO_LARGE, "page record of %d bytes does not fit the shared-memory pipeline",
              P.L.record_bytes);
@@ -1226,7 +1227,7 @@ int launch_attn_g4(const AttnParams& P, const TqFast& fk, const TqFast& fv, cuda
   memcpy(av.s1, fv.s1, 16); memcpy(av.s2, fv.s2, 16); memcpy(av.cent16, fv.cent16, 32); av.alpha = fv.lut_alpha;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3((P.num_splits * P.hkv + 1) / 2, P.batch);
+  cfg.gridDim = dim3((P.num_splits * P.hkv + G4_GROUPS - 1) / G4_GROUPS, P.batch);
   cfg.blockDim = dim3(G4_THREADS);
   cfg.dynamicSmemBytes = need;
   cfg.stream = st;

@@ -168,8 +168,53 @@ struct TqQuantDst {
   int32_t rscale_const; // cache mode: store rnorm * sqrt(pi/2)/sqrt(d) so that attention needs one multiply
 };
 
+// address of vector v's record field (elem_bytes per token and head) in plain arrays or in a paged cache;
+// ok = false when the token's slot is negative (skip it)
+__device__ __forceinline__ uint8_t* tq_dst_ptr(uint8_t* base, const TqQuantDst& dst, int64_t v, int32_t elem_bytes,
+                                               bool& ok) {
+  if (dst.page_tokens == 0) return base + v * elem_bytes;
+  // 32-bit arithmetic whenever the numbers allow it (64-bit division costs ~100 instructions)
+  int64_t tok;
+  int32_t head;
+  if ((dst.heads & (dst.heads - 1)) == 0) {
+    const int sh = 31 - __clz(dst.heads);
+    tok = v >> sh;
+    head = (int32_t)(v & (dst.heads - 1));
+  } else if (v < 0x7fffffffLL) {
+    const uint32_t v32 = (uint32_t)v, h32 = (uint32_t)dst.heads;
+    const uint32_t t32 = v32 / h32;
+    tok = t32;
+    head = (int32_t)(v32 - t32 * h32);
+  } else {
+    tok = v / dst.heads;
+    head = (int32_t)(v - tok * dst.heads);
+  }
+  const int64_t slot = dst.slots ? dst.slots[tok] : tok;
+  if (slot < 0) {
+    ok = false;
+    return base;
+  }
+  int64_t page;
+  int32_t within;
+  if ((dst.page_tokens & (dst.page_tokens - 1)) == 0) {
+    const int sh = 31 - __clz(dst.page_tokens);
+    page = slot >> sh;
+    within = (int32_t)(slot & (dst.page_tokens - 1));
+  } else if (slot < 0x7fffffffLL) {
+    const uint32_t pg = (uint32_t)slot / (uint32_t)dst.page_tokens;
+    page = pg;
+    within = (int32_t)((uint32_t)slot - pg * (uint32_t)dst.page_tokens);
+  } else {
+    page = slot / dst.page_tokens;
+    within = (int32_t)(slot - page * dst.page_tokens);
+  }
+  return base + page * dst.page_stride + head * dst.head_stride + (int64_t)within * elem_bytes;
+}
+
 int tq_quantize_wht_launch(const TqFast& f, const void* x, int32_t dtype, int64_t ld, int64_t n,
                            const TqQuantDst& dst, bool want_qjl, cudaStream_t st);
+bool tq_quantize_mma_try(const TqFast& f, const void* x, int32_t dtype, int64_t ld, int64_t n, const TqQuantDst& dst,
+                         bool want_qjl, cudaStream_t st, int* rc);
 int tq_q8_0_append_launch(const void* x, int32_t dtype, int64_t n_tokens, int32_t heads, uint8_t* q_base,
                           uint8_t* scale_base, const int64_t* slots, int32_t page_tokens,
                           int64_t page_stride, int64_t head_stride, cudaStream_t st);

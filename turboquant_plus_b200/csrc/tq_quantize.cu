@@ -18,47 +18,6 @@
 // the index is assembled as a float, and eight 3-bit indices are packed by an exact fp32 Horner sum
 // (< 2^24) that is turned into an integer once per group.
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint8_t* tq_dst_ptr(uint8_t* base, const TqQuantDst& dst, int64_t v, int32_t elem_bytes,
-                                               bool& ok) {
-  if (dst.page_tokens == 0) return base + v * elem_bytes;
-  // 32-bit arithmetic whenever the numbers allow it (64-bit division costs ~100 instructions)
-  int64_t tok;
-  int32_t head;
-  if ((dst.heads & (dst.heads - 1)) == 0) {
-    const int sh = 31 - __clz(dst.heads);
-    tok = v >> sh;
-    head = (int32_t)(v & (dst.heads - 1));
-  } else if (v < 0x7fffffffLL) {
-    const uint32_t v32 = (uint32_t)v, h32 = (uint32_t)dst.heads;
-    const uint32_t t32 = v32 / h32;
-    tok = t32;
-    head = (int32_t)(v32 - t32 * h32);
-  } else {
-    tok = v / dst.heads;
-    head = (int32_t)(v - tok * dst.heads);
-  }
-  const int64_t slot = dst.slots ? dst.slots[tok] : tok;
-  if (slot < 0) {
-    ok = false;
-    return base;
-  }
-  int64_t page;
-  int32_t within;
-  if ((dst.page_tokens & (dst.page_tokens - 1)) == 0) {
-    const int sh = 31 - __clz(dst.page_tokens);
-    page = slot >> sh;
-    within = (int32_t)(slot & (dst.page_tokens - 1));
-  } else if (slot < 0x7fffffffLL) {
-    const uint32_t pg = (uint32_t)slot / (uint32_t)dst.page_tokens;
-    page = pg;
-    within = (int32_t)((uint32_t)slot - pg * (uint32_t)dst.page_tokens);
-  } else {
-    page = slot / dst.page_tokens;
-    within = (int32_t)(slot - page * dst.page_tokens);
-  }
-  return base + page * dst.page_stride + head * dst.head_stride + (int64_t)within * elem_bytes;
-}
-
 template <typename Tin, int BITS, bool SYM, bool QJL>
 __global__ void __launch_bounds__(256) k_quantize_wht(const TqFast f, const Tin* __restrict__ x, int64_t ld, int64_t n,
                                                       const TqQuantDst dst) {
@@ -312,6 +271,8 @@ int tq_quantize_wht_launch(const TqFast& f, const void* x, int32_t dtype, int64_
                            bool want_qjl, cudaStream_t st) {
   if (n == 0) return TQ_OK;
   TQ_REQUIRE(tq_aligned(x, 16), TQ_ERR_ALIGN, "input rows must be 16-byte aligned");
+  int rc = TQ_OK;  // 16-bit inputs into a packed stream: Hadamard transform on the tensor cores
+  if (tq_quantize_mma_try(f, x, dtype, ld, n, dst, want_qjl, st, &rc)) return rc;
   switch (dtype) {
     case TQ_F32:
       TQ_REQUIRE(ld % 4 == 0, TQ_ERR_ALIGN, "fp32 row stride must be a multiple of 4 elements");

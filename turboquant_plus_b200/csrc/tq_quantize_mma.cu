@@ -1,0 +1,319 @@
+// d = 128 sign-WHT quantizer for 16-bit inputs, with the Hadamard transform on the tensor cores.
+//
+//   k_quantize_mma<Tin, BITS, NORMC>   Tin = __half or __nv_bfloat16, symmetric codebook, packed output.
+//
+// H128 = H8 (x) H16 (element e = 16 i + j).  A warp takes 16 vectors at a time:
+//   * the 16 x 128 tile is copied to shared memory with 16-byte asynchronous copies (double buffered) and read
+//     back as MMA operands with ldmatrix (rows padded to 272 bytes so that the eight rows of a matrix fall into
+//     different bank groups);
+//   * for each i, one m16n8k16 MMA per 8 output columns contracts the 16 inputs x[v][16 i + j'] with
+//     sign1[16 i + j'] * H16[j'][j].  Inputs are 16-bit, the matrix entries are +-1: every product is exact and
+//     the sums are accumulated in fp32;
+//   * thread (g, t) then holds, for vectors g and g + 8 and for every i, the columns j = 8 nt + 2 t + c: the 8-point
+//     transform over i is three butterfly stages in its own registers;
+//   * ||x|| is taken from the transformed values (||H x||^2 = 128 ||x||^2), magnitudes are compared against the
+//     positive boundaries scaled by ||x|| sqrt(d), the sign comes from the value itself, sign2 mirrors the index,
+//     and eight indices at a time are packed by an exact fp32 Horner sum;
+//   * a 4 x 4 transpose of words inside each quad of lanes leaves every lane with 32 consecutive indices of its
+//     vector, which it stores as the reference's most-significant-bit-first stream (turboquant/utils.py pack_indices
+//     order, the layout the cache keeps).
+// Everything else (fp32 input, QJL stage, asymmetric codebooks, unpacked output) stays with k_quantize_wht.
+#include "tq_internal.cuh"
+
+namespace {
+
+constexpr int QM_THREADS = 128;
+constexpr int QM_WARPS = 4;
+constexpr int QM_ROWS = 16;
+constexpr int QM_ROWB = 272;  // 256 data bytes + 16 bytes of padding
+
+template <typename T> struct QmIn;
+template <> struct QmIn<__half> {
+  static constexpr uint32_t ONE = 0x3C00u, MINUS = 0xBC00u;
+  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+};
+template <> struct QmIn<__nv_bfloat16> {
+  static constexpr uint32_t ONE = 0x3F80u, MINUS = 0xBF80u;
+  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+};
+
+__device__ __forceinline__ uint32_t qm_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint32_t qm_bit(const uint32_t (&m)[4], int e) { return (m[e >> 5] >> (e & 31)) & 1u; }
+// 1.0f when a > b, else 0.0f, in one instruction
+__device__ __forceinline__ float qm_gt(float a, float b) {
+  float d;
+  asm("set.gt.f32.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
+  return d;
+}
+
+template <typename Tin, int BITS, bool NORMC>
+__global__ void __launch_bounds__(QM_THREADS, 4) k_quantize_mma(const TqFast f, const Tin* __restrict__ x, int64_t ld,
+                                                                int64_t n, const TqQuantDst dst) {
+  constexpr int NC = 1 << BITS, HALF = NC / 2, NT = HALF - 1;  // NT positive boundaries
+  constexpr int IDXB = 16 * BITS;
+  constexpr float RADIX = (float)NC;
+  __shared__ __align__(16) uint8_t tile[QM_WARPS][2][QM_ROWS * QM_ROWB];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+
+  // B operands: rows k = 2t, 2t+1 (register 0) and 2t+8, 2t+9 (register 1) of sign1 * H16, column 8 nt + g
+  uint32_t bfr[8][2][2];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int col = 8 * nt + g;
+        uint32_t r = 0;
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int k = 2 * t + 8 * h + e;
+          const uint32_t neg = qm_bit(f.s1, 16 * i + k) ^ (uint32_t)(__popc(k & col) & 1);
+          r |= (neg ? QmIn<Tin>::MINUS : QmIn<Tin>::ONE) << (16 * e);
+        }
+        bfr[i][nt][h] = r;
+      }
+  // sign2 mirrors an index (i -> 2^b - 1 - i): an XOR of the packed word.  Word tp of this lane packs, most
+  // significant first, the elements 16 (2 tp + (k >> 2)) + 8 ((k >> 1) & 1) + 2 t + (k & 1), k = 0..7.
+  uint32_t flip[4];
+#pragma unroll
+  for (int tp = 0; tp < 4; ++tp) {
+    uint32_t m = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int e = 16 * (2 * tp + (k >> 2)) + 8 * ((k >> 1) & 1) + 2 * t + (k & 1);
+      if (qm_bit(f.s2, e)) m |= (uint32_t)(NC - 1) << (BITS * (7 - k));
+    }
+    flip[tp] = m;
+  }
+  float bnd[NT > 0 ? NT : 1], dsq[NT > 0 ? NT : 1];  // positive boundaries; steps of the squared centroids
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    bnd[j] = f.bnd[HALF + j];
+    dsq[j] = f.cent[HALF + j + 1] * f.cent[HALF + j + 1] - f.cent[HALF + j] * f.cent[HALF + j];
+  }
+  const float c0sq = f.cent[HALF] * f.cent[HALF];
+
+  const int64_t ntiles = (n + QM_ROWS - 1) / QM_ROWS;
+  const int64_t stride = (int64_t)gridDim.x * QM_WARPS;
+  int64_t ti = (int64_t)blockIdx.x * QM_WARPS + warp;
+  auto issue = [&](int64_t tile_i, int buf) {
+    const int64_t v0 = tile_i * QM_ROWS;
+    const uint32_t sbase = qm_smem(&tile[warp][buf][0]);
+#pragma unroll
+    for (int r2 = 0; r2 < 8; ++r2) {
+      const int row = 2 * r2 + (lane >> 4), chunk = lane & 15;
+      if (v0 + row < n)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sbase + row * QM_ROWB + chunk * 16),
+                     "l"(x + (v0 + row) * ld + chunk * 8)
+                     : "memory");
+    }
+  };
+  if (ti < ntiles) issue(ti, 0);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+
+  for (int it = 0; ti < ntiles; ti += stride, ++it) {
+    if (ti + stride < ntiles) issue(ti + stride, (it + 1) & 1);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncwarp();
+    const int64_t v0 = ti * QM_ROWS;
+
+    // ---- 16-point stage on the tensor cores ----
+    float acc[8][2][4];
+    {
+      const uint32_t abase = qm_smem(&tile[warp][it & 1][0]) + ((lane & 7) + 8 * ((lane >> 3) & 1)) * QM_ROWB + 16 * (lane >> 4);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        uint32_t a[4];
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
+                     : "r"(abase + 32 * i));
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          acc[i][nt][0] = acc[i][nt][1] = acc[i][nt][2] = acc[i][nt][3] = 0.f;
+          QmIn<Tin>::mma(acc[i][nt], a, bfr[i][nt][0], bfr[i][nt][1]);
+        }
+      }
+    }
+    // ---- 8-point stage over i, in registers ----
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int h = 1; h < 8; h <<= 1)
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if ((i & h) == 0) {
+              const float a = acc[i][nt][r], b = acc[i + h][nt][r];
+              acc[i][nt][r] = a + b;
+              acc[i + h][nt][r] = a - b;
+            }
+
+    // ---- the lane's two vectors: rows g (registers 0,1) and g + 8 (registers 2,3) ----
+#pragma unroll
+    for (int vs = 0; vs < 2; ++vs) {
+      const int64_t v = v0 + g + 8 * vs;
+      const bool ok = v < n;
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int c = 0; c < 2; ++c) ss = fmaf(acc[i][nt][2 * vs + c], acc[i][nt][2 * vs + c], ss);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+      const float nrm = sqrtf(ss) * TQ_RSQRT_D;          // ||H x|| = sqrt(d) ||x||
+      const float safe = nrm > 0.f ? nrm : 1.0f;          // turboquant/polar_quant.py:74
+      const float ts = safe * TQ_SQRT_D;                  // the values are y * ||x|| * sqrt(d), y the rotated unit vector
+      float thr[NT > 0 ? NT : 1];
+#pragma unroll
+      for (int j = 0; j < NT; ++j) thr[j] = bnd[j] * ts;
+
+      float cc = 0.f;
+      uint32_t w[4];
+#pragma unroll
+      for (int tp = 0; tp < 4; ++tp) {
+        float wf[2] = {0.f, 0.f};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float u = acc[2 * tp + (k >> 2)][(k >> 1) & 1][2 * vs + (k & 1)];
+          const float a = fabsf(u);
+          float m5 = 0.5f;                                 // magnitude level + 1/2
+#pragma unroll
+          for (int j = 0; j < NT; ++j) {
+            const float p = qm_gt(a, thr[j]);
+            m5 += p;
+            if (NORMC) cc = fmaf(p, dsq[j], cc);
+          }
+          // index = HALF - 1/2 + sign * m5; a value of exactly zero is not above the centre boundary
+          const float ub = u - 1e-30f;
+          const float digit = __int_as_float(__float_as_int(m5) | (__float_as_int(ub) & 0x80000000));
+          constexpr int HG = BITS == 4 ? 4 : 8;            // digits per exact fp32 Horner sum (<= 24 bits)
+          wf[k / HG] = fmaf(wf[k / HG], RADIX, digit);
+        }
+        // + (HALF - 1/2) in every digit turns the signed digits into indices; the sums are whole numbers < 2^24
+        if constexpr (BITS == 4) {
+          constexpr float OFF = 7.5f * 4369.0f;            // 4369 = (16^4 - 1) / 15
+          w[tp] = (__float2uint_rn(wf[0] + OFF) << 16) | __float2uint_rn(wf[1] + OFF);
+        } else {
+          constexpr float OFF = ((float)HALF - 0.5f) * (float)(((1u << (8 * BITS)) - 1) / (NC - 1));
+          w[tp] = __float2uint_rn(wf[0] + OFF);
+        }
+        if (nrm > 0.f) w[tp] ^= flip[tp];                  // a zero vector keeps the index of the value 0
+      }
+      float invn = 1.0f;
+      if (NORMC) {
+        cc += __shfl_xor_sync(0xffffffffu, cc, 1);
+        cc += __shfl_xor_sync(0xffffffffu, cc, 2);
+        float cn = sqrtf(fmaf((float)TQ_D, c0sq, cc));
+        cn = cn > 1e-10f ? cn : 1.0f;                      // turboquant/polar_quant.py:110-111
+        invn = 1.0f / cn;
+      }
+      // ---- 4 x 4 transpose inside the quad: afterwards w[s] is the word lane s packed for this lane ----
+      {
+        const bool b0 = t & 1, b1 = t & 2;
+#pragma unroll
+        for (int jb = 0; jb < 4; jb += 2) {
+          const uint32_t send = b0 ? w[jb] : w[jb + 1];
+          const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 1);
+          if (b0) w[jb] = recv; else w[jb + 1] = recv;
+        }
+#pragma unroll
+        for (int jb = 0; jb < 2; ++jb) {
+          const uint32_t send = b1 ? w[jb] : w[jb + 2];
+          const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 2);
+          if (b1) w[jb] = recv; else w[jb + 2] = recv;
+        }
+      }
+      // w[s] = [P(2t,0,s) P(2t,1,s) P(2t+1,0,s) P(2t+1,1,s)], P(i,nt,s) the pair of elements 16 i + 8 nt + 2 s, + 1.
+      // Stream order inside this lane's 32 elements: for q = (i & 1, nt): P(., ., 0) P(., ., 1) P(., ., 2) P(., ., 3).
+      constexpr int FW = 2 * BITS;
+      constexpr uint32_t FM = (1u << FW) - 1;
+      uint32_t o[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t r = 0;
+#pragma unroll
+        for (int s = 0; s < 4; ++s) r |= ((w[s] >> (FW * (3 - q))) & FM) << (FW * (3 - s));
+        o[q] = r;
+      }
+      if (ok && dst.idx) {
+        bool good = true;
+        uint8_t* p = tq_dst_ptr(dst.idx, dst, v, IDXB, good);
+        if (good) {
+          p += 4 * BITS * t;
+          if (BITS == 3) {
+            uint32_t* p32 = reinterpret_cast<uint32_t*>(p);
+            p32[0] = __byte_perm((o[0] << 8) | (o[1] >> 16), 0, 0x0123);
+            p32[1] = __byte_perm((o[1] << 16) | (o[2] >> 8), 0, 0x0123);
+            p32[2] = __byte_perm((o[2] << 24) | o[3], 0, 0x0123);
+          } else if (BITS == 2) {
+            *reinterpret_cast<uint2*>(p) =
+                make_uint2(__byte_perm((o[0] << 16) | o[1], 0, 0x0123), __byte_perm((o[2] << 16) | o[3], 0, 0x0123));
+          } else if (BITS == 4) {
+            *reinterpret_cast<uint4*>(p) = make_uint4(__byte_perm(o[0], 0, 0x0123), __byte_perm(o[1], 0, 0x0123),
+                                                      __byte_perm(o[2], 0, 0x0123), __byte_perm(o[3], 0, 0x0123));
+          } else {  // 1 bit: 4 bytes per lane
+            *reinterpret_cast<uint32_t*>(p) = __byte_perm((o[0] << 24) | (o[1] << 16) | (o[2] << 8) | o[3], 0, 0x0123);
+          }
+        }
+      }
+      if (ok && t == 0) {
+        if (dst.norm) dst.norm[v] = nrm;
+        if (dst.scale) {
+          bool good = true;
+          float* p = reinterpret_cast<float*>(tq_dst_ptr(reinterpret_cast<uint8_t*>(dst.scale), dst, v, 4, good));
+          if (good) *p = nrm * invn;
+        }
+      }
+    }
+    __syncwarp();  // every lane is done with this buffer before the copies of the tile after next land in it
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+template <typename Tin, int BITS>
+int launch_mma(const TqFast& f, const Tin* x, int64_t ld, int64_t n, const TqQuantDst& dst, cudaStream_t st) {
+  const int64_t tiles = (n + QM_ROWS - 1) / QM_ROWS;
+  const int64_t ctas = (tiles + QM_WARPS - 1) / QM_WARPS;
+  const int64_t cap = (int64_t)tq_num_sms() * 4;
+  const int grid = (int)(ctas < cap ? ctas : cap);
+  if (f.norm_correction && dst.scale)
+    k_quantize_mma<Tin, BITS, true><<<grid, QM_THREADS, 0, st>>>(f, x, ld, n, dst);
+  else
+    k_quantize_mma<Tin, BITS, false><<<grid, QM_THREADS, 0, st>>>(f, x, ld, n, dst);
+  return tq_launch_check("k_quantize_mma");
+}
+
+}  // namespace
+
+// Returns true when this kernel serves the request (rc then holds the launch status).
+bool tq_quantize_mma_try(const TqFast& f, const void* x, int32_t dtype, int64_t ld, int64_t n, const TqQuantDst& dst,
+                         bool want_qjl, cudaStream_t st, int* rc) {
+  if (want_qjl || !f.symmetric || !dst.idx || dst.idx_u8 || dst.qjl || dst.rnorm) return false;
+  if (dtype != TQ_F16 && dtype != TQ_BF16) return false;
+  if (f.bits < 2 || f.bits > 4 || ld % 8 != 0) return false;
+#define TQ_CASE(B)                                                                                           \
+  case B:                                                                                                    \
+    *rc = dtype == TQ_F16 ? launch_mma<__half, B>(f, (const __half*)x, ld, n, dst, st)                       \
+                          : launch_mma<__nv_bfloat16, B>(f, (const __nv_bfloat16*)x, ld, n, dst, st);        \
+    return true;
+  switch (f.bits) {
+    TQ_CASE(2)
+    TQ_CASE(3)
+    TQ_CASE(4)
+  }
+#undef TQ_CASE
+  return false;
+}
