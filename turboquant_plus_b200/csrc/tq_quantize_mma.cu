@@ -30,18 +30,19 @@ constexpr int QM_ROWB = 272;  // 256 data bytes + 16 bytes of padding
 template <typename T> struct QmIn;
 template <> struct QmIn<__half> {
   static constexpr uint32_t ONE = 0x3C00u, MINUS = 0xBC00u;
+  // c = a . b (zero accumulator)
   static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
   }
 };
 template <> struct QmIn<__nv_bfloat16> {
   static constexpr uint32_t ONE = 0x3F80u, MINUS = 0xBF80u;
   static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
   }
 };
 
@@ -63,7 +64,9 @@ __global__ void __launch_bounds__(QM_THREADS, 4) k_quantize_mma(const TqFast f, 
   __shared__ __align__(16) uint8_t tile[QM_WARPS][2][QM_ROWS * QM_ROWB];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
 
-  // B operands: rows k = 2t, 2t+1 (register 0) and 2t+8, 2t+9 (register 1) of sign1 * H16, column 8 nt + g
+  // B operands: rows k = 2t, 2t+1 (register 0) and 2t+8, 2t+9 (register 1) of sign1 * H16.  The 16 output columns
+  // are dealt to the two n-tiles so that the accumulator columns of lane t (2t, 2t+1 of each tile) are the four
+  // consecutive outputs j = 4t .. 4t+3.
   uint32_t bfr[8][2][2];
 #pragma unroll
   for (int i = 0; i < 8; ++i)
@@ -71,7 +74,7 @@ __global__ void __launch_bounds__(QM_THREADS, 4) k_quantize_mma(const TqFast f, 
     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        const int col = 8 * nt + g;
+        const int col = 4 * (g >> 1) + 2 * nt + (g & 1);  // this lane's B column g of tile nt is output j = col
         uint32_t r = 0;
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
@@ -82,14 +85,14 @@ __global__ void __launch_bounds__(QM_THREADS, 4) k_quantize_mma(const TqFast f, 
         bfr[i][nt][h] = r;
       }
   // sign2 mirrors an index (i -> 2^b - 1 - i): an XOR of the packed word.  Word tp of this lane packs, most
-  // significant first, the elements 16 (2 tp + (k >> 2)) + 8 ((k >> 1) & 1) + 2 t + (k & 1), k = 0..7.
+  // significant first, the elements 16 (2 tp + (k >> 2)) + 4 t + (k & 3), k = 0..7.
   uint32_t flip[4];
 #pragma unroll
   for (int tp = 0; tp < 4; ++tp) {
     uint32_t m = 0;
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
-      const int e = 16 * (2 * tp + (k >> 2)) + 8 * ((k >> 1) & 1) + 2 * t + (k & 1);
+      const int e = 16 * (2 * tp + (k >> 2)) + 4 * t + (k & 3);
       if (qm_bit(f.s2, e)) m |= (uint32_t)(NC - 1) << (BITS * (7 - k));
     }
     flip[tp] = m;
@@ -138,10 +141,7 @@ __global__ void __launch_bounds__(QM_THREADS, 4) k_quantize_mma(const TqFast f, 
                      : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
                      : "r"(abase + 32 * i));
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-          acc[i][nt][0] = acc[i][nt][1] = acc[i][nt][2] = acc[i][nt][3] = 0.f;
-          QmIn<Tin>::mma(acc[i][nt], a, bfr[i][nt][0], bfr[i][nt][1]);
-        }
+        for (int nt = 0; nt < 2; ++nt) QmIn<Tin>::mma(acc[i][nt], a, bfr[i][nt][0], bfr[i][nt][1]);
       }
     }
     // ---- 8-point stage over i, in registers ----
@@ -155,8 +155,17 @@ __global__ void __launch_bounds__(QM_THREADS, 4) k_quantize_mma(const TqFast f, 
           for (int i = 0; i < 8; ++i)
             if ((i & h) == 0) {
               const float a = acc[i][nt][r], b = acc[i + h][nt][r];
-              acc[i][nt][r] = a + b;
-              acc[i + h][nt][r] = a - b;
+              if (h < 4) {
+                acc[i][nt][r] = a + b;
+                acc[i + h][nt][r] = a - b;
+              } else {
+                // The last stage produces the NEGATED transform: "sign bit clear" then means value <= 0 for every
+                // nonzero value and for zeros that arise by cancellation (x - x = +0), which is how the reference
+                // decides the centre boundary (not above it -> lower index).  A zero formed from two zero inputs
+                // can come out as -0 and take the upper of the two central indices; it sits exactly on the boundary.
+                acc[i][nt][r] = (-a) - b;
+                acc[i + h][nt][r] = b - a;
+              }
             }
 
     // ---- the lane's two vectors: rows g (registers 0,1) and g + 8 (registers 2,3) ----
@@ -187,18 +196,17 @@ __global__ void __launch_bounds__(QM_THREADS, 4) k_quantize_mma(const TqFast f, 
         float wf[2] = {0.f, 0.f};
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const float u = acc[2 * tp + (k >> 2)][(k >> 1) & 1][2 * vs + (k & 1)];
-          const float a = fabsf(u);
+          const float nu = acc[2 * tp + (k >> 2)][(k >> 1) & 1][2 * vs + (k & 1)];  // minus the transformed value
+          const float a = fabsf(nu);
           float m5 = 0.5f;                                 // magnitude level + 1/2
 #pragma unroll
           for (int j = 0; j < NT; ++j) {
             const float p = qm_gt(a, thr[j]);
             m5 += p;
-            if (NORMC) cc = fmaf(p, dsq[j], cc);
+            if (NORMC && BITS == 4) cc = fmaf(p, dsq[j], cc);
           }
-          // index = HALF - 1/2 + sign * m5; a value of exactly zero is not above the centre boundary
-          const float ub = u - 1e-30f;
-          const float digit = __int_as_float(__float_as_int(m5) | (__float_as_int(ub) & 0x80000000));
+          // index = HALF - 1/2 + sign * m5, sign = -1 where the value is <= 0, i.e. where nu's sign bit is clear
+          const float digit = __int_as_float(__float_as_int(m5) | (~__float_as_int(nu) & 0x80000000));
           constexpr int HG = BITS == 4 ? 4 : 8;            // digits per exact fp32 Horner sum (<= 24 bits)
           wf[k / HG] = fmaf(wf[k / HG], RADIX, digit);
         }
@@ -210,9 +218,32 @@ __global__ void __launch_bounds__(QM_THREADS, 4) k_quantize_mma(const TqFast f, 
           constexpr float OFF = ((float)HALF - 0.5f) * (float)(((1u << (8 * BITS)) - 1) / (NC - 1));
           w[tp] = __float2uint_rn(wf[0] + OFF);
         }
-        if (nrm > 0.f) w[tp] ^= flip[tp];                  // a zero vector keeps the index of the value 0
+        // a zero vector takes the index of the value 0 in every coordinate (no mirroring either)
+        constexpr uint32_t ZERO_WORD = (uint32_t)(((1ull << (8 * BITS)) - 1) / (NC - 1)) * (HALF - 1);
+        w[tp] = nrm > 0.f ? (w[tp] ^ flip[tp]) : ZERO_WORD;
       }
       float invn = 1.0f;
+      if (NORMC && BITS != 4) {
+        // ||c[idx]||^2 from a histogram of magnitude levels: field = [s | low], level m = s ? low : ~low, and
+        // n_j = #{m >= j} is a population count over the packed words (mirroring an index keeps its level)
+        constexpr uint32_t M0 = (uint32_t)(((1ull << (8 * BITS)) - 1) / (NC - 1));  // bit 0 of every field
+        uint32_t n1 = 0, n2 = 0, n3 = 0;
+#pragma unroll
+        for (int tp = 0; tp < 4; ++tp) {
+          const uint32_t sneg = ~(w[tp] >> (BITS - 1)) & M0;               // fields with s = 0
+          const uint32_t xw = w[tp] ^ (sneg * (uint32_t)(HALF - 1));        // low bits complemented there
+          if (BITS == 3) {
+            const uint32_t b0 = xw & M0, b1 = (xw >> 1) & M0;
+            n1 += __popc(b0 | b1);
+            n2 += __popc(b1);
+            n3 += __popc(b0 & b1);
+          } else {
+            n1 += __popc(xw & M0);
+          }
+        }
+        cc = (float)n1 * dsq[0];
+        if (BITS == 3) cc = fmaf((float)n2, dsq[1], fmaf((float)n3, dsq[2], cc));
+      }
       if (NORMC) {
         cc += __shfl_xor_sync(0xffffffffu, cc, 1);
         cc += __shfl_xor_sync(0xffffffffu, cc, 2);
@@ -236,36 +267,29 @@ __global__ void __launch_bounds__(QM_THREADS, 4) k_quantize_mma(const TqFast f, 
           if (b1) w[jb] = recv; else w[jb + 2] = recv;
         }
       }
-      // w[s] = [P(2t,0,s) P(2t,1,s) P(2t+1,0,s) P(2t+1,1,s)], P(i,nt,s) the pair of elements 16 i + 8 nt + 2 s, + 1.
-      // Stream order inside this lane's 32 elements: for q = (i & 1, nt): P(., ., 0) P(., ., 1) P(., ., 2) P(., ., 3).
-      constexpr int FW = 2 * BITS;
-      constexpr uint32_t FM = (1u << FW) - 1;
-      uint32_t o[4];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint32_t r = 0;
-#pragma unroll
-        for (int s = 0; s < 4; ++s) r |= ((w[s] >> (FW * (3 - q))) & FM) << (FW * (3 - s));
-        o[q] = r;
-      }
+      // w[s] = [run(2t, s) | run(2t+1, s)], run(i, s) = the indices of elements 16 i + 4 s .. + 3 (4 BITS bits).
+      // This lane's 32 consecutive elements are run(2t,0..3) run(2t+1,0..3): 32 BITS bits, most significant first.
+      constexpr int RW = 4 * BITS;
       if (ok && dst.idx) {
         bool good = true;
         uint8_t* p = tq_dst_ptr(dst.idx, dst, v, IDXB, good);
         if (good) {
           p += 4 * BITS * t;
           if (BITS == 3) {
+            const uint32_t h0 = w[0] >> RW, h1 = w[1] >> RW, h2 = w[2] >> RW, h3 = w[3] >> RW;
+            const uint32_t l0 = w[0] & 0xfffu, l1 = w[1] & 0xfffu, l2 = w[2] & 0xfffu, l3 = w[3] & 0xfffu;
             uint32_t* p32 = reinterpret_cast<uint32_t*>(p);
-            p32[0] = __byte_perm((o[0] << 8) | (o[1] >> 16), 0, 0x0123);
-            p32[1] = __byte_perm((o[1] << 16) | (o[2] >> 8), 0, 0x0123);
-            p32[2] = __byte_perm((o[2] << 24) | o[3], 0, 0x0123);
+            p32[0] = __byte_perm((h0 << 20) | (h1 << 8) | (h2 >> 4), 0, 0x0123);
+            p32[1] = __byte_perm((h2 << 28) | (h3 << 16) | (l0 << 4) | (l1 >> 8), 0, 0x0123);
+            p32[2] = __byte_perm((l1 << 24) | (l2 << 12) | l3, 0, 0x0123);
           } else if (BITS == 2) {
-            *reinterpret_cast<uint2*>(p) =
-                make_uint2(__byte_perm((o[0] << 16) | o[1], 0, 0x0123), __byte_perm((o[2] << 16) | o[3], 0, 0x0123));
-          } else if (BITS == 4) {
-            *reinterpret_cast<uint4*>(p) = make_uint4(__byte_perm(o[0], 0, 0x0123), __byte_perm(o[1], 0, 0x0123),
-                                                      __byte_perm(o[2], 0, 0x0123), __byte_perm(o[3], 0, 0x0123));
-          } else {  // 1 bit: 4 bytes per lane
-            *reinterpret_cast<uint32_t*>(p) = __byte_perm((o[0] << 24) | (o[1] << 16) | (o[2] << 8) | o[3], 0, 0x0123);
+            // 8-bit runs: bytes h0 h1 h2 h3 l0 l1 l2 l3 in memory order
+            const uint32_t a01 = __byte_perm(w[0], w[1], 0x4051), a23 = __byte_perm(w[2], w[3], 0x4051);  // bytes h h l l
+            *reinterpret_cast<uint2*>(p) = make_uint2(__byte_perm(a01, a23, 0x5410), __byte_perm(a01, a23, 0x7632));
+          } else {
+            // 16-bit runs: big-endian halves h0 h1 h2 h3 l0 l1 l2 l3
+            *reinterpret_cast<uint4*>(p) = make_uint4(__byte_perm(w[0], w[1], 0x6723), __byte_perm(w[2], w[3], 0x6723),
+                                                      __byte_perm(w[0], w[1], 0x4501), __byte_perm(w[2], w[3], 0x4501));
           }
         }
       }
@@ -303,7 +327,7 @@ bool tq_quantize_mma_try(const TqFast& f, const void* x, int32_t dtype, int64_t 
                          bool want_qjl, cudaStream_t st, int* rc) {
   if (want_qjl || !f.symmetric || !dst.idx || dst.idx_u8 || dst.qjl || dst.rnorm) return false;
   if (dtype != TQ_F16 && dtype != TQ_BF16) return false;
-  if (f.bits < 2 || f.bits > 4 || ld % 8 != 0) return false;
+  if (f.bits < 2 || f.bits > 4 || ld % 8 != 0) return false;  // (1-bit codebooks have no magnitude levels to test)
 #define TQ_CASE(B)                                                                                           \
   case B:                                                                                                    \
     *rc = dtype == TQ_F16 ? launch_mma<__half, B>(f, (const __half*)x, ld, n, dst, st)                       \
