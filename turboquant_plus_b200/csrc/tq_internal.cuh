@@ -170,9 +170,22 @@ struct TqQuantDst {
 
 // address of vector v's record field (elem_bytes per token and head) in plain arrays or in a paged cache;
 // ok = false when the token's slot is negative (skip it)
+// The part of that address that every field of the record shares: byte offset of (page, head) and the token's
+// position inside the page; field address = base + offset + within * elem_bytes.
+__device__ __forceinline__ int64_t tq_dst_record(const TqQuantDst& dst, int64_t v, int64_t& within, bool& ok);
+
 __device__ __forceinline__ uint8_t* tq_dst_ptr(uint8_t* base, const TqQuantDst& dst, int64_t v, int32_t elem_bytes,
                                                bool& ok) {
-  if (dst.page_tokens == 0) return base + v * elem_bytes;
+  int64_t within;
+  const int64_t off = tq_dst_record(dst, v, within, ok);
+  return base + off + within * elem_bytes;
+}
+
+__device__ __forceinline__ int64_t tq_dst_record(const TqQuantDst& dst, int64_t v, int64_t& within64, bool& ok) {
+  if (dst.page_tokens == 0) {
+    within64 = v;
+    return 0;
+  }
   // 32-bit arithmetic whenever the numbers allow it (64-bit division costs ~100 instructions)
   int64_t tok;
   int32_t head;
@@ -192,7 +205,8 @@ __device__ __forceinline__ uint8_t* tq_dst_ptr(uint8_t* base, const TqQuantDst& 
   const int64_t slot = dst.slots ? dst.slots[tok] : tok;
   if (slot < 0) {
     ok = false;
-    return base;
+    within64 = 0;
+    return 0;
   }
   int64_t page;
   int32_t within;
@@ -208,7 +222,8 @@ __device__ __forceinline__ uint8_t* tq_dst_ptr(uint8_t* base, const TqQuantDst& 
     page = slot / dst.page_tokens;
     within = (int32_t)(slot - page * dst.page_tokens);
   }
-  return base + page * dst.page_stride + head * dst.head_stride + (int64_t)within * elem_bytes;
+  within64 = within;
+  return page * dst.page_stride + head * dst.head_stride;
 }
 
 int tq_quantize_wht_launch(const TqFast& f, const void* x, int32_t dtype, int64_t ld, int64_t n,

@@ -188,6 +188,7 @@ __global__ void __launch_bounds__(QM_THREADS, 4) k_quantize_mma(const TqFast f, 
       float thr[NT > 0 ? NT : 1];
 #pragma unroll
       for (int j = 0; j < NT; ++j) thr[j] = bnd[j] * ts;
+      const float d31 = BITS == 3 ? thr[2] - thr[0] : 0.f;
 
       float cc = 0.f;
       uint32_t w[4];
@@ -198,12 +199,21 @@ __global__ void __launch_bounds__(QM_THREADS, 4) k_quantize_mma(const TqFast f, 
         for (int k = 0; k < 8; ++k) {
           const float nu = acc[2 * tp + (k >> 2)][(k >> 1) & 1][2 * vs + (k & 1)];  // minus the transformed value
           const float a = fabsf(nu);
-          float m5 = 0.5f;                                 // magnitude level + 1/2
+          float m5;                                        // magnitude level + 1/2
+          if constexpr (BITS == 3) {
+            // two tests instead of three: against the middle boundary, then against the lower or the upper one
+            // (picked arithmetically; the upper one is thr[0] + d31, within an ulp of thr[2])
+            const float p2 = qm_gt(a, thr[1]);
+            const float p1 = qm_gt(a, fmaf(p2, d31, thr[0]));
+            m5 = fmaf(p2, 2.0f, p1 + 0.5f);
+          } else {
+            m5 = 0.5f;
 #pragma unroll
-          for (int j = 0; j < NT; ++j) {
-            const float p = qm_gt(a, thr[j]);
-            m5 += p;
-            if (NORMC && BITS == 4) cc = fmaf(p, dsq[j], cc);
+            for (int j = 0; j < NT; ++j) {
+              const float p = qm_gt(a, thr[j]);
+              m5 += p;
+              if (NORMC && BITS == 4) cc = fmaf(p, dsq[j], cc);
+            }
           }
           // index = HALF - 1/2 + sign * m5, sign = -1 where the value is <= 0, i.e. where nu's sign bit is clear
           const float digit = __int_as_float(__float_as_int(m5) | (~__float_as_int(nu) & 0x80000000));
@@ -270,11 +280,12 @@ __global__ void __launch_bounds__(QM_THREADS, 4) k_quantize_mma(const TqFast f, 
       // w[s] = [run(2t, s) | run(2t+1, s)], run(i, s) = the indices of elements 16 i + 4 s .. + 3 (4 BITS bits).
       // This lane's 32 consecutive elements are run(2t,0..3) run(2t+1,0..3): 32 BITS bits, most significant first.
       constexpr int RW = 4 * BITS;
-      if (ok && dst.idx) {
-        bool good = true;
-        uint8_t* p = tq_dst_ptr(dst.idx, dst, v, IDXB, good);
-        if (good) {
-          p += 4 * BITS * t;
+      bool good = ok;
+      int64_t within = 0;
+      const int64_t rec_off = ok ? tq_dst_record(dst, v, within, good) : 0;
+      if (good && dst.idx) {
+        {
+          uint8_t* p = dst.idx + rec_off + within * IDXB + 4 * BITS * t;
           if (BITS == 3) {
             const uint32_t h0 = w[0] >> RW, h1 = w[1] >> RW, h2 = w[2] >> RW, h3 = w[3] >> RW;
             const uint32_t l0 = w[0] & 0xfffu, l1 = w[1] & 0xfffu, l2 = w[2] & 0xfffu, l3 = w[3] & 0xfffu;
@@ -295,11 +306,7 @@ __global__ void __launch_bounds__(QM_THREADS, 4) k_quantize_mma(const TqFast f, 
       }
       if (ok && t == 0) {
         if (dst.norm) dst.norm[v] = nrm;
-        if (dst.scale) {
-          bool good = true;
-          float* p = reinterpret_cast<float*>(tq_dst_ptr(reinterpret_cast<uint8_t*>(dst.scale), dst, v, 4, good));
-          if (good) *p = nrm * invn;
-        }
+        if (dst.scale && good) *reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(dst.scale) + rec_off + within * 4) = nrm * invn;
       }
     }
     __syncwarp();  // every lane is done with this buffer before the copies of the tile after next land in it
