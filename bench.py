@@ -490,18 +490,111 @@ def run_other_workload(args):
         dist.destroy_process_group()
 
 
+def run_config3(args):
+    """config3: Llama-3-70B shape, one layer: 131,072 tokens of fp16 K/V (8 KV heads, sharded over the ranks) are
+    quantize-on-appended as turbo3 into 128-token pages in 8,192-token chunks, then one 128-query chunk x 64 query
+    heads runs chunked-prefill attention (tcgen05) over the whole prefix.  Prints append vectors/s (HBM roofline)
+    and prefill TFLOP/s (tensor roofline)."""
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    import turboquant_plus_b200 as tq
+    n, hq_all, hkv_all, chunk, tq_len = 131072, 64, 8, 8192, 128
+    hkv, hq = hkv_all // world, hq_all // world
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(7 + rank)
+    cache = tq.PagedKVCache(D, hkv, n // PT, PT, "turbo3", "turbo3", seed=42, device=dev)
+    k = torch.randn((n, hkv, D), generator=gen, device=dev).half()
+    v = torch.randn((n, hkv, D), generator=gen, device=dev).half()
+    slots = torch.arange(n, device=dev)
+
+    def append_all():
+        for lo in range(0, n, chunk):
+            cache.append(k[lo:lo + chunk], v[lo:lo + chunk], slots[lo:lo + chunk])
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    append_all()
+    torch.cuda.synchronize(dev)
+    graph = torch.cuda.CUDAGraph()      # the 32 launches of one pass, replayed without host overhead
+    with torch.cuda.graph(graph):
+        append_all()
+    for _ in range(max(args.warmup, 3)):
+        graph.replay()
+    sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    sync()
+    append_ms = e0.elapsed_time(e1) / args.steps
+    bt = torch.arange(n // PT, device=dev, dtype=torch.int32)[None]
+    kv_len = torch.tensor([n], dtype=torch.int32, device=dev)
+    q = torch.randn((1, tq_len, hq, D), generator=gen, device=dev).half()
+    out = torch.empty_like(q)
+    for _ in range(3):
+        cache.prefill_attend(q, bt, kv_len, out=out)
+    sync()
+    e0.record()
+    for _ in range(args.steps):
+        cache.prefill_attend(q, bt, kv_len, out=out)
+    e1.record()
+    sync()
+    prefill_ms = e0.elapsed_time(e1) / args.steps
+    assert cache.kernel_status() == 0 and torch.isfinite(out.float()).all()
+    if world > 1:
+        t = torch.tensor([append_ms, prefill_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        append_ms, prefill_ms = float(t[0]), float(t[1])
+    if rank == 0:
+        vectors = 2.0 * n * hkv_all
+        visible = sum(n - tq_len + i + 1 for i in range(tq_len))
+        flops = 2.0 * 2 * hq_all * D * visible
+        hbm, src = peaks()
+        tpeak, tsrc = tensor_peak()
+        print(json.dumps({
+            "metric": "quantize_append_vectors_per_s", "value": vectors / (append_ms * 1e-3), "unit": "vectors/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": append_ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16 in, exact +-1 tensor-core products, f32 accumulate", "data": "synthetic",
+            "config": {"workload": "config3: one layer, 64q/8kv heads, d128, 131072 tokens appended as turbo3 K+V in "
+                                   "8192-token chunks, then a 128-query chunk of prefill attention over the prefix",
+                       "parallelism": f"KV heads sharded x{world}", "l2": "inputs larger than L2"},
+            "roofline": {"bound": "hbm", "achieved": vectors * 308 / (append_ms * 1e-3) / 1e9 / world, "peak": hbm,
+                         "unit": "GB/s", "frac": vectors * 308 / (append_ms * 1e-3) / 1e9 / world / hbm,
+                         "peak_source": src, "kernel": "k_quantize_mma<half,3>", "bytes_per_vector": 308},
+            "prefill": {"ms": prefill_ms, "tflops": flops / (prefill_ms * 1e-3) / 1e12,
+                        "frac_of_tensor_peak": flops / (prefill_ms * 1e-3) / 1e12 / world / tpeak, "peak": tpeak,
+                        "peak_source": tsrc, "kernel": "k_prefill_attn<3,3> (tcgen05)"},
+            "gpu_launches": 2 * (n // chunk)}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="config1", choices=["config1", "config2", "config4"],
+    ap.add_argument("--workload", default="config1", choices=["config1", "config2", "config3", "config4"],
                     help="config1 is the headline workload; the others print a line of the same shape")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "config3":
+        run_config3(args)
     elif args.workload != "config1":
         run_other_workload(args)
     else:
