@@ -118,3 +118,45 @@ class KVCacheCompressor:
         return PagedKVCache(self.head_dim, num_kv_heads, num_pages, page_tokens, k_format, v_format, seed=self.seed,
                             norm_correction=self.norm_correction, rotation=self.rotation_kind, device=self.device,
                             k_quantizer=kq, v_quantizer=vq)
+
+    # ---- streaming interface (additive; the reference only has the bulk compress / decompress above) ----
+    def init_cache(self, num_layers: int, num_kv_heads: int, num_pages: int, page_tokens: int = 128, formats=None):
+        """Allocate paged caches for `num_layers` layers that share this compressor's quantizers.  `formats` is one
+        (k_format, v_format) pair or a per-layer list; default K "prod<k_bits>", V "turbo<v_bits>"."""
+        default = (f"prod{self.k_bits}", f"turbo{self.v_bits}")
+        if formats is None:
+            formats = [default] * num_layers
+        elif isinstance(formats[0], str):
+            formats = [tuple(formats)] * num_layers
+        assert len(formats) == num_layers
+        self._layers, shared = [], {}
+        for kf, vf in formats:
+            if (kf, vf) not in shared:
+                shared[(kf, vf)] = self.paged(num_kv_heads, num_pages, page_tokens, kf, vf)
+                self._layers.append(shared[(kf, vf)])
+            else:
+                from .paged import PagedKVCache
+                donor = shared[(kf, vf)]
+                self._layers.append(PagedKVCache(self.head_dim, num_kv_heads, num_pages, page_tokens, kf, vf,
+                                                 seed=self.seed, norm_correction=self.norm_correction,
+                                                 rotation=self.rotation_kind, device=self.device,
+                                                 k_quantizer=donor.k_quantizer, v_quantizer=donor.v_quantizer))
+        return self
+
+    def _layer(self, layer: int):
+        assert getattr(self, "_layers", None), "call init_cache() first"
+        return self._layers[layer]
+
+    def append(self, k, v, layer: int, slot_mapping):
+        """Quantize-on-append: k, v (tokens, num_kv_heads, head_dim) CUDA tensors into the slots
+        page * page_tokens + position of `slot_mapping` (negative slots are skipped)."""
+        self._layer(layer).append(k, v, slot_mapping)
+
+    def attend(self, q, layer: int, seq_lens, block_table, scale=None, **kw):
+        """Decode attention of q (batch, num_q_heads, head_dim) over layer `layer`'s packed cache."""
+        return self._layer(layer).attend(q, block_table, seq_lens, scale=scale, **kw)
+
+    def prefill_attend(self, q_chunk, layer: int, kv_lens, block_table, scale=None, **kw):
+        """Causal attention of a chunk of new queries (batch, chunk_tokens, num_q_heads, head_dim) whose K/V rows
+        have already been appended."""
+        return self._layer(layer).prefill_attend(q_chunk, block_table, kv_lens, scale=scale, **kw)
