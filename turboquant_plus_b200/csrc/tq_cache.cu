@@ -11,6 +11,26 @@ extern "C" int tq_cache_append(const tq_quantizer* kq, const tq_quantizer* vq, c
   TQ_REQUIRE(tq_aligned(pool_dev, 128), TQ_ERR_ALIGN, "cache pool must be 128-byte aligned");
   cudaStream_t st = (cudaStream_t)stream;
   const int H = L->num_kv_heads;
+  // PolarQuant K and V from 16-bit rows: both tensors in one launch while launches are short enough for their fixed
+  // cost to matter (measured: 6.0 vs 5.7 G vectors/s at 65,536 vectors per tensor, 7.6 vs 8.1 at 1,048,576)
+  if (n_tokens * H <= 131072 && kq && vq && L->k_format >= TQ_FMT_TURBO2 && L->k_format <= TQ_FMT_TURBO4 && L->v_format == L->k_format &&
+      kq->rotation == TQ_ROT_WHT && vq->rotation == TQ_ROT_WHT && kq->d == TQ_D && vq->d == TQ_D &&
+      kq->bits == L->k_format && vq->bits == L->v_format) {
+    TqQuantDst dk, dv;
+    memset(&dk, 0, sizeof(dk));
+    dk.slots = slot_dev;
+    dk.page_stride = L->page_stride;
+    dk.head_stride = L->head_stride;
+    dk.page_tokens = L->page_tokens;
+    dk.heads = H;
+    dv = dk;
+    dk.idx = pool_dev + L->k_idx_off;
+    dk.scale = reinterpret_cast<float*>(pool_dev + L->k_scale_off);
+    dv.idx = pool_dev + L->v_idx_off;
+    dv.scale = reinterpret_cast<float*>(pool_dev + L->v_scale_off);
+    int rc = TQ_OK;
+    if (tq_quantize_mma_try_pair(kq->fast, k_dev, dk, vq->fast, v_dev, dv, dtype, TQ_D, n_tokens * H, st, &rc)) return rc;
+  }
   for (int which = 0; which < 2; ++which) {
     const int fmt = which == 0 ? L->k_format : L->v_format;
     const tq_quantizer* q = which == 0 ? kq : vq;

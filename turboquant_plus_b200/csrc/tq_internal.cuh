@@ -230,6 +230,8 @@ int tq_quantize_wht_launch(const TqFast& f, const void* x, int32_t dtype, int64_
                            const TqQuantDst& dst, bool want_qjl, cudaStream_t st);
 bool tq_quantize_mma_try(const TqFast& f, const void* x, int32_t dtype, int64_t ld, int64_t n, const TqQuantDst& dst,
                          bool want_qjl, cudaStream_t st, int* rc);
+bool tq_quantize_mma_try_pair(const TqFast& f0, const void* x0, const TqQuantDst& d0, const TqFast& f1, const void* x1,
+                              const TqQuantDst& d1, int32_t dtype, int64_t ld, int64_t n, cudaStream_t st, int* rc);
 int tq_q8_0_append_launch(const void* x, int32_t dtype, int64_t n_tokens, int32_t heads, uint8_t* q_base,
                           uint8_t* scale_base, const int64_t* slots, int32_t page_tokens,
                           int64_t page_stride, int64_t head_stride, cudaStream_t st);

@@ -56,12 +56,11 @@ __device__ __forceinline__ float qm_gt(float a, float b) {
 }
 
 template <typename Tin, int BITS, bool NORMC>
-__global__ void __launch_bounds__(QM_THREADS, 4) k_quantize_mma(const TqFast f, const Tin* __restrict__ x, int64_t ld,
-                                                                int64_t n, const TqQuantDst dst) {
+__device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__ x, int64_t ld, int64_t n,
+                                        const TqQuantDst& dst, uint8_t (&tile)[QM_WARPS][2][QM_ROWS * QM_ROWB]) {
   constexpr int NC = 1 << BITS, HALF = NC / 2, NT = HALF - 1;  // NT positive boundaries
   constexpr int IDXB = 16 * BITS;
   constexpr float RADIX = (float)NC;
-  __shared__ __align__(16) uint8_t tile[QM_WARPS][2][QM_ROWS * QM_ROWB];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
 
   // B operands: rows k = 2t, 2t+1 (register 0) and 2t+8, 2t+9 (register 1) of sign1 * H16.  The 16 output columns
@@ -314,6 +313,27 @@ __global__ void __launch_bounds__(QM_THREADS, 4) k_quantize_mma(const TqFast f, 
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
+template <typename Tin, int BITS, bool NORMC>
+__global__ void __launch_bounds__(QM_THREADS, 4) k_quantize_mma(const TqFast f, const Tin* __restrict__ x, int64_t ld,
+                                                                int64_t n, const TqQuantDst dst) {
+  __shared__ __align__(16) uint8_t tile[QM_WARPS][2][QM_ROWS * QM_ROWB];
+  qm_body<Tin, BITS, NORMC>(f, x, ld, n, dst, tile);
+}
+
+// Two tensors of the same shape in one launch (the K and V rows of a cache append): blockIdx.y picks the job.
+struct QmJob {
+  TqFast f;
+  const void* x;
+  TqQuantDst dst;
+};
+template <typename Tin, int BITS, bool NORMC>
+__global__ void __launch_bounds__(QM_THREADS, 4) k_quantize_mma_pair(const __grid_constant__ QmJob j0,
+                                                                     const __grid_constant__ QmJob j1, int64_t ld, int64_t n) {
+  __shared__ __align__(16) uint8_t tile[QM_WARPS][2][QM_ROWS * QM_ROWB];
+  if (blockIdx.y == 0) qm_body<Tin, BITS, NORMC>(j0.f, reinterpret_cast<const Tin*>(j0.x), ld, n, j0.dst, tile);
+  else qm_body<Tin, BITS, NORMC>(j1.f, reinterpret_cast<const Tin*>(j1.x), ld, n, j1.dst, tile);
+}
+
 template <typename Tin, int BITS>
 int launch_mma(const TqFast& f, const Tin* x, int64_t ld, int64_t n, const TqQuantDst& dst, cudaStream_t st) {
   const int64_t tiles = (n + QM_ROWS - 1) / QM_ROWS;
@@ -327,14 +347,53 @@ int launch_mma(const TqFast& f, const Tin* x, int64_t ld, int64_t n, const TqQua
   return tq_launch_check("k_quantize_mma");
 }
 
+template <typename Tin, int BITS>
+int launch_mma_pair(const QmJob& j0, const QmJob& j1, int64_t ld, int64_t n, bool normc, cudaStream_t st) {
+  const int64_t tiles = (n + QM_ROWS - 1) / QM_ROWS;
+  const int64_t ctas = (tiles + QM_WARPS - 1) / QM_WARPS;
+  const int64_t cap = (int64_t)tq_num_sms() * 2;  // two jobs share the SMs
+  dim3 grid((unsigned)(ctas < cap ? ctas : cap), 2);
+  if (normc) k_quantize_mma_pair<Tin, BITS, true><<<grid, QM_THREADS, 0, st>>>(j0, j1, ld, n);
+  else k_quantize_mma_pair<Tin, BITS, false><<<grid, QM_THREADS, 0, st>>>(j0, j1, ld, n);
+  return tq_launch_check("k_quantize_mma_pair");
+}
+
+bool qm_serves(const TqFast& f, int32_t dtype, int64_t ld, const TqQuantDst& dst, bool want_qjl) {
+  if (want_qjl || !f.symmetric || !dst.idx || dst.idx_u8 || dst.qjl || dst.rnorm) return false;
+  if (dtype != TQ_F16 && dtype != TQ_BF16) return false;
+  return f.bits >= 2 && f.bits <= 4 && ld % 8 == 0;  // (1-bit codebooks have no magnitude levels to test)
+}
+
 }  // namespace
+
+// K and V of one append in a single launch, when both take this kernel with the same template arguments.
+bool tq_quantize_mma_try_pair(const TqFast& f0, const void* x0, const TqQuantDst& d0, const TqFast& f1, const void* x1,
+                              const TqQuantDst& d1, int32_t dtype, int64_t ld, int64_t n, cudaStream_t st, int* rc) {
+  if (!qm_serves(f0, dtype, ld, d0, false) || !qm_serves(f1, dtype, ld, d1, false)) return false;
+  if (f0.bits != f1.bits || (f0.norm_correction && d0.scale) != (f1.norm_correction && d1.scale)) return false;
+  if (!tq_aligned(x0, 16) || !tq_aligned(x1, 16) || n == 0) return false;
+  QmJob j0, j1;
+  j0.f = f0; j0.x = x0; j0.dst = d0;
+  j1.f = f1; j1.x = x1; j1.dst = d1;
+  const bool normc = f0.norm_correction && d0.scale;
+#define TQ_CASE(B)                                                                              \
+  case B:                                                                                       \
+    *rc = dtype == TQ_F16 ? launch_mma_pair<__half, B>(j0, j1, ld, n, normc, st)                \
+                          : launch_mma_pair<__nv_bfloat16, B>(j0, j1, ld, n, normc, st);        \
+    return true;
+  switch (f0.bits) {
+    TQ_CASE(2)
+    TQ_CASE(3)
+    TQ_CASE(4)
+  }
+#undef TQ_CASE
+  return false;
+}
 
 // Returns true when this kernel serves the request (rc then holds the launch status).
 bool tq_quantize_mma_try(const TqFast& f, const void* x, int32_t dtype, int64_t ld, int64_t n, const TqQuantDst& dst,
                          bool want_qjl, cudaStream_t st, int* rc) {
-  if (want_qjl || !f.symmetric || !dst.idx || dst.idx_u8 || dst.qjl || dst.rnorm) return false;
-  if (dtype != TQ_F16 && dtype != TQ_BF16) return false;
-  if (f.bits < 2 || f.bits > 4 || ld % 8 != 0) return false;  // (1-bit codebooks have no magnitude levels to test)
+  if (!qm_serves(f, dtype, ld, dst, want_qjl)) return false;
 #define TQ_CASE(B)                                                                                           \
   case B:                                                                                                    \
     *rc = dtype == TQ_F16 ? launch_mma<__half, B>(f, (const __half*)x, ld, n, dst, st)                       \
