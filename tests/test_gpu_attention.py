@@ -336,3 +336,26 @@ def test_overlap_launch_and_compressor_streaming_api(tq):
     assert comp._layers[1].k_format == "prod3" and max_rel(out, ref) < TOL
     with pytest.raises(Exception):      # prefill over PROD keys is not built: the error must surface
         comp.prefill_attend(torch.zeros((1, 8, hq, D), device="cuda"), 0, torch.tensor([300]), bt)
+
+
+@pytest.mark.gpu
+def test_many_splits_long_context(tq):
+    """One sequence, one KV head, 70,000 tokens: the split plan cuts it into ~270 two-page splits, so the merge by
+    the last split folds more than 64 partials (several rounds) -- and the two groups of a CTA serve different
+    splits of the same head.  Checked against the oracle over the dequantized cache."""
+    import torch
+    rng = np.random.default_rng(33)
+    n, hkv, hq = 70000, 1, 4
+    cache = tq.PagedKVCache(D, hkv, num_pages=(n + 127) // 128, seed=42)
+    ks = [(rng.standard_normal((n, hkv, D)) * np.exp(0.3 * rng.standard_normal((n, hkv, 1)))).astype(np.float16)]
+    vs = [rng.standard_normal((n, hkv, D)).astype(np.float16)]
+    bt = fill_cache(cache, ks, vs, [n], rng)
+    q = rng.standard_normal((1, hq, D)).astype(np.float32)
+    out = cache.attend(torch.as_tensor(q).cuda(), bt, torch.tensor([n])).cpu().numpy()
+    assert cache.kernel_status() == 0
+    ref = oracle_attention(cache, ks, vs, q, [n])
+    err = max_rel(out, ref)
+    print(f"70,000 tokens, 1 KV head: max-rel {err:.2e}")
+    assert err < TOL
+    out2 = cache.attend(torch.as_tensor(q).cuda(), bt, torch.tensor([n]), overlap=True).cpu().numpy()
+    assert np.array_equal(out, out2)
