@@ -539,23 +539,505 @@ __global__ void __launch_bounds__(PF_THREADS, 2) k_prefill_attn(const PrefillPar
   }
 }
 
+
+// ------------------------------------------------------------------------------------------
+// k_prefill_attn2: the same computation with the work split over specialised warps (one CTA per SM, 288 threads):
+//   warps 0-3  rows: thread r owns row r = lane r of tensor memory: reads S, online softmax, writes P, rescales O
+//              (lazily: only when its row maximum grows by more than 2^4), epilogue;
+//   warps 4-7  producer: thread t dequantizes token t of the page (K, then V) into double-buffered operand tiles
+//              and copies the per-token scales beside them; one of them issues the bulk copies of the page records;
+//   warp 8     one lane issues every tcgen05.mma: S_{i+1} = Q K_{i+1}^T is queued before O += P_i V_i, so the
+//              tensor core works on the next page while the row warps are in the softmax of this one.
+// Tensor memory, all 512 columns: Q hi 0-63 | Q lo 64-127 | S0 128-255 | S1 256-383 | O 384-511 (fp32, accumulated
+// by the MMAs across pages).  P overlays the first 64 columns of its S buffer.  Hand-offs are mbarriers (counts in
+// brackets): k_ready/v_ready [128 producer arrivals], s_full/o_done [tcgen05.commit], p_ready [128 row arrivals];
+// buffer b of page i completes each of them for the (i >> 1)-th time, which fixes the parity to wait for.  Every
+// wait is bounded; a role that gives up raises the CTA's fail flag, the others see it or run out of time
+// themselves, and the tensor memory is released on every path.
+// ------------------------------------------------------------------------------------------
+constexpr int PF2_THREADS = 288;
+constexpr float PF2_SLACK = 4.0f;
+
+template <int KB, int VB> struct PfSmem2 {
+  static constexpr int LK = PfLut<KB>::BYTES, LV = PfLut<VB>::BYTES;
+  static constexpr int ALIGN = 128;
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = LK;
+  static constexpr int OFF_BAR = LK + LV;               // 12 mbarriers, tensor-memory base, fail flag
+  static constexpr int OFF_SC = OFF_BAR + 128;          // float scales[2 buffers][K, V][128 tokens]
+  static constexpr int OFF_KT = OFF_SC + 2048;          // K operand tiles, 2 x 32 KB
+  static constexpr int OFF_VT = OFF_KT + 65536;         // V operand tiles
+  static constexpr int OFF_ST = OFF_VT + 65536;         // two page records
+  static size_t bytes(int record_bytes) { return (size_t)ALIGN + OFF_ST + 2 * (size_t)record_bytes; }
+};
+
+__device__ __forceinline__ void pf_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(sptr(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(addr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+        "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+        "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31]) : "memory");
+}
+__device__ __forceinline__ void rows_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+// bounded wait whose verdict is the same in every lane of the warp (warp-collective tcgen05 instructions follow)
+__device__ __forceinline__ bool pf_wait_warp(uint64_t* bar, uint32_t parity) {
+  return __all_sync(0xffffffffu, pf_wait(bar, parity));
+}
+// AND of a predicate over the 128 producer threads (named barrier 1)
+__device__ __forceinline__ bool producers_all(bool ok) {
+  uint32_t r;
+  asm volatile("{\n .reg .pred p, q;\n setp.ne.b32 p, %1, 0;\n bar.red.and.pred q, 1, 128, p;\n selp.u32 %0, 1, 0, q;\n}\n"
+               : "=r"(r) : "r"((uint32_t)ok) : "memory");
+  return r != 0;
+}
+
+template <int KB, int VB>
+__global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillParams P, const TqFast fk, const TqFast fv) {
+  using SP = PfSmem2<KB, VB>;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  const int rb = blockIdx.x / P.num_splits, split = blockIdx.x - rb * P.num_splits, kvh = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int PT = P.L.page_tokens;  // 128 (checked on the host)
+  const int kv_len = P.kv_lens[b];
+  const int nrows = P.tq * P.group;
+  const int rtid = tid & 127;                        // row (warps 0-3) or token (warps 4-7) this thread serves
+  const int row = rb * PF_ROWS + rtid;
+  const bool is_row = tid < 128, is_prod = tid >= 128 && tid < 256;
+  const bool row_ok = is_row && row < nrows;
+  const int qi = row_ok ? row / P.group : 0, hl = row_ok ? row - qi * P.group : 0;
+  const int pos = row_ok ? kv_len - P.tq + qi : -1;
+  const int last_row = min(nrows, (rb + 1) * PF_ROWS) - 1;
+  const int pos_max = kv_len - P.tq + last_row / P.group;
+  const int np_all = min(P.max_pages, pos_max >= 0 ? pos_max / PT + 1 : 0);
+  const int ns = np_all > 0 ? (np_all + P.chunk_pages - 1) / P.chunk_pages : 1;
+  if (split >= ns) return;                           // nothing to do, and no tensor memory taken yet
+  const int page_lo = split * P.chunk_pages;
+  const int np = max(0, min(np_all, page_lo + P.chunk_pages) - page_lo);
+
+  const uint32_t raw = sptr(smem_raw);
+  uint8_t* sm = smem_raw + (((raw + SP::ALIGN - 1) & ~(uint32_t)(SP::ALIGN - 1)) - raw);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + SP::OFF_BAR);
+  uint64_t *rec_full = bars, *k_ready = bars + 2, *v_ready = bars + 4, *s_full = bars + 6, *p_ready = bars + 8,
+           *o_done = bars + 10;
+  uint32_t* tbase = reinterpret_cast<uint32_t*>(sm + SP::OFF_BAR + 96);
+  volatile int* fail = reinterpret_cast<volatile int*>(sm + SP::OFF_BAR + 104);
+  float* scales = reinterpret_cast<float*>(sm + SP::OFF_SC);
+  uint8_t* ktile = sm + SP::OFF_KT;
+  uint8_t* vtile = sm + SP::OFF_VT;
+  uint8_t* stage0 = sm + SP::OFF_ST;
+  const uint32_t rec = (uint32_t)P.L.record_bytes;
+  const int32_t* bt = P.block_table + (size_t)b * P.max_pages;
+
+  auto issue = [&](int i) {
+    const int64_t page = bt[page_lo + i];
+    const uint8_t* src = P.pool + page * P.L.page_stride + (int64_t)kvh * P.L.head_stride;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(sptr(&rec_full[i & 1])), "r"(rec) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     sptr(stage0 + (size_t)(i & 1) * rec)), "l"(src), "r"(rec), "r"(sptr(&rec_full[i & 1])) : "memory");
+  };
+  if (tid == 128) {
+    for (int i = 0; i < 2; ++i) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sptr(&rec_full[i])) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;" ::"r"(sptr(&k_ready[i])) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;" ::"r"(sptr(&v_ready[i])) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sptr(&s_full[i])) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;" ::"r"(sptr(&p_ready[i])) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sptr(&o_done[i])) : "memory");
+    }
+    *fail = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (np > 0) issue(0);
+    if (np > 1) issue(1);
+  }
+  if (warp == 0) {  // tensor memory: all 512 columns of the SM (one CTA per SM)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sptr(tbase)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (!is_row) {
+    // table fill by the 160 threads that do not rotate a query
+    for (int i = tid - 128; i < PfLut<KB>::BYTES / 16; i += PF2_THREADS - 128) {
+      if (PfLut<KB>::REPL) {
+        const int e = i >> 3;
+        const uint32_t v = (uint32_t)fk.cent16[e >> KB] | ((uint32_t)fk.cent16[e & ((1 << KB) - 1)] << 16);
+        reinterpret_cast<uint4*>(sm + SP::OFF_K)[i] = make_uint4(v, v, v, v);
+      } else {
+        uint32_t v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int e = 4 * i + k;
+          v[k] = (uint32_t)fk.cent16[e >> KB] | ((uint32_t)fk.cent16[e & ((1 << KB) - 1)] << 16);
+        }
+        reinterpret_cast<uint4*>(sm + SP::OFF_K)[i] = make_uint4(v[0], v[1], v[2], v[3]);
+      }
+    }
+    for (int i = tid - 128; i < PfLut<VB>::BYTES / 16; i += PF2_THREADS - 128) {
+      if (PfLut<VB>::REPL) {
+        const int e = i >> 3;
+        const uint32_t v = (uint32_t)fv.cent16[e >> VB] | ((uint32_t)fv.cent16[e & ((1 << VB) - 1)] << 16);
+        reinterpret_cast<uint4*>(sm + SP::OFF_V)[i] = make_uint4(v, v, v, v);
+      } else {
+        uint32_t v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int e = 4 * i + k;
+          v[k] = (uint32_t)fv.cent16[e >> VB] | ((uint32_t)fv.cent16[e & ((1 << VB) - 1)] << 16);
+        }
+        reinterpret_cast<uint4*>(sm + SP::OFF_V)[i] = make_uint4(v[0], v[1], v[2], v[3]);
+      }
+    }
+  }
+
+  // ---- prologue (row warps): this row's query, rotated by the K rotation, scaled, fp16 hi + lo into tensor memory ----
+  float o[TQ_D];
+  if (is_row) {
+    const size_t qoff = (((size_t)b * P.tq + qi) * P.hq + (size_t)kvh * P.group + hl) * TQ_D;
+#pragma unroll
+    for (int e = 0; e < TQ_D; e += 4) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (row_ok) {
+        if (P.q_dtype == TQ_F32) {
+          v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(P.q) + qoff + e);
+        } else if (P.q_dtype == TQ_F16) {
+          const uint2 w = *reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(P.q) + qoff + e);
+          const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
+          const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
+          v = make_float4(a.x, a.y, c.x, c.y);
+        } else {
+          const uint2 w = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(P.q) + qoff + e);
+          const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w.x));
+          const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w.y));
+          v = make_float4(a.x, a.y, c.x, c.y);
+        }
+      }
+      o[e] = v.x; o[e + 1] = v.y; o[e + 2] = v.z; o[e + 3] = v.w;
+    }
+    if (P.k_rot_t) {
+      // dense rotation: stage the rows transposed in the (still unused) operand tiles, then y = R x per thread
+      float* xs = reinterpret_cast<float*>(ktile);  // [k][row], 64 KB
+#pragma unroll
+      for (int k = 0; k < TQ_D; ++k) xs[k * PF_ROWS + rtid] = o[k];
+#pragma unroll
+      for (int j = 0; j < TQ_D; ++j) o[j] = 0.f;
+      for (int k = 0; k < TQ_D; ++k) {
+        const float xv = xs[k * PF_ROWS + rtid];
+        const float4* rr = reinterpret_cast<const float4*>(P.k_rot_t + (size_t)k * TQ_D);
+#pragma unroll
+        for (int j = 0; j < TQ_D; j += 4) {
+          const float4 r4 = __ldg(rr + (j >> 2));
+          o[j] = fmaf(r4.x, xv, o[j]); o[j + 1] = fmaf(r4.y, xv, o[j + 1]);
+          o[j + 2] = fmaf(r4.z, xv, o[j + 2]); o[j + 3] = fmaf(r4.w, xv, o[j + 3]);
+        }
+      }
+    } else {
+      row_wht128(o, fk.s1, fk.s2);
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();  // tensor-memory base, tables and barriers visible; the dense staging area is free again
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tb = *tbase;
+  const uint32_t TQc = 0, TQLc = 64, TSc = 128, TOc = 384;   // S buffer b at TSc + 128 b; P overlays its first 64 columns
+
+  if (is_row) {
+    // =========================== row warps ===========================
+    const uint32_t tm = tb + ((uint32_t)(warp * 32) << 16);  // this warp's 32 lanes
+    {
+      const float sk = P.qscale / fk.lut_alpha;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t u[16], ul[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float a = o[32 * c + 2 * j] * sk, bq = o[32 * c + 2 * j + 1] * sk;
+          const __half2 h = __floats2half2_rn(a, bq);
+          const float2 hf = __half22float2(h);
+          u[j] = *reinterpret_cast<const uint32_t*>(&h);
+          ul[j] = pf_pack(a - hf.x, bq - hf.y);
+        }
+        tmem_st16(tm + TQc + 16 * c, u);
+        tmem_st16(tm + TQLc + 16 * c, ul);
+      }
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    asm volatile("bar.sync 3, 160;" ::: "memory");   // with the MMA warp: the queries are in tensor memory
+
+    float m_run = -INFINITY, l_run = 0.f;
+    for (int i = 0; i < np; ++i) {
+      if (*fail) break;
+      const int bf = i & 1;
+      const uint32_t ph = (uint32_t)((i >> 1) & 1);
+      if (!pf_wait_warp(&s_full[bf], ph)) { *fail = 1; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const float* ksc = scales + bf * 256;
+      const float* vsc = ksc + 128;
+      const uint32_t ts = tm + TSc + 128 * bf;
+      const int t0 = (page_lo + i) * PT;
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(ts + 32 * c, v);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int t = 32 * c + j;
+          const float sv = __uint_as_float(v[j]) * ksc[t];
+          mx = fmaxf(mx, (t0 + t <= pos) ? sv : -INFINITY);
+        }
+      }
+      // The row maximum moves only when it grows by more than 2^PF2_SLACK (probabilities stay below 2^PF2_SLACK).
+      // O lives in tensor memory and is being accumulated by the MMAs: a rescale waits for the product of the
+      // page before, multiplies the row in place, and only then lets this page's product start (p_ready below).
+      float resc = 1.0f;
+      if (i == 0) {
+        m_run = mx;
+      } else if (mx > m_run + PF2_SLACK) {
+        resc = pf_exp2(m_run - mx);   // m_run == -inf (nothing seen yet) gives 0: the row of O is zero anyway
+        m_run = mx;
+        l_run *= resc;
+      }
+      if (i > 0 && __any_sync(0xffffffffu, resc != 1.0f)) {
+        if (!pf_wait_warp(&o_done[(i - 1) & 1], (uint32_t)(((i - 1) >> 1) & 1))) { *fail = 1; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld32(tm + TOc + 32 * c, v);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * resc);
+          tmem_st32(tm + TOc + 32 * c, v);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      }
+      const float m_use = m_run == -INFINITY ? 0.f : m_run;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32], u[16];
+        tmem_ld32(ts + 32 * c, v);
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          const int t = 32 * c + j;
+          const bool s0 = t0 + t <= pos, s1 = t0 + t + 1 <= pos;
+          const float p0 = s0 ? pf_exp2(__uint_as_float(v[j]) * ksc[t] - m_use) : 0.f;
+          const float p1 = s1 ? pf_exp2(__uint_as_float(v[j + 1]) * ksc[t + 1] - m_use) : 0.f;
+          l_run += p0 + p1;
+          u[j >> 1] = pf_pack(s0 ? p0 * vsc[t] : 0.f, s1 ? p1 * vsc[t + 1] : 0.f);
+        }
+        tmem_st16(ts + 16 * c, u);  // P chunk c overlays S columns that have been consumed
+      }
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      pf_arrive(&p_ready[bf]);
+    }
+    // the accumulated row of O, once the last product has completed
+#pragma unroll
+    for (int j = 0; j < TQ_D; ++j) o[j] = 0.f;
+    if (np > 0 && !*fail) {
+      if (!pf_wait_warp(&o_done[(np - 1) & 1], (uint32_t)(((np - 1) >> 1) & 1))) {
+        *fail = 1;
+      } else {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld32(tm + TOc + 32 * c, v);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[32 * c + j] = __uint_as_float(v[j]);
+        }
+      }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();  // every role is done with tensor memory
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tb), "r"(512u) : "memory");
+    if (*fail) {
+      if (tid == 0) atomicExch(P.status, 1);
+      return;
+    }
+    // ---- split partial / merge by the last split / epilogue: the 128 row threads only ----
+    if (ns > 1) {
+      const size_t slot0 = (((size_t)b * P.hkv + kvh) * P.row_blocks + rb) * P.num_splits;
+      {
+        float4* po = reinterpret_cast<float4*>(P.part_o + ((slot0 + split) * PF_ROWS + tid) * TQ_D);
+#pragma unroll
+        for (int j = 0; j < TQ_D; j += 4) po[j >> 2] = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+        reinterpret_cast<float2*>(P.part_ml)[(slot0 + split) * PF_ROWS + tid] = make_float2(m_run, l_run);
+      }
+      __threadfence();
+      rows_sync();
+      if (tid == 0) {
+        int* tk = P.tickets + ((size_t)b * P.hkv + kvh) * P.row_blocks + rb;
+        const int prev = atomicAdd(tk, 1);
+        int last = 0;
+        if (prev == ns - 1) {
+          *tk = 0;  // zero again for the next call
+          last = 1;
+        }
+        *fail = last;  // reuse the flag word as "this CTA merges"
+      }
+      rows_sync();
+      if (!*fail) return;
+      __threadfence();
+      float M = -INFINITY;
+      for (int s_i = 0; s_i < ns; ++s_i)
+        M = fmaxf(M, __ldcg(reinterpret_cast<const float2*>(P.part_ml) + (slot0 + s_i) * PF_ROWS + tid).x);
+#pragma unroll
+      for (int j = 0; j < TQ_D; ++j) o[j] = 0.f;
+      l_run = 0.f;
+      for (int s_i = 0; s_i < ns; ++s_i) {
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(P.part_ml) + (slot0 + s_i) * PF_ROWS + tid);
+        const float f = ml.x == -INFINITY ? 0.f : exp2f(ml.x - M);
+        l_run = fmaf(ml.y, f, l_run);
+        const float4* po = reinterpret_cast<const float4*>(P.part_o + ((slot0 + s_i) * PF_ROWS + tid) * TQ_D);
+#pragma unroll
+        for (int j = 0; j < TQ_D; j += 4) {
+          const float4 v = __ldcg(po + (j >> 2));
+          o[j] = fmaf(v.x, f, o[j]); o[j + 1] = fmaf(v.y, f, o[j + 1]);
+          o[j + 2] = fmaf(v.z, f, o[j + 2]); o[j + 3] = fmaf(v.w, f, o[j + 3]);
+        }
+      }
+    }
+    {
+      const float inv = l_run > 0.f ? 1.0f / (l_run * fv.lut_alpha) : 0.f;
+#pragma unroll
+      for (int j = 0; j < TQ_D; ++j) o[j] *= inv;
+      if (P.v_rot) {
+        float* ys = reinterpret_cast<float*>(ktile);  // [k][row]; the operand tiles are idle by now
+#pragma unroll
+        for (int k = 0; k < TQ_D; ++k) ys[k * PF_ROWS + tid] = o[k];
+#pragma unroll
+        for (int j = 0; j < TQ_D; ++j) o[j] = 0.f;
+        for (int k = 0; k < TQ_D; ++k) {
+          const float yv = ys[k * PF_ROWS + tid];
+          const float4* rr = reinterpret_cast<const float4*>(P.v_rot + (size_t)k * TQ_D);
+#pragma unroll
+          for (int j = 0; j < TQ_D; j += 4) {
+            const float4 r4 = __ldg(rr + (j >> 2));
+            o[j] = fmaf(r4.x, yv, o[j]); o[j + 1] = fmaf(r4.y, yv, o[j + 1]);
+            o[j + 2] = fmaf(r4.z, yv, o[j + 2]); o[j + 3] = fmaf(r4.w, yv, o[j + 3]);
+          }
+        }
+      } else {
+        row_wht128(o, fv.s2, fv.s1);  // R^T = D1 (H/sqrt d) D2
+      }
+      if (row_ok) {
+        const size_t ooff = (((size_t)b * P.tq + qi) * P.hq + (size_t)kvh * P.group + hl) * TQ_D;
+        if (P.out_dtype == TQ_F32) {
+          float4* op = reinterpret_cast<float4*>(reinterpret_cast<float*>(P.out) + ooff);
+#pragma unroll
+          for (int j = 0; j < TQ_D; j += 4) op[j >> 2] = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+        } else if (P.out_dtype == TQ_F16) {
+          uint2* op = reinterpret_cast<uint2*>(reinterpret_cast<__half*>(P.out) + ooff);
+#pragma unroll
+          for (int j = 0; j < TQ_D; j += 4) op[j >> 2] = make_uint2(pf_pack(o[j], o[j + 1]), pf_pack(o[j + 2], o[j + 3]));
+        } else {
+          __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(P.out) + ooff;
+#pragma unroll
+          for (int j = 0; j < TQ_D; ++j) op[j] = __float2bfloat16_rn(o[j]);
+        }
+      }
+    }
+    return;
+  }
+
+  if (is_prod) {
+    // =========================== producer warps ===========================
+    const uint32_t lk_base = sptr(sm + SP::OFF_K) + (PfLut<KB>::REPL ? lane * 4 : 0);
+    const uint32_t lv_base = sptr(sm + SP::OFF_V) + (PfLut<VB>::REPL ? lane * 4 : 0);
+    const uint32_t tile_row = (uint32_t)(rtid >> 3) * 2048 + (uint32_t)(rtid & 7) * 16;  // token rtid inside an operand tile
+    for (int i = 0; i < np; ++i) {
+      const int bf = i & 1;
+      const uint32_t ph = (uint32_t)((i >> 1) & 1);
+      // tiles and scales of buffer bf are free once the product of page i - 2 has completed
+      bool ok = !*fail;
+      if (ok && i >= 2) ok = pf_wait(&o_done[bf], (uint32_t)(((i - 2) >> 1) & 1));
+      if (ok) ok = pf_wait(&rec_full[bf], ph);
+      if (!producers_all(ok)) {  // the 128 producers go on or give up together (they share a named barrier below)
+        *fail = 1;
+        break;
+      }
+      const uint8_t* st = stage0 + (size_t)bf * rec;
+      pf_dequant_token<KB>(st + P.L.k_idx_off + rtid * (16 * KB), ktile + bf * 32768 + tile_row, lk_base);
+      scales[bf * 256 + rtid] = reinterpret_cast<const float*>(st + P.L.k_scale_off)[rtid];
+      scales[bf * 256 + 128 + rtid] = reinterpret_cast<const float*>(st + P.L.v_scale_off)[rtid];
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      pf_arrive(&k_ready[bf]);
+      pf_dequant_token<VB>(st + P.L.v_idx_off + rtid * (16 * VB), vtile + bf * 32768 + tile_row, lv_base);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      pf_arrive(&v_ready[bf]);
+      asm volatile("bar.sync 1, 128;" ::: "memory");   // every producer has read this record: its stage can be refilled
+      if (tid == 128 && i + 2 < np) issue(i + 2);
+    }
+    if (*fail && tid == 128) {  // copies in flight get the same bounded time before the CTA leaves
+      for (int st_i = 0; st_i < 2; ++st_i) pf_wait(&rec_full[st_i], 0), pf_wait(&rec_full[st_i], 1);
+    }
+  } else {
+    // =========================== MMA warp ===========================
+    asm volatile("bar.sync 3, 160;" ::: "memory");
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (lane == 0 && np > 0) {
+      const uint32_t idesc_s = umma_idesc(128, 128, false), idesc_o = umma_idesc(128, 128, true);
+      auto qk = [&](int i) {   // S_i = Q K_i^T (fp16 hi and lo halves of Q), into S buffer i & 1
+        const int bf = i & 1;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t kd = umma_desc(sptr(ktile + bf * 32768) + ks * 256, 128, 2048);
+          umma_ts(tb + TSc + 128 * bf, tb + TQc + ks * 8, kd, idesc_s, ks > 0);
+          umma_ts(tb + TSc + 128 * bf, tb + TQLc + ks * 8, kd, idesc_s, 1);
+        }
+        umma_commit(&s_full[bf]);
+      };
+      bool okay = pf_wait(&k_ready[0], 0);
+      if (okay) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        qk(0);
+      }
+      for (int i = 0; okay && i < np; ++i) {
+        if (*fail) break;
+        const int bf = i & 1;
+        const uint32_t ph = (uint32_t)((i >> 1) & 1);
+        if (i + 1 < np) {
+          if (!pf_wait(&k_ready[(i + 1) & 1], (uint32_t)(((i + 1) >> 1) & 1))) { okay = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          qk(i + 1);
+        }
+        if (!pf_wait(&p_ready[bf], ph) || !pf_wait(&v_ready[bf], ph)) { okay = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)   // O += P_i V_i: P from tensor memory, V tile MN-major, N = 128
+          umma_ts(tb + TOc, tb + TSc + 128 * bf + ks * 8, umma_desc(sptr(vtile + bf * 32768) + ks * 4096, 2048, 128),
+                  idesc_o, (i > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(&o_done[bf]);
+      }
+      if (!okay) *fail = 1;
+    }
+    __syncwarp();
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();  // matches the row warps' barrier before the tensor memory is released
+}
+
 }  // namespace
 
 template <int KB, int VB>
 static int launch_prefill(const PrefillParams& P, const TqFast& fk, const TqFast& fv, cudaStream_t st) {
-  const size_t need = PfSmem<KB, VB>::bytes(P.L.record_bytes);
-  TQ_REQUIRE(need <= 113 * 1024, TQ_ERR_TOO_LARGE, "page record of %d bytes does not fit the prefill pipeline",
+  const size_t need = PfSmem2<KB, VB>::bytes(P.L.record_bytes);
+  constexpr size_t LIMIT = 220 * 1024;  // one CTA per SM (it also takes all 512 tensor-memory columns)
+  TQ_REQUIRE(need <= LIMIT, TQ_ERR_TOO_LARGE, "page record of %d bytes does not fit the prefill pipeline",
              P.L.record_bytes);
   static thread_local int configured_dev = -1;
   int dev = 0;
   TQ_CUDA(cudaGetDevice(&dev));
   if (configured_dev != dev) {
-    TQ_CUDA(cudaFuncSetAttribute(k_prefill_attn<KB, VB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 113 * 1024));
+    TQ_CUDA(cudaFuncSetAttribute(k_prefill_attn2<KB, VB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)LIMIT));
     configured_dev = dev;
   }
   dim3 grid(P.row_blocks * P.num_splits, P.hkv, P.batch);
-  k_prefill_attn<KB, VB><<<grid, PF_THREADS, need, st>>>(P, fk, fv);
-  return tq_launch_check("k_prefill_attn");
+  k_prefill_attn2<KB, VB><<<grid, PF2_THREADS, need, st>>>(P, fk, fv);
+  return tq_launch_check("k_prefill_attn2");
 }
 
 struct PfPlan {
@@ -568,7 +1050,7 @@ static PfPlan pf_plan(int batch, int chunk_tokens, int hq, int hkv, int max_page
   PfPlan p;
   p.row_blocks = (chunk_tokens * (hq / hkv) + PF_ROWS - 1) / PF_ROWS;
   const long base = (long)p.row_blocks * hkv * batch;
-  const int slots = 2 * tq_num_sms();
+  const int slots = tq_num_sms();  // one CTA per SM
   int s = (int)((slots + base - 1) / base);
   const int cap = max_pages / 8 > 1 ? max_pages / 8 : 1;  // at least eight pages per split
   if (s > cap) s = cap;
