@@ -773,20 +773,32 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
       const uint32_t ph = (uint32_t)((i >> 1) & 1);
       if (!pf_wait_warp(&s_full[bf], ph)) { *fail = 1; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const float* ksc = scales + bf * 256;
-      const float* vsc = ksc + 128;
+      const float4* ksc4 = reinterpret_cast<const float4*>(scales + bf * 256);
+      const float4* vsc4 = ksc4 + 32;
       const uint32_t ts = tm + TSc + 128 * bf;
       const int t0 = (page_lo + i) * PT;
+      // a page that every row of this warp sees completely needs no causal mask (rows without a query count as
+      // seeing everything: nothing of theirs is stored)
+      const bool masked = !__all_sync(0xffffffffu, !row_ok || t0 + PT - 1 <= pos);
+      // pass 1: scaled scores into registers, row maximum
+      float sv[128];
       float mx = -INFINITY;
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
         tmem_ld32(ts + 32 * c, v);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int t = 32 * c + j;
-          const float sv = __uint_as_float(v[j]) * ksc[t];
-          mx = fmaxf(mx, (t0 + t <= pos) ? sv : -INFINITY);
+        for (int j = 0; j < 32; j += 4) {
+          const float4 k4 = ksc4[8 * c + (j >> 2)];
+          const float kk[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int t = 32 * c + j + e;
+            float x = __uint_as_float(v[j + e]) * kk[e];
+            if (masked) x = (t0 + t <= pos) ? x : -INFINITY;
+            sv[t] = x;
+            mx = fmaxf(mx, x);
+          }
         }
       }
       // The row maximum moves only when it grows by more than 2^PF2_SLACK (probabilities stay below 2^PF2_SLACK).
@@ -794,7 +806,9 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
       // page before, multiplies the row in place, and only then lets this page's product start (p_ready below).
       float resc = 1.0f;
       if (i == 0) {
-        m_run = mx;
+        // the reference starts PF2_SLACK above the first page's maximum: a later page then moves it only when it
+        // beats that maximum by 2^(2 PF2_SLACK), which is rare -- and every move stalls the row on the tensor core
+        m_run = mx + PF2_SLACK;
       } else if (mx > m_run + PF2_SLACK) {
         resc = pf_exp2(m_run - mx);   // m_run == -inf (nothing seen yet) gives 0: the row of O is zero anyway
         m_run = mx;
@@ -813,19 +827,19 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
+      // pass 2: probabilities (masked scores are -inf and give 0), row sum, P * (V scale) as packed fp16
       const float m_use = m_run == -INFINITY ? 0.f : m_run;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32], u[16];
-        tmem_ld32(ts + 32 * c, v);
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          const int t = 32 * c + j;
-          const bool s0 = t0 + t <= pos, s1 = t0 + t + 1 <= pos;
-          const float p0 = s0 ? pf_exp2(__uint_as_float(v[j]) * ksc[t] - m_use) : 0.f;
-          const float p1 = s1 ? pf_exp2(__uint_as_float(v[j + 1]) * ksc[t + 1] - m_use) : 0.f;
-          l_run += p0 + p1;
-          u[j >> 1] = pf_pack(s0 ? p0 * vsc[t] : 0.f, s1 ? p1 * vsc[t + 1] : 0.f);
+      for (int c = 0; c < 4; ++c) {
+        uint32_t u[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          const float4 s4 = vsc4[8 * c + (j >> 2)];
+          const float p0 = pf_exp2(sv[32 * c + j] - m_use), p1 = pf_exp2(sv[32 * c + j + 1] - m_use);
+          const float p2 = pf_exp2(sv[32 * c + j + 2] - m_use), p3 = pf_exp2(sv[32 * c + j + 3] - m_use);
+          l_run += (p0 + p1) + (p2 + p3);
+          u[j >> 1] = pf_pack(p0 * s4.x, p1 * s4.y);
+          u[(j >> 1) + 1] = pf_pack(p2 * s4.z, p3 * s4.w);
         }
         tmem_st16(ts + 16 * c, u);  // P chunk c overlays S columns that have been consumed
       }
@@ -1045,16 +1059,25 @@ struct PfPlan {
   size_t part_o, part_ml, total;
 };
 static const size_t PF_TAIL = 65536 * 4 + 256;  // tickets + status word, at the end of the workspace
+static const long PF_CTA_COST_PAGES = 2;  // prologue, partial and merge of a CTA, in units of one page of the main loop
 
 static PfPlan pf_plan(int batch, int chunk_tokens, int hq, int hkv, int max_pages) {
   PfPlan p;
   p.row_blocks = (chunk_tokens * (hq / hkv) + PF_ROWS - 1) / PF_ROWS;
   const long base = (long)p.row_blocks * hkv * batch;
   const int slots = tq_num_sms();  // one CTA per SM
-  int s = (int)((slots + base - 1) / base);
   const int cap = max_pages / 8 > 1 ? max_pages / 8 : 1;  // at least eight pages per split
-  if (s > cap) s = cap;
-  if (s < 1) s = 1;
+  // splits per row block: the count that minimises (waves of CTAs) x (pages per split + fixed cost of a CTA)
+  int s = 1;
+  long best = -1;
+  for (int c = 1; c <= cap && c <= 64; ++c) {
+    const long waves = (base * c + slots - 1) / slots;
+    const long cost = waves * ((max_pages + c - 1) / c + PF_CTA_COST_PAGES);
+    if (best < 0 || cost < best) {
+      best = cost;
+      s = c;
+    }
+  }
   p.chunk_pages = (max_pages + s - 1) / s;
   p.num_splits = (max_pages + p.chunk_pages - 1) / p.chunk_pages;
   const size_t slots_total = (size_t)base * p.num_splits;
