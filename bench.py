@@ -82,7 +82,7 @@ def prefill_probe(torch, tq, dev, gen):
     visible = sum(n - tq_len + i + 1 for i in range(tq_len))       # cached positions seen by the chunk's queries
     flops = 2 * 2 * hq * D * visible
     peak, src = tensor_peak()
-    return {"bound": "tensor", "kernel": "k_prefill_attn<3,3> (tcgen05)", "achieved": flops / (ms * 1e-3) / 1e12,
+    return {"bound": "tensor", "kernel": "k_prefill_attn2<3,3> (tcgen05)", "achieved": flops / (ms * 1e-3) / 1e12,
             "peak": peak, "unit": "TFLOP/s", "frac": flops / (ms * 1e-3) / 1e12 / peak, "peak_source": src,
             "ms": ms, "ctas": (tq_len * hq // hkv // 128) * hkv,
             "workload": f"{tq_len}-query chunk, {hq}q/{hkv}kv heads, ctx {n}, turbo3 K+V, one layer"}
@@ -575,7 +575,7 @@ def run_config3(args):
                          "peak_source": src, "kernel": "k_quantize_mma<half,3>", "bytes_per_vector": 308},
             "prefill": {"ms": prefill_ms, "tflops": flops / (prefill_ms * 1e-3) / 1e12,
                         "frac_of_tensor_peak": flops / (prefill_ms * 1e-3) / 1e12 / world / tpeak, "peak": tpeak,
-                        "peak_source": tsrc, "kernel": "k_prefill_attn<3,3> (tcgen05)"},
+                        "peak_source": tsrc, "kernel": "k_prefill_attn2<3,3> (tcgen05)"},
             "gpu_launches": 2 * (n // chunk)}), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -1,21 +1,12 @@
 // Chunked-prefill attention over the packed paged cache on the 5th-generation tensor cores (tcgen05).
 //
-// One CTA = 128 threads = 128 rows of (query token, query head) pairs that share a KV head; thread r owns row r,
-// which is also lane r of tensor memory.  Per 128-token page:
-//   1. the packed page record arrives by one bulk async copy (two stages, prefetch one page ahead);
-//   2. all threads dequantize the K indices (2b-bit pairs -> fp16 centroid pairs through a lane-replicated
-//      table) into a K-major, unswizzled tcgen05 operand tile in shared memory;
-//   3. one thread issues S = Q K^T: 16 x tcgen05.mma (M128 N128 K16; fp16 hi and lo halves of Q), A = the rotated queries that live in
-//      tensor memory for the whole kernel, accumulator in tensor memory; while it runs everybody dequantizes V
-//      into an MN-major operand tile;
-//   4. every thread reads its S row back (tcgen05.ld), applies the per-token K scale and the causal mask, keeps
-//      the online softmax state in registers, and stores P * (V scale) as packed fp16 over the first half of
-//      the S columns (tcgen05.st) -- P is the A operand of the second product straight from tensor memory;
-//   5. O_page = P V: 2 x 8 tcgen05.mma (two N=64 halves, one after the other); each half is read back and
-//      added to the fp32 accumulator row held in registers (rescaled when the running max moved).
-// Tensor-memory budget: 256 columns per CTA = Q hi 64 | Q lo 64 | S 128 (P overlays its first 64, one O half at
-// a time its last 64), so two CTAs fit the 512 columns of an SM.  Every wait is bounded in time; a CTA that gives up
-// sets the status word, stops issuing work and still frees its tensor memory.
+// One CTA = 128 rows of (query token, query head) pairs that share a KV head; row r is lane r of tensor memory.
+// Per 128-token page: the packed page record arrives by a bulk async copy; producer warps turn the K and V indices
+// (2b-bit pairs -> fp16 centroid pairs through a lane-replicated table) into unswizzled tcgen05 operand tiles in
+// shared memory (K-major for K, MN-major for V); S = Q K^T and O += P V run as tcgen05.mma with the rotated queries
+// (fp16 hi + lo halves), S, P and O all in tensor memory; the row warps do the online softmax between the two
+// products.  The kernel, its roles, its tensor-memory map and its hand-offs are described above k_prefill_attn2.
+// Every wait is bounded in time; a CTA that gives up sets the status word and still frees its tensor memory.
 #include "tq_internal.cuh"
 
 namespace {
@@ -188,360 +179,8 @@ __device__ __forceinline__ void pf_dequant_token(const uint8_t* src, uint8_t* ds
 }
 
 
-template <int KB, int VB> struct PfSmem {
-  static constexpr int LK = PfLut<KB>::BYTES, LV = PfLut<VB>::BYTES;
-  static constexpr int ALIGN = 128;                     // table addresses are formed by addition here
-  static constexpr int OFF_K = 0;
-  static constexpr int OFF_V = LK;
-  static constexpr int OFF_BAR = LK + LV;               // 4 mbarriers, tensor-memory base, flags
-  static constexpr int OFF_KT = OFF_BAR + 128;          // K operand tile, 128 tokens x 128 dims fp16
-  static constexpr int OFF_VT = OFF_KT + 32768;         // V operand tile
-  static constexpr int OFF_ST = OFF_VT + 32768;         // two page records
-  static size_t bytes(int record_bytes) { return (size_t)ALIGN + OFF_ST + 2 * (size_t)record_bytes; }
-};
-
-template <int KB, int VB>
-__global__ void __launch_bounds__(PF_THREADS, 2) k_prefill_attn(const PrefillParams P, const TqFast fk, const TqFast fv) {
-  using SP = PfSmem<KB, VB>;
-  extern __shared__ __align__(128) uint8_t smem_raw[];
-  const int rb = blockIdx.x / P.num_splits, split = blockIdx.x - rb * P.num_splits, kvh = blockIdx.y, b = blockIdx.z;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int PT = P.L.page_tokens;  // 128 (checked on the host)
-  const int kv_len = P.kv_lens[b];
-  const int nrows = P.tq * P.group;
-  const int row = rb * PF_ROWS + tid;  // row = query index * group + head within the group
-  const bool row_ok = row < nrows;
-  const int qi = row_ok ? row / P.group : 0, hl = row_ok ? row - qi * P.group : 0;
-  const int pos = row_ok ? kv_len - P.tq + qi : -1;  // last cache position this row attends to
-  const int last_row = min(nrows, (rb + 1) * PF_ROWS) - 1;
-  const int pos_max = kv_len - P.tq + last_row / P.group;
-  const int np_all = min(P.max_pages, pos_max >= 0 ? pos_max / PT + 1 : 0);  // never walk past the block table
-  const int ns = np_all > 0 ? (np_all + P.chunk_pages - 1) / P.chunk_pages : 1;  // splits that have pages (>= 1)
-  if (split >= ns) return;                       // nothing to do, and no tensor memory taken yet
-  const int page_lo = split * P.chunk_pages;
-  const int np = max(0, min(np_all, page_lo + P.chunk_pages) - page_lo);
-
-  const uint32_t raw = sptr(smem_raw);
-  uint8_t* sm = smem_raw + (((raw + SP::ALIGN - 1) & ~(uint32_t)(SP::ALIGN - 1)) - raw);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + SP::OFF_BAR);   // [0],[1] page stages, [2] S ready, [3] O ready
-  uint32_t* tbase = reinterpret_cast<uint32_t*>(sm + SP::OFF_BAR + 64);
-  volatile int* fail = reinterpret_cast<volatile int*>(sm + SP::OFF_BAR + 72);
-  uint8_t* ktile = sm + SP::OFF_KT;
-  uint8_t* vtile = sm + SP::OFF_VT;
-  uint8_t* stage0 = sm + SP::OFF_ST;
-  const uint32_t rec = (uint32_t)P.L.record_bytes;
-  const int32_t* bt = P.block_table + (size_t)b * P.max_pages;
-
-  auto issue = [&](int i) {
-    const int64_t page = bt[page_lo + i];
-    const uint8_t* src = P.pool + page * P.L.page_stride + (int64_t)kvh * P.L.head_stride;
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(sptr(&bars[i & 1])), "r"(rec) : "memory");
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     sptr(stage0 + (size_t)(i & 1) * rec)), "l"(src), "r"(rec), "r"(sptr(&bars[i & 1])) : "memory");
-  };
-  if (tid == 0) {
-    for (int i = 0; i < 4; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sptr(&bars[i])) : "memory");
-    *fail = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    if (np > 0) issue(0);
-  }
-  if (warp == 0) {  // tensor memory: 256 columns
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sptr(tbase)), "r"(256u) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  pf_lut_fill<KB>(sm + SP::OFF_K, fk.cent16, tid);
-  pf_lut_fill<VB>(sm + SP::OFF_V, fv.cent16, tid);
-
-  // ---- prologue: this row's query, rotated by the K rotation, scaled, as packed fp16 into tensor memory ----
-  float o[TQ_D];
-  {
-    const size_t qoff = (((size_t)b * P.tq + qi) * P.hq + (size_t)kvh * P.group + hl) * TQ_D;
-#pragma unroll
-    for (int e = 0; e < TQ_D; e += 4) {
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (row_ok) {
-        if (P.q_dtype == TQ_F32) {
-          v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(P.q) + qoff + e);
-        } else if (P.q_dtype == TQ_F16) {
-          const uint2 w = *reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(P.q) + qoff + e);
-          const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
-          const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
-          v = make_float4(a.x, a.y, c.x, c.y);
-        } else {
-          const uint2 w = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(P.q) + qoff + e);
-          const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w.x));
-          const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w.y));
-          v = make_float4(a.x, a.y, c.x, c.y);
-        }
-      }
-      o[e] = v.x; o[e + 1] = v.y; o[e + 2] = v.z; o[e + 3] = v.w;
-    }
-    if (P.k_rot_t) {
-      // dense rotation: stage the rows transposed in the (still unused) operand tiles, then y = R x per thread
-      float* xs = reinterpret_cast<float*>(ktile);  // [k][row], 64 KB = both tiles
-#pragma unroll
-      for (int k = 0; k < TQ_D; ++k) xs[k * PF_ROWS + tid] = o[k];
-#pragma unroll
-      for (int j = 0; j < TQ_D; ++j) o[j] = 0.f;
-      for (int k = 0; k < TQ_D; ++k) {
-        const float xv = xs[k * PF_ROWS + tid];
-        const float4* rr = reinterpret_cast<const float4*>(P.k_rot_t + (size_t)k * TQ_D);
-#pragma unroll
-        for (int j = 0; j < TQ_D; j += 4) {
-          const float4 r4 = __ldg(rr + (j >> 2));
-          o[j] = fmaf(r4.x, xv, o[j]); o[j + 1] = fmaf(r4.y, xv, o[j + 1]);
-          o[j + 2] = fmaf(r4.z, xv, o[j + 2]); o[j + 3] = fmaf(r4.w, xv, o[j + 3]);
-        }
-      }
-    } else {
-      row_wht128(o, fk.s1, fk.s2);
-    }
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();  // tensor-memory base address visible; dense staging buffer free again
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tm = *tbase + ((uint32_t)(warp * 32) << 16);  // this warp's 32 lanes
-  // columns: Q hi 0..63 | Q lo 64..127 | S 128..255; P overlays S 128..191; one O half at a time in 192..255
-  const uint32_t TQc = 0, TQLc = 64, TSc = 128, TPc = 128, TOc = 192;
-  {
-    // fp16 hi + lo halves of the scaled query: two accumulating products keep the query at ~fp32 accuracy
-    const float sk = P.qscale / fk.lut_alpha;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t u[16], ul[16];
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const float a = o[32 * c + 2 * j] * sk, bq = o[32 * c + 2 * j + 1] * sk;
-        const __half2 h = __floats2half2_rn(a, bq);
-        const float2 hf = __half22float2(h);
-        u[j] = *reinterpret_cast<const uint32_t*>(&h);
-        ul[j] = pf_pack(a - hf.x, bq - hf.y);
-      }
-      tmem_st16(tm + TQc + 16 * c, u);
-      tmem_st16(tm + TQLc + 16 * c, ul);
-    }
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-  }
-#pragma unroll
-  for (int j = 0; j < TQ_D; ++j) o[j] = 0.f;
-  float m_run = -INFINITY, l_run = 0.f;
-  const uint32_t lk_base = sptr(sm + SP::OFF_K) + (PfLut<KB>::REPL ? lane * 4 : 0);
-  const uint32_t lv_base = sptr(sm + SP::OFF_V) + (PfLut<VB>::REPL ? lane * 4 : 0);
-  const uint32_t tile_row = (uint32_t)(tid >> 3) * 2048 + (uint32_t)(tid & 7) * 16;  // token tid inside an operand tile
-  const uint32_t idesc_s = umma_idesc(128, 128, false), idesc_o = umma_idesc(128, 64, true);
-
-  for (int i = 0; i < np; ++i) {
-    if (tid == 0 && i + 1 < np) issue(i + 1);
-    if (!*fail && !pf_wait(&bars[i & 1], (uint32_t)((i >> 1) & 1))) *fail = 1;
-    const uint8_t* st = stage0 + (size_t)(i & 1) * rec;
-    // ---- K indices of token `tid` -> K-major operand tile ----
-    pf_dequant_token<KB>(st + P.L.k_idx_off + tid * (16 * KB), ktile + tile_row, lk_base);
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (*fail) break;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (tid == 0) {
-      // S[128 rows x 128 tokens] = Q (tensor memory) . K^T: eight K=16 steps
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const uint64_t kd = umma_desc(sptr(ktile) + ks * 256, 128, 2048);
-        umma_ts(*tbase + TSc, *tbase + TQc + ks * 8, kd, idesc_s, ks > 0);
-        umma_ts(*tbase + TSc, *tbase + TQLc + ks * 8, kd, idesc_s, 1);
-      }
-      umma_commit(&bars[2]);
-    }
-    // ---- meanwhile: V indices of token `tid` -> MN-major operand tile (same physical layout) ----
-    pf_dequant_token<VB>(st + P.L.v_idx_off + tid * (16 * VB), vtile + tile_row, lv_base);
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    if (!pf_wait(&bars[2], (uint32_t)(i & 1))) *fail = 1;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    // ---- softmax over this page for row `tid` ----
-    const float* ksc = reinterpret_cast<const float*>(st + P.L.k_scale_off);
-    const float* vsc = reinterpret_cast<const float*>(st + P.L.v_scale_off);
-    const int t0 = (page_lo + i) * PT;
-    float mx = -INFINITY;
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
-      uint32_t v[32];
-      tmem_ld32(tm + TSc + 32 * c, v);
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int t = 32 * c + j;
-        const float sv = __uint_as_float(v[j]) * ksc[t];
-        mx = fmaxf(mx, (t0 + t <= pos) ? sv : -INFINITY);
-      }
-    }
-    const float m_new = fmaxf(m_run, mx);
-    const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row that has seen nothing yet
-    const float resc = pf_exp2(m_run - m_use);
-    m_run = m_new;
-    l_run *= resc;
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
-      uint32_t v[32], u[16];
-      tmem_ld32(tm + TSc + 32 * c, v);
-#pragma unroll
-      for (int j = 0; j < 32; j += 2) {
-        const int t = 32 * c + j;
-        const bool s0 = t0 + t <= pos, s1 = t0 + t + 1 <= pos;
-        const float p0 = s0 ? pf_exp2(__uint_as_float(v[j]) * ksc[t] - m_use) : 0.f;
-        const float p1 = s1 ? pf_exp2(__uint_as_float(v[j + 1]) * ksc[t + 1] - m_use) : 0.f;
-        l_run += p0 + p1;
-        u[j >> 1] = pf_pack(s0 ? p0 * vsc[t] : 0.f, s1 ? p1 * vsc[t + 1] : 0.f);
-      }
-      tmem_st16(tm + TPc + 16 * c, u);  // P chunk c overlays S columns that have been consumed
-    }
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-    if (resc != 1.0f) {
-#pragma unroll
-      for (int j = 0; j < TQ_D; ++j) o[j] *= resc;
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (*fail) break;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    // O_page[128 rows x 128 dims] = P (tensor memory) . V in two N=64 halves through the same 64 columns
-#pragma unroll 1
-    for (int h = 0; h < 2; ++h) {
-      if (tid == 0) {
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma_ts(*tbase + TOc, *tbase + TPc + ks * 8, umma_desc(sptr(vtile) + h * 1024 + ks * 4096, 2048, 128),
-                  idesc_o, ks > 0);
-        umma_commit(&bars[3]);
-      }
-      if (!pf_wait(&bars[3], (uint32_t)((2 * i + h) & 1))) *fail = 1;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (h == 0) {
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t v[32];
-          tmem_ld32(tm + TOc + 32 * c, v);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) o[32 * c + j] += __uint_as_float(v[j]);
-        }
-      } else {
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t v[32];
-          tmem_ld32(tm + TOc + 32 * c, v);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) o[64 + 32 * c + j] += __uint_as_float(v[j]);
-        }
-      }
-      if (h == 0) {  // everybody has read half 0 before half 1 overwrites the columns
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      }
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();  // operand tiles, the page record and the S / O columns are free again
-    if (*fail) break;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  }
-  const bool failed = *fail != 0;
-  if (failed) {  // a prefetched page may still be on its way: give it the same bounded time before leaving
-    for (int st_i = 0; st_i < 2; ++st_i) pf_wait(&bars[st_i], 0), pf_wait(&bars[st_i], 1);
-  }
-  // every tensor-core operation of this CTA has completed: give the tensor memory back before the epilogue
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(*tbase), "r"(256u) : "memory");
-  if (failed) {
-    if (tid == 0) atomicExch(P.status, 1);
-    return;
-  }
-  if (ns > 1) {
-    // ---- split partial out; the last split of this row block to finish folds them (fixed order) ----
-    const size_t slot0 = (((size_t)b * P.hkv + kvh) * P.row_blocks + rb) * P.num_splits;
-    {
-      float4* po = reinterpret_cast<float4*>(P.part_o + ((slot0 + split) * PF_ROWS + tid) * TQ_D);
-#pragma unroll
-      for (int j = 0; j < TQ_D; j += 4) po[j >> 2] = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
-      reinterpret_cast<float2*>(P.part_ml)[(slot0 + split) * PF_ROWS + tid] = make_float2(m_run, l_run);
-    }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-      int* tk = P.tickets + ((size_t)b * P.hkv + kvh) * P.row_blocks + rb;
-      const int prev = atomicAdd(tk, 1);
-      int last = 0;
-      if (prev == ns - 1) {
-        *tk = 0;  // zero again for the next call
-        last = 1;
-      }
-      *fail = last;  // reuse the flag word as "this CTA merges"
-    }
-    __syncthreads();
-    if (!*fail) return;
-    __threadfence();
-    float M = -INFINITY;
-    for (int s_i = 0; s_i < ns; ++s_i)
-      M = fmaxf(M, __ldcg(reinterpret_cast<const float2*>(P.part_ml) + (slot0 + s_i) * PF_ROWS + tid).x);
-#pragma unroll
-    for (int j = 0; j < TQ_D; ++j) o[j] = 0.f;
-    l_run = 0.f;
-    for (int s_i = 0; s_i < ns; ++s_i) {
-      const float2 ml = __ldcg(reinterpret_cast<const float2*>(P.part_ml) + (slot0 + s_i) * PF_ROWS + tid);
-      const float f = ml.x == -INFINITY ? 0.f : exp2f(ml.x - M);
-      l_run = fmaf(ml.y, f, l_run);
-      const float4* po = reinterpret_cast<const float4*>(P.part_o + ((slot0 + s_i) * PF_ROWS + tid) * TQ_D);
-#pragma unroll
-      for (int j = 0; j < TQ_D; j += 4) {
-        const float4 v = __ldcg(po + (j >> 2));
-        o[j] = fmaf(v.x, f, o[j]); o[j + 1] = fmaf(v.y, f, o[j + 1]);
-        o[j + 2] = fmaf(v.z, f, o[j + 2]); o[j + 3] = fmaf(v.w, f, o[j + 3]);
-      }
-    }
-  }
-  // ---- epilogue: normalise, rotate back, store ----
-  {
-    const float inv = l_run > 0.f ? 1.0f / (l_run * fv.lut_alpha) : 0.f;
-#pragma unroll
-    for (int j = 0; j < TQ_D; ++j) o[j] *= inv;
-    if (P.v_rot) {
-      float* ys = reinterpret_cast<float*>(ktile);  // [k][row]
-#pragma unroll
-      for (int k = 0; k < TQ_D; ++k) ys[k * PF_ROWS + tid] = o[k];
-#pragma unroll
-      for (int j = 0; j < TQ_D; ++j) o[j] = 0.f;
-      for (int k = 0; k < TQ_D; ++k) {
-        const float yv = ys[k * PF_ROWS + tid];
-        const float4* rr = reinterpret_cast<const float4*>(P.v_rot + (size_t)k * TQ_D);
-#pragma unroll
-        for (int j = 0; j < TQ_D; j += 4) {
-          const float4 r4 = __ldg(rr + (j >> 2));
-          o[j] = fmaf(r4.x, yv, o[j]); o[j + 1] = fmaf(r4.y, yv, o[j + 1]);
-          o[j + 2] = fmaf(r4.z, yv, o[j + 2]); o[j + 3] = fmaf(r4.w, yv, o[j + 3]);
-        }
-      }
-    } else {
-      row_wht128(o, fv.s2, fv.s1);  // R^T = D1 (H/sqrt d) D2
-    }
-    if (row_ok) {
-      const size_t ooff = (((size_t)b * P.tq + qi) * P.hq + (size_t)kvh * P.group + hl) * TQ_D;
-      if (P.out_dtype == TQ_F32) {
-        float4* op = reinterpret_cast<float4*>(reinterpret_cast<float*>(P.out) + ooff);
-#pragma unroll
-        for (int j = 0; j < TQ_D; j += 4) op[j >> 2] = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
-      } else if (P.out_dtype == TQ_F16) {
-        uint2* op = reinterpret_cast<uint2*>(reinterpret_cast<__half*>(P.out) + ooff);
-#pragma unroll
-        for (int j = 0; j < TQ_D; j += 4) op[j >> 2] = make_uint2(pf_pack(o[j], o[j + 1]), pf_pack(o[j + 2], o[j + 3]));
-      } else {
-        __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(P.out) + ooff;
-#pragma unroll
-        for (int j = 0; j < TQ_D; ++j) op[j] = __float2bfloat16_rn(o[j]);
-      }
-    }
-  }
-}
-
-
 // ------------------------------------------------------------------------------------------
-// k_prefill_attn2: the same computation with the work split over specialised warps (one CTA per SM, 288 threads):
+// k_prefill_attn2: the work split over specialised warps (one CTA per SM, 288 threads):
 //   warps 0-3  rows: thread r owns row r = lane r of tensor memory: reads S, online softmax, writes P, rescales O
 //              (lazily: only when its row maximum grows by more than 2^4), epilogue;
 //   warps 4-7  producer: thread t dequantizes token t of the page (K, then V) into double-buffered operand tiles
@@ -1059,7 +698,7 @@ struct PfPlan {
   size_t part_o, part_ml, total;
 };
 static const size_t PF_TAIL = 65536 * 4 + 256;  // tickets + status word, at the end of the workspace
-static const long PF_CTA_COST_PAGES = 2;  // prologue, partial and merge of a CTA, in units of one page of the main loop
+static const long PF_CTA_COST_PAGES = 16;  // prologue, partial and merge of a CTA, in units of one page of the main loop
 
 static PfPlan pf_plan(int batch, int chunk_tokens, int hq, int hkv, int max_pages) {
   PfPlan p;
