@@ -359,7 +359,7 @@ def run_ours(args):
                          "peak_source": f"{peak_src} copy bandwidth",
                          # dram__bytes_read.sum + dram__bytes_write.sum of one launch, ncu capture summarised in
                          # profiles/k_decode_attn_turbo3_ctx32768.md
-                         "traffic": 27321600,
+                         "traffic": 27338240,
                          "kernel": "k_decode_attn_g4<3,3>", "us_per_launch": kernel_s * 1e6,
                          "bytes_per_launch": CTX * HKV * BYTES_PER_KV_TOKEN},
             "roofline_quantize": {"bound": "hbm", "kernel": "k_quantize_mma<half,3>, 2 launches of 2^22 vectors into pages",
