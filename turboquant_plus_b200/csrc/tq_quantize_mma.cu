@@ -9,11 +9,13 @@
 //   * for each i, one m16n8k16 MMA per 8 output columns contracts the 16 inputs x[v][16 i + j'] with
 //     sign1[16 i + j'] * H16[j'][j].  Inputs are 16-bit, the matrix entries are +-1: every product is exact and
 //     the sums are accumulated in fp32;
-//   * thread (g, t) then holds, for vectors g and g + 8 and for every i, the columns j = 8 nt + 2 t + c: the 8-point
-//     transform over i is three butterfly stages in its own registers;
+//   * the 16 output columns are dealt to the two n-tiles so that thread (g, t) holds, for vectors g and g + 8 and
+//     for every i, the four consecutive columns j = 4 t .. 4 t + 3: the 8-point transform over i is three butterfly
+//     stages in its own registers (the last one negated, so that the sign bit alone decides the centre boundary);
 //   * ||x|| is taken from the transformed values (||H x||^2 = 128 ||x||^2), magnitudes are compared against the
-//     positive boundaries scaled by ||x|| sqrt(d), the sign comes from the value itself, sign2 mirrors the index,
-//     and eight indices at a time are packed by an exact fp32 Horner sum;
+//     positive boundaries scaled by ||x|| sqrt(d) (two tests for 3 bits), sign2 mirrors the index by an XOR, eight
+//     indices at a time are packed by an exact fp32 Horner sum, and the norm correction comes from a
+//     population-count histogram of the magnitude levels;
 //   * a 4 x 4 transpose of words inside each quad of lanes leaves every lane with 32 consecutive indices of its
 //     vector, which it stores as the reference's most-significant-bit-first stream (turboquant/utils.py pack_indices
 //     order, the layout the cache keeps).
