@@ -224,6 +224,12 @@ int tq_decode_attn(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cach
  * the workspace and the output written, afterwards).  Set it when the preceding kernel does not write
  * those three -- e.g. the attention call of another layer -- or never signals early completion. */
 #define TQ_DECODE_OVERLAP 8
+/* TQ_DECODE_SPARSE_V (bit 4): sparse V as in the reference's docs/papers/sparse-v-dequant.md:64-84 -- the V
+ * dequantization and accumulation are skipped where the attention weight exp(score - running max) is below 1e-6;
+ * here per 16-token tile of a warp (skipped when every weight of the tile, for every query head of the group, is
+ * below the threshold).  The weights still count in the softmax denominator.  Off by default: results then differ
+ * from dense attention by at most (number of skipped positions) x 1e-6 relative to the largest weight. */
+#define TQ_DECODE_SPARSE_V 16
 int tq_decode_attn_phases(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cache_layout* layout,
                           const uint8_t* pool_dev, const int32_t* block_table_dev,
                           int32_t max_pages_per_seq, const int32_t* seq_lens_dev, const void* q_dev,

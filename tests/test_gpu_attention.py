@@ -359,3 +359,31 @@ def test_many_splits_long_context(tq):
     assert err < TOL
     out2 = cache.attend(torch.as_tensor(q).cuda(), bt, torch.tensor([n]), overlap=True).cpu().numpy()
     assert np.array_equal(out, out2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("group", [4, 8])
+def test_sparse_v_option(tq, group):
+    """TQ_DECODE_SPARSE_V skips the V work of 16-token tiles whose weights are all below 1e-6 of the running maximum
+    (the reference's sparse V, docs/papers/sparse-v-dequant.md:64-84).  With keys of very different norms most tiles
+    qualify; the output must stay within the attention tolerance of the dense oracle and within 1e-4 of the dense
+    kernel, and on flat weights (nothing below the threshold) it must equal the dense kernel bit for bit."""
+    import torch
+    rng = np.random.default_rng(41 + group)
+    n, hkv = 6000, 2
+    hq = hkv * group
+    cache = tq.PagedKVCache(D, hkv, num_pages=(n + 127) // 128, seed=42)
+    scale = np.exp(1.2 * rng.standard_normal((n, hkv, 1)))          # a few tokens dominate the softmax
+    ks = [(rng.standard_normal((n, hkv, D)) * scale).astype(np.float16)]
+    vs = [rng.standard_normal((n, hkv, D)).astype(np.float16)]
+    bt = fill_cache(cache, ks, vs, [n], rng)
+    q = (3.0 * rng.standard_normal((1, hq, D))).astype(np.float32)
+    qd = torch.as_tensor(q).cuda()
+    dense = cache.attend(qd, bt, torch.tensor([n])).cpu().numpy()
+    sparse = cache.attend(qd, bt, torch.tensor([n]), sparse_v=True).cpu().numpy()
+    ref = oracle_attention(cache, ks, vs, q, [n])
+    print(f"group {group}: sparse vs oracle {max_rel(sparse, ref):.2e}, sparse vs dense kernel {max_rel(sparse, dense):.2e}")
+    assert max_rel(sparse, ref) < TOL and max_rel(sparse, dense) < 1e-4
+    flat = cache.attend(torch.zeros_like(qd), bt, torch.tensor([n]))
+    flat_s = cache.attend(torch.zeros_like(qd), bt, torch.tensor([n]), sparse_v=True)
+    assert torch.equal(flat, flat_s)

@@ -18,6 +18,7 @@ ROT_DENSE, ROT_WHT = 0, 1
 FMT_TURBO2, FMT_TURBO3, FMT_TURBO4, FMT_Q8_0 = 2, 3, 4, 8
 FMT_PROD2, FMT_PROD3, FMT_PROD4 = 18, 19, 20
 DECODE_OVERLAP = 8  # tq_decode_attn_phases: TQ_DECODE_OVERLAP
+DECODE_SPARSE_V = 16  # TQ_DECODE_SPARSE_V
 FORMATS = {"turbo2": FMT_TURBO2, "turbo3": FMT_TURBO3, "turbo4": FMT_TURBO4, "q8_0": FMT_Q8_0,
            "prod2": FMT_PROD2, "prod3": FMT_PROD3, "prod4": FMT_PROD4}
 

@@ -30,6 +30,11 @@ constexpr int ATT_WARPS = 8;
 constexpr int ATT_STAGES = 3;
 constexpr int MAX_G = 8;  // query heads per KV head handled by one N=8 MMA tile
 constexpr long long WAIT_CYCLES = 1LL << 30;  // ~0.5 s at the SM clock: upper bound of any single wait
+// Sparse V (docs/papers/sparse-v-dequant.md:64-84 of the reference: "if (attn_weight < 1e-6f) continue;" before the V
+// dequantization of a position, the weight being exp(score - running max)): here the unit is a 16-token tile of one
+// warp -- the tile's V lookups and MMAs are skipped when every weight in it, for every head, is below the threshold.
+// The weights still enter the softmax denominators.
+constexpr float SPARSE_V_TAU = 1e-6f;
 constexpr int MAX_TICKETS = 65536;                    // (sequence, kv head) pairs per call
 constexpr size_t TAIL_BYTES = (size_t)MAX_TICKETS * 4 + 256;  // tickets + status word at the end of a workspace
 
@@ -156,6 +161,7 @@ struct AttnParams {
   int32_t max_pages, batch, hq, hkv, group, chunk_pages, num_splits;
   int32_t stages;      // 2 or 3 page records in flight per CTA
   int32_t overlap;     // launched with programmatic stream serialization: see TQ_DECODE_OVERLAP
+  int32_t sparse_v;    // skip the V work of a 16-token tile whose weights are all below SPARSE_V_TAU: TQ_DECODE_SPARSE_V
   tq_cache_layout L;
 };
 
@@ -638,6 +644,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn(const AttnParams
           o[j][0] *= r0; o[j][1] *= r1; o[j][2] *= r0; o[j][3] *= r1;
         }
       }
+      if (P.sparse_v && !__any_sync(0xffffffffu, fmaxf(fmaxf(p00, p01), fmaxf(p10, p11)) >= SPARSE_V_TAU)) continue;
       // probabilities (* V scale), as fp16, transposed into the B-operand layout (tokens on K)
       float vs0 = 1.0f, vs1 = 1.0f;
       if (!VT::Q8) {
@@ -1041,6 +1048,7 @@ __global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_c
       const float p0 = fast_exp2(sc0 - m0), p1 = fast_exp2(sc1 - m1);
       l0 += p0;
       l1 += p1;
+      if (P.sparse_v && !__any_sync(0xffffffffu, fmaxf(p0, p1) >= SPARSE_V_TAU)) continue;
       const float vs = ok ? *reinterpret_cast<const float*>(st + vs_off + 4 * tb) : 0.f;
       const uint32_t hp = pack_h2(p0 * vs, p1 * vs);
       uint32_t pb[4];
@@ -1376,6 +1384,7 @@ extern "C" int tq_decode_attn_phases(const tq_quantizer* kq, const tq_quantizer*
   P.num_splits = plan.num_splits;
   P.stages = L->record_bytes > 24 * 1024 ? 2 : 3;
   P.overlap = (phases & TQ_DECODE_OVERLAP) ? 1 : 0;
+  P.sparse_v = (phases & TQ_DECODE_SPARSE_V) ? 1 : 0;
   P.L = *L;
   TqFast none;
   memset(&none, 0, sizeof(none));

@@ -127,7 +127,8 @@ class PagedKVCache:
             self._ws = torch.zeros((int(need),), dtype=torch.uint8, device=self.device)
         return self._ws
 
-    def attend(self, q, block_table, seq_lens, scale=None, out=None, workspace=None, phases=7, overlap=False):
+    def attend(self, q, block_table, seq_lens, scale=None, out=None, workspace=None, phases=7, overlap=False,
+               sparse_v=False):
         """q: (batch, num_q_heads, head_dim) CUDA tensor; block_table: (batch, max_pages) int32 page
         numbers; seq_lens: (batch,) int32.  Returns (batch, num_q_heads, head_dim) in q's dtype.
 
@@ -137,6 +138,8 @@ class PagedKVCache:
         not signal early completion)."""
         if overlap:
             phases = int(phases) | nv.DECODE_OVERLAP
+        if sparse_v:  # skip V work where every weight of a 16-token tile is below 1e-6 (the reference's sparse V)
+            phases = int(phases) | nv.DECODE_SPARSE_V
         torch = nv.require_cuda()
         q = q.contiguous()
         bsz, hq, d = q.shape
