@@ -115,6 +115,23 @@ int tq_dequantize(const tq_quantizer* q, const uint8_t* packed_dev, const uint8_
                   float shrinkage, int64_t n, void* out_dev, int32_t out_dtype, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * tq_quantize_residual: PolarQuant.quantize_and_residual (turboquant/polar_quant.py:121-132) in one
+ * launch, dense mode, fp64 arithmetic: indices (one per byte; or NULL), norms (or NULL) and
+ * x - dequantize(indices, norms) as fp64 rows of stride ld_res elements.  x may be a column slice of
+ * a wider matrix (row stride ld), and so may the residual: the two sub-vector quantizers of
+ * OutlierTurboQuant.quantize (turboquant/outlier.py:110-150) write the halves of one residual
+ * matrix, which tq_qjl_quantize then sketches.
+ * tq_dequantize_strided: PolarQuant.dequantize into (accumulate = 0) or added onto (accumulate = 1)
+ * a column slice of fp64 rows of stride ld_out: the scatter-and-add of OutlierTurboQuant.dequantize
+ * (turboquant/outlier.py:180-208).
+ * ------------------------------------------------------------------------------------------ */
+int tq_quantize_residual(const tq_quantizer* q, const void* x_dev, int32_t x_dtype, int64_t ld, int64_t n,
+                         uint8_t* out_idx_dev, float* out_norm_dev, double* out_residual_dev,
+                         int64_t ld_res, void* stream);
+int tq_dequantize_strided(const tq_quantizer* q, const uint8_t* idx_dev, const float* norm_dev, int64_t n,
+                          double* out_dev, int64_t ld_out, int32_t accumulate, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Primitives with their own reference functions.
  * ------------------------------------------------------------------------------------------ */
 /* utils.pack_indices (turboquant/utils.py:71-98): count indices (one per byte) -> MSB-first

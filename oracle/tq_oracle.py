@@ -285,6 +285,60 @@ def prod_ratio(d, bit_width, original_bits=16):
 
 
 # --------------------------------------------------------------------------
+# outlier.py
+# --------------------------------------------------------------------------
+def outlier_split(d: int, target_bits: float):
+    """(n_outlier, high_bits, n_normal, low_bits): round(d * frac) leading channels get one more bit.
+    turboquant/outlier.py:45-66."""
+    low = int(np.floor(target_bits))
+    n_out = int(round(d * (target_bits - low)))
+    return n_out, low + 1, d - n_out, low
+
+
+class OutlierOracle:
+    """Fractional bit rates: the first n_outlier channels are their own PolarQuant sub-vector at
+    (high_bits - 1) bits with the rotation drawn from ``seed``, the remaining channels another at
+    (low_bits - 1) bits with ``seed + 500``; one QJL (``seed + 1000``) sketches the residual of the whole
+    vector.  turboquant/outlier.py:69-108 (constructor), :110-178 (quantize), :180-208 (dequantize)."""
+
+    def __init__(self, d: int, target_bits: float, seed: int = 42):
+        self.d = d
+        self.n_out, self.high_bits, self.n_norm, self.low_bits = outlier_split(d, target_bits)
+        self.effective_bits = (self.n_out * self.high_bits + self.n_norm * self.low_bits) / d
+        self.r_out = dense_rotation(self.n_out, np.random.default_rng(seed)) if self.n_out > 0 else None
+        self.r_norm = dense_rotation(self.n_norm, np.random.default_rng(seed + 500)) if self.n_norm > 0 else None
+        self.c_out = centroids(self.high_bits - 1, self.n_out) if self.n_out > 0 else None
+        self.c_norm = centroids(self.low_bits - 1, self.n_norm) if self.n_norm > 0 else None
+        self.s = qjl_matrix(d, np.random.default_rng(seed + 1000))
+
+    def quantize(self, x: np.ndarray) -> dict:
+        """x: (batch, d).  Keys follow OutlierCompressedVector (turboquant/outlier.py:33-42)."""
+        res = np.zeros(x.shape, dtype=np.float64)
+        code = {}
+        if self.n_out > 0:
+            code["outlier_indices"], code["outlier_norms"], res[:, :self.n_out] = polar_residual(
+                x[:, np.arange(self.n_out)], self.r_out, self.c_out)   # fancy indexing as at outlier.py:119: the
+            # copy it makes has its own memory order, which decides the summation order of the norm
+        if self.n_norm > 0:
+            code["normal_indices"], code["normal_norms"], res[:, self.n_out:] = polar_residual(
+                x[:, np.arange(self.n_out, self.d)], self.r_norm, self.c_norm)
+        code["qjl_signs"], code["residual_norms"] = qjl_quantize(res, self.s)
+        return code
+
+    def dequantize(self, code: dict) -> np.ndarray:
+        out = qjl_dequantize(code["qjl_signs"], code["residual_norms"], self.s)
+        if self.n_out > 0:
+            out[:, :self.n_out] += polar_dequantize(code["outlier_indices"], code["outlier_norms"], self.r_out, self.c_out)
+        if self.n_norm > 0:
+            out[:, self.n_out:] += polar_dequantize(code["normal_indices"], code["normal_norms"], self.r_norm, self.c_norm)
+        return out
+
+    def compression_ratio(self, original_bits: int = 16) -> float:
+        """Three 32-bit norms per vector.  turboquant/outlier.py:210-217."""
+        return self.d * original_bits / (self.d * self.effective_bits + 96)
+
+
+# --------------------------------------------------------------------------
 # utils.py
 # --------------------------------------------------------------------------
 def pack_signs(z: np.ndarray) -> np.ndarray:

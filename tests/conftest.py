@@ -45,5 +45,10 @@ def g_prim():
 
 
 @pytest.fixture(scope="session")
+def g_outlier():
+    return load_golden("outlier_d128.npz")
+
+
+@pytest.fixture(scope="session")
 def g_kv():
     return load_golden("kv_attention.npz")

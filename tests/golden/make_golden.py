@@ -196,6 +196,29 @@ def main():
     kv["stats_keys"] = np.array(sorted(st))
     kv["stats_vals"] = np.array([st[k] for k in sorted(st)], dtype=np.float64)
     np.savez_compressed(os.path.join(HERE, "kv_attention.npz"), **kv)
+    # ---------------- OutlierTurboQuant (fractional bit rates) ----------------
+    from turboquant.outlier import OutlierTurboQuant
+    xo = keys(48, 23).astype(np.float64)
+    xo[7] = 0.0
+    outl = {"x": xo}
+    for tb in (2.5, 3.5, 3.25):
+        oq = OutlierTurboQuant(D, tb, seed=42)
+        c = oq.quantize(xo)
+        tag = f"t{int(round(tb * 100))}"
+        outl[f"{tag}_split"] = np.array([oq.n_outlier, oq.high_bits, oq.n_normal, oq.low_bits])
+        outl[f"{tag}_outlier_idx"] = c.outlier_indices.astype(np.uint8)
+        outl[f"{tag}_outlier_norms"] = c.outlier_norms
+        outl[f"{tag}_normal_idx"] = c.normal_indices.astype(np.uint8)
+        outl[f"{tag}_normal_norms"] = c.normal_norms
+        outl[f"{tag}_signs"] = pack_bits(c.qjl_signs)
+        outl[f"{tag}_rnorms"] = c.residual_norms
+        outl[f"{tag}_deq"] = oq.dequantize(c)
+        outl[f"{tag}_ratio"] = np.asarray(oq.compression_ratio())
+        outl[f"{tag}_effective_bits"] = np.asarray(oq.effective_bits)
+        c1 = oq.quantize(xo[3])
+        outl[f"{tag}_single_deq"] = oq.dequantize(c1)
+    np.savez_compressed(os.path.join(HERE, "outlier_d128.npz"), **outl)
+
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)) // 1024, "KB")

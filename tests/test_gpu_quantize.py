@@ -108,6 +108,97 @@ def test_prod_golden(tq, g_const, g_prod, mode, b):
     assert t.compressed_size_bits(100) == 100 * (128 * b + 32)
 
 
+@pytest.mark.parametrize("target_bits", [2.5, 3.5, 3.25])
+def test_outlier_golden(tq, g_outlier, target_bits):
+    """OutlierTurboQuant (turboquant/outlier.py) against the fixture made by running the reference: same split, the
+    indices of both channel groups (equal outside the boundary band), norms to 1e-6, sign sketch of the whole residual
+    (a sign may differ only where the projection is within rounding of zero), reconstruction from the reference's own
+    code and from ours."""
+    g, tag = g_outlier, f"t{int(round(target_bits * 100))}"
+    x = g["x"]
+    oq = tq.OutlierTurboQuant(D, target_bits, seed=42)
+    orc = o.OutlierOracle(D, target_bits, seed=42)
+    assert [oq.n_outlier, oq.high_bits, oq.n_normal, oq.low_bits] == g[f"{tag}_split"].tolist()
+    assert oq.effective_bits == float(g[f"{tag}_effective_bits"]) and oq.compression_ratio() == float(g[f"{tag}_ratio"])
+    c = oq.quantize(x)
+    assert c.effective_bits == oq.effective_bits
+    rows_ok = np.ones(len(x), dtype=bool)
+    for name, sl, rot, cb in (("outlier", slice(0, oq.n_outlier), orc.r_out, orc.c_out),
+                              ("normal", slice(oq.n_outlier, D), orc.r_norm, orc.c_norm)):
+        idx, nrm = getattr(c, name + "_indices"), getattr(c, name + "_norms")
+        _, _, y = o.polar_quantize(np.ascontiguousarray(x[:, sl]), rot, cb, return_rotated=True)
+        mism, _ = check_indices(idx, g[f"{tag}_{name}_idx"], y, cb)
+        assert idx.dtype == np.int64 and nrm.dtype == np.float64
+        assert np.allclose(nrm, g[f"{tag}_{name}_norms"], rtol=1e-6, atol=0)
+        rows_ok &= (idx == g[f"{tag}_{name}_idx"]).all(axis=1)
+        assert np.array_equal(pq_rotation(oq, name), rot)
+    ref_signs = o.unpack_signs(g[f"{tag}_signs"], D)
+    assert c.qjl_signs.dtype == np.int8 and set(np.unique(c.qjl_signs)) <= {-1, 1}
+    flips = (c.qjl_signs != ref_signs)[rows_ok]
+    assert flips.sum() == 0, f"{int(flips.sum())} sign flips"
+    assert (c.qjl_signs[7] == 1).all() and c.residual_norms[7] == 0.0          # the zero vector
+    assert np.allclose(c.residual_norms[rows_ok], g[f"{tag}_rnorms"][rows_ok], rtol=1e-6)
+    ref = g[f"{tag}_deq"]
+    scale = np.maximum(np.abs(ref).max(axis=1, keepdims=True), 1e-300)
+    ref_code = tq.OutlierCompressedVector(
+        outlier_indices=g[f"{tag}_outlier_idx"].astype(np.int64), outlier_norms=g[f"{tag}_outlier_norms"],
+        normal_indices=g[f"{tag}_normal_idx"].astype(np.int64), normal_norms=g[f"{tag}_normal_norms"],
+        qjl_signs=ref_signs, residual_norms=g[f"{tag}_rnorms"], effective_bits=oq.effective_bits)
+    assert (np.abs(oq.dequantize(ref_code) - ref) / scale).max() < 1e-7        # norms travel as fp32
+    assert (np.abs(oq.dequantize(c) - ref)[rows_ok] / scale[rows_ok]).max() < 1e-6
+    # single-vector convention (turboquant/outlier.py:152-165) and batch == single (tests/test_outlier.py:82-97)
+    c1 = oq.quantize(x[3])
+    assert c1.qjl_signs.shape == (D,) and np.shape(c1.residual_norms) == () and c1.outlier_indices.shape == (oq.n_outlier,)
+    x1 = oq.dequantize(c1)
+    assert x1.shape == (D,) and np.abs(x1 - g[f"{tag}_single_deq"]).max() < 1e-6 * np.abs(x1).max()
+    assert np.abs(x1 - oq.dequantize(c)[3]).max() < 1e-10 * np.abs(x1).max()
+
+
+def pq_rotation(oq, name):
+    return getattr(oq, "pq_" + name).rotation
+
+
+def test_outlier_quality_and_device_path(tq):
+    """Round-trip quality as the reference tests it (tests/test_outlier.py:30-48: 3.5 bits on unit vectors, mean MSE
+    below twice the 3-bit bound), an integer rate (no outlier group) and CUDA tensors in and out, fp32 input."""
+    import torch
+    rng = np.random.default_rng(99)
+    x = rng.standard_normal((200, D))
+    x /= np.linalg.norm(x, axis=1, keepdims=True)
+    oq = tq.OutlierTurboQuant(D, 3.5, seed=42)
+    mse = np.mean((x - oq.dequantize(oq.quantize(x))) ** 2)
+    assert mse < 0.03 * 2.0
+    orc = o.OutlierOracle(D, 3.5, seed=42)
+    assert abs(mse - np.mean((x - orc.dequantize(orc.quantize(x))) ** 2)) < 1e-9
+    whole = tq.OutlierTurboQuant(D, 3.0, seed=42)
+    assert whole.n_outlier == 0 and whole.pq_outlier is None
+    cw = whole.quantize(x)
+    assert cw.outlier_indices.size == 0
+    ow = o.OutlierOracle(D, 3.0, seed=42)
+    assert np.abs(whole.dequantize(cw) - ow.dequantize(ow.quantize(x))).max() < 1e-6
+    xt = torch.as_tensor(x, dtype=torch.float32).cuda()
+    ct = oq.quantize(xt)
+    assert ct.qjl_signs.is_cuda and ct.outlier_indices.dtype == torch.uint8
+    back = oq.dequantize(ct)
+    assert back.is_cuda and back.dtype == torch.float64
+    ref32 = orc.dequantize(orc.quantize(x.astype(np.float32).astype(np.float64)))
+    rows = (ct.outlier_indices.cpu().numpy() == orc.quantize(x.astype(np.float32).astype(np.float64))["outlier_indices"]).all(axis=1)
+    assert rows.mean() > 0.9 and np.abs(back.cpu().numpy() - ref32)[rows].max() < 1e-5
+
+
+def test_polar_residual_fused(tq, g_polar):
+    """PolarQuant.quantize_and_residual (turboquant/polar_quant.py:121-132), dense mode, in one launch."""
+    x = g_polar["x"].astype(np.float64)
+    q = tq.PolarQuant(D, 3, seed=42)
+    idx, nrm, res = q.quantize_and_residual(x)
+    ri, rn, rr = o.polar_residual(x, q.rotation, q.centroids)
+    rows = (idx == ri).all(axis=1)
+    assert rows.mean() > 0.9 and np.allclose(nrm, rn, rtol=1e-6)
+    assert np.abs(res - rr)[rows].max() < 1e-12 * np.abs(x).max()
+    i1, n1, r1 = q.quantize_and_residual(x[2])
+    assert i1.shape == (D,) and np.shape(n1) == () and np.abs(r1 - rr[2]).max() < 1e-12 * np.abs(x).max()
+
+
 def test_qjl_golden(tq, g_const, g_qjl):
     qj = tq.QJL(D, seed=123)
     assert np.array_equal(qj.S, g_const["qjl_123"])

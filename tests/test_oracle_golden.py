@@ -122,6 +122,26 @@ def test_attention_matches_reference(g_const, g_kv, mode, kk):
     assert np.array_equal(kv2.s, consts["s"])
 
 
+@pytest.mark.parametrize("target_bits", [2.5, 3.5, 3.25])
+def test_outlier_matches_reference(g_outlier, target_bits):
+    """OutlierTurboQuant (turboquant/outlier.py): channel split, both sub-vector codes, the sign sketch of the whole
+    residual and the reconstruction, bit for bit."""
+    g, tag = g_outlier, f"t{int(round(target_bits * 100))}"
+    oq = o.OutlierOracle(D, target_bits, seed=42)
+    assert [oq.n_out, oq.high_bits, oq.n_norm, oq.low_bits] == g[f"{tag}_split"].tolist()
+    assert oq.effective_bits == float(g[f"{tag}_effective_bits"]) and oq.compression_ratio() == float(g[f"{tag}_ratio"])
+    code = oq.quantize(g["x"])
+    assert np.array_equal(code["outlier_indices"].astype(np.uint8), g[f"{tag}_outlier_idx"])
+    assert np.array_equal(code["normal_indices"].astype(np.uint8), g[f"{tag}_normal_idx"])
+    assert np.array_equal(code["outlier_norms"], g[f"{tag}_outlier_norms"])
+    assert np.array_equal(code["normal_norms"], g[f"{tag}_normal_norms"])
+    assert np.array_equal(o.pack_signs(code["qjl_signs"]), g[f"{tag}_signs"])
+    assert np.array_equal(code["residual_norms"], g[f"{tag}_rnorms"])
+    assert np.array_equal(oq.dequantize(code), g[f"{tag}_deq"])
+    one = oq.dequantize(oq.quantize(g["x"][3:4]))[0]
+    assert np.abs(one - g[f"{tag}_single_deq"]).max() < 1e-13 * np.abs(one).max()   # a lone row sums its norm in another order
+
+
 def test_live_reference_if_present():
     """Differential check against the reference tree itself where it is mounted."""
     import os

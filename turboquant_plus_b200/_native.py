@@ -62,6 +62,8 @@ SIGNATURES = {
     "tq_unpack_bits": (C.c_int, [_P, _I64, _I32, _P, _P]),
     "tq_sign_wht_f64": (C.c_int, [_P, _I64, _I32, _I32, _P, _P, _P, _P]),
     "tq_nearest_centroid_f64": (C.c_int, [_P, _I64, _P, _I32, _P, _P]),
+    "tq_quantize_residual": (C.c_int, [_P, _P, _I32, _I64, _I64, _P, _P, _P, _I64, _P]),
+    "tq_dequantize_strided": (C.c_int, [_P, _P, _P, _I64, _P, _I64, _I32, _P]),
     "tq_qjl_quantize": (C.c_int, [_P, _P, _I32, _I64, _P, _P, _P]),
     "tq_qjl_dequantize": (C.c_int, [_P, _P, _P, _F, _I64, _P, _I32, _P]),
     "tq_cache_layout_init": (C.c_int, [C.POINTER(CacheLayout), _I32, _I32, _I32, _I32, _I32]),

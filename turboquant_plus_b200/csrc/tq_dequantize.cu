@@ -119,6 +119,10 @@ template <> __device__ __forceinline__ double tq_from_double<double>(double v) {
 template <> __device__ __forceinline__ float tq_from_double<float>(double v) { return (float)v; }
 template <> __device__ __forceinline__ __half tq_from_double<__half>(double v) { return __float2half_rn((float)v); }
 
+__device__ __forceinline__ double tq_as_double(double v) { return v; }
+__device__ __forceinline__ double tq_as_double(float v) { return (double)v; }
+__device__ __forceinline__ double tq_as_double(__half v) { return (double)__half2float(v); }
+
 template <typename Tout>
 __global__ void __launch_bounds__(128) k_dequantize_dense(const double* __restrict__ rot, const double* __restrict__ s,
                                                           const double* __restrict__ cent, int d, int bits,
@@ -127,7 +131,7 @@ __global__ void __launch_bounds__(128) k_dequantize_dense(const double* __restri
                                                           const float* __restrict__ norm,
                                                           const uint8_t* __restrict__ qjl,
                                                           const float* __restrict__ rnorm, double shrink, int64_t n,
-                                                          Tout* __restrict__ out) {
+                                                          Tout* __restrict__ out, int64_t ld_out, int accumulate) {
   extern __shared__ __align__(16) double sm[];
   double* ys = sm;                    // [d][DV]
   double* zs = sm + (size_t)d * DV;   // [d][DV] (QJL signs scaled), only when qjl
@@ -202,7 +206,8 @@ __global__ void __launch_bounds__(128) k_dequantize_dense(const double* __restri
         }
         double r = (acc[v] / cn) * (double)norm[v0 + v];
         if (qjl) r += acz[v] * (qc * (double)rnorm[v0 + v]);
-        out[(v0 + v) * d + j] = tq_from_double<Tout>(r);
+        Tout* o = out + (v0 + v) * ld_out + j;
+        *o = accumulate ? tq_from_double<Tout>(tq_as_double(*o) + r) : tq_from_double<Tout>(r);
       }
     }
   }
@@ -259,7 +264,7 @@ extern "C" int tq_dequantize(const tq_quantizer* q, const uint8_t* packed_dev, c
       TQ_CUDA(cudaFuncSetAttribute(k_dequantize_dense<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));  \
     k_dequantize_dense<T><<<grid, 128, smem, st>>>(q->rot, q->s, q->cent64, q->d, q->bits, q->norm_correction,      \
                                                    packed_dev, idx_dev, norm_dev, qjl_dev, rnorm_dev,               \
-                                                   (double)shrinkage, n, (T*)out_dev);                              \
+                                                   (double)shrinkage, n, (T*)out_dev, (int64_t)q->d, 0);            \
   } while (0)
   switch (out_dtype) {
     case TQ_F64: TQ_DD(double); break;
@@ -270,5 +275,25 @@ extern "C" int tq_dequantize(const tq_quantizer* q, const uint8_t* packed_dev, c
       return TQ_ERR_UNSUPPORTED;
   }
 #undef TQ_DD
+  return tq_launch_check("k_dequantize_dense");
+}
+
+extern "C" int tq_dequantize_strided(const tq_quantizer* q, const uint8_t* idx_dev, const float* norm_dev, int64_t n,
+                                     double* out_dev, int64_t ld_out, int32_t accumulate, void* stream) {
+  TQ_REQUIRE(q, TQ_ERR_INVALID, "tq_dequantize_strided: quantizer is null");
+  TQ_REQUIRE(q->rotation == TQ_ROT_DENSE && q->rot, TQ_ERR_UNSUPPORTED,
+             "tq_dequantize_strided: needs a dense-mode quantizer with a rotation");
+  TQ_REQUIRE(n >= 0, TQ_ERR_INVALID, "tq_dequantize_strided: n must be >= 0");
+  if (n == 0) return TQ_OK;
+  TQ_REQUIRE(idx_dev && norm_dev && out_dev, TQ_ERR_INVALID, "tq_dequantize_strided: null buffer");
+  TQ_REQUIRE(ld_out >= q->d, TQ_ERR_INVALID, "tq_dequantize_strided: row stride %lld smaller than d", (long long)ld_out);
+  TQ_REQUIRE(tq_aligned(out_dev, 8), TQ_ERR_ALIGN, "tq_dequantize_strided: output rows must be 8-byte aligned");
+  const size_t smem = (size_t)q->d * DV * 8;
+  const int grid = (int)((n + DV - 1) / DV);
+  if (smem > 48 * 1024)
+    TQ_CUDA(cudaFuncSetAttribute(k_dequantize_dense<double>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  k_dequantize_dense<double><<<grid, 128, smem, (cudaStream_t)stream>>>(
+      q->rot, q->s, q->cent64, q->d, q->bits, q->norm_correction, nullptr, idx_dev, norm_dev, nullptr, nullptr, 1.0, n,
+      out_dev, ld_out, accumulate ? 1 : 0);
   return tq_launch_check("k_dequantize_dense");
 }

@@ -335,6 +335,8 @@ struct TqDenseArgs {
   uint8_t *out_packed, *out_idx;
   float *out_norm, *out_scale, *out_rnorm;
   uint8_t* out_qjl;
+  double* out_res;  // x - dequantize(quantize(x)), fp64 rows of stride ld_res; or null
+  int64_t ld_res;
 };
 
 constexpr int TV = 8;  // vectors per CTA
@@ -436,7 +438,7 @@ __global__ void __launch_bounds__(128) k_quantize_dense(const TqDenseArgs a, con
     cn = cn > 1e-10 ? cn : 1.0;
     if (a.out_scale) a.out_scale[v0 + tid] = (float)(a.norm_correction ? (double)s_normf[tid] / cn : (double)s_normf[tid]);
   }
-  if (a.out_qjl == nullptr && a.out_rnorm == nullptr) return;
+  if (a.out_qjl == nullptr && a.out_rnorm == nullptr && a.out_res == nullptr) return;
 
   // ---- residual + QJL: x_hat = norm * R^T yhat', r = x - x_hat, z = sign(S r) ----
   for (int i = tid; i < d * TV; i += 128) {
@@ -476,6 +478,7 @@ __global__ void __launch_bounds__(128) k_quantize_dense(const TqDenseArgs a, con
       const double res = xs[(size_t)j * TV + v] - acc[v] * (WIDE ? s_norm[v] : (double)s_normf[v]);
       xs[(size_t)j * TV + v] = res;
       racc[v] += res * res;
+      if (a.out_res && v < nv) a.out_res[(v0 + v) * a.ld_res + j] = res;
     }
   }
   if (tid < TV) s_red[tid] = 0.0;
@@ -585,6 +588,34 @@ extern "C" int tq_quantize(const tq_quantizer* q, const void* x_dev, int32_t x_d
   a.out_qjl = out_qjl_dev;
   a.out_rnorm = out_rnorm_dev;
   return launch_dense(q, x_dev, x_dtype, ld, n, a, st);
+}
+
+extern "C" int tq_quantize_residual(const tq_quantizer* q, const void* x_dev, int32_t x_dtype, int64_t ld, int64_t n,
+                                    uint8_t* out_idx_dev, float* out_norm_dev, double* out_residual_dev,
+                                    int64_t ld_res, void* stream) {
+  TQ_REQUIRE(q, TQ_ERR_INVALID, "tq_quantize_residual: quantizer is null");
+  TQ_REQUIRE(q->rotation == TQ_ROT_DENSE && q->rot, TQ_ERR_UNSUPPORTED,
+             "tq_quantize_residual: needs a dense-mode quantizer with a rotation");
+  TQ_REQUIRE(n >= 0, TQ_ERR_INVALID, "tq_quantize_residual: n must be >= 0");
+  if (n == 0) return TQ_OK;
+  TQ_REQUIRE(x_dev && out_residual_dev, TQ_ERR_INVALID, "tq_quantize_residual: null buffer");
+  TQ_REQUIRE(ld >= q->d && ld_res >= q->d, TQ_ERR_INVALID, "tq_quantize_residual: row strides %lld / %lld smaller than d",
+             (long long)ld, (long long)ld_res);
+  TQ_REQUIRE(tq_aligned(out_residual_dev, 8), TQ_ERR_ALIGN, "tq_quantize_residual: residual rows must be 8-byte aligned");
+  TqDenseArgs a;
+  memset(&a, 0, sizeof(a));
+  a.rot = q->rot;
+  a.rot_t = q->rot_t;
+  a.cent = q->cent64;
+  a.bnd = q->bnd64;
+  a.d = q->d;
+  a.bits = q->bits;
+  a.norm_correction = q->norm_correction;
+  a.out_idx = out_idx_dev;
+  a.out_norm = out_norm_dev;
+  a.out_res = out_residual_dev;
+  a.ld_res = ld_res;
+  return launch_dense(q, x_dev, x_dtype, ld, n, a, (cudaStream_t)stream);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -147,6 +147,27 @@ class PolarQuant:
     def quantize_and_residual(self, x):
         """(indices, norms, x - dequantize(indices, norms)) (turboquant/polar_quant.py:121-132)."""
         torch = nv.require_cuda()
+        if not self._is_wht:
+            # dense mode: one launch, the residual taken against the fp64 norm as the reference does
+            xt, was_numpy, src_dtype = to_device(x, self.device, allow_f64=True)
+            if xt.dtype == torch.bfloat16:
+                xt = xt.float()
+            single = xt.dim() == 1
+            xt = xt.reshape(1, -1) if single else xt.reshape(-1, xt.shape[-1])
+            if xt.shape[1] != self.d:
+                raise ValueError(f"expected vectors of dimension {self.d}, got {xt.shape[1]}")
+            n = xt.shape[0]
+            idx = torch.empty((n, self.d), dtype=torch.uint8, device=xt.device)
+            nrm = torch.empty((n,), dtype=torch.float32, device=xt.device)
+            res = torch.empty((n, self.d), dtype=torch.float64, device=xt.device)
+            with torch.cuda.device(xt.device):
+                nv.call("tq_quantize_residual", self._native(xt.device).handle, nv.ptr(xt), nv.torch_dtype_code(xt.dtype),
+                        xt.stride(0), n, nv.ptr(idx), nv.ptr(nrm), nv.ptr(res), self.d, nv.stream_ptr())
+            if was_numpy:
+                idx = idx.cpu().numpy().astype(np.int64)
+                nrm = nrm.cpu().numpy().astype(src_dtype if src_dtype is not None else np.float64)
+                res = res.cpu().numpy()
+            return (idx[0], nrm[0], res[0]) if single else (idx, nrm, res)
         indices, norms = self.quantize(x)
         x_hat = self.dequantize(indices, norms)
         if isinstance(x, torch.Tensor):
