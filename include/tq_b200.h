@@ -132,6 +132,23 @@ int tq_dequantize_strided(const tq_quantizer* q, const uint8_t* idx_dev, const f
                           double* out_dev, int64_t ld_out, int32_t accumulate, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * tq_requantize: temporal decay of stored codes, requantize_3to2 of
+ * benchmarks/temporal_decay_prototype.py:93-125 for any source / destination widths (dst <= src):
+ * old tokens are re-coded with fewer bits without leaving the rotated domain.  Both quantizers are
+ * sign-WHT mode with the same sign vectors (same seed).
+ *   packed_src_dev  n * 16*bits_src bytes, the packed index stream tq_quantize writes
+ *   scale_src_dev   n floats, the factor that multiplies the source centroids (out_scale_dev of
+ *                   tq_quantize: norm / ||centroids[idx]||, the prototype's dequantize_3bit); with
+ *                   scale_is_norm != 0 the vector norms instead, divided by ||centroids[idx]|| here
+ *   packed_dst_dev  n * 16*bits_dst bytes
+ *   norm_dst_dev    n floats, the norm of the source reconstruction (the prototype's recon_norm); or NULL
+ *   scale_dst_dev   n floats, the prototype's corrected_norm: recon_norm / ||centroids_dst[idx_dst]||
+ * ------------------------------------------------------------------------------------------ */
+int tq_requantize(const tq_quantizer* src_q, const tq_quantizer* dst_q, const uint8_t* packed_src_dev,
+                  const float* scale_src_dev, int32_t scale_is_norm, int64_t n, uint8_t* packed_dst_dev,
+                  float* norm_dst_dev, float* scale_dst_dev, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Primitives with their own reference functions.
  * ------------------------------------------------------------------------------------------ */
 /* utils.pack_indices (turboquant/utils.py:71-98): count indices (one per byte) -> MSB-first

@@ -549,3 +549,24 @@ def rope_rotate(x: np.ndarray, positions: np.ndarray, base: float = 10000.0) -> 
     out[..., 0::2] = x[..., 0::2] * c - x[..., 1::2] * s
     out[..., 1::2] = x[..., 0::2] * s + x[..., 1::2] * c
     return out.astype(x.dtype)
+
+
+# --------------------------------------------------------------------------
+# benchmarks/temporal_decay_prototype.py
+# --------------------------------------------------------------------------
+def decay_requantize(idx_src: np.ndarray, norm_src, c_src: np.ndarray, c_dst: np.ndarray, mid_dst: np.ndarray):
+    """One vector's codes re-quantized to a narrower codebook in the rotated domain: dequantize with the norm
+    correction of the source codebook, renormalise, np.digitize against the destination midpoints (a tie goes to the
+    upper cell), corrected norm for the destination codebook.  Returns (idx_dst uint8, corrected_norm).
+    benchmarks/temporal_decay_prototype.py:71-80 (dequantize_3bit), :93-125 (requantize_3to2)."""
+    cs = c_src[idx_src]
+    rn = np.sqrt(np.sum(cs ** 2))
+    values = cs * (norm_src / rn if rn > 1e-10 else norm_src)
+    recon = np.linalg.norm(values)
+    if recon > 1e-10:
+        unit = values / recon
+    else:
+        unit, recon = values, 0.0
+    idx_dst = np.digitize(unit, mid_dst).astype(np.uint8)
+    cn = np.sqrt(np.sum(c_dst[idx_dst] ** 2))
+    return idx_dst, (recon / cn if cn > 1e-10 else recon)

@@ -50,5 +50,10 @@ def g_outlier():
 
 
 @pytest.fixture(scope="session")
+def g_decay():
+    return load_golden("temporal_decay.npz")
+
+
+@pytest.fixture(scope="session")
 def g_kv():
     return load_golden("kv_attention.npz")

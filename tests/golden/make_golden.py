@@ -219,6 +219,24 @@ def main():
         outl[f"{tag}_single_deq"] = oq.dequantize(c1)
     np.savez_compressed(os.path.join(HERE, "outlier_d128.npz"), **outl)
 
+    # ---------------- temporal decay prototype (3 -> 2 bits in the rotated domain) ----------------
+    sys.path.insert(0, os.path.join(REF, "benchmarks"))
+    import temporal_decay_prototype as tdp
+    s1, s2, pd = random_rotation_fast(D, np.random.default_rng(42))
+    xd = keys(64, 31)
+    xd[9] = 0.0
+    dec = {"x": xd, "c3": tdp.CENTROIDS_3BIT, "c2": tdp.CENTROIDS_2BIT, "mid3": tdp.MIDPOINTS_3BIT,
+           "mid2": tdp.MIDPOINTS_2BIT, "idx3": np.zeros((64, D), np.uint8), "norms": np.zeros(64, np.float32),
+           "idx2": np.zeros((64, D), np.uint8), "corrected": np.zeros(64), "deq3": np.zeros((64, D))}
+    for i in range(64):
+        nrm = np.linalg.norm(xd[i])
+        rot = apply_fast_rotation(xd[i] / nrm if nrm > 0 else xd[i], s1, s2, pd)
+        dec["idx3"][i] = tdp.quantize_3bit(rot)
+        dec["norms"][i] = nrm
+        dec["deq3"][i] = tdp.dequantize_3bit(dec["idx3"][i], nrm)
+        dec["idx2"][i], dec["corrected"][i] = tdp.requantize_3to2(dec["idx3"][i], nrm)
+    np.savez_compressed(os.path.join(HERE, "temporal_decay.npz"), **dec)
+
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)) // 1024, "KB")

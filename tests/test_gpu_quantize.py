@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 
 from oracle import tq_oracle as o
-from tests.helpers import D, check_indices, wht_dense
+from tests.helpers import D, boundary_band, check_indices, wht_dense
 
 pytestmark = pytest.mark.gpu
 
@@ -197,6 +197,60 @@ def test_polar_residual_fused(tq, g_polar):
     assert np.abs(res - rr)[rows].max() < 1e-12 * np.abs(x).max()
     i1, n1, r1 = q.quantize_and_residual(x[2])
     assert i1.shape == (D,) and np.shape(n1) == () and np.abs(r1 - rr[2]).max() < 1e-12 * np.abs(x).max()
+
+
+def test_temporal_decay_golden(tq, g_decay):
+    """tq_requantize against the fixture made by running requantize_3to2 of the reference's
+    benchmarks/temporal_decay_prototype.py (its constants as the two codebooks): 2-bit indices equal except where the
+    renormalised value is within the boundary band of a midpoint, corrected norms to 1e-6; then the device path
+    (packed stream and scale straight from quantize_device) against the same restatement, and the argument checks."""
+    import torch
+    from turboquant_plus_b200 import temporal_decay as td
+    g = g_decay
+    src = tq.PolarQuant(D, 3, seed=42, rotation="wht", centroids=g["c3"])
+    dst = tq.PolarQuant(D, 2, seed=42, rotation="wht", centroids=g["c2"])
+    idx2, corrected = td.requantize(src, dst, g["idx3"], g["norms"])
+    unit = g["c3"][g["idx3"]] / np.linalg.norm(g["c3"][g["idx3"]], axis=1, keepdims=True)
+    unit[9] = 0.0
+    mism, _ = check_indices(idx2, g["idx2"], unit, g["c2"])
+    rows = (idx2 == g["idx2"]).all(axis=1)
+    assert rows.mean() > 0.9 and np.allclose(corrected[rows], g["corrected"][rows], rtol=1e-6, atol=0)
+    assert corrected[9] == 0.0
+    i1, c1 = td.requantize(src, dst, g["idx3"][5], g["norms"][5])
+    assert i1.shape == (D,) and np.array_equal(i1, idx2[5]) and c1 == corrected[5]
+    # device path with the Lloyd-Max codebooks, 4 -> 3, 4 -> 2, 3 -> 2, 3 -> 1 bits
+    x = torch.as_tensor(o.synth_keys(4099, seed=3)).cuda().half()
+    for bs, bd in ((4, 3), (4, 2), (3, 2), (3, 1), (2, 2)):
+        a = tq.PolarQuant(D, bs, seed=42, rotation="wht")
+        b = tq.PolarQuant(D, bd, seed=42, rotation="wht")
+        code = a.quantize_device(x, packed=True, want_scale=True)
+        out = td.requantize_device(a, b, code["packed"], code["scale"])
+        ia = o.unpack_idx(code["packed"].cpu().numpy().reshape(-1), bs, len(x) * D).reshape(-1, D)
+        ib = o.unpack_idx(out["packed"].cpu().numpy().reshape(-1), bd, len(x) * D).reshape(-1, D)
+        sc, new_scale, new_norm = code["scale"].cpu().numpy(), out["scale"].cpu().numpy(), out["norm"].cpu().numpy()
+        mid = o.boundaries(b.centroids)
+        bad = 0
+        for r in range(0, len(ia), 41):
+            nrm = sc[r] * np.linalg.norm(a.centroids[ia[r]])
+            want_idx, want_scale = o.decay_requantize(ia[r], nrm, a.centroids, b.centroids, mid)
+            u = a.centroids[ia[r]] / np.linalg.norm(a.centroids[ia[r]])
+            near = np.abs(u[:, None] - mid).min(axis=1) <= boundary_band(b.centroids)
+            assert (ib[r] == want_idx)[~near].all()
+            if (ib[r] == want_idx).all():
+                assert abs(new_scale[r] - want_scale) <= 2e-6 * want_scale and abs(new_norm[r] - nrm) <= 2e-6 * nrm
+            else:
+                bad += 1
+        assert bad <= 2
+        # the narrower code still points the same way: cosine with the source reconstruction
+        ya, yb = a.centroids[ia] * sc[:, None], b.centroids[ib] * new_scale[:, None]
+        cos = (ya * yb).sum(1) / np.maximum(np.linalg.norm(ya, axis=1) * np.linalg.norm(yb, axis=1), 1e-30)
+        print(f"{bs} -> {bd} bits: mean cosine {cos.mean():.4f}")
+        assert cos.mean() > {1: 0.78, 2: 0.93, 3: 0.98}[bd]
+    other = tq.PolarQuant(D, 2, seed=43, rotation="wht")
+    with pytest.raises(ValueError):
+        td.requantize_device(a, other, code["packed"], code["scale"])
+    with pytest.raises(ValueError):
+        td.requantize_device(b, tq.PolarQuant(D, 3, seed=42, rotation="wht"), out["packed"], out["scale"])
 
 
 def test_qjl_golden(tq, g_const, g_qjl):

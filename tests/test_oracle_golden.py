@@ -142,6 +142,15 @@ def test_outlier_matches_reference(g_outlier, target_bits):
     assert np.abs(one - g[f"{tag}_single_deq"]).max() < 1e-13 * np.abs(one).max()   # a lone row sums its norm in another order
 
 
+def test_temporal_decay_matches_reference(g_decay):
+    """requantize_3to2 (benchmarks/temporal_decay_prototype.py:93-125) with the prototype's own constants."""
+    g = g_decay
+    for i in range(len(g["x"])):
+        idx2, corrected = o.decay_requantize(g["idx3"][i], g["norms"][i], g["c3"], g["c2"], g["mid2"])
+        assert np.array_equal(idx2, g["idx2"][i]) and corrected == g["corrected"][i]
+    assert g["corrected"][9] == 0.0 and (g["idx2"][9] == g["idx2"][9][0]).all()      # the zero vector
+
+
 def test_live_reference_if_present():
     """Differential check against the reference tree itself where it is mounted."""
     import os
