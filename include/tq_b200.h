@@ -220,6 +220,27 @@ int tq_cache_store(const tq_cache_layout* layout, uint8_t* pool_dev, int32_t whi
                    const uint8_t* packed_dev, const float* scale_dev, const uint8_t* qjl_dev,
                    const float* rscale_dev, int64_t n_tokens, const int64_t* slot_dev, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Wire / on-disk block formats of the reference's documents (its llama.cpp fork's cache types;
+ * docs/papers/block-size-experiment.md:25-37, docs/papers/turbo4-resurrection.md:125-138,169,208):
+ *   turbo3: fp16 norm | qs[B/4] (low two index bits, element j in bits 2(j%4) of byte j/4) | signs[B/8]
+ *           (third index bit, element j in bit j%8 of byte j/8); B = 32, 64 or 128 elements per block
+ *   turbo2: fp16 norm | qs[B/4]
+ *   turbo4: fp16 norm | fp16 rnorm (unused, written as 0) | qs[64] nibbles, element j in bits 4(j%2)
+ *           of byte j/2; 128 elements per block
+ * The norm of every block of a 128-element vector is the cache's scale (||x|| / ||centroids[idx]||)
+ * rounded to fp16.  Blocks are laid out [n_tokens][num_kv_heads][128 / block_elems][block bytes] for
+ * the tokens at slot_dev[t] (negative: skipped); which = 0 converts the K tensor, 1 the V tensor.
+ * tq_block_bytes: bytes of one block, or -1 for a combination that does not exist.
+ * ------------------------------------------------------------------------------------------ */
+int64_t tq_block_bytes(int32_t format, int32_t block_elems);
+int tq_cache_export_blocks(const tq_cache_layout* layout, const uint8_t* pool_dev, int32_t which,
+                           const int64_t* slot_dev, int64_t n_tokens, int32_t block_elems,
+                           uint8_t* out_dev, void* stream);
+int tq_cache_import_blocks(const tq_cache_layout* layout, uint8_t* pool_dev, int32_t which,
+                           const int64_t* slot_dev, int64_t n_tokens, int32_t block_elems,
+                           const uint8_t* in_dev, void* stream);
+
 /* Scratch for tq_decode_attn (split partials + rotated queries), bytes; 256-byte aligned buffer. */
 int64_t tq_decode_workspace_bytes(int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
                                   int32_t max_pages_per_seq);

@@ -570,3 +570,52 @@ def decay_requantize(idx_src: np.ndarray, norm_src, c_src: np.ndarray, c_dst: np
     idx_dst = np.digitize(unit, mid_dst).astype(np.uint8)
     cn = np.sqrt(np.sum(c_dst[idx_dst] ** 2))
     return idx_dst, (recon / cn if cn > 1e-10 else recon)
+
+
+# --------------------------------------------------------------------------
+# block formats of the reference's documents (no code in the reference tree: parity unpinned, the
+# layouts restate docs/papers/block-size-experiment.md:25-37 and docs/papers/turbo4-resurrection.md:125-138,169,208)
+# --------------------------------------------------------------------------
+def block_bytes(bits: int, block_elems: int) -> int:
+    if bits == 4:
+        return 4 + block_elems // 2
+    return 2 + block_elems // 4 + (block_elems // 8 if bits == 3 else 0)
+
+
+def blocks_encode(idx: np.ndarray, scale: float, bits: int, block_elems: int) -> np.ndarray:
+    """One 128-element vector's indices and corrected norm as 128 / block_elems storage blocks (uint8)."""
+    out = []
+    for b0 in range(0, len(idx), block_elems):
+        blk = idx[b0:b0 + block_elems].astype(np.uint32)
+        head = np.frombuffer(np.float16(scale).tobytes(), dtype=np.uint8)
+        if bits == 4:
+            qs = (blk[0::2] | (blk[1::2] << 4)).astype(np.uint8)
+            out += [head, np.zeros(2, np.uint8), qs]
+            continue
+        low = blk & 3
+        qs = (low[0::4] | (low[1::4] << 2) | (low[2::4] << 4) | (low[3::4] << 6)).astype(np.uint8)
+        out += [head, qs]
+        if bits == 3:
+            hi = (blk >> 2) & 1
+            out.append(sum(hi[j::8] << j for j in range(8)).astype(np.uint8))
+    return np.concatenate(out)
+
+
+def blocks_decode(raw: np.ndarray, bits: int, block_elems: int, d: int = 128):
+    """Inverse, written with the documents' extraction expressions.  Returns (indices, norm of the first block)."""
+    bb = block_bytes(bits, block_elems)
+    idx = np.zeros(d, dtype=np.uint8)
+    for b in range(d // block_elems):
+        blk = raw[b * bb:(b + 1) * bb]
+        if bits == 4:
+            qs = blk[4:]
+            for j in range(block_elems):
+                idx[b * block_elems + j] = (qs[j // 2] >> ((j % 2) * 4)) & 0xF
+            continue
+        qs, signs = blk[2:2 + block_elems // 4], blk[2 + block_elems // 4:]
+        for j in range(block_elems):
+            m = (qs[j // 4] >> ((j % 4) * 2)) & 0x3
+            if bits == 3 and signs[j // 8] & (1 << (j % 8)):
+                m |= 4
+            idx[b * block_elems + j] = m
+    return idx, float(np.frombuffer(raw[:2].tobytes(), dtype=np.float16)[0])

@@ -387,3 +387,64 @@ def test_sparse_v_option(tq, group):
     flat = cache.attend(torch.zeros_like(qd), bt, torch.tensor([n]))
     flat_s = cache.attend(torch.zeros_like(qd), bt, torch.tensor([n]), sparse_v=True)
     assert torch.equal(flat, flat_s)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt,block", [("turbo3", 32), ("turbo3", 128), ("turbo3", 64), ("turbo2", 32), ("turbo2", 128),
+                                       ("turbo4", 128)])
+def test_block_codec_and_state_dict(tq, fmt, block):
+    """Wire formats (the block layouts of the reference's documents: turbo3 14 B / 32 or 50 B / 128, turbo4 68 B / 128):
+    exported bytes equal the NumPy restatement of the documents' extraction expressions, import into a second cache
+    restores the index arrays bit for bit and the scales to fp16, attention over the imported cache stays inside the
+    tolerance; state_dict / load_state_dict reproduce the pool and the attention output exactly."""
+    import torch
+    rng = np.random.default_rng(17)
+    n, hkv, hq, bits = 300, 2, 8, int(fmt[-1])
+    cache = tq.PagedKVCache(D, hkv, num_pages=4, k_format=fmt, v_format=fmt, seed=42)
+    ks = [rng.standard_normal((n, hkv, D)).astype(np.float16)]
+    vs = [rng.standard_normal((n, hkv, D)).astype(np.float16)]
+    bt = fill_cache(cache, ks, vs, [n], rng)
+    t = np.arange(n)
+    slots = torch.as_tensor(bt[0].numpy()[t // 128].astype(np.int64) * 128 + t % 128)
+    assert cache.block_bytes("k", block) == o.block_bytes(bits, block) == {(3, 32): 14, (3, 64): 26, (3, 128): 50,
+                                                                        (2, 32): 10, (2, 128): 34, (4, 128): 68}[(bits, block)]
+    L, pool = cache.layout, cache.pool.cpu().numpy()
+    other = tq.PagedKVCache(D, hkv, num_pages=4, k_format=fmt, v_format=fmt, seed=42)
+    for which, idx_off, scale_off in (("k", L.k_idx_off, L.k_scale_off), ("v", L.v_idx_off, L.v_scale_off)):
+        blocks = cache.export_blocks(which, slots, block)
+        assert tuple(blocks.shape) == (n, hkv, D // block, o.block_bytes(bits, block))
+        raw = blocks.cpu().numpy()
+        for tok in (0, 1, 127, 128, 299):
+            page, off = int(slots[tok]) // 128, int(slots[tok]) % 128
+            for h in range(hkv):
+                rec = pool[page, h]
+                idx = o.unpack_idx(rec[idx_off + off * 16 * bits: idx_off + (off + 1) * 16 * bits], bits, D)
+                scale = rec[scale_off + 4 * off: scale_off + 4 * off + 4].view(np.float32)[0]
+                assert np.array_equal(raw[tok, h].reshape(-1), o.blocks_encode(idx, scale, bits, block))
+                back, nrm = o.blocks_decode(raw[tok, h].reshape(-1), bits, block)
+                assert np.array_equal(back, idx) and nrm == float(np.float16(scale))
+        other.import_blocks(which, blocks, slots, block)
+    p2 = other.pool.cpu().numpy()
+    pages = np.unique(bt[0].numpy())
+    for page in pages:
+        for h in range(hkv):
+            a, b = pool[page, h], p2[page, h]
+            valid = min(128, n - 128 * int(np.where(bt[0].numpy() == page)[0][0]))
+            for off_i, off_s in ((L.k_idx_off, L.k_scale_off), (L.v_idx_off, L.v_scale_off)):
+                assert np.array_equal(a[off_i: off_i + valid * 16 * bits], b[off_i: off_i + valid * 16 * bits])
+                sa = a[off_s: off_s + 4 * valid].view(np.float32)
+                sb = b[off_s: off_s + 4 * valid].view(np.float32)
+                assert np.array_equal(sa.astype(np.float16).astype(np.float32), sb)
+    q = torch.as_tensor(rng.standard_normal((1, hq, D)).astype(np.float32)).cuda()
+    ref = cache.attend(q, bt, torch.tensor([n])).cpu().numpy()
+    got = other.attend(q, bt, torch.tensor([n])).cpu().numpy()
+    assert max_rel(got, ref) < TOL
+    clone = tq.PagedKVCache(D, hkv, num_pages=4, k_format=fmt, v_format=fmt, seed=42)
+    clone.load_state_dict(cache.state_dict())
+    assert torch.equal(clone.pool, cache.pool)
+    assert np.array_equal(clone.attend(q, bt, torch.tensor([n])).cpu().numpy(), ref)
+    with pytest.raises(ValueError):
+        tq.PagedKVCache(D, hkv, num_pages=5, k_format=fmt, v_format=fmt).load_state_dict(cache.state_dict())
+    if bits == 4:
+        with pytest.raises(ValueError):
+            cache.block_bytes("k", 32)

@@ -151,6 +151,20 @@ def test_temporal_decay_matches_reference(g_decay):
     assert g["corrected"][9] == 0.0 and (g["idx2"][9] == g["idx2"][9][0]).all()      # the zero vector
 
 
+def test_block_formats_have_the_documented_sizes_and_round_trip():
+    """Block layouts of the reference's documents (docs/papers/block-size-experiment.md:33-37: 14 B per 32, 26 B per 64,
+    50 B per 128 for turbo3; docs/papers/turbo4-resurrection.md:208: 68 B per 128 for turbo4).  No reference code
+    exists for them in the tree: this pins sizes and the extraction expressions only."""
+    assert [o.block_bytes(3, b) for b in (32, 64, 128)] == [14, 26, 50] and o.block_bytes(4, 128) == 68
+    rng = np.random.default_rng(0)
+    for bits, block in ((3, 32), (3, 64), (3, 128), (2, 32), (2, 128), (4, 128)):
+        idx = rng.integers(0, 1 << bits, D).astype(np.uint8)
+        raw = o.blocks_encode(idx, 0.731, bits, block)
+        assert raw.dtype == np.uint8 and len(raw) == o.block_bytes(bits, block) * (D // block)
+        back, nrm = o.blocks_decode(raw, bits, block)
+        assert np.array_equal(back, idx) and nrm == float(np.float16(0.731))
+
+
 def test_live_reference_if_present():
     """Differential check against the reference tree itself where it is mounted."""
     import os

@@ -62,6 +62,9 @@ SIGNATURES = {
     "tq_unpack_bits": (C.c_int, [_P, _I64, _I32, _P, _P]),
     "tq_sign_wht_f64": (C.c_int, [_P, _I64, _I32, _I32, _P, _P, _P, _P]),
     "tq_nearest_centroid_f64": (C.c_int, [_P, _I64, _P, _I32, _P, _P]),
+    "tq_block_bytes": (C.c_int64, [_I32, _I32]),
+    "tq_cache_export_blocks": (C.c_int, [_P, _P, _I32, _P, _I64, _I32, _P, _P]),
+    "tq_cache_import_blocks": (C.c_int, [_P, _P, _I32, _P, _I64, _I32, _P, _P]),
     "tq_requantize": (C.c_int, [_P, _P, _P, _P, _I32, _I64, _P, _P, _P, _P]),
     "tq_quantize_residual": (C.c_int, [_P, _P, _I32, _I64, _I64, _P, _P, _P, _I64, _P]),
     "tq_dequantize_strided": (C.c_int, [_P, _P, _P, _I64, _P, _I64, _I32, _P]),

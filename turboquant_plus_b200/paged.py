@@ -184,6 +184,55 @@ class PagedKVCache:
                     nv.ptr(out), nv.torch_dtype_code(out.dtype), nv.stream_ptr())
         return out
 
+    # ---- wire / on-disk forms ---------------------------------------------------------------------------
+    def block_bytes(self, which: str, block_elems: int = 128) -> int:
+        fmt = self.k_format if which == "k" else self.v_format
+        n = int(nv.load().tq_block_bytes(nv.FORMATS[fmt], block_elems))
+        if n < 0:
+            raise ValueError(f"no block format for {fmt} with {block_elems} elements per block")
+        return n
+
+    def export_blocks(self, which: str, slot_mapping, block_elems: int = 128):
+        """The K ("k") or V ("v") codes of the tokens at ``slot_mapping`` in the block format the reference's
+        documents describe for its llama.cpp fork (turbo3: fp16 norm, 2-bit plane, high-bit plane; turbo2; turbo4
+        nibbles): uint8 CUDA tensor (n_tokens, num_kv_heads, 128 // block_elems, block bytes)."""
+        torch = nv.require_cuda()
+        bb = self.block_bytes(which, block_elems)
+        slots = slot_mapping.to(device=self.device, dtype=torch.int64).contiguous()
+        out = torch.zeros((slots.numel(), self.num_kv_heads, self.head_dim // block_elems, bb), dtype=torch.uint8,
+                          device=self.device)
+        with torch.cuda.device(self.device):
+            nv.call("tq_cache_export_blocks", C.byref(self.layout), nv.ptr(self.pool), 0 if which == "k" else 1,
+                    nv.ptr(slots), slots.numel(), block_elems, nv.ptr(out), nv.stream_ptr())
+        return out
+
+    def import_blocks(self, which: str, blocks, slot_mapping, block_elems: int = 128):
+        """Inverse of export_blocks: writes the codes into the records of the tokens at ``slot_mapping``."""
+        torch = nv.require_cuda()
+        bb = self.block_bytes(which, block_elems)
+        slots = slot_mapping.to(device=self.device, dtype=torch.int64).contiguous()
+        blocks = blocks.to(device=self.device, dtype=torch.uint8).contiguous()
+        if blocks.numel() != slots.numel() * self.num_kv_heads * (self.head_dim // block_elems) * bb:
+            raise ValueError("block buffer does not match (n_tokens, num_kv_heads, 128 // block_elems, block bytes)")
+        with torch.cuda.device(self.device):
+            nv.call("tq_cache_import_blocks", C.byref(self.layout), nv.ptr(self.pool), 0 if which == "k" else 1,
+                    nv.ptr(slots), slots.numel(), block_elems, nv.ptr(blocks), nv.stream_ptr())
+
+    def state_dict(self) -> dict:
+        """Everything needed to rebuild the cache contents elsewhere: geometry, formats and the pool bytes (host
+        tensor).  Quantizer constants are not stored; they follow from the seed the cache is built with."""
+        return {"head_dim": self.head_dim, "num_kv_heads": self.num_kv_heads, "num_pages": self.num_pages,
+                "page_tokens": self.page_tokens, "k_format": self.k_format, "v_format": self.v_format,
+                "record_bytes": int(self.layout.record_bytes), "pool": self.pool.cpu()}
+
+    def load_state_dict(self, state: dict) -> None:
+        for key in ("head_dim", "num_kv_heads", "num_pages", "page_tokens", "k_format", "v_format"):
+            if state[key] != getattr(self, key):
+                raise ValueError(f"cache state mismatch: {key} is {state[key]!r}, this cache has {getattr(self, key)!r}")
+        if int(state["record_bytes"]) != int(self.layout.record_bytes):
+            raise ValueError("cache state mismatch: record size")
+        self.pool.copy_(state["pool"].to(self.device))
+
     def kernel_status(self, workspace=None) -> int:
         """0 after a clean decode; 1 if a bounded wait inside the kernel gave up (synchronises)."""
         ws = self._ws if workspace is None else workspace
