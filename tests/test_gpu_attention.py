@@ -448,3 +448,85 @@ def test_block_codec_and_state_dict(tq, fmt, block):
     if bits == 4:
         with pytest.raises(ValueError):
             cache.block_bytes("k", 32)
+
+
+@pytest.mark.gpu
+def test_model_hooks_and_cache_adapter(tq):
+    """Caller-side adapters.  (1) patch_model_attention (the reference's benchmarks/benchmark_norm_correction.py:45-96):
+    the keys a layer's k_proj produces come back quantize -> dequantized per KV head with seed = head index; checked
+    against the oracle's dense PolarQuant round trip on a stand-in model with the attribute layout the hook walks.
+    (2) TurboQuantCache: update() of a prompt then of single positions, attend() for a chunk (prefill kernel) and for
+    one position (decode kernel) against dequantize-then-attend."""
+    import torch
+    from turboquant_plus_b200 import integration as integ
+    torch.manual_seed(0)
+    hidden, heads, hkv = 512, 4, 2           # head_dim 128
+
+    class Attn(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.k_proj = torch.nn.Linear(hidden, hkv * D, bias=False)
+
+    class Layer(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.self_attn = Attn()
+
+    class Inner(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layers = torch.nn.ModuleList([Layer(), Layer()])
+
+    class Model(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.model = Inner()
+            self.config = type("Cfg", (), {"hidden_size": hidden, "num_attention_heads": heads,
+                                           "num_key_value_heads": hkv})()
+
+    model = Model().cuda()
+    x = torch.randn(2, 9, hidden, device="cuda")
+    plain = [layer.self_attn.k_proj(x) for layer in model.model.layers]
+    hooks = integ.patch_model_attention(model, lambda d, seed: tq.TurboQuantMSE(d, 3, seed=seed))
+    patched = [layer.self_attn.k_proj(x) for layer in model.model.layers]
+    integ.unpatch_model(hooks)
+    assert all(isinstance(layer.self_attn.k_proj, torch.nn.Linear) for layer in model.model.layers)
+    for k0, k1 in zip(plain, patched):
+        assert k1.shape == k0.shape and k1.dtype == k0.dtype
+        k0n = k0.detach().cpu().numpy().astype(np.float64).reshape(2 * 9, hkv, D)
+        for h in range(hkv):
+            rot = o.dense_rotation(D, np.random.default_rng(h))
+            c = o.centroids(3, D)
+            i, nrm = o.polar_quantize(k0n[:, h], rot, c)
+            want = o.polar_dequantize(i, nrm, rot, c)
+            got = k1.detach().cpu().numpy().reshape(2 * 9, hkv, D)[:, h]
+            assert max_rel(got, want) < 1e-5
+
+    rng = np.random.default_rng(3)
+    B, hq, prompt, extra = 2, 8, 150, 3
+    cache = integ.TurboQuantCache(num_layers=2, head_dim=D, num_kv_heads=hkv, max_batch=B, max_seq_len=300)
+    k = rng.standard_normal((B, hkv, prompt + extra, D)).astype(np.float16)
+    v = rng.standard_normal((B, hkv, prompt + extra, D)).astype(np.float16)
+    q = rng.standard_normal((B, hq, prompt + extra, D)).astype(np.float16)
+    kt, vt, qt = (torch.as_tensor(a).cuda() for a in (k, v, q))
+    layer = 1
+    pq = cache.store.layers[layer]
+    kh = np.stack([[oracle_roundtrip(pq, k[b, h].astype(np.float32), "k") for h in range(hkv)] for b in range(B)])
+    vh = np.stack([[oracle_roundtrip(pq, v[b, h].astype(np.float32), "v") for h in range(hkv)] for b in range(B)])
+    assert cache.update(kt[:, :, :prompt], vt[:, :, :prompt], layer) == prompt and cache.get_seq_length(layer) == prompt
+    chunk = 16
+    out = cache.attend(qt[:, :, prompt - chunk:prompt], layer)
+    assert tuple(out.shape) == (B, hq, chunk, D)
+    ref = o.attend_chunk_gqa(q[:, :, prompt - chunk:prompt].transpose(0, 2, 1, 3).astype(np.float64),
+                             kh[:, :, :prompt], vh[:, :, :prompt], [prompt] * B)
+    assert max_rel(out.permute(0, 2, 1, 3).float().cpu().numpy().reshape(-1, D), ref.reshape(-1, D)) < TOL
+    for step in range(extra):
+        n = prompt + step
+        cache.update(kt[:, :, n:n + 1], vt[:, :, n:n + 1], layer)
+        out1 = cache.attend(qt[:, :, n:n + 1], layer)
+        assert tuple(out1.shape) == (B, hq, 1, D)
+        ref1 = o.attend_gqa(q[:, :, n].astype(np.float64), kh[:, :, :n + 1], vh[:, :, :n + 1], [n + 1] * B)
+        assert max_rel(out1[:, :, 0].float().cpu().numpy(), ref1) < TOL
+    assert cache.get_seq_length(0) == 0
+    with pytest.raises(ValueError):
+        cache.update(kt[:, :, :200], vt[:, :, :200], layer)
