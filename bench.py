@@ -596,13 +596,83 @@ def run_config3(args):
         dist.destroy_process_group()
 
 
+def run_side_kernels(args):
+    """--workload side: the kernels next to the hot path (temporal-decay re-quantization, block-format export and
+    import, OutlierTurboQuant), each timed alone with CUDA events on inputs larger than L2 and set against the HBM
+    peak by its algorithmic bytes.  Not the headline line: one JSON line with a list of kernels."""
+    import torch
+    import turboquant_plus_b200 as tq
+    from turboquant_plus_b200 import temporal_decay as td
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peak, peak_src = peaks()
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(5)
+
+    def timed(fn):
+        for _ in range(args.warmup):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1) / args.steps
+
+    rows = []
+
+    def row(name, ms, nbytes, units, unit_name):
+        rows.append({"kernel": name, "ms": ms, unit_name + "_per_s": units / (ms * 1e-3),
+                     "hbm_gbs_algorithmic": nbytes / (ms * 1e-3) / 1e9,
+                     "frac_of_hbm_peak": nbytes / (ms * 1e-3) / 1e9 / peak})
+
+    n = 1 << 22                                   # 4 Mi vectors: 218 MB of 3-bit codes in, 168 MB of 2-bit codes out
+    x = torch.randn((n, D), generator=gen, device=dev).half()
+    a = tq.PolarQuant(D, 3, seed=42, rotation="wht", device=dev)
+    b = tq.PolarQuant(D, 2, seed=42, rotation="wht", device=dev)
+    code = a.quantize_device(x, packed=True, want_scale=True)
+    del x
+    row("k_requantize 3->2 bits", timed(lambda: td.requantize_device(a, b, code["packed"], code["scale"])),
+        n * (48 + 4 + 32 + 8), n, "vectors")
+    del code
+
+    hkv, pages = 8, 2048                          # 262,144 tokens x 8 heads: 218 MB of records
+    cache = tq.PagedKVCache(D, hkv, pages, k_format="turbo3", v_format="turbo3", seed=42, device=dev)
+    for lo in range(0, pages * PT, 32768):
+        k = torch.randn((32768, hkv, D), generator=gen, device=dev).half()
+        cache.append(k, k, torch.arange(lo, lo + 32768, device=dev))
+    slots = torch.arange(pages * PT, device=dev)
+    nvec = pages * PT * hkv
+    for block in (32, 128):
+        bb = cache.block_bytes("k", block) * (D // block)
+        blocks = cache.export_blocks("k", slots, block)
+        row(f"k_cache_blocks export turbo3 K, {block}-element blocks", timed(lambda: cache.export_blocks("k", slots, block)),
+            nvec * (52 + bb), nvec, "vectors")
+        row(f"k_cache_blocks import turbo3 K, {block}-element blocks",
+            timed(lambda: cache.import_blocks("k", blocks, slots, block)), nvec * (52 + bb), nvec, "vectors")
+        del blocks
+    del cache
+
+    m = 1 << 16                                   # fp64 reference-parity path (dense rotations): compute bound
+    xo = torch.randn((m, D), generator=gen, device=dev, dtype=torch.float64)
+    oq = tq.OutlierTurboQuant(D, 3.5, seed=42, device=dev)
+    c = oq.quantize_device(xo)
+    row("OutlierTurboQuant.quantize 3.5 bits (fp64, 3 launches)", timed(lambda: oq.quantize_device(xo)),
+        m * (D * 8 + D + 8 + 16 + 4), m, "vectors")
+    row("OutlierTurboQuant.dequantize 3.5 bits (fp64, 3 launches)", timed(lambda: oq.dequantize_device(c)),
+        m * (D * 8 + D + 8 + 16 + 4), m, "vectors")
+    print(json.dumps({"metric": "side_kernels", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+                      "data": "synthetic", "hbm_peak_gbs": peak, "hbm_peak_source": peak_src, "kernels": rows}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="config1", choices=["config1", "config2", "config3", "config4"],
+    ap.add_argument("--workload", default="config1", choices=["config1", "config2", "config3", "config4", "side"],
                     help="config1 is the headline workload; the others print a line of the same shape")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -610,6 +680,8 @@ def main():
         run_reference(args)
     elif args.workload == "config3":
         run_config3(args)
+    elif args.workload == "side":
+        run_side_kernels(args)
     elif args.workload != "config1":
         run_other_workload(args)
     else:

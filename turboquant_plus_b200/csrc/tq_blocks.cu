@@ -12,8 +12,9 @@
 // documents' extraction expressions and sizes.  The sign vectors of the rotation are not part of a block: caches
 // interoperate only between quantizers built with the same signs.
 //
-// One thread converts 32 elements of one vector: 4*bits whole bytes of the MSB-first index stream on the cache
-// side, one storage block (or a quarter / half of one) on the block side.  Pure byte shuffling, bound by HBM.
+// One thread converts 32 elements of one vector: 4*bits bytes (whole words) of the MSB-first index stream on the
+// cache side, one storage block (or a quarter / half of one) on the block side.  Pure bit shuffling in registers,
+// bound by HBM.
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -36,70 +37,116 @@ struct BlkArgs {
   int32_t heads, page_tokens, bits, B, idx_off, scale_off;
 };
 
-template <bool EXPORT>
+__device__ __forceinline__ uint32_t bswap32(uint32_t x) { return __byte_perm(x, 0, 0x0123); }
+
+// BITS is a template parameter and every loop is unrolled, so the 32 indices of a thread live in registers; the
+// cache side moves as BITS aligned words (4*BITS bytes at a multiple of 4*BITS), the block side as halfwords
+// (blocks start on even addresses only: 14- and 50-byte blocks).
+template <bool EXPORT, int BITS>
 __global__ void __launch_bounds__(256) k_cache_blocks(const BlkArgs a) {
   const int64_t total = a.n_tokens * a.heads * 4;
-  const int bb = blk_bytes(a.bits, a.B), per_vec = (TQ_D / a.B) * bb;
+  const int bb = blk_bytes(BITS, a.B), per_vec = (TQ_D / a.B) * bb;
+  constexpr int HDR = BITS == 4 ? 4 : 2;
   for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
     const int sub = (int)(i & 3);
     const int64_t vec = i >> 2, tok = vec / a.heads;
     const int head = (int)(vec - tok * a.heads);
     const int64_t slot = a.slots[tok];
-    if (slot < 0) continue;
+    const int e0 = 32 * sub, blk = e0 / a.B, e = e0 % a.B;
+    uint16_t* bp = reinterpret_cast<uint16_t*>(a.blocks + vec * per_vec + (size_t)blk * bb);
+    uint16_t* qs = bp + HDR / 2 + (BITS == 4 ? e / 4 : e / 8);          // 16 (nibbles) or 8 bytes of this thread
+    uint16_t* sg = bp + HDR / 2 + a.B / 8 + e / 16;                      // turbo3: 4 bytes of high bits
+    if (slot < 0) {
+      if (EXPORT) {  // a skipped token leaves zero blocks
+        if (e == 0) { bp[0] = 0; if (BITS == 4) bp[1] = 0; }
+#pragma unroll
+        for (int k = 0; k < (BITS == 4 ? 8 : 4); ++k) qs[k] = 0;
+        if (BITS == 3) { sg[0] = 0; sg[1] = 0; }
+      }
+      continue;
+    }
     const int64_t page = slot / a.page_tokens;
     const int off = (int)(slot - page * a.page_tokens);
     uint8_t* rec = a.pool + page * a.page_stride + (int64_t)head * a.head_stride;
-    uint8_t* stream = rec + a.idx_off + (size_t)off * (16 * a.bits) + sub * 4 * a.bits;  // 32 indices, MSB first
+    uint32_t* stream = reinterpret_cast<uint32_t*>(rec + a.idx_off + (size_t)off * (16 * BITS)) + sub * BITS;
     float* scale = reinterpret_cast<float*>(rec + a.scale_off) + off;
-    const int e0 = 32 * sub, blk = e0 / a.B, e = e0 % a.B;
-    uint8_t* bp = a.blocks + vec * per_vec + (size_t)blk * bb;
-    const int hdr = a.bits == 4 ? 4 : 2;
-    uint8_t idx[32];
+    uint32_t idx[32];
     if (EXPORT) {
-      unsigned long long w = 0;
-      int have = 0, pos = 0;
+      uint32_t w[BITS];
+#pragma unroll
+      for (int k = 0; k < BITS; ++k) w[k] = bswap32(stream[k]);       // 32*BITS bits, first index in the top bits
+#pragma unroll
       for (int k = 0; k < 32; ++k) {
-        while (have < a.bits) { w = (w << 8) | stream[pos++]; have += 8; }
-        idx[k] = (uint8_t)((w >> (have - a.bits)) & ((1u << a.bits) - 1u));
-        have -= a.bits;
+        const int start = k * BITS, wi = start >> 5, o = start & 31;
+        uint32_t m;
+        if (o + BITS <= 32) m = w[wi] >> (32 - BITS - o);
+        else m = __funnelshift_l(w[wi + 1 < BITS ? wi + 1 : wi], w[wi], o + BITS - 32);
+        idx[k] = m & ((1u << BITS) - 1u);
       }
       if (e == 0) {
-        *reinterpret_cast<__half*>(bp) = __float2half_rn(*scale);
-        if (a.bits == 4) *reinterpret_cast<uint16_t*>(bp + 2) = 0;
+        const __half hs = __float2half_rn(*scale);
+        bp[0] = *reinterpret_cast<const uint16_t*>(&hs);
+        if (BITS == 4) bp[1] = 0;
       }
-      if (a.bits == 4) {
-        for (int k = 0; k < 16; ++k) bp[hdr + e / 2 + k] = (uint8_t)(idx[2 * k] | (idx[2 * k + 1] << 4));
-      } else {
+      if (BITS == 4) {
+#pragma unroll
         for (int k = 0; k < 8; ++k)
-          bp[hdr + e / 4 + k] = (uint8_t)((idx[4 * k] & 3) | ((idx[4 * k + 1] & 3) << 2) | ((idx[4 * k + 2] & 3) << 4) |
-                                          ((idx[4 * k + 3] & 3) << 6));
-        if (a.bits == 3)
-          for (int k = 0; k < 4; ++k) {
-            uint32_t s = 0;
-            for (int j = 0; j < 8; ++j) s |= (uint32_t)((idx[8 * k + j] >> 2) & 1) << j;
-            bp[hdr + a.B / 4 + e / 8 + k] = (uint8_t)s;
+          qs[k] = (uint16_t)(idx[4 * k] | (idx[4 * k + 1] << 4) | (idx[4 * k + 2] << 8) | (idx[4 * k + 3] << 12));
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          uint32_t v = 0;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v |= (idx[8 * k + j] & 3u) << (2 * j);
+          qs[k] = (uint16_t)v;
+        }
+        if (BITS == 3) {
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {
+            uint32_t v = 0;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v |= ((idx[16 * k + j] >> 2) & 1u) << j;
+            sg[k] = (uint16_t)v;
           }
+        }
       }
     } else {
-      for (int k = 0; k < 32; ++k) {
-        const int j = e + k;
-        uint32_t m;
-        if (a.bits == 4) {
-          m = (bp[hdr + j / 2] >> ((j % 2) * 4)) & 15u;
-        } else {
-          m = (bp[hdr + j / 4] >> ((j % 4) * 2)) & 3u;
-          if (a.bits == 3 && (bp[hdr + a.B / 4 + j / 8] & (1u << (j % 8)))) m |= 4u;
+      if (BITS == 4) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t v = qs[k];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) idx[4 * k + j] = (v >> (4 * j)) & 15u;
         }
-        idx[k] = (uint8_t)m;
+      } else {
+        uint32_t hi = 0;
+        if (BITS == 3) hi = (uint32_t)sg[0] | ((uint32_t)sg[1] << 16);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint32_t v = qs[k];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) idx[8 * k + j] = ((v >> (2 * j)) & 3u) | (((hi >> (8 * k + j)) & 1u) << 2);
+        }
       }
-      unsigned long long w = 0;
-      int have = 0, pos = 0;
+      uint32_t w[BITS];
+#pragma unroll
+      for (int k = 0; k < BITS; ++k) w[k] = 0;
+#pragma unroll
       for (int k = 0; k < 32; ++k) {
-        w = (w << a.bits) | idx[k];
-        have += a.bits;
-        while (have >= 8) { stream[pos++] = (uint8_t)(w >> (have - 8)); have -= 8; }
+        const int start = k * BITS, wi = start >> 5, o = start & 31;
+        if (o + BITS <= 32) {
+          w[wi] |= idx[k] << (32 - BITS - o);
+        } else {
+          w[wi] |= idx[k] >> (o + BITS - 32);
+          if (wi + 1 < BITS) w[wi + 1] |= idx[k] << (64 - BITS - o);
+        }
       }
-      if (sub == 0) *scale = __half2float(*reinterpret_cast<const __half*>(a.blocks + vec * per_vec));
+#pragma unroll
+      for (int k = 0; k < BITS; ++k) stream[k] = bswap32(w[k]);
+      if (sub == 0) {
+        const uint16_t raw = *reinterpret_cast<const uint16_t*>(a.blocks + vec * per_vec);
+        *scale = __half2float(*reinterpret_cast<const __half*>(&raw));
+      }
     }
   }
 }
@@ -136,8 +183,13 @@ int run_blocks(bool exp, const tq_cache_layout* L, uint8_t* pool, int32_t which,
   int64_t g = (total + 255) / 256;
   const int64_t cap = (int64_t)tq_num_sms() * 16;
   if (g > cap) g = cap;
-  if (exp) k_cache_blocks<true><<<(int)g, 256, 0, (cudaStream_t)stream>>>(a);
-  else k_cache_blocks<false><<<(int)g, 256, 0, (cudaStream_t)stream>>>(a);
+#define TQ_BLK(E, B_) k_cache_blocks<E, B_><<<(int)g, 256, 0, (cudaStream_t)stream>>>(a)
+  if (exp) {
+    if (bits == 2) TQ_BLK(true, 2); else if (bits == 3) TQ_BLK(true, 3); else TQ_BLK(true, 4);
+  } else {
+    if (bits == 2) TQ_BLK(false, 2); else if (bits == 3) TQ_BLK(false, 3); else TQ_BLK(false, 4);
+  }
+#undef TQ_BLK
   return tq_launch_check("k_cache_blocks");
 }
 

@@ -8,7 +8,7 @@
 // per vector and is bound by HBM.
 //
 // Layout of the work: 8 lanes per vector, 16 coordinates per lane (2*bits bytes of the MSB-first index stream, which
-// start on a byte boundary), 4 vectors per warp; the two sums of squares are reduced over the 8 lanes with shuffles.
+// start on a 2-byte boundary and are read as halfwords), 4 vectors per warp; the two sums of squares are reduced over the 8 lanes with shuffles.
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <string.h>
@@ -32,30 +32,40 @@ __device__ __forceinline__ float rq_sum8(float v) {
   return v;
 }
 
+template <int BS, int BD>
 __global__ void __launch_bounds__(256) k_requantize(const RqTables T, const uint8_t* __restrict__ src,
                                                     const float* __restrict__ scale_src, int64_t n,
                                                     int scale_is_norm, uint8_t* __restrict__ dst,
                                                     float* __restrict__ norm_dst, float* __restrict__ scale_dst) {
+  // codebooks in shared memory: the lanes of a warp look up different entries, which the constant bank serialises
+  __shared__ float s_src[16], s_dst[16];
+  if (threadIdx.x < 16) {
+    s_src[threadIdx.x] = T.cent_src[threadIdx.x];
+    s_dst[threadIdx.x] = T.cent_dst[threadIdx.x];
+  }
+  __syncthreads();
+  float mid[(1 << BD) - 1];
+#pragma unroll
+  for (int i = 0; i < (1 << BD) - 1; ++i) mid[i] = T.mid_dst[i];
   const int lane = threadIdx.x & 31, sub = lane & 7;
   const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-  const int bs = T.bits_src, bd = T.bits_dst;
-  const int n_mid = (1 << bd) - 1;
   for (int64_t v0 = warp * 4; v0 < n; v0 += nwarps * 4) {  // n is uniform, so whole warps leave together
     const int64_t v = v0 + (lane >> 3);
     const bool ok = v < n;
-    // this lane's 16 fields: 2*bs bytes, big-endian, first coordinate in the top bits
+    // this lane's 16 fields: BS halfwords of the big-endian stream, first coordinate in the top bits
     uint64_t word = 0;
     if (ok) {
-      const uint8_t* p = src + v * (16 * bs) + sub * 2 * bs;
-      for (int i = 0; i < 2 * bs; ++i) word = (word << 8) | p[i];
+      const uint16_t* p = reinterpret_cast<const uint16_t*>(src + v * (16 * BS) + sub * 2 * BS);
+#pragma unroll
+      for (int i = 0; i < BS; ++i) word = (word << 16) | (uint64_t)__byte_perm((uint32_t)p[i], 0, 0x4401);
     }
     float sc = ok ? scale_src[v] : 0.f;
     float val[16], ss = 0.f;
 #pragma unroll
     for (int k = 0; k < 16; ++k) {
-      const uint32_t m = (uint32_t)(word >> (bs * (15 - k))) & ((1u << bs) - 1u);
-      val[k] = T.cent_src[m];
+      const uint32_t m = (uint32_t)(word >> (BS * (15 - k))) & ((1u << BS) - 1u);
+      val[k] = s_src[m];
       ss = fmaf(val[k], val[k], ss);
     }
     if (scale_is_norm) {  // the prototype's dequantize_3bit: norm / ||centroids[idx]||
@@ -78,15 +88,18 @@ __global__ void __launch_bounds__(256) k_requantize(const RqTables T, const uint
     for (int k = 0; k < 16; ++k) {
       const float u = tiny ? val[k] : val[k] * inv;
       int m = 0;
-      for (int b = 0; b < n_mid; ++b) m += (T.mid_dst[b] <= u) ? 1 : 0;
-      out = (out << bd) | (uint64_t)m;
-      const float c = T.cent_dst[m];
+#pragma unroll
+      for (int b = 0; b < (1 << BD) - 1; ++b) m += (mid[b] <= u) ? 1 : 0;
+      out = (out << BD) | (uint64_t)m;
+      const float c = s_dst[m];
       cc = fmaf(c, c, cc);
     }
     const float cn = sqrtf(rq_sum8(cc));
     if (ok) {
-      uint8_t* q = dst + v * (16 * bd) + sub * 2 * bd;
-      for (int i = 0; i < 2 * bd; ++i) q[i] = (uint8_t)(out >> (8 * (2 * bd - 1 - i)));
+      uint16_t* q = reinterpret_cast<uint16_t*>(dst + v * (16 * BD) + sub * 2 * BD);
+#pragma unroll
+      for (int i = 0; i < BD; ++i)
+        q[i] = (uint16_t)__byte_perm((uint32_t)(out >> (16 * (BD - 1 - i))), 0, 0x4401);
       if (sub == 0) {
         if (norm_dst) norm_dst[v] = recon;
         scale_dst[v] = cn > 1e-10f ? recon / cn : recon;
@@ -123,7 +136,24 @@ extern "C" int tq_requantize(const tq_quantizer* src_q, const tq_quantizer* dst_
   const int64_t want = (warps + 7) / 8;
   const int64_t cap = (int64_t)tq_num_sms() * 8;
   const int grid = (int)(want < cap ? want : cap);
-  k_requantize<<<grid, 256, 0, (cudaStream_t)stream>>>(T, packed_src_dev, scale_src_dev, n, scale_is_norm ? 1 : 0,
-                                                      packed_dst_dev, norm_dst_dev, scale_dst_dev);
+  TQ_REQUIRE(tq_aligned(packed_src_dev, 2) && tq_aligned(packed_dst_dev, 2), TQ_ERR_ALIGN,
+             "tq_requantize: index streams must be 2-byte aligned");
+#define TQ_RQ(S, D_)                                                                                              \
+  k_requantize<S, D_><<<grid, 256, 0, (cudaStream_t)stream>>>(T, packed_src_dev, scale_src_dev, n,              \
+                                                               scale_is_norm ? 1 : 0, packed_dst_dev, norm_dst_dev, \
+                                                               scale_dst_dev)
+  switch (T.bits_src * 8 + T.bits_dst) {
+    case 4 * 8 + 4: TQ_RQ(4, 4); break;
+    case 4 * 8 + 3: TQ_RQ(4, 3); break;
+    case 4 * 8 + 2: TQ_RQ(4, 2); break;
+    case 4 * 8 + 1: TQ_RQ(4, 1); break;
+    case 3 * 8 + 3: TQ_RQ(3, 3); break;
+    case 3 * 8 + 2: TQ_RQ(3, 2); break;
+    case 3 * 8 + 1: TQ_RQ(3, 1); break;
+    case 2 * 8 + 2: TQ_RQ(2, 2); break;
+    case 2 * 8 + 1: TQ_RQ(2, 1); break;
+    default: TQ_RQ(1, 1); break;
+  }
+#undef TQ_RQ
   return tq_launch_check("k_requantize");
 }

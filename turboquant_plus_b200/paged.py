@@ -199,8 +199,8 @@ class PagedKVCache:
         torch = nv.require_cuda()
         bb = self.block_bytes(which, block_elems)
         slots = slot_mapping.to(device=self.device, dtype=torch.int64).contiguous()
-        out = torch.zeros((slots.numel(), self.num_kv_heads, self.head_dim // block_elems, bb), dtype=torch.uint8,
-                          device=self.device)
+        out = torch.empty((slots.numel(), self.num_kv_heads, self.head_dim // block_elems, bb), dtype=torch.uint8,
+                          device=self.device)        # the kernel writes every byte (zeros for skipped tokens)
         with torch.cuda.device(self.device):
             nv.call("tq_cache_export_blocks", C.byref(self.layout), nv.ptr(self.pool), 0 if which == "k" else 1,
                     nv.ptr(slots), slots.numel(), block_elems, nv.ptr(out), nv.stream_ptr())
