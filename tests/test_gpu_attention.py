@@ -530,3 +530,47 @@ def test_model_hooks_and_cache_adapter(tq):
     assert cache.get_seq_length(0) == 0
     with pytest.raises(ValueError):
         cache.update(kt[:, :, :200], vt[:, :, :200], layer)
+
+
+@pytest.mark.gpu
+def test_layered_decode_step_from_host_buffers(tq):
+    """LayeredKVCache.decode_step: pinned host buffers in, one captured graph (slot computation, quantize-on-append of
+    every layer on its own branch, attention per layer), host buffer out.  Three layers with a per-layer format table,
+    two sequences of different lengths, four steps; every step's output is checked against dequantize-then-attend over
+    everything appended so far."""
+    import torch
+    from turboquant_plus_b200.layered import LayeredKVCache
+    rng = np.random.default_rng(29)
+    L, hkv, hq, B, steps = 3, 2, 8, 2, 4
+    lens = [130, 40]
+    formats = [("turbo4", "turbo4"), ("turbo3", "turbo3"), ("turbo3", "turbo2")]
+    cache = LayeredKVCache(L, D, hkv, num_pages=6, formats=formats, seed=42)
+    bt = torch.tensor([[0, 1, 2], [3, 4, 5]], dtype=torch.int32)
+    ks = [[rng.standard_normal((n + steps, hkv, D)).astype(np.float16) for n in lens] for _ in range(L)]
+    vs = [[rng.standard_normal((n + steps, hkv, D)).astype(np.float16) for n in lens] for _ in range(L)]
+    for i in range(L):
+        for b, n in enumerate(lens):
+            t = np.arange(n)
+            slots = torch.as_tensor(bt[b].numpy()[t // 128].astype(np.int64) * 128 + t % 128)
+            cache.append(i, torch.as_tensor(ks[i][b][:n]).cuda(), torch.as_tensor(vs[i][b][:n]).cuda(), slots)
+    cache.prepare_decode(B, hq, bt, torch.tensor(lens))
+    qh = torch.empty((L, B, hq, D), dtype=torch.float16).pin_memory()
+    kh = torch.empty((L, B, hkv, D), dtype=torch.float16).pin_memory()
+    vh = torch.empty((L, B, hkv, D), dtype=torch.float16).pin_memory()
+    oh = torch.empty((L, B, hq, D), dtype=torch.float16).pin_memory()
+    for s in range(steps):
+        q = rng.standard_normal((L, B, hq, D)).astype(np.float16)
+        qh.copy_(torch.as_tensor(q))
+        for i in range(L):
+            for b, n in enumerate(lens):
+                kh[i, b] = torch.as_tensor(ks[i][b][n + s])
+                vh[i, b] = torch.as_tensor(vs[i][b][n + s])
+        out = cache.decode_step(qh, kh, vh, oh).float().numpy().copy()
+        now = [n + s + 1 for n in lens]
+        for i in range(L):
+            ref = oracle_attention(cache.layers[i], [ks[i][b][:now[b]] for b in range(B)],
+                                   [vs[i][b][:now[b]] for b in range(B)], q[i].astype(np.float32), now)
+            err = max_rel(out[i], ref)
+            assert err < TOL, f"step {s} layer {i}: {err:.2e}"
+    assert cache._step["len"].cpu().tolist() == [n + steps for n in lens]
+    assert cache.layers[0].kernel_status(cache.layers[0]._ws) == 0

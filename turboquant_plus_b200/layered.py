@@ -66,15 +66,27 @@ class LayeredKVCache:
         }
         ws = self.layers[0].workspace(batch, num_q_heads, st["bt"].shape[1])
 
+        append_stream = torch.cuda.Stream(device=dev)
+        appended = [torch.cuda.Event() for _ in self.layers]
+
         def body():
+            main = torch.cuda.current_stream(dev)
             pos = st["len"].to(torch.int64)
             page = st["bt"][st["rows"], pos // self.page_tokens].to(torch.int64)
             st["slots"].copy_(page * self.page_tokens + pos % self.page_tokens)
             st["len"].add_(1)
+            # The step's K/V rows of every layer are on the device when the step starts, so the quantize-on-append
+            # launches form their own branch of the graph: layer i's attention waits for layer i's append only, and
+            # the small append kernels run in the tails of the attention kernels of earlier layers.
+            append_stream.wait_stream(main)
+            with torch.cuda.stream(append_stream):
+                for i, layer in enumerate(self.layers):
+                    layer.append(st["k"][i], st["v"][i], st["slots"])
+                    appended[i].record(append_stream)
             for i, layer in enumerate(self.layers):
-                layer.append(st["k"][i], st["v"][i], st["slots"])
-                # the preceding kernel is this layer's append (it completes before its dependents start) or,
-                # across layers, another attention call: neither writes what this kernel reads early
+                main.wait_event(appended[i])
+                # the preceding kernel of this stream is another layer's attention call, which does not write what
+                # this kernel reads before its dependency wait; this layer's append has completed (event)
                 layer.attend(st["q"][i], st["bt"], st["len"], out=st["out"][i], workspace=ws, overlap=True)
 
         side = torch.cuda.Stream(device=dev)
