@@ -241,6 +241,15 @@ int tq_cache_import_blocks(const tq_cache_layout* layout, uint8_t* pool_dev, int
                            const int64_t* slot_dev, int64_t n_tokens, int32_t block_elems,
                            const uint8_t* in_dev, void* stream);
 
+/* tq_requantize on the records of paged caches: the K (which = 0) or V (which = 1) codes of the tokens at
+ * src_slot_dev[t] of one cache are re-quantized into the records at dst_slot_dev[t] of a cache with a narrower
+ * format (same KV heads, quantizers of the same seed); negative slots are skipped.  Old pages of a sequence move
+ * to a pool that costs fewer bytes per token; tq_decode_attn_lse + tq_attn_merge then attend over both pools. */
+int tq_cache_requantize(const tq_quantizer* src_q, const tq_quantizer* dst_q, const tq_cache_layout* src_layout,
+                        const uint8_t* src_pool_dev, const int64_t* src_slot_dev,
+                        const tq_cache_layout* dst_layout, uint8_t* dst_pool_dev, const int64_t* dst_slot_dev,
+                        int32_t which, int64_t n_tokens, void* stream);
+
 /* Scratch for tq_decode_attn (split partials + rotated queries), bytes; 256-byte aligned buffer. */
 int64_t tq_decode_workspace_bytes(int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
                                   int32_t max_pages_per_seq);
@@ -291,6 +300,20 @@ int tq_decode_attn_phases(const tq_quantizer* kq, const tq_quantizer* vq, const 
                           int32_t q_dtype, int32_t batch, int32_t num_q_heads, float scale,
                           void* workspace_dev, int64_t workspace_bytes, void* out_dev, int32_t out_dtype,
                           int32_t phases, void* stream);
+
+/* tq_decode_attn_phases that also returns, per (sequence, query head), the natural logarithm of the softmax
+ * denominator sum_t exp(scale * q.k_t) over the attended tokens (-inf for an empty sequence), and tq_attn_merge,
+ * which joins the outputs of two calls over disjoint parts of a sequence: out = (e^la a + e^lb b) / (e^la + e^lb),
+ * lse_out = log(e^la + e^lb) (or NULL); rows = batch * num_q_heads rows of 128; out may be one of the inputs.
+ * Together they attend over a sequence whose old pages live in another cache at fewer bits (temporal decay,
+ * benchmarks/temporal_decay_prototype.py) -- new surface, the reference never runs attention over its caches. */
+int tq_decode_attn_lse(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cache_layout* layout,
+                       const uint8_t* pool_dev, const int32_t* block_table_dev, int32_t max_pages_per_seq,
+                       const int32_t* seq_lens_dev, const void* q_dev, int32_t q_dtype, int32_t batch,
+                       int32_t num_q_heads, float scale, void* workspace_dev, int64_t workspace_bytes,
+                       void* out_dev, int32_t out_dtype, int32_t phases, float* lse_dev, void* stream);
+int tq_attn_merge(const void* out_a_dev, const float* lse_a_dev, const void* out_b_dev, const float* lse_b_dev,
+                  int64_t rows, int32_t dtype, void* out_dev, float* lse_out_dev, void* stream);
 
 /* Chunked-prefill attention over the packed cache on the tcgen05 tensor cores: a chunk of
  * `chunk_tokens` new tokens per sequence, whose K/V rows have already been appended, attends

@@ -574,3 +574,68 @@ def test_layered_decode_step_from_host_buffers(tq):
             assert err < TOL, f"step {s} layer {i}: {err:.2e}"
     assert cache._step["len"].cpu().tolist() == [n + steps for n in lens]
     assert cache.layers[0].kernel_status(cache.layers[0]._ws) == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("group", [4, 8])
+def test_decayed_pages_and_merged_attention(tq, group):
+    """Temporal decay at cache level: the first three pages of a 600-token turbo3 sequence are re-quantized into a
+    turbo2 cache (tq_cache_requantize), attention runs over the old part (turbo2 cache) and the recent part (turbo3
+    cache) separately and the two are joined from their log-sum-exps.  Oracle: old tokens dequantized from the
+    restated requantize_3to2 of the reference's prototype, recent tokens from the 3-bit code, one softmax over all.
+    Also: lse of a plain call equals the oracle's log-sum-exp, merging with an empty part changes nothing."""
+    import torch
+    from turboquant_plus_b200.paged import merge_attention
+    rng = np.random.default_rng(31 + group)
+    n, old, hkv = 600, 384, 2
+    hq = hkv * group
+    hot = tq.PagedKVCache(D, hkv, num_pages=5, k_format="turbo3", v_format="turbo3", seed=42)
+    cold = tq.PagedKVCache(D, hkv, num_pages=3, k_format="turbo2", v_format="turbo2", seed=42)
+    ks = [rng.standard_normal((n, hkv, D)).astype(np.float16)]
+    vs = [rng.standard_normal((n, hkv, D)).astype(np.float16)]
+    bt = fill_cache(hot, ks, vs, [n], rng)
+    q = rng.standard_normal((1, hq, D)).astype(np.float32)
+    qd = torch.as_tensor(q).cuda()
+    # plain call: lse against the oracle
+    out_all, lse_all = hot.attend(qd, bt, torch.tensor([n]), return_lse=True)
+    kh = np.stack([oracle_roundtrip(hot, ks[0][:, h], "k") for h in range(hkv)])          # (hkv, n, D)
+    vh = np.stack([oracle_roundtrip(hot, vs[0][:, h], "v") for h in range(hkv)])
+    logits = np.stack([kh[h // group] @ q[0, h].astype(np.float64) / np.sqrt(D) for h in range(hq)])   # (hq, n)
+    want_lse = np.log(np.exp(logits - logits.max(1, keepdims=True)).sum(1)) + logits.max(1)
+    assert np.abs(lse_all.cpu().numpy()[0] - want_lse).max() < 2e-3
+    # decay the first three pages
+    t = np.arange(old)
+    src_slots = torch.as_tensor(bt[0].numpy()[t // 128].astype(np.int64) * 128 + t % 128)
+    dst_slots = torch.as_tensor(t.astype(np.int64))
+    hot.decay_into(cold, src_slots, dst_slots)
+    bt_cold = torch.tensor([[0, 1, 2]], dtype=torch.int32)
+    bt_hot = bt[:, old // 128:].contiguous()
+    oa, la = cold.attend(qd, bt_cold, torch.tensor([old]), return_lse=True)
+    ob, lb = hot.attend(qd, bt_hot, torch.tensor([n - old]), return_lse=True)
+    got, lse = merge_attention(oa, la, ob, lb)
+    # oracle for the old part: 3-bit code -> requantize_3to2 restatement -> rotate back
+    for which, quant3, quant2, xs, hat in (("k", hot.k_quantizer, cold.k_quantizer, ks[0], kh),
+                                           ("v", hot.v_quantizer, cold.v_quantizer, vs[0], vh)):
+        for h in range(hkv):
+            x32 = xs[:old, h].astype(np.float32)
+            i3, nrm = o.polar_quantize(x32, quant3.rotation, quant3.centroids)
+            y = np.zeros((old, D))
+            for r in range(old):
+                i2, corrected = o.decay_requantize(i3[r], nrm[r], quant3.centroids, quant2.centroids,
+                                                   o.boundaries(quant2.centroids))
+                y[r] = quant2.centroids[i2] * corrected
+            hat[h, :old] = y @ quant3.rotation          # x = R^T y, row-wise
+    ref = o.attend_gqa(q.astype(np.float64), kh[None], vh[None], [n])
+    err = max_rel(got.cpu().numpy(), ref)
+    print(f"group {group}: decayed + recent, merged: max-rel {err:.2e}")
+    assert err < TOL
+    logits2 = np.stack([kh[h // group] @ q[0, h].astype(np.float64) / np.sqrt(D) for h in range(hq)])
+    want2 = np.log(np.exp(logits2 - logits2.max(1, keepdims=True)).sum(1)) + logits2.max(1)
+    assert np.abs(lse.cpu().numpy()[0] - want2).max() < 2e-3
+    # an empty part: lse = -inf, the merge returns the other part
+    oe, le = cold.attend(qd, bt_cold, torch.tensor([0]), return_lse=True)
+    assert torch.isinf(le).all() and (le < 0).all() and (oe == 0).all()
+    same, ls = merge_attention(oe, le, ob, lb)
+    assert torch.equal(same, ob) and torch.allclose(ls, lb)
+    with pytest.raises(ValueError):
+        cold.decay_into(hot, dst_slots, src_slots)         # wider destination

@@ -65,6 +65,9 @@ SIGNATURES = {
     "tq_block_bytes": (C.c_int64, [_I32, _I32]),
     "tq_cache_export_blocks": (C.c_int, [_P, _P, _I32, _P, _I64, _I32, _P, _P]),
     "tq_cache_import_blocks": (C.c_int, [_P, _P, _I32, _P, _I64, _I32, _P, _P]),
+    "tq_cache_requantize": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _I32, _I64, _P]),
+    "tq_decode_attn_lse": (C.c_int, [_P, _P, _P, _P, _P, _I32, _P, _P, _I32, _I32, _I32, _F, _P, _I64, _P, _I32, _I32, _P, _P]),
+    "tq_attn_merge": (C.c_int, [_P, _P, _P, _P, _I64, _I32, _P, _P, _P]),
     "tq_requantize": (C.c_int, [_P, _P, _P, _P, _I32, _I64, _P, _P, _P, _P]),
     "tq_quantize_residual": (C.c_int, [_P, _P, _I32, _I64, _I64, _P, _P, _P, _I64, _P]),
     "tq_dequantize_strided": (C.c_int, [_P, _P, _P, _I64, _P, _I64, _I32, _P]),

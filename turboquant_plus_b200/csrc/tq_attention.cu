@@ -153,6 +153,7 @@ struct AttnParams {
   int32_t* tickets;    // [B*Hkv], zero between calls
   int32_t* status;
   void* out;           // [B][Hq][128] (out_dtype)
+  float* lse;          // [B][Hq] natural log of the softmax denominator (with the maximum folded in); or null
   const float* v_rot;  // dense V rotation, row-major fp32 (nullptr: sign-WHT or identity)
   float qscale;        // softmax scale * log2(e)
   int32_t q_dtype, out_dtype;
@@ -308,6 +309,8 @@ __device__ __forceinline__ void fold_splits(const AttnParams& P, float v_alpha, 
     acc.z += __shfl_xor_sync(0xffffffffu, acc.z, 16); acc.w += __shfl_xor_sync(0xffffffffu, acc.w, 16);
   }
   PHASE_STAMP(12);
+  // M and Lsum are in the log2 domain of the scaled scores: ln sum exp(score) = ln 2 (M + log2 Lsum)
+  if (P.lse && half == 0 && lane == 0) P.lse[row0 + head] = (M + log2f(Lsum)) * 0.6931471805599453f;
   // attention output in V's rotated space
   const float inv = 1.0f / (Lsum * (V_Q8 ? 1.0f : v_alpha));
   if (parity == 0)
@@ -402,6 +405,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn(const AttnParams
   const size_t row0 = (size_t)b * P.hq + (size_t)kvh * P.group;  // first query / output row of this CTA
   if (n_pages == 0 && split == 0) {  // empty sequence: zeros
     for (int e = tid; e < P.group * TQ_D; e += ATT_THREADS) store_out(P.out, P.out_dtype, row0 * TQ_D + e, 0.f);
+    if (P.lse && tid < P.group) P.lse[row0 + tid] = -INFINITY;
     return;
   }
   if (page_lo >= n_pages) return;
@@ -929,8 +933,10 @@ __global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_c
   // every thread waits before it can touch the workspace or the output (the query warps already have)
   if (P.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
   const int n_pages = (seq_len + PT - 1) / PT;
-  if (n_pages == 0 && split == 0)  // empty sequence: zeros (split 0 exists for every kv head)
+  if (n_pages == 0 && split == 0) {  // empty sequence: zeros (split 0 exists for every kv head)
     for (int e = tid; e < P.group * TQ_D; e += ATT_THREADS) store_out(P.out, P.out_dtype, row0 * TQ_D + e, 0.f);
+    if (P.lse && tid < P.group) P.lse[row0 + tid] = -INFINITY;
+  }
   const int np = min(n_pages, page_lo + P.chunk_pages) - page_lo;
   const int ns = (n_pages + P.chunk_pages - 1) / P.chunk_pages;
   PHASE_STAMP(6);
@@ -1291,12 +1297,11 @@ extern "C" int tq_decode_attn(const tq_quantizer* kq, const tq_quantizer* vq, co
                                batch, num_q_heads, scale, workspace_dev, workspace_bytes, out_dev, out_dtype, 3, stream);
 }
 
-extern "C" int tq_decode_attn_phases(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cache_layout* L,
-                                     const uint8_t* pool_dev, const int32_t* block_table_dev,
-                                     int32_t max_pages_per_seq, const int32_t* seq_lens_dev, const void* q_dev,
-                                     int32_t q_dtype, int32_t batch, int32_t num_q_heads, float scale,
-                                     void* workspace_dev, int64_t workspace_bytes, void* out_dev, int32_t out_dtype,
-                                     int32_t phases, void* stream) {
+static int decode_impl(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cache_layout* L,
+                       const uint8_t* pool_dev, const int32_t* block_table_dev, int32_t max_pages_per_seq,
+                       const int32_t* seq_lens_dev, const void* q_dev, int32_t q_dtype, int32_t batch,
+                       int32_t num_q_heads, float scale, void* workspace_dev, int64_t workspace_bytes, void* out_dev,
+                       int32_t out_dtype, int32_t phases, float* lse_dev, void* stream) {
   TQ_REQUIRE(L, TQ_ERR_INVALID, "tq_decode_attn: layout missing");
   TQ_REQUIRE(batch >= 0 && num_q_heads >= 1 && max_pages_per_seq >= 1, TQ_ERR_INVALID, "bad sizes");
   if (batch == 0) return TQ_OK;
@@ -1368,6 +1373,7 @@ extern "C" int tq_decode_attn_phases(const tq_quantizer* kq, const tq_quantizer*
   P.tickets = reinterpret_cast<int32_t*>(ws + workspace_bytes - TAIL_BYTES);
   P.status = reinterpret_cast<int32_t*>(ws + workspace_bytes - 256);
   P.out = out_dev;
+  P.lse = lse_dev;
   P.v_rot = v_dense ? vq->rot32 : nullptr;
   P.qscale = qscale;
   P.q_dtype = q_dtype;
@@ -1408,6 +1414,77 @@ extern "C" int tq_decode_attn_phases(const tq_quantizer* kq, const tq_quantizer*
   TQ_ATT(18, 2) TQ_ATT(18, 3) TQ_ATT(19, 2) TQ_ATT(19, 3) TQ_ATT(19, 4) TQ_ATT(20, 3) TQ_ATT(20, 4)
 #undef TQ_ATT
   return rc;
+}
+
+extern "C" int tq_decode_attn_phases(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cache_layout* L,
+                                     const uint8_t* pool_dev, const int32_t* block_table_dev,
+                                     int32_t max_pages_per_seq, const int32_t* seq_lens_dev, const void* q_dev,
+                                     int32_t q_dtype, int32_t batch, int32_t num_q_heads, float scale,
+                                     void* workspace_dev, int64_t workspace_bytes, void* out_dev, int32_t out_dtype,
+                                     int32_t phases, void* stream) {
+  return decode_impl(kq, vq, L, pool_dev, block_table_dev, max_pages_per_seq, seq_lens_dev, q_dev, q_dtype, batch,
+                     num_q_heads, scale, workspace_dev, workspace_bytes, out_dev, out_dtype, phases, nullptr, stream);
+}
+
+extern "C" int tq_decode_attn_lse(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cache_layout* L,
+                                  const uint8_t* pool_dev, const int32_t* block_table_dev, int32_t max_pages_per_seq,
+                                  const int32_t* seq_lens_dev, const void* q_dev, int32_t q_dtype, int32_t batch,
+                                  int32_t num_q_heads, float scale, void* workspace_dev, int64_t workspace_bytes,
+                                  void* out_dev, int32_t out_dtype, int32_t phases, float* lse_dev, void* stream) {
+  TQ_REQUIRE(lse_dev, TQ_ERR_INVALID, "tq_decode_attn_lse: lse buffer is null");
+  return decode_impl(kq, vq, L, pool_dev, block_table_dev, max_pages_per_seq, seq_lens_dev, q_dev, q_dtype, batch,
+                     num_q_heads, scale, workspace_dev, workspace_bytes, out_dev, out_dtype, phases, lse_dev, stream);
+}
+
+// out = (e^la a + e^lb b) / (e^la + e^lb) per row: joins the attention outputs of two disjoint parts of one sequence
+// (say, old pages kept at fewer bits in another cache) from their log-sum-exps.  One warp per 128-wide row.
+template <typename T>
+__global__ void __launch_bounds__(256) k_attn_merge(const T* a, const float* la, const T* b, const float* lb,
+                                                    int64_t rows, T* out, float* lse_out) {  // out may be a or b
+  const int lane = threadIdx.x & 31;
+  const int64_t row = ((int64_t)blockIdx.x * 256 + threadIdx.x) >> 5;
+  if (row >= rows) return;
+  const float x = la[row], y = lb[row], m = fmaxf(x, y);
+  float wa = 0.5f, wb = 0.5f, l = m;
+  if (m == -INFINITY) { wa = wb = 0.f; }   // both parts empty: zeros
+  else {
+    const float ea = __expf(x - m), eb = __expf(y - m);
+    wa = ea / (ea + eb);
+    wb = eb / (ea + eb);
+    l = m + logf(ea + eb);
+  }
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int64_t i = row * TQ_D + 4 * lane + k;
+    const float av = wa == 0.f ? 0.f : (float)a[i] * wa, bv = wb == 0.f ? 0.f : (float)b[i] * wb;
+    out[i] = (T)(av + bv);
+  }
+  if (lse_out && lane == 0) lse_out[row] = l;
+}
+
+extern "C" int tq_attn_merge(const void* out_a_dev, const float* lse_a_dev, const void* out_b_dev,
+                             const float* lse_b_dev, int64_t rows, int32_t dtype, void* out_dev, float* lse_out_dev,
+                             void* stream) {
+  TQ_REQUIRE(rows >= 0, TQ_ERR_INVALID, "tq_attn_merge: rows must be >= 0");
+  if (rows == 0) return TQ_OK;
+  TQ_REQUIRE(out_a_dev && lse_a_dev && out_b_dev && lse_b_dev && out_dev, TQ_ERR_INVALID, "tq_attn_merge: null buffer");
+  const int grid = (int)((rows * 32 + 255) / 256);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == TQ_F32)
+    k_attn_merge<float><<<grid, 256, 0, st>>>((const float*)out_a_dev, lse_a_dev, (const float*)out_b_dev, lse_b_dev, rows,
+                                              (float*)out_dev, lse_out_dev);
+  else if (dtype == TQ_F16)
+    k_attn_merge<__half><<<grid, 256, 0, st>>>((const __half*)out_a_dev, lse_a_dev, (const __half*)out_b_dev, lse_b_dev,
+                                               rows, (__half*)out_dev, lse_out_dev);
+  else if (dtype == TQ_BF16)
+    k_attn_merge<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)out_a_dev, lse_a_dev,
+                                                      (const __nv_bfloat16*)out_b_dev, lse_b_dev, rows,
+                                                      (__nv_bfloat16*)out_dev, lse_out_dev);
+  else {
+    tq_set_error("tq_attn_merge: outputs must be fp16, bf16 or fp32, got dtype %d", dtype);
+    return TQ_ERR_UNSUPPORTED;
+  }
+  return tq_launch_check("k_attn_merge");
 }
 
 // ------------------------------------------------------------------------------------------

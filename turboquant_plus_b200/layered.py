@@ -22,16 +22,24 @@ class LayeredKVCache:
             formats = [tuple(formats)] * num_layers
         assert len(formats) == num_layers
         self.formats = [tuple(f) for f in formats]
-        self.layers = []
-        shared = {}
-        for kf, vf in self.formats:
-            donor = shared.get((kf, vf))
-            layer = PagedKVCache(head_dim, num_kv_heads, num_pages, page_tokens, kf, vf, seed=seed,
-                                 norm_correction=norm_correction, rotation=rotation, device=device,
-                                 k_quantizer=donor.k_quantizer if donor else None,
-                                 v_quantizer=donor.v_quantizer if donor else None)
-            shared.setdefault((kf, vf), layer)
-            self.layers.append(layer)
+        # Layers of one (K format, V format) pair share the quantizers and one pool tensor: layer j of the group owns
+        # pages [j * num_pages, (j + 1) * num_pages) of it.  `groups` holds, per pair, a cache object over the whole
+        # tensor, through which one launch appends a token to every layer of the group.
+        self.layers = [None] * num_layers
+        self.groups = []
+        by_format = {}
+        for i, fmt in enumerate(self.formats):
+            by_format.setdefault(fmt, []).append(i)
+        for (kf, vf), members in by_format.items():
+            whole = PagedKVCache(head_dim, num_kv_heads, num_pages * len(members), page_tokens, kf, vf, seed=seed,
+                                 norm_correction=norm_correction, rotation=rotation, device=device)
+            for j, i in enumerate(members):
+                self.layers[i] = PagedKVCache(head_dim, num_kv_heads, num_pages, page_tokens, kf, vf, seed=seed,
+                                              norm_correction=norm_correction, rotation=rotation, device=device,
+                                              k_quantizer=whole.k_quantizer, v_quantizer=whole.v_quantizer,
+                                              pool=whole.pool[j * num_pages:(j + 1) * num_pages])
+            self.groups.append((whole, members))
+        self.num_pages = num_pages
         self.device = self.layers[0].device
         self.num_layers, self.head_dim, self.num_kv_heads = num_layers, head_dim, num_kv_heads
         self.page_tokens = page_tokens
@@ -66,27 +74,27 @@ class LayeredKVCache:
         }
         ws = self.layers[0].workspace(batch, num_q_heads, st["bt"].shape[1])
 
-        append_stream = torch.cuda.Stream(device=dev)
-        appended = [torch.cuda.Event() for _ in self.layers]
+        # per format group: which layers, and where each layer's pages start inside the group's pool
+        plans = []
+        for whole, members in self.groups:
+            idx = None if members == list(range(L)) else torch.tensor(members, device=dev)
+            base = (torch.arange(len(members), device=dev, dtype=torch.int64) * (self.num_pages * self.page_tokens))[:, None]
+            plans.append((whole, idx, base, len(members)))
 
         def body():
-            main = torch.cuda.current_stream(dev)
             pos = st["len"].to(torch.int64)
             page = st["bt"][st["rows"], pos // self.page_tokens].to(torch.int64)
             st["slots"].copy_(page * self.page_tokens + pos % self.page_tokens)
             st["len"].add_(1)
-            # The step's K/V rows of every layer are on the device when the step starts, so the quantize-on-append
-            # launches form their own branch of the graph: layer i's attention waits for layer i's append only, and
-            # the small append kernels run in the tails of the attention kernels of earlier layers.
-            append_stream.wait_stream(main)
-            with torch.cuda.stream(append_stream):
-                for i, layer in enumerate(self.layers):
-                    layer.append(st["k"][i], st["v"][i], st["slots"])
-                    appended[i].record(append_stream)
+            # one quantize-on-append launch per format group: the new token of every layer of the group at once
+            for whole, idx, base, n in plans:
+                k = st["k"] if idx is None else st["k"].index_select(0, idx)
+                v = st["v"] if idx is None else st["v"].index_select(0, idx)
+                whole.append(k.reshape(n * batch, self.num_kv_heads, d), v.reshape(n * batch, self.num_kv_heads, d),
+                             (base + st["slots"][None, :]).reshape(-1))
             for i, layer in enumerate(self.layers):
-                main.wait_event(appended[i])
-                # the preceding kernel of this stream is another layer's attention call, which does not write what
-                # this kernel reads before its dependency wait; this layer's append has completed (event)
+                # the preceding kernel is an append (it never signals early completion, so this kernel starts after it)
+                # or another layer's attention call, which does not write what this kernel reads early
                 layer.attend(st["q"][i], st["bt"], st["len"], out=st["out"][i], workspace=ws, overlap=True)
 
         side = torch.cuda.Stream(device=dev)
@@ -102,18 +110,35 @@ class LayeredKVCache:
             body()
         st["len"].copy_(saved)
         st["graph"] = graph
+        st["body"] = body
         self._step = st
         return st
 
     def decode_step(self, q_host, k_host, v_host, out_host):
-        """One decode step from host buffers (pinned tensors shaped like the static device buffers):
-        H2D of the step's queries and new K/V rows, the captured graph, D2H of the outputs."""
+        """One decode step from host buffers (tensors shaped like the static device buffers): H2D of the step's
+        queries and new K/V rows, the captured launches, D2H of the outputs.  With pinned buffers the copies are
+        nodes of the same graph as the kernels, captured the first time a set of buffers is seen, so that a step
+        is one graph launch and one synchronisation; pass the same buffers every step."""
         torch = nv.require_cuda()
         st = self._step
-        st["q"].copy_(q_host, non_blocking=True)
-        st["k"].copy_(k_host, non_blocking=True)
-        st["v"].copy_(v_host, non_blocking=True)
-        st["graph"].replay()
-        out_host.copy_(st["out"], non_blocking=True)
+        hosts = (q_host, k_host, v_host, out_host)
+        if all(t.is_pinned() for t in hosts):
+            key = tuple(t.data_ptr() for t in hosts)
+            if st.get("io_key") != key:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    st["q"].copy_(q_host, non_blocking=True)
+                    st["k"].copy_(k_host, non_blocking=True)
+                    st["v"].copy_(v_host, non_blocking=True)
+                    st["body"]()
+                    out_host.copy_(st["out"], non_blocking=True)
+                st["io_graph"], st["io_key"], st["io_refs"] = graph, key, hosts   # the graph holds raw host pointers
+            st["io_graph"].replay()
+        else:
+            st["q"].copy_(q_host, non_blocking=True)
+            st["k"].copy_(k_host, non_blocking=True)
+            st["v"].copy_(v_host, non_blocking=True)
+            st["graph"].replay()
+            out_host.copy_(st["out"], non_blocking=True)
         torch.cuda.current_stream(self.device).synchronize()
         return out_host

@@ -31,7 +31,7 @@ class PagedKVCache:
     def __init__(self, head_dim: int, num_kv_heads: int, num_pages: int, page_tokens: int = 128,
                  k_format: str = "turbo3", v_format: str = "turbo3", seed: int = 42,
                  norm_correction: bool = True, rotation: str = "wht", device=None,
-                 k_quantizer=None, v_quantizer=None):
+                 k_quantizer=None, v_quantizer=None, pool=None):
         torch = nv.require_cuda()
         if k_format not in nv.FORMATS or v_format not in nv.FORMATS:
             raise ValueError(f"unknown cache format {k_format!r} / {v_format!r}")
@@ -56,8 +56,11 @@ class PagedKVCache:
             v_quantizer = PolarQuant(head_dim, _fmt_bits(v_format), seed=seed + 500, norm_correction=norm_correction,
                                      rotation=rotation, device=self.device)
         self.k_quantizer, self.v_quantizer = k_quantizer, v_quantizer
-        self.pool = torch.zeros((num_pages, num_kv_heads, self.layout.record_bytes), dtype=torch.uint8,
-                                device=self.device)
+        if pool is None:
+            pool = torch.zeros((num_pages, num_kv_heads, self.layout.record_bytes), dtype=torch.uint8, device=self.device)
+        elif tuple(pool.shape) != (num_pages, num_kv_heads, self.layout.record_bytes) or not pool.is_contiguous():
+            raise ValueError("pool must be a contiguous uint8 tensor of shape (num_pages, num_kv_heads, record bytes)")
+        self.pool = pool        # may be a slice of a larger tensor that several caches share (LayeredKVCache)
         self._ws = None
         self._dummy = None
 
@@ -128,14 +131,17 @@ class PagedKVCache:
         return self._ws
 
     def attend(self, q, block_table, seq_lens, scale=None, out=None, workspace=None, phases=7, overlap=False,
-               sparse_v=False):
+               sparse_v=False, return_lse=False):
         """q: (batch, num_q_heads, head_dim) CUDA tensor; block_table: (batch, max_pages) int32 page
         numbers; seq_lens: (batch,) int32.  Returns (batch, num_q_heads, head_dim) in q's dtype.
 
         overlap=True lets the kernel start while the preceding kernel of the stream is still running; until
         that kernel has completed it only reads cache pages, the block table and the sequence lengths.  Use it
         when the preceding kernel does not write those (another layer's attention, an append kernel that does
-        not signal early completion)."""
+        not signal early completion).
+
+        return_lse=True returns (out, lse) with lse (batch, num_q_heads) fp32, the natural log of the softmax
+        denominator: what merge_attention needs to join calls over disjoint parts of a sequence."""
         if overlap:
             phases = int(phases) | nv.DECODE_OVERLAP
         if sparse_v:  # skip V work where every weight of a 16-token tile is below 1e-6 (the reference's sparse V)
@@ -150,11 +156,36 @@ class PagedKVCache:
         if out is None:
             out = torch.empty_like(q)
         with torch.cuda.device(self.device):
+            if return_lse:
+                lse = torch.empty((bsz, hq), dtype=torch.float32, device=self.device)
+                nv.call("tq_decode_attn_lse", self._handle(self.k_quantizer), self._handle(self.v_quantizer),
+                        C.byref(self.layout), nv.ptr(self.pool), nv.ptr(bt), bt.shape[1], nv.ptr(sl), nv.ptr(q),
+                        nv.torch_dtype_code(q.dtype), bsz, hq, float(scale) if scale else 0.0, nv.ptr(ws), ws.numel(),
+                        nv.ptr(out), nv.torch_dtype_code(out.dtype), int(phases), nv.ptr(lse), nv.stream_ptr())
+                return out, lse
             nv.call("tq_decode_attn_phases", self._handle(self.k_quantizer), self._handle(self.v_quantizer),
                     C.byref(self.layout), nv.ptr(self.pool), nv.ptr(bt), bt.shape[1], nv.ptr(sl), nv.ptr(q),
                     nv.torch_dtype_code(q.dtype), bsz, hq, float(scale) if scale else 0.0, nv.ptr(ws), ws.numel(),
                     nv.ptr(out), nv.torch_dtype_code(out.dtype), int(phases), nv.stream_ptr())
         return out
+
+    def decay_into(self, dst: "PagedKVCache", src_slots, dst_slots):
+        """Temporal decay at cache level (benchmarks/temporal_decay_prototype.py:93-125): the K and V codes of the
+        tokens at ``src_slots`` of this cache are re-quantized, in the rotated domain, into the records at
+        ``dst_slots`` of ``dst``, a cache with narrower turboN formats built from the same seed.  The caller then
+        frees the source pages and attends over both caches with ``attend(..., return_lse=True)`` +
+        ``merge_attention``."""
+        torch = nv.require_cuda()
+        ss = src_slots.to(device=self.device, dtype=torch.int64).contiguous()
+        ds = dst_slots.to(device=self.device, dtype=torch.int64).contiguous()
+        if ss.numel() != ds.numel():
+            raise ValueError("src_slots and dst_slots must name the same number of tokens")
+        with torch.cuda.device(self.device):
+            for which, (a, b) in enumerate(((self.k_quantizer, dst.k_quantizer), (self.v_quantizer, dst.v_quantizer))):
+                if a is None or b is None:
+                    raise nv.TQError("decay_into converts turboN tensors; q8_0 tensors have no narrower codebook")
+                nv.call("tq_cache_requantize", self._handle(a), dst._handle(b), C.byref(self.layout), nv.ptr(self.pool),
+                        nv.ptr(ss), C.byref(dst.layout), nv.ptr(dst.pool), nv.ptr(ds), which, ss.numel(), nv.stream_ptr())
 
     def prefill_attend(self, q, block_table, kv_lens, scale=None, out=None, workspace=None):
         """Chunked prefill on the tcgen05 tensor cores.  q: (batch, chunk_tokens, num_q_heads, head_dim) CUDA
@@ -241,3 +272,19 @@ class PagedKVCache:
         st = C.c_int32(0)
         nv.call("tq_decode_status_sync", nv.ptr(ws), ws.numel(), C.byref(st))
         return st.value
+
+
+def merge_attention(out_a, lse_a, out_b, lse_b, out=None):
+    """Joins the attention outputs of two disjoint parts of a sequence from their log-sum-exps:
+    (e^la a + e^lb b) / (e^la + e^lb).  Returns (out, lse); out may be one of the inputs."""
+    torch = nv.require_cuda()
+    out_a, out_b = out_a.contiguous(), out_b.contiguous()
+    assert out_a.shape == out_b.shape and out_a.dtype == out_b.dtype and out_a.shape[-1] == 128
+    rows = out_a.numel() // 128
+    if out is None:
+        out = torch.empty_like(out_a)
+    lse = torch.empty((rows,), dtype=torch.float32, device=out_a.device)
+    with torch.cuda.device(out_a.device):
+        nv.call("tq_attn_merge", nv.ptr(out_a), nv.ptr(lse_a.contiguous()), nv.ptr(out_b), nv.ptr(lse_b.contiguous()), rows,
+                nv.torch_dtype_code(out_a.dtype), nv.ptr(out), nv.ptr(lse), nv.stream_ptr())
+    return out, lse.reshape(lse_a.shape)
