@@ -559,6 +559,9 @@ def test_layered_decode_step_from_host_buffers(tq):
     vh = torch.empty((L, B, hkv, D), dtype=torch.float16).pin_memory()
     oh = torch.empty((L, B, hq, D), dtype=torch.float16).pin_memory()
     for s in range(steps):
+        if s == 2:          # the cache's own staging buffers: q, k, v adjacent, one copy per step, a new graph
+            qh, kh, vh, oh = cache.host_buffers()
+            assert kh.data_ptr() == qh.data_ptr() + qh.numel() * 2 and qh.is_pinned() and vh.is_pinned()
         q = rng.standard_normal((L, B, hq, D)).astype(np.float16)
         qh.copy_(torch.as_tensor(q))
         for i in range(L):

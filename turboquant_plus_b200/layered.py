@@ -62,10 +62,15 @@ class LayeredKVCache:
         torch = nv.require_cuda()
         dtype = dtype or torch.float16
         dev, L, d = self.device, self.num_layers, self.head_dim
+        # q, k and v of a step are three views of one buffer, so that host buffers laid out the same way
+        # (host_buffers()) arrive with a single copy
+        nq, nk = L * batch * num_q_heads * d, L * batch * self.num_kv_heads * d
+        qkv = torch.zeros((nq + 2 * nk,), dtype=dtype, device=dev)
         st = {
-            "q": torch.zeros((L, batch, num_q_heads, d), dtype=dtype, device=dev),
-            "k": torch.zeros((L, batch, self.num_kv_heads, d), dtype=dtype, device=dev),
-            "v": torch.zeros((L, batch, self.num_kv_heads, d), dtype=dtype, device=dev),
+            "qkv": qkv,
+            "q": qkv[:nq].view(L, batch, num_q_heads, d),
+            "k": qkv[nq:nq + nk].view(L, batch, self.num_kv_heads, d),
+            "v": qkv[nq + nk:].view(L, batch, self.num_kv_heads, d),
             "out": torch.zeros((L, batch, num_q_heads, d), dtype=dtype, device=dev),
             "bt": block_table.to(device=dev, dtype=torch.int32).contiguous(),
             "len": seq_lens.to(device=dev, dtype=torch.int32).clone(),
@@ -114,6 +119,30 @@ class LayeredKVCache:
         self._step = st
         return st
 
+    def host_buffers(self):
+        """Pinned host tensors (q, k, v, out) for decode_step, q/k/v carved from one allocation in the order of the
+        device buffers: a step then needs one host-to-device copy instead of three."""
+        torch = nv.require_cuda()
+        st = self._step
+        flat = torch.zeros(st["qkv"].shape, dtype=st["qkv"].dtype).pin_memory()
+        nq, nk = st["q"].numel(), st["k"].numel()
+        out = torch.zeros(st["out"].shape, dtype=st["out"].dtype).pin_memory()
+        return (flat[:nq].view(st["q"].shape), flat[nq:nq + nk].view(st["k"].shape), flat[nq + nk:].view(st["v"].shape), out)
+
+    def _copy_in(self, q_host, k_host, v_host):
+        st = self._step
+        esz = q_host.element_size()
+        if (q_host.is_contiguous() and k_host.is_contiguous() and v_host.is_contiguous()
+                and k_host.data_ptr() == q_host.data_ptr() + q_host.numel() * esz
+                and v_host.data_ptr() == k_host.data_ptr() + k_host.numel() * esz
+                and q_host.dtype == st["qkv"].dtype and q_host.numel() == st["q"].numel()):
+            flat = q_host.reshape(-1).as_strided((st["qkv"].numel(),), (1,))     # the three views as one extent
+            st["qkv"].copy_(flat, non_blocking=True)
+        else:
+            st["q"].copy_(q_host, non_blocking=True)
+            st["k"].copy_(k_host, non_blocking=True)
+            st["v"].copy_(v_host, non_blocking=True)
+
     def decode_step(self, q_host, k_host, v_host, out_host):
         """One decode step from host buffers (tensors shaped like the static device buffers): H2D of the step's
         queries and new K/V rows, the captured launches, D2H of the outputs.  With pinned buffers the copies are
@@ -127,17 +156,13 @@ class LayeredKVCache:
             if st.get("io_key") != key:
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph):
-                    st["q"].copy_(q_host, non_blocking=True)
-                    st["k"].copy_(k_host, non_blocking=True)
-                    st["v"].copy_(v_host, non_blocking=True)
+                    self._copy_in(q_host, k_host, v_host)
                     st["body"]()
                     out_host.copy_(st["out"], non_blocking=True)
                 st["io_graph"], st["io_key"], st["io_refs"] = graph, key, hosts   # the graph holds raw host pointers
             st["io_graph"].replay()
         else:
-            st["q"].copy_(q_host, non_blocking=True)
-            st["k"].copy_(k_host, non_blocking=True)
-            st["v"].copy_(v_host, non_blocking=True)
+            self._copy_in(q_host, k_host, v_host)
             st["graph"].replay()
             out_host.copy_(st["out"], non_blocking=True)
         torch.cuda.current_stream(self.device).synchronize()
