@@ -642,3 +642,65 @@ def test_decayed_pages_and_merged_attention(tq, group):
     assert torch.equal(same, ob) and torch.allclose(ls, lb)
     with pytest.raises(ValueError):
         cold.decay_into(hot, dst_slots, src_slots)         # wider destination
+
+
+@pytest.mark.gpu
+def test_side_entry_points_edge_cases(tq):
+    """Skipped tokens (negative slots), empty calls and argument errors of the block codec, the cache-level
+    re-quantization and the merge."""
+    import torch
+    from turboquant_plus_b200.paged import merge_attention
+    rng = np.random.default_rng(5)
+    n, hkv = 40, 2
+    cache = tq.PagedKVCache(D, hkv, num_pages=2, k_format="turbo3", v_format="turbo3", seed=42)
+    x = torch.as_tensor(rng.standard_normal((n, hkv, D)).astype(np.float16)).cuda()
+    cache.append(x, x, torch.arange(n))
+    slots = torch.arange(n)
+    slots[3] = -1
+    slots[17] = -5
+    blocks = cache.export_blocks("k", slots, 32)
+    assert (blocks[3] == 0).all() and (blocks[17] == 0).all() and (blocks[4] != 0).any()
+    full = cache.export_blocks("k", torch.arange(n), 32)
+    keep = [i for i in range(n) if i not in (3, 17)]
+    assert torch.equal(blocks[keep], full[keep])
+    other = tq.PagedKVCache(D, hkv, num_pages=2, k_format="turbo3", v_format="turbo3", seed=42)
+    other.import_blocks("k", blocks, slots, 32)
+    L = cache.layout
+    a, b = cache.pool.cpu().numpy()[0, 0], other.pool.cpu().numpy()[0, 0]
+    assert np.array_equal(a[L.k_idx_off + 4 * 48: L.k_idx_off + 5 * 48], b[L.k_idx_off + 4 * 48: L.k_idx_off + 5 * 48])
+    assert not b[L.k_idx_off + 3 * 48: L.k_idx_off + 4 * 48].any()        # skipped on import: record untouched
+    assert tuple(cache.export_blocks("v", torch.zeros(0, dtype=torch.int64), 128).shape) == (0, hkv, 1, 50)
+    with pytest.raises(ValueError):
+        cache.export_blocks("k", slots, 48)
+    with pytest.raises(ValueError):
+        other.import_blocks("k", blocks[:5], slots, 32)
+    q8 = tq.PagedKVCache(D, hkv, num_pages=2, k_format="q8_0", v_format="turbo3", seed=42)
+    with pytest.raises(ValueError):
+        q8.block_bytes("k", 32)
+    # cache-level re-quantization: skipped tokens leave the destination untouched
+    cold = tq.PagedKVCache(D, hkv, num_pages=2, k_format="turbo2", v_format="turbo2", seed=42)
+    cache.decay_into(cold, slots, torch.arange(n))
+    c = cold.pool.cpu().numpy()[0, 0]
+    Lc = cold.layout
+    assert not c[Lc.k_idx_off + 3 * 32: Lc.k_idx_off + 4 * 32].any() and c[Lc.k_idx_off + 4 * 32: Lc.k_idx_off + 5 * 32].any()
+    cache.decay_into(cold, torch.zeros(0, dtype=torch.int64), torch.zeros(0, dtype=torch.int64))
+    with pytest.raises(ValueError):
+        cache.decay_into(cold, slots, torch.arange(n - 1))
+    wrong_seed = tq.PagedKVCache(D, hkv, num_pages=2, k_format="turbo2", v_format="turbo2", seed=43)
+    with pytest.raises(ValueError):
+        cache.decay_into(wrong_seed, slots, torch.arange(n))
+    with pytest.raises(tq._native.TQError):
+        q8.decay_into(cold, slots, torch.arange(n))
+    # merge: equal log-sum-exps average, fp16 and fp32, in place
+    for dt in (torch.float16, torch.float32, torch.bfloat16):
+        oa = torch.randn((3, 4, D), device="cuda").to(dt)
+        ob = torch.randn((3, 4, D), device="cuda").to(dt)
+        la = torch.tensor([[0.0, 1.0, -2.0, 5.0]] * 3, device="cuda")
+        lb = torch.tensor([[0.0, -1.0, 2.0, float("-inf")]] * 3, device="cuda")
+        got, lse = merge_attention(oa, la, ob, lb)
+        wa = torch.exp(la - torch.logaddexp(la, lb))[..., None]
+        want = oa.float() * wa + ob.float() * (1 - wa)
+        assert (got.float() - want).abs().max() < (1e-5 if dt == torch.float32 else 2e-2)
+        assert torch.allclose(lse, torch.logaddexp(la, lb), atol=1e-5)
+        inplace, _ = merge_attention(oa, la, ob, lb, out=oa)
+        assert inplace.data_ptr() == oa.data_ptr() and torch.equal(inplace, got)

@@ -153,9 +153,10 @@ __global__ void __launch_bounds__(256) k_cache_blocks(const BlkArgs a) {
 
 int run_blocks(bool exp, const tq_cache_layout* L, uint8_t* pool, int32_t which, const int64_t* slot_dev,
                int64_t n_tokens, int32_t block_elems, uint8_t* blocks, void* stream) {
-  TQ_REQUIRE(L && pool && slot_dev, TQ_ERR_INVALID, "block codec: null argument");
+  TQ_REQUIRE(L, TQ_ERR_INVALID, "block codec: layout is null");
   TQ_REQUIRE(which == 0 || which == 1, TQ_ERR_INVALID, "which must be 0 (K) or 1 (V)");
   TQ_REQUIRE(n_tokens >= 0, TQ_ERR_INVALID, "n_tokens must be >= 0");
+  TQ_REQUIRE(n_tokens == 0 || (pool && slot_dev), TQ_ERR_INVALID, "block codec: null argument");
   const int fmt = which == 0 ? L->k_format : L->v_format;
   TQ_REQUIRE(fmt == TQ_FMT_TURBO2 || fmt == TQ_FMT_TURBO3 || fmt == TQ_FMT_TURBO4, TQ_ERR_UNSUPPORTED,
              "block formats exist for turbo2 / turbo3 / turbo4 tensors, got format %d", fmt);

@@ -199,10 +199,11 @@ extern "C" int tq_cache_requantize(const tq_quantizer* src_q, const tq_quantizer
                                    const uint8_t* src_pool_dev, const int64_t* src_slot_dev,
                                    const tq_cache_layout* dst_layout, uint8_t* dst_pool_dev, const int64_t* dst_slot_dev,
                                    int32_t which, int64_t n_tokens, void* stream) {
-  TQ_REQUIRE(src_layout && dst_layout && src_pool_dev && dst_pool_dev && src_slot_dev && dst_slot_dev, TQ_ERR_INVALID,
-             "tq_cache_requantize: null argument");
+  TQ_REQUIRE(src_layout && dst_layout, TQ_ERR_INVALID, "tq_cache_requantize: layout is null");
   TQ_REQUIRE(which == 0 || which == 1, TQ_ERR_INVALID, "which must be 0 (K) or 1 (V)");
   TQ_REQUIRE(n_tokens >= 0, TQ_ERR_INVALID, "n_tokens must be >= 0");
+  TQ_REQUIRE(n_tokens == 0 || (src_pool_dev && dst_pool_dev && src_slot_dev && dst_slot_dev), TQ_ERR_INVALID,
+             "tq_cache_requantize: null argument");
   TQ_REQUIRE(src_layout->num_kv_heads == dst_layout->num_kv_heads, TQ_ERR_INVALID,
              "tq_cache_requantize: the caches differ in KV heads");
   const int sf = which == 0 ? src_layout->k_format : src_layout->v_format;
