@@ -371,7 +371,7 @@ def run_ours(args):
                          # dram__bytes_read.sum + dram__bytes_write.sum of one launch, ncu capture summarised in
                          # profiles/k_decode_attn_turbo3_ctx32768.md
                          "traffic": 27338240,
-                         "kernel": "k_decode_attn_g4<3,3>", "us_per_launch": kernel_s * 1e6,
+                         "kernel": "k_decode_attn_g4<3,3,dense V>", "us_per_launch": kernel_s * 1e6,
                          "bytes_per_launch": CTX * HKV * BYTES_PER_KV_TOKEN},
             "sparse_v_option": {"ms_per_step": ms_sparse_step, "kv_tokens_per_s": tokens_step / (ms_sparse_step * 1e-3),
                                 "max_rel_deviation_from_dense": sparse_dev,

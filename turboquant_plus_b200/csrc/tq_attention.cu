@@ -833,7 +833,7 @@ constexpr size_t g4_group_bytes(int record_bytes, int nstages) {
   return (((size_t)(SP::OFF_STAGE - SP::OFF_Q) + (stages > merge ? stages : merge)) + 127) / 128 * 128;
 }
 
-template <int KB, int VB>
+template <int KB, int VB, bool SPARSE>
 __global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_constant__ AttnParams P, const __grid_constant__ AttnQuant fk,
                                                                     const __grid_constant__ AttnQuant fv) {
   using SP = SmemPlan<KB, VB>;
@@ -1054,7 +1054,8 @@ __global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_c
       const float p0 = fast_exp2(sc0 - m0), p1 = fast_exp2(sc1 - m1);
       l0 += p0;
       l1 += p1;
-      if (P.sparse_v && !__any_sync(0xffffffffu, fmaxf(p0, p1) >= SPARSE_V_TAU)) continue;
+      // a template parameter, not a run-time flag: the possible jump keeps the V loads below it from being issued early
+      if (SPARSE && !__any_sync(0xffffffffu, fmaxf(p0, p1) >= SPARSE_V_TAU)) continue;
       const float vs = ok ? *reinterpret_cast<const float*>(st + vs_off + 4 * tb) : 0.f;
       const uint32_t hp = pack_h2(p0 * vs, p1 * vs);
       uint32_t pb[4];
@@ -1220,7 +1221,7 @@ int launch_attn(const AttnParams& P, const TqFast& fk, const TqFast& fv, cudaStr
   return tq_launch_check("k_decode_attn");
 }
 
-template <int KB, int VB>
+template <int KB, int VB, bool SPARSE>
 int launch_attn_g4(const AttnParams& P, const TqFast& fk, const TqFast& fv, cudaStream_t st) {
   using SP = SmemPlan<KB, VB>;
   const size_t need = (size_t)SP::ALIGN + SP::OFF_Q + G4_GROUPS * g4_group_bytes<KB, VB>(P.L.record_bytes, P.stages);
@@ -1231,7 +1232,7 @@ int launch_attn_g4(const AttnParams& P, const TqFast& fk, const TqFast& fv, cuda
   int dev = 0;
   TQ_CUDA(cudaGetDevice(&dev));
   if (configured_dev != dev) {
-    TQ_CUDA(cudaFuncSetAttribute(k_decode_attn_g4<KB, VB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)LIMIT));
+    TQ_CUDA(cudaFuncSetAttribute(k_decode_attn_g4<KB, VB, SPARSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)LIMIT));
     configured_dev = dev;
   }
   AttnQuant ak, av;
@@ -1250,7 +1251,7 @@ int launch_attn_g4(const AttnParams& P, const TqFast& fk, const TqFast& fv, cuda
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = P.overlap ? 1 : 0;
-  TQ_CUDA(cudaLaunchKernelEx(&cfg, k_decode_attn_g4<KB, VB>, P, ak, av));
+  TQ_CUDA(cudaLaunchKernelEx(&cfg, k_decode_attn_g4<KB, VB, SPARSE>, P, ak, av));
   return tq_launch_check("k_decode_attn_g4");
 }
 
@@ -1402,7 +1403,8 @@ static int decode_impl(const tq_quantizer* kq, const tq_quantizer* vq, const tq_
   // PolarQuant K and V with at most four query heads per KV head take the kernel specialised for that shape
   const bool g4 = group <= G4_HEADS && !k_q8 && !v_q8 && !k_prod;
 #define TQ_ATT_G4(K, V) \
-  if (g4 && L->k_format == K && L->v_format == V) rc = launch_attn_g4<K, V>(P, fk, fv, st);
+  if (g4 && L->k_format == K && L->v_format == V)               \
+    rc = P.sparse_v ? launch_attn_g4<K, V, true>(P, fk, fv, st) : launch_attn_g4<K, V, false>(P, fk, fv, st);
   TQ_ATT_G4(2, 2) TQ_ATT_G4(2, 3) TQ_ATT_G4(2, 4) TQ_ATT_G4(3, 2) TQ_ATT_G4(3, 3) TQ_ATT_G4(3, 4) TQ_ATT_G4(4, 2)
   TQ_ATT_G4(4, 3) TQ_ATT_G4(4, 4)
 #undef TQ_ATT_G4
