@@ -996,6 +996,7 @@ __global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_c
       const int tb = tile * 16;
       if (tb >= valid) break;
       // ---------------- S = K_tile (16 tokens x 128) . [q_hi | q_lo] ----------------
+      const float ks = *reinterpret_cast<const float*>(st + ks_off + 4 * tb);
       float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
       {
         uint32_t w0[KW], w1[KW];
@@ -1017,12 +1018,32 @@ __global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_c
           else mma16816(sa, a0, a1, a2, a3, qf[j][0], qf[j][1]);
         }
       }
+      // the V words and both scales of this tile are fetched here, ahead of the softmax arithmetic that separates
+      // them from their use: the loads then wait under it instead of in front of the table lookups
+      uint32_t vw[4][2];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const uint8_t* pv = st + v_off + tb * VIDXB + q4 * VIDXB;
+        if constexpr (VB == 3) {
+          const uint16_t* phw = reinterpret_cast<const uint16_t*>(pv);
+          const uint32_t a = phw[0], bb = phw[1], c = phw[2];
+          vw[q4][0] = __byte_perm(a, bb, 0x0145);
+          vw[q4][1] = __byte_perm(c, 0, 0x0144);
+        } else if constexpr (VB == 2) {
+          vw[q4][0] = __byte_perm(*reinterpret_cast<const uint32_t*>(pv), 0, 0x0123);
+          vw[q4][1] = 0;
+        } else {
+          const uint2 v2 = *reinterpret_cast<const uint2*>(pv);
+          vw[q4][0] = __byte_perm(v2.x, 0, 0x0123);
+          vw[q4][1] = __byte_perm(v2.y, 0, 0x0123);
+        }
+      }
+      const float vs_raw = *reinterpret_cast<const float*>(st + vs_off + 4 * tb);
       // hi + lo: the partner lane (t ^ 2) holds the other half of the same heads
       const float give0 = upper ? sa[0] + sb[0] : sa[2] + sb[2], give1 = upper ? sa[1] + sb[1] : sa[3] + sb[3];
       const float keep0 = upper ? sa[2] + sb[2] : sa[0] + sb[0], keep1 = upper ? sa[3] + sb[3] : sa[1] + sb[1];
       const int tok = tb + g + (upper ? 8 : 0);
       const bool ok = tok < valid;
-      const float ks = *reinterpret_cast<const float*>(st + ks_off + 4 * tb);
       float sc0 = (keep0 + __shfl_xor_sync(0xffffffffu, give0, 2)) * ks;
       float sc1 = (keep1 + __shfl_xor_sync(0xffffffffu, give1, 2)) * ks;
       sc0 = ok ? sc0 : -INFINITY;
@@ -1056,7 +1077,7 @@ __global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_c
       l1 += p1;
       // a template parameter, not a run-time flag: the possible jump keeps the V loads below it from being issued early
       if (SPARSE && !__any_sync(0xffffffffu, fmaxf(p0, p1) >= SPARSE_V_TAU)) continue;
-      const float vs = ok ? *reinterpret_cast<const float*>(st + vs_off + 4 * tb) : 0.f;
+      const float vs = ok ? vs_raw : 0.f;
       const uint32_t hp = pack_h2(p0 * vs, p1 * vs);
       uint32_t pb[4];
 #pragma unroll
@@ -1066,23 +1087,8 @@ __global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_c
       constexpr int SHV = PairLut<VB>::SHIFT;
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
-        const uint8_t* pv = st + v_off + tb * VIDXB + q4 * VIDXB;
-        uint32_t w[2];
-        if constexpr (VB == 3) {
-          const uint16_t* phw = reinterpret_cast<const uint16_t*>(pv);
-          const uint32_t a = phw[0], bb = phw[1], c = phw[2];
-          w[0] = __byte_perm(a, bb, 0x0145);
-          w[1] = __byte_perm(c, 0, 0x0144);
-        } else if constexpr (VB == 2) {
-          w[0] = __byte_perm(*reinterpret_cast<const uint32_t*>(pv), 0, 0x0123);
-          w[1] = 0;
-        } else {
-          const uint2 v2 = *reinterpret_cast<const uint2*>(pv);
-          w[0] = __byte_perm(v2.x, 0, 0x0123);
-          w[1] = __byte_perm(v2.y, 0, 0x0123);
-        }
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj) h[q4][jj] = lds32(field_off<2 * VB, SHV, 2>(w, jj) | lv_base);
+        for (int jj = 0; jj < 8; ++jj) h[q4][jj] = lds32(field_off<2 * VB, SHV, 2>(vw[q4], jj) | lv_base);
       }
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
