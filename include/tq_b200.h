@@ -255,11 +255,14 @@ int64_t tq_decode_workspace_bytes(int32_t batch, int32_t num_q_heads, int32_t nu
                                   int32_t max_pages_per_seq);
 /* A workspace must be initialised once after it is allocated (or be zero-filled): its last 256 KB hold
  * the per-(sequence, KV head) tickets with which the last split to finish elects itself to merge the
- * others, and a status word.  Every call leaves the tickets at zero again.  Enqueues one memset. */
+ * others, and a status word.  Every call that runs to completion leaves the tickets at zero again; after a
+ * call whose status reads 1 (below) re-initialise the workspace before it is used again.  Enqueues one memset. */
 int tq_decode_workspace_init(void* workspace_dev, int64_t workspace_bytes, void* stream);
-/* After a synchronisation: 0 if the last tq_decode_attn that used this workspace finished cleanly,
- * 1 if a bounded wait inside the kernel gave up (results invalid). Copies 4 bytes to the host. */
-int tq_decode_status_sync(const void* workspace_dev, int64_t workspace_bytes, int32_t* status_out);
+/* After a synchronisation: 0 if every tq_decode_attn / tq_prefill_attn that used this workspace since the
+ * previous tq_decode_status_sync finished cleanly, 1 if a bounded wait inside one of those kernels gave up
+ * (results of the calls since then are invalid).  The kernels only ever set the word; this call copies it to
+ * the host (4 bytes, synchronous) and, when it was set, clears it. */
+int tq_decode_status_sync(void* workspace_dev, int64_t workspace_bytes, int32_t* status_out);
 
 /* Decode attention straight off the packed cache: for every sequence b and query head h,
  * softmax(q k^T * scale) v over the first seq_lens[b] cached tokens of KV head
@@ -285,8 +288,9 @@ int tq_decode_attn(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cach
  * TQ_DECODE_OVERLAP (bit 3) launches the attention kernel with programmatic stream serialization:
  * it may start while the preceding kernel of the stream is still running, and until that kernel has
  * completed it only reads the cache pages, the block table and the sequence lengths (queries are read,
- * the workspace and the output written, afterwards).  Set it when the preceding kernel does not write
- * those three -- e.g. the attention call of another layer -- or never signals early completion. */
+ * the workspace and the output written, afterwards).  Set it only when the preceding kernel writes none of
+ * those three -- e.g. the attention call of another layer; after a tq_cache_append into the same pool launch
+ * without it. */
 #define TQ_DECODE_OVERLAP 8
 /* TQ_DECODE_SPARSE_V (bit 4): sparse V as in the reference's docs/papers/sparse-v-dequant.md:64-84 -- the V
  * dequantization and accumulation are skipped where the attention weight exp(score - running max) is below 1e-6;
@@ -294,6 +298,13 @@ int tq_decode_attn(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cach
  * below the threshold).  The weights still count in the softmax denominator.  Off by default: results then differ
  * from dense attention by at most (number of skipped positions) x 1e-6 relative to the largest weight. */
 #define TQ_DECODE_SPARSE_V 16
+/* TQ_DECODE_NO_DEQUANT (bit 5): measurement only, the "no-dequant ceiling" of the reference's
+ * docs/decode-speed-hardware-analysis.md:25-41 -- the kernel copies the same records, runs the same barriers,
+ * tensor-core instructions, softmax and merges, but feeds the packed words to the tensor cores instead of
+ * looking centroids up.  The outputs are meaningless; the run time is what the kernel would cost if
+ * dequantization were free.  Honoured by the kernel for turbo3 K and V with <= 4 query heads per KV head on
+ * 128-token pages; other shapes ignore the bit. */
+#define TQ_DECODE_NO_DEQUANT 32
 int tq_decode_attn_phases(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cache_layout* layout,
                           const uint8_t* pool_dev, const int32_t* block_table_dev,
                           int32_t max_pages_per_seq, const int32_t* seq_lens_dev, const void* q_dev,
@@ -354,10 +365,14 @@ int tq_prefill_attn(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cac
  *     cudaGetSymbolAddress, with that device current).  Make that first call before any stream
  *     capture begins on the device.
  *   - All calls on a device share the one array, and it keeps whatever the previous call left.
- *     The kernels do not depend on old contents (the status word is reset by the first kernel of
- *     every call, every partial that is read was written in the same call), but two calls that
- *     overlap on the GPU -- different streams, or different host threads -- race on it.  Issue
- *     calls that use this entry point on one stream per device, or order them with events.
+ *     The kernels do not depend on old contents (every call first clears, with an asynchronous
+ *     memset on `stream`, the ticket counters it is going to use, and every partial that is read
+ *     was written in the same call), but two calls that overlap on the GPU -- different streams,
+ *     or different host threads -- race on it.  Issue calls that use this entry point on one
+ *     stream per device, or order them with events.
+ *   - tq_decode_static_status_sync reads (and clears) the array's status word the way
+ *     tq_decode_status_sync does for a caller-owned workspace: 0 after clean calls, 1 if a bounded
+ *     wait inside the kernel gave up since the previous read.  It synchronises (a 4-byte copy).
  *   - Arguments and results are those of tq_decode_attn without workspace_dev/workspace_bytes;
  *     the outputs are bit-identical to tq_decode_attn on the same inputs.
  * ------------------------------------------------------------------------------------------ */
@@ -367,6 +382,8 @@ int tq_decode_attn_static(const tq_quantizer* kq, const tq_quantizer* vq, const 
                           int32_t max_pages_per_seq, const int32_t* seq_lens_dev, const void* q_dev,
                           int32_t q_dtype, int32_t batch, int32_t num_q_heads, float scale,
                           void* out_dev, int32_t out_dtype, void* stream);
+/* Status word of the built-in scratch array of the current device (no counterpart in the reference). */
+int tq_decode_static_status_sync(int32_t* status_out);
 
 #ifdef __cplusplus
 }

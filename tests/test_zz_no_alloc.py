@@ -58,6 +58,9 @@ def test_static_scratch_matches_workspace_entry_point_twice():
         assert err < 2e-3                      # the tolerance of the attention tests ...
         assert torch.equal(got, ref)           # ... and in fact the same bits: same kernels, same split order
         assert torch.isfinite(got).all()
+        # the shared array has a status word of its own: no bounded wait gave up in either call
+        st = C.c_int32(-1)
+        assert nv.load().tq_decode_static_status_sync(C.byref(st)) == 0 and st.value == 0
 
 
 def test_static_scratch_refuses_shapes_beyond_its_size():

@@ -19,6 +19,7 @@ FMT_TURBO2, FMT_TURBO3, FMT_TURBO4, FMT_Q8_0 = 2, 3, 4, 8
 FMT_PROD2, FMT_PROD3, FMT_PROD4 = 18, 19, 20
 DECODE_OVERLAP = 8  # tq_decode_attn_phases: TQ_DECODE_OVERLAP
 DECODE_SPARSE_V = 16  # TQ_DECODE_SPARSE_V
+DECODE_NO_DEQUANT = 32  # TQ_DECODE_NO_DEQUANT (measurement only)
 FORMATS = {"turbo2": FMT_TURBO2, "turbo3": FMT_TURBO3, "turbo4": FMT_TURBO4, "q8_0": FMT_Q8_0,
            "prod2": FMT_PROD2, "prod3": FMT_PROD3, "prod4": FMT_PROD4}
 
@@ -88,6 +89,7 @@ SIGNATURES = {
                                   _F, _P, _I64, _P, _I32, _P]),
     "tq_decode_attn_static": (C.c_int, [_P, _P, C.POINTER(CacheLayout), _P, _P, _I32, _P, _P, _I32, _I32, _I32,
                                         _F, _P, _I32, _P]),
+    "tq_decode_static_status_sync": (C.c_int, [C.POINTER(_I32)]),
 }
 
 _lib = None

@@ -1,0 +1,523 @@
+// Decode attention, PolarQuant K and V, at most four query heads per KV head, 128-token pages: the shape of the
+// headline workload (Llama-3-8B: 32 query / 8 KV heads, turbo3 K and V).  Same pipeline and the same split /
+// ticket protocol as k_decode_attn (tq_attention.cu); what changes is how the 8 columns of the MMA tiles are
+// spent, and that everything the page loop needs is a compile-time constant:
+//   * S = K q^T: columns 0..3 carry the fp16 "hi" halves of the four query heads, columns 4..7 the "lo" halves,
+//     so one m16n8k16 per 16 dims instead of two; the halves meet through one lane exchange (lane ^ 2), after
+//     which thread (g, t) owns one token (g + 8 (t >> 1)) and two heads (2 (t & 1), + 1).
+//   * O^T += V^T P^T: a k-slot pair is (token, dim parity) instead of (token, token'), column n is
+//     (head n >> 1, parity n & 1), and the P operand is p on the matching parity, 0 on the other.  A pair-table
+//     word (two dims of one token) is then an A-operand register as it comes: no re-pairing permutes, 32 dims per
+//     MMA, and O takes 16 accumulator registers per thread: o[blk] = head t, dims 16 g + 4 blk .. + 3.
+//   * the running maxima are only reduced across the warp when some score exceeds them.
+//   * page size (128 tokens = one 16-token tile per warp and page), pipeline depth (3 records) and every offset
+//     inside a record are template constants; record bytes are read through 32-bit shared-memory addresses with
+//     immediate offsets; only the last page of a sequence runs the variant that masks tokens past the end.
+#include "tq_attention.cuh"
+
+namespace {
+
+using namespace tqatt;
+
+// What the kernel needs of a quantizer, packed into 80 bytes so that the whole parameter block is six 64-byte
+// lines: parameters live in the constant bank, every line misses once per launch, and the misses of one warp
+// are serial.  The warps therefore touch one line each before anything else happens.
+struct AttnQuant {
+  uint32_t s1[4], s2[4];
+  uint16_t cent16[16];
+  float alpha;
+  uint32_t pad[3];
+};
+static_assert(sizeof(AttnQuant) == 80, "AttnQuant layout");
+
+constexpr int G4_HEADS = 4;
+constexpr int G4_HSTRIDE = TQ_D + 4;  // floats between heads in the warp-merge buffer: 16-byte stores stay conflict-free
+constexpr int G4_PT = 128;            // tokens per page
+constexpr int G4_NS = 3;              // page records in flight per group
+
+// One CTA per SM runs TWO independent 256-thread groups (own split, own pipeline, own barrier), sharing only the
+// pair tables.  Two separate 256-thread CTAs on one SM did the same work, but the warp schedulers favoured the
+// CTA that arrived first: it finished its pages in 9.7 us, its neighbour in 12.6 us, and the SM idled at half
+// occupancy in between.  Warps of one CTA have the same age and progress together.
+constexpr int G4_GROUPS = 2;
+constexpr int G4_THREADS = G4_GROUPS * ATT_THREADS;
+
+constexpr int up128(int x) { return (x + 127) / 128 * 128; }
+
+// Record layout of a (page, head) for 128-token pages, as tq_cache_layout_init lays it out, and the carve-up of
+// the CTA's shared memory: the two pair tables (shared by the groups), then per group the query buffer, the
+// mbarriers and flags, and the pipeline stages (reused as the warp-merge buffer after the page loop).
+template <int KB, int VB> struct G4 {
+  static constexpr int KIDXB = 16 * KB, VIDXB = 16 * VB;  // index bytes per token
+  static constexpr int K_IDX = 0;
+  static constexpr int K_SCALE = K_IDX + G4_PT * KIDXB;
+  static constexpr int V_IDX = K_SCALE + G4_PT * 4;
+  static constexpr int V_SCALE = V_IDX + G4_PT * VIDXB;
+  static constexpr int REC = V_SCALE + G4_PT * 4;
+  static constexpr int LK = PairLut<KB>::BYTES, LV = PairLut<VB>::BYTES;
+  static constexpr int ALIGN = (LK > LV ? LK : LV) > 512 ? (LK > LV ? LK : LV) : 512;  // largest table
+  static constexpr int OFF_K = LK >= LV ? 0 : LV;   // the larger table first: each stays aligned to its own size
+  static constexpr int OFF_V = LK >= LV ? LK : 0;
+  static constexpr int OFF_GROUPS = up128(LK + LV);
+  static constexpr int G_Q = 0;                                   // float [4 heads][128]
+  static constexpr int G_BAR = G_Q + G4_HEADS * TQ_D * 4;         // 3 mbarriers, then two flag words at + 64
+  static constexpr int G_STAGE = G_BAR + 128;
+  static constexpr int MERGE = ATT_WARPS * G4_HEADS * (G4_HSTRIDE + 2) * 4;
+  static constexpr int GROUP_BYTES = up128(G_STAGE + (G4_NS * REC > MERGE ? G4_NS * REC : MERGE));
+  static constexpr int SMEM = ALIGN + OFF_GROUPS + G4_GROUPS * GROUP_BYTES;
+};
+
+// ---- shared-memory loads through 32-bit addresses with immediate offsets ----------------------------------------
+// Not volatile: the compiler may schedule and combine them.  What keeps a load of a pipeline stage behind the wait
+// for that stage is a data dependency: the stage address is formed from a value the wait produces.
+template <int OFF> __device__ __forceinline__ uint32_t lds_u32(uint32_t a) {
+  uint32_t v;
+  asm("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(a), "n"(OFF));
+  return v;
+}
+template <int OFF> __device__ __forceinline__ float lds_f32(uint32_t a) {
+  float v;
+  asm("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(a), "n"(OFF));
+  return v;
+}
+template <int OFF> __device__ __forceinline__ uint2 lds_u64(uint32_t a) {
+  uint2 v;
+  asm("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(a), "n"(OFF));
+  return v;
+}
+template <int OFF> __device__ __forceinline__ uint4 lds_u128(uint32_t a) {
+  uint4 v;
+  asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a), "n"(OFF));
+  return v;
+}
+
+// One row chunk of K indices (a thread's 32 dims of one token: 4 KB bytes at a 4 KB-byte-aligned address) as
+// big-endian words: word k holds stream bits 32 k .. 32 k + 31, first bit in the most significant position.
+template <int KB, int OFF> __device__ __forceinline__ void load_k_words(uint32_t a, uint32_t (&w)[KB]) {
+  if constexpr (KB == 2) {
+    const uint2 v = lds_u64<OFF>(a);
+    w[0] = __byte_perm(v.x, 0, 0x0123);
+    w[1] = __byte_perm(v.y, 0, 0x0123);
+  } else if constexpr (KB == 3) {
+    w[0] = __byte_perm(lds_u32<OFF>(a), 0, 0x0123);
+    w[1] = __byte_perm(lds_u32<OFF + 4>(a), 0, 0x0123);
+    w[2] = __byte_perm(lds_u32<OFF + 8>(a), 0, 0x0123);
+  } else {
+    const uint4 v = lds_u128<OFF>(a);
+    w[0] = __byte_perm(v.x, 0, 0x0123);
+    w[1] = __byte_perm(v.y, 0, 0x0123);
+    w[2] = __byte_perm(v.z, 0, 0x0123);
+    w[3] = __byte_perm(v.w, 0, 0x0123);
+  }
+}
+
+// A thread's 16 dims of one V token (2 VB bytes at byte offset 2 VB g of the token's row) as two big-endian words.
+// Three-bit rows put that chunk on a 2-byte boundary: two aligned words that cover it are loaded from `a` (the
+// chunk's address rounded down to 4 bytes) and the six bytes are picked out with selectors that depend on whether
+// the chunk starts the word (even g) or sits in its upper half (odd g).
+template <int VB, int OFF> __device__ __forceinline__ void load_v_words(uint32_t a, uint32_t sel0, uint32_t sel1, uint32_t (&w)[2]) {
+  if constexpr (VB == 2) {
+    w[0] = __byte_perm(lds_u32<OFF>(a), 0, 0x0123);
+    w[1] = 0;
+  } else if constexpr (VB == 3) {
+    const uint32_t x0 = lds_u32<OFF>(a), x1 = lds_u32<OFF + 4>(a);
+    w[0] = __byte_perm(x0, x1, sel0);
+    w[1] = __byte_perm(x0, x1, sel1);
+  } else {
+    const uint2 v = lds_u64<OFF>(a);
+    w[0] = __byte_perm(v.x, 0, 0x0123);
+    w[1] = __byte_perm(v.y, 0, 0x0123);
+  }
+}
+
+// Per-thread state of the page loop.
+struct G4State {
+  float o[4][4];
+  float m0, m1, l0, l1;
+};
+
+// One 16-token tile of one warp: scores against the four query heads, online softmax, O^T += V^T P^T.
+//   st      shared-memory address of the page record
+//   MASKED  the page may end inside or before this tile (`valid` tokens of the page exist)
+//   NODEQ   measurement variant: the table lookups are left out and the packed words themselves are fed to the
+//           tensor cores (copies, barriers, MMAs, softmax and merges as in the real kernel; results meaningless)
+template <int KB, int VB, bool MASKED, bool SPARSE, bool NODEQ>
+__device__ __forceinline__ void g4_tile(G4State& S, uint32_t st, const uint32_t (&qf)[8][2], uint32_t lk_base, uint32_t lv_base,
+                                        uint32_t k_thr, uint32_t ks_thr, uint32_t v_thr, uint32_t vs_thr, uint32_t vsel0,
+                                        uint32_t vsel1, int src0, uint32_t psel, int rsrc, bool upper, int t, int tok_in_page,
+                                        int valid) {
+  using C = G4<KB, VB>;
+  constexpr float MAX_SLACK = 4.0f;
+  // ---------------- S = K_tile (16 tokens x 128) . [q_hi | q_lo] ----------------
+  const float ks = lds_f32<0>(st + ks_thr);
+  float s[4] = {0.f, 0.f, 0.f, 0.f};
+  {
+    uint32_t w0[KB], w1[KB];
+    load_k_words<KB, 0>(st + k_thr, w0);
+    load_k_words<KB, 8 * C::KIDXB>(st + k_thr, w1);
+    constexpr int SH = PairLut<KB>::SHIFT;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      uint32_t a0, a1, a2, a3;
+      if constexpr (NODEQ) {
+        a0 = w0[j % KB]; a1 = w1[j % KB]; a2 = w0[(j + 1) % KB]; a3 = w1[(j + 1) % KB];
+      } else {
+        a0 = lds32(field_off<2 * KB, SH, KB>(w0, 2 * j) | lk_base);
+        a1 = lds32(field_off<2 * KB, SH, KB>(w1, 2 * j) | lk_base);
+        a2 = lds32(field_off<2 * KB, SH, KB>(w0, 2 * j + 1) | lk_base);
+        a3 = lds32(field_off<2 * KB, SH, KB>(w1, 2 * j + 1) | lk_base);
+      }
+      mma16816(s, a0, a1, a2, a3, qf[j][0], qf[j][1]);
+    }
+  }
+  // the V words and scale of this tile are fetched here, ahead of the softmax arithmetic that separates them from
+  // their use: the loads then wait under it instead of in front of the table lookups
+  uint32_t vw[4][2];
+  load_v_words<VB, 0>(st + v_thr, vsel0, vsel1, vw[0]);
+  load_v_words<VB, C::VIDXB>(st + v_thr, vsel0, vsel1, vw[1]);
+  load_v_words<VB, 2 * C::VIDXB>(st + v_thr, vsel0, vsel1, vw[2]);
+  load_v_words<VB, 3 * C::VIDXB>(st + v_thr, vsel0, vsel1, vw[3]);
+  const float vs_raw = lds_f32<0>(st + vs_thr);
+  // hi + lo: the partner lane (t ^ 2) holds the other half of the same heads
+  const float give0 = upper ? s[0] : s[2], give1 = upper ? s[1] : s[3];
+  const float keep0 = upper ? s[2] : s[0], keep1 = upper ? s[3] : s[1];
+  const float sum0 = keep0 + __shfl_xor_sync(0xffffffffu, give0, 2);
+  const float sum1 = keep1 + __shfl_xor_sync(0xffffffffu, give1, 2);
+  // ---------------- online softmax (log2 domain), heads 2(t&1) and 2(t&1)+1 ----------------
+  // The running maxima move only when a score exceeds them by more than 2^MAX_SLACK: probabilities then stay
+  // below 2^MAX_SLACK (far inside fp16 and fp32 range) and almost every tile skips the warp reduction and the
+  // rescaling of O.  The normalised result is the same up to rounding.
+  bool ok = true;
+  float d0 = fmaf(sum0, ks, -S.m0), d1 = fmaf(sum1, ks, -S.m1);   // score - running maximum
+  if constexpr (MASKED) {
+    ok = tok_in_page < valid;
+    d0 = ok ? d0 : -INFINITY;
+    d1 = ok ? d1 : -INFINITY;
+  }
+  if (__any_sync(0xffffffffu, (d0 > MAX_SLACK) || (d1 > MAX_SLACK))) {
+    float sc0 = sum0 * ks, sc1 = sum1 * ks;
+    if constexpr (MASKED) {
+      sc0 = ok ? sc0 : -INFINITY;
+      sc1 = ok ? sc1 : -INFINITY;
+    }
+    float mx0 = sc0, mx1 = sc1;
+#pragma unroll
+    for (int sh = 2; sh < 32; sh <<= 1) {
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, sh));
+    }
+    const float mn0 = fmaxf(S.m0, mx0), mn1 = fmaxf(S.m1, mx1);  // finite: the tile's first token exists
+    const float r0 = fast_exp2(S.m0 - mn0), r1 = fast_exp2(S.m1 - mn1);
+    S.m0 = mn0;
+    S.m1 = mn1;
+    S.l0 *= r0;
+    S.l1 *= r1;
+    d0 = sc0 - mn0;
+    d1 = sc1 - mn1;
+    const float ra = __shfl_sync(0xffffffffu, r0, rsrc), rb = __shfl_sync(0xffffffffu, r1, rsrc);
+    const float r = (t & 1) ? rb : ra;                        // O of this thread belongs to head t
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      S.o[j][0] *= r; S.o[j][1] *= r; S.o[j][2] *= r; S.o[j][3] *= r;
+    }
+  }
+  const float p0 = fast_exp2(d0), p1 = fast_exp2(d1);
+  S.l0 += p0;
+  S.l1 += p1;
+  // a template parameter, not a run-time flag: the possible jump keeps the V loads below it from being issued early
+  if (SPARSE && !__any_sync(0xffffffffu, fmaxf(p0, p1) >= SPARSE_V_TAU)) return;
+  const float vs = MASKED ? (ok ? vs_raw : 0.f) : vs_raw;   // a stale scale must not meet p = 0
+  const uint32_t hp = pack_h2(p0 * vs, p1 * vs);
+  uint32_t pb[4];
+#pragma unroll
+  for (int q4 = 0; q4 < 4; ++q4) pb[q4] = __byte_perm(__shfl_sync(0xffffffffu, hp, src0 + 4 * q4), 0, psel);
+  // ---------------- O^T += V_tile^T . P^T : tokens 4t .. 4t+3 of the tile, dims 16g .. 16g+15 ----------------
+  uint32_t h[4][8];
+  constexpr int SHV = PairLut<VB>::SHIFT;
+#pragma unroll
+  for (int q4 = 0; q4 < 4; ++q4) {
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj) {
+      if constexpr (NODEQ) h[q4][jj] = vw[q4][jj & 1] ^ (uint32_t)jj;
+      else h[q4][jj] = lds32(field_off<2 * VB, SHV, 2>(vw[q4], jj) | lv_base);
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+#pragma unroll
+    for (int blk = 0; blk < 4; ++blk)
+      mma16816(S.o[blk], h[2 * u][2 * blk], h[2 * u][2 * blk + 1], h[2 * u + 1][2 * blk], h[2 * u + 1][2 * blk + 1],
+               pb[2 * u], pb[2 * u + 1]);
+  }
+}
+
+template <int KB, int VB, bool SPARSE, bool NODEQ>
+__global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_constant__ AttnParams P, const __grid_constant__ AttnQuant fk,
+                                                                    const __grid_constant__ AttnQuant fv) {
+  using C = G4<KB, VB>;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  const int grp = threadIdx.x >> 8;              // which of the CTA's two groups
+  // groups are numbered (kv head, split) so that an odd number of splits does not leave half a CTA empty
+  const int gidx = G4_GROUPS * blockIdx.x + grp, b = blockIdx.y;
+  const bool exists = gidx < P.num_splits * P.hkv;
+  const int kvh = exists ? gidx / P.num_splits : 0, split = exists ? gidx % P.num_splits : P.num_splits;
+  const int tid = threadIdx.x & 255, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int bar_id = 1 + grp;
+  {  // one parameter line per warp, all misses in flight together
+    const uint32_t* pp = reinterpret_cast<const uint32_t*>(&P);
+    uint32_t touch;
+    if (warp < 4) touch = pp[min(16 * warp, (int)(sizeof(AttnParams) / 4) - 1)];
+    else if (warp < 6) touch = warp == 4 ? fk.s1[0] : fk.pad[2];
+    else touch = warp == 6 ? fv.s1[0] : fv.pad[2];
+    asm volatile("" ::"r"(touch));
+  }
+  // Programmatic dependent launch: let the next kernel in the stream start its own prologue as soon as SMs free
+  // up.  Everything this kernel does before griddepcontrol.wait below reads only the cache, the block table and
+  // the sequence lengths; queries are read, and the workspace and the output written, after the wait, i.e.
+  // after the preceding kernel has completed and its writes are visible.  Both instructions do nothing in a
+  // launch without the attribute.
+  if (P.overlap) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int page_lo = split * P.chunk_pages;
+  const size_t row0 = (size_t)b * P.hq + (size_t)kvh * P.group;
+  const int32_t* bt = P.block_table + (size_t)b * P.max_pages;
+  const uint32_t raw = smem_u32(smem_raw);
+  uint8_t* sm = smem_raw + (((raw + C::ALIGN - 1) & ~(uint32_t)(C::ALIGN - 1)) - raw);
+  uint8_t* smg = sm + C::OFF_GROUPS + (size_t)grp * C::GROUP_BYTES;   // this group's private part
+  float* qbuf = reinterpret_cast<float*>(smg + C::G_Q);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smg + C::G_BAR);
+  volatile int* s_flags = reinterpret_cast<volatile int*>(smg + C::G_BAR + 64);
+  uint8_t* stage0 = smg + C::G_STAGE;
+  constexpr int PRODUCER = ATT_THREADS - 32;  // lane 0 of the last warp issues every bulk copy
+  const uint8_t* pool_head = P.pool + (int64_t)kvh * P.L.head_stride;
+
+  auto issue = [&](int stage, int64_t page) {
+    uint64_t* bar = &bars[stage];
+    mbar_expect_tx(bar, C::REC);
+    bulk_g2s(stage0 + stage * C::REC, pool_head + page * P.L.page_stride, C::REC, bar);
+  };
+
+  // The warps take different roles so that their global-load latencies (and their instruction fetches, which are
+  // cold in every launch) overlap: the producer sends the first pages on their way as early as it can, the first
+  // `group` warps rotate one query head each, the others fill the pair tables.
+  // A length beyond the block-table row (or a negative one) is clamped: page numbers are only ever read from the
+  // row's max_pages entries and the split count stays inside the plan the workspace was sized for.
+  const int seq_len = min(max(P.seq_lens[b], 0), P.max_pages * G4_PT);
+  const int n_pages = (seq_len + G4_PT - 1) / G4_PT;
+  const int np = min(n_pages, page_lo + P.chunk_pages) - page_lo;   // pages of this group (<= 0: none)
+  int pg_ahead = 0;  // producer: block-table entry of the page issued in the next iteration
+  float x[4] = {0.f, 0.f, 0.f, 0.f};
+  if (tid == PRODUCER) {
+    int pg_next[G4_NS];
+#pragma unroll
+    for (int i = 0; i < G4_NS; ++i) pg_next[i] = bt[min(page_lo + i, P.max_pages - 1)];
+#pragma unroll
+    for (int s = 0; s < G4_NS; ++s) mbar_init(&bars[s], 1);
+    s_flags[0] = 0;
+    s_flags[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (np > 0) {
+      issue(0, pg_next[0]);
+      if (np > 1) issue(1, pg_next[1]);
+      pg_ahead = pg_next[2];
+    }
+  } else if (warp < P.group) {
+    if (P.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (P.k_pre) load_q4(P.qrot, TQ_F32, (row0 + warp) * TQ_D + 4 * lane, x);
+    else load_q4(P.q, P.q_dtype, (row0 + warp) * TQ_D + 4 * lane, x);
+    if (!P.k_pre) {
+      warp_wht128(x, fk.s1, fk.s2, lane);
+      const float sk = P.qscale / fk.alpha;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) x[k] *= sk;
+    }
+    // 16-byte chunk c = 8 t + j of head h sits at 8 t + (j ^ (t + 4 (h & 1))): the fragment reads below (fixed j,
+    // all t and h) then touch every bank group instead of one
+    const int tq = lane >> 3, jq = lane & 7;
+    *reinterpret_cast<float4*>(qbuf + warp * TQ_D + 4 * (8 * tq + (jq ^ (tq + 4 * (warp & 1))))) =
+        make_float4(x[0], x[1], x[2], x[3]);
+  }
+  __syncwarp();
+  if (warp >= P.group) {
+    const int fh = ATT_THREADS - 32 * P.group;   // table-filling threads per group; both groups share the work
+    lut_fill<KB>(sm + C::OFF_K, fk.cent16, grp * fh + tid - 32 * P.group, G4_GROUPS * fh);
+    lut_fill<VB>(sm + C::OFF_V, fv.cent16, grp * fh + tid - 32 * P.group, G4_GROUPS * fh);
+  }
+  // every thread waits before it can touch the workspace or the output (the query warps already have)
+  if (P.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (n_pages == 0 && split == 0) {  // empty sequence: zeros (split 0 exists for every kv head)
+    for (int e = tid; e < P.group * TQ_D; e += ATT_THREADS) store_out(P.out, P.out_dtype, row0 * TQ_D + e, 0.f);
+    if (P.lse && tid < P.group) P.lse[row0 + tid] = -INFINITY;
+  }
+  const int ns = (n_pages + P.chunk_pages - 1) / P.chunk_pages;
+  __syncthreads();               // the only CTA-wide barrier: tables, query buffers and mbarriers are ready
+  if (np <= 0) return;           // this group has no pages (its split lies beyond the sequence)
+
+  // B operand of S = K q^T: column g is head g & 3, hi half for g < 4, lo half otherwise
+  uint32_t qf[8][2];
+  {
+    const int head = g & 3;
+    const bool hv = head < P.group, lo = g >= 4;
+    const float* qp = qbuf + (hv ? head : 0) * TQ_D + 32 * t;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float4 v = hv ? *reinterpret_cast<const float4*>(qp + 4 * (j ^ (t + 4 * (head & 1)))) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const __half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
+      const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+      qf[j][0] = lo ? pack_h2(v.x - f0.x, v.y - f0.y) : *reinterpret_cast<const uint32_t*>(&h0);
+      qf[j][1] = lo ? pack_h2(v.z - f1.x, v.w - f1.y) : *reinterpret_cast<const uint32_t*>(&h1);
+    }
+  }
+  const uint32_t lk_base = smem_u32(sm + C::OFF_K) + (PairLut<KB>::REPL ? lane * 4 : 0);
+  const uint32_t lv_base = smem_u32(sm + C::OFF_V) + (PairLut<VB>::REPL ? lane * 4 : 0);
+  // P operand: this thread's column is (head g >> 1, parity g & 1); the owner of p[token][head] is lane
+  // 4 (token & 7) + 2 (token >> 3) + (head >> 1), half (head & 1) of its packed pair
+  const int src0 = 16 * (t & 1) + 2 * (t >> 1) + (g >> 2);            // token 4t; token 4t + i is 4 i lanes further
+  const uint32_t psel = ((g >> 1) & 1) ? ((g & 1) ? 0x3244u : 0x4432u) : ((g & 1) ? 0x1044u : 0x4410u);
+  const int rsrc = (lane & ~3) | (t >> 1);                             // a lane that tracks head t's running maximum
+  const bool upper = t >= 2;                                           // keeps token g + 8 after the exchange
+
+  G4State S;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) S.o[j][0] = S.o[j][1] = S.o[j][2] = S.o[j][3] = 0.f;
+  S.m0 = S.m1 = -INFINITY;
+  S.l0 = S.l1 = 0.f;
+
+  // byte offsets inside a page record of what this thread reads in its warp's tile (tokens 16 warp .. + 15)
+  const int tok_in_page = 16 * warp + g + (upper ? 8 : 0);
+  const uint32_t k_thr = C::K_IDX + (16 * warp + g) * C::KIDXB + t * (C::KIDXB / 4);
+  const uint32_t ks_thr = C::K_SCALE + 4 * tok_in_page;
+  const uint32_t v_chunk = C::V_IDX + (16 * warp + 4 * t) * C::VIDXB + g * (2 * VB);
+  const uint32_t v_thr = v_chunk & ~3u;
+  const uint32_t vs_thr = C::V_SCALE + 4 * tok_in_page;
+  const bool v_odd = (v_chunk & 2u) != 0;
+  const uint32_t vsel0 = v_odd ? 0x2345u : 0x0123u, vsel1 = v_odd ? 0x6744u : 0x4544u;
+  const uint32_t stage_addr = smem_u32(stage0);
+  // pages 0 .. np-2 of the group are full; the last one is full unless the sequence ends inside it
+  const int last_valid = seq_len - (page_lo + np - 1) * G4_PT;          // >= 1
+  const int n_full = last_valid >= G4_PT ? np : np - 1;
+
+  int stage = 0;
+  uint32_t parity = 0;
+  for (int i = 0; i < np; ++i) {
+    if (tid == PRODUCER && i + G4_NS - 1 < np) {
+      issue(stage == 0 ? G4_NS - 1 : stage - 1, pg_ahead);            // stage of page i + 2 = stage of page i - 1
+      pg_ahead = bt[min(page_lo + i + G4_NS, P.max_pages - 1)];
+    }
+    if (!s_flags[0] && !mbar_wait_bounded(&bars[stage], parity)) s_flags[0] = 1;
+    // the stage address carries a value the wait above produced (always zero), so that no load of the stage can
+    // be scheduled ahead of the wait
+    uint32_t dep;
+    asm volatile("mov.u32 %0, 0;" : "=r"(dep)::"memory");
+    const uint32_t st = stage_addr + stage * C::REC + dep;
+    if (i < n_full) {
+      g4_tile<KB, VB, false, SPARSE, NODEQ>(S, st, qf, lk_base, lv_base, k_thr, ks_thr, v_thr, vs_thr, vsel0, vsel1, src0, psel,
+                                            rsrc, upper, t, tok_in_page, G4_PT);
+    } else if (16 * warp < last_valid) {
+      g4_tile<KB, VB, true, SPARSE, NODEQ>(S, st, qf, lk_base, lv_base, k_thr, ks_thr, v_thr, vs_thr, vsel0, vsel1, src0, psel,
+                                           rsrc, upper, t, tok_in_page, last_valid);
+    }
+    group_sync(bar_id);  // every warp of the group is done with this stage before it is refilled
+    if (++stage == G4_NS) {
+      stage = 0;
+      parity ^= 1u;
+    }
+  }
+
+  // ---------------- merge the eight warps, write the split partial ----------------
+#pragma unroll
+  for (int sh = 2; sh < 32; sh <<= 1) {
+    S.l0 += __shfl_xor_sync(0xffffffffu, S.l0, sh);
+    S.l1 += __shfl_xor_sync(0xffffffffu, S.l1, sh);
+  }
+  float* so = reinterpret_cast<float*>(stage0);                    // [warp][head 4][G4_HSTRIDE]
+  float* sml = so + ATT_WARPS * G4_HEADS * G4_HSTRIDE;             // [warp][head 4][2]
+#pragma unroll
+  for (int blk = 0; blk < 4; ++blk)
+    *reinterpret_cast<float4*>(so + (size_t)(warp * G4_HEADS + t) * G4_HSTRIDE + 16 * g + 4 * blk) =
+        make_float4(S.o[blk][0], S.o[blk][1], S.o[blk][2], S.o[blk][3]);
+  if (g == 0 && t < 2) {
+    *reinterpret_cast<float4*>(sml + (warp * G4_HEADS + 2 * t) * 2) = make_float4(S.m0, S.l0, S.m1, S.l1);
+  }
+  group_sync(bar_id);
+  {
+    // thread (head, pair of dims): 4 heads x 64 pairs = 256 threads; the eight warps' rows are added in warp order
+    const int head = tid >> 6, dim = 2 * (tid & 63);
+    if (head < P.group) {
+      float mw[ATT_WARPS], M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < ATT_WARPS; ++w) {
+        mw[w] = sml[(w * G4_HEADS + head) * 2];
+        M = fmaxf(M, mw[w]);
+      }
+      float a0 = 0.f, a1 = 0.f, Lsum = 0.f;
+#pragma unroll
+      for (int w = 0; w < ATT_WARPS; ++w) {
+        const float f = mw[w] == -INFINITY ? 0.f : fast_exp2(mw[w] - M);
+        const float2 v = *reinterpret_cast<const float2*>(so + (size_t)(w * G4_HEADS + head) * G4_HSTRIDE + dim);
+        a0 = fmaf(v.x, f, a0);
+        a1 = fmaf(v.y, f, a1);
+        Lsum = fmaf(sml[(w * G4_HEADS + head) * 2 + 1], f, Lsum);
+      }
+      const size_t slot = (row0 + head) * P.num_splits + split;
+      *reinterpret_cast<float2*>(P.part_o + slot * TQ_D + dim) = make_float2(a0, a1);
+      if (dim == 0) *reinterpret_cast<float2*>(P.part_ml + slot * 2) = make_float2(M, Lsum);
+    }
+  }
+  finish_splits<false>(P, fv.s1, fv.s2, fv.alpha, qbuf, stage0, s_flags, row0, ns, b, kvh, tid, bar_id);
+}
+
+template <int KB, int VB, bool SPARSE, bool NODEQ>
+int launch_attn_g4(const AttnParams& P, const TqFast& fk, const TqFast& fv, cudaStream_t st) {
+  using C = G4<KB, VB>;
+  static_assert(C::SMEM <= 227 * 1024, "shared-memory plan of the specialised decode kernel");
+  static thread_local int configured_dev = -1;  // per instantiation
+  int dev = 0;
+  TQ_CUDA(cudaGetDevice(&dev));
+  if (configured_dev != dev) {
+    TQ_CUDA(cudaFuncSetAttribute(k_decode_attn_g4<KB, VB, SPARSE, NODEQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+    configured_dev = dev;
+  }
+  AttnQuant ak, av;
+  memset(&ak, 0, sizeof(ak));
+  memset(&av, 0, sizeof(av));
+  memcpy(ak.s1, fk.s1, 16); memcpy(ak.s2, fk.s2, 16); memcpy(ak.cent16, fk.cent16, 32); ak.alpha = fk.lut_alpha;
+  memcpy(av.s1, fv.s1, 16); memcpy(av.s2, fv.s2, 16); memcpy(av.cent16, fv.cent16, 32); av.alpha = fv.lut_alpha;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((P.num_splits * P.hkv + G4_GROUPS - 1) / G4_GROUPS, P.batch);
+  cfg.blockDim = dim3(G4_THREADS);
+  cfg.dynamicSmemBytes = C::SMEM;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = P.overlap ? 1 : 0;
+  TQ_CUDA(cudaLaunchKernelEx(&cfg, k_decode_attn_g4<KB, VB, SPARSE, NODEQ>, P, ak, av));
+  return tq_launch_check("k_decode_attn_g4");
+}
+
+template <int KB, int VB>
+bool layout_matches(const tq_cache_layout& L) {
+  using C = G4<KB, VB>;
+  return L.page_tokens == G4_PT && L.k_idx_off == C::K_IDX && L.k_scale_off == C::K_SCALE && L.v_idx_off == C::V_IDX &&
+         L.v_scale_off == C::V_SCALE && L.record_bytes == C::REC && L.k_idx_bytes == C::KIDXB && L.v_idx_bytes == C::VIDXB;
+}
+
+}  // namespace
+
+bool tq_decode_g4_try(const tqatt::AttnParams& P, const TqFast& fk, const TqFast& fv, cudaStream_t st, int* rc) {
+  const int kf = P.L.k_format, vf = P.L.v_format;
+  if (P.group > G4_HEADS || kf < TQ_FMT_TURBO2 || kf > TQ_FMT_TURBO4 || vf < TQ_FMT_TURBO2 || vf > TQ_FMT_TURBO4) return false;
+#define TQ_ATT_G4(K, V)                                                                                              \
+  if (kf == K && vf == V) {                                                                                          \
+    if (!layout_matches<K, V>(P.L)) return false;                                                                    \
+    if (P.nodeq && K == 3 && V == 3) *rc = launch_attn_g4<3, 3, false, true>(P, fk, fv, st); \
+    else *rc = P.sparse_v ? launch_attn_g4<K, V, true, false>(P, fk, fv, st) : launch_attn_g4<K, V, false, false>(P, fk, fv, st); \
+    return true;                                                                                                     \
+  }
+  TQ_ATT_G4(2, 2) TQ_ATT_G4(2, 3) TQ_ATT_G4(2, 4) TQ_ATT_G4(3, 2) TQ_ATT_G4(3, 3) TQ_ATT_G4(3, 4) TQ_ATT_G4(4, 2)
+  TQ_ATT_G4(4, 3) TQ_ATT_G4(4, 4)
+#undef TQ_ATT_G4
+  return false;
+}

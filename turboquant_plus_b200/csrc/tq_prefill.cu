@@ -506,14 +506,16 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();  // every role is done with tensor memory
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tb), "r"(512u) : "memory");
-    if (*fail) {
-      if (tid == 0) atomicExch(P.status, 1);
-      return;
-    }
+    // A CTA that gave up a wait reports it, writes no partial and merges nothing, but still takes its ticket below:
+    // the counter of its (sequence, KV head, row block) then returns to zero like after a clean call, and a later
+    // call on the same workspace cannot elect its merger too early.
+    const bool failed = *fail != 0;   // stable: every role has passed the barrier above
+    if (failed && tid == 0) atomicExch(P.status, 1);
+    if (failed && ns <= 1) return;
     // ---- split partial / merge by the last split / epilogue: the 128 row threads only ----
     if (ns > 1) {
       const size_t slot0 = (((size_t)b * P.hkv + kvh) * P.row_blocks + rb) * P.num_splits;
-      {
+      if (!failed) {
         float4* po = reinterpret_cast<float4*>(P.part_o + ((slot0 + split) * PF_ROWS + tid) * TQ_D);
 #pragma unroll
         for (int j = 0; j < TQ_D; j += 4) po[j >> 2] = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
@@ -532,7 +534,7 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
         *fail = last;  // reuse the flag word as "this CTA merges"
       }
       rows_sync();
-      if (!*fail) return;
+      if (!*fail || failed) return;
       __threadfence();
       float M = -INFINITY;
       for (int s_i = 0; s_i < ns; ++s_i)

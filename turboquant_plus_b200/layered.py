@@ -98,9 +98,10 @@ class LayeredKVCache:
                 whole.append(k.reshape(n * batch, self.num_kv_heads, d), v.reshape(n * batch, self.num_kv_heads, d),
                              (base + st["slots"][None, :]).reshape(-1))
             for i, layer in enumerate(self.layers):
-                # the preceding kernel is an append (it never signals early completion, so this kernel starts after it)
-                # or another layer's attention call, which does not write what this kernel reads early
-                layer.attend(st["q"][i], st["bt"], st["len"], out=st["out"][i], workspace=ws, overlap=True)
+                # only an attention call that follows another layer's attention call may start early: that kernel
+                # writes nothing this one reads before its dependency wait.  The first call follows the append,
+                # which writes the cache page of the new token, so it is launched in stream order.
+                layer.attend(st["q"][i], st["bt"], st["len"], out=st["out"][i], workspace=ws, overlap=(i > 0))
 
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))

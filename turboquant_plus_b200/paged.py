@@ -137,8 +137,8 @@ class PagedKVCache:
 
         overlap=True lets the kernel start while the preceding kernel of the stream is still running; until
         that kernel has completed it only reads cache pages, the block table and the sequence lengths.  Use it
-        when the preceding kernel does not write those (another layer's attention, an append kernel that does
-        not signal early completion).
+        only when the preceding kernel writes none of those (another layer's attention call); after an append
+        into this cache launch in stream order (overlap=False).
 
         return_lse=True returns (out, lse) with lse (batch, num_q_heads) fp32, the natural log of the softmax
         denominator: what merge_attention needs to join calls over disjoint parts of a sequence."""
