@@ -174,12 +174,16 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    r = cpu_reference_run(max(1, min(args.steps, 20)), 1)
-    line = {"metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+    # one step is ~0.6 s of NumPy on the host cores: W warm-up steps and K timed steps as asked (K capped at 40 so that
+    # the arm ends within a few minutes)
+    steps = max(1, min(args.steps, 40))
+    r = cpu_reference_run(steps, args.warmup)
+    line = {"metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
             "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f64", "data": "synthetic", "impl": "reference",
             "config": {"workload": "decode attention, 32q/8kv heads, d=128, batch 1, ctx 32768, turbo3 K+V "
-                                   "(reference algorithm: dequantize the cache, then NumPy attention)"},
+                                   "(reference algorithm: dequantize the cache, then NumPy attention; the quantization "
+                                   "of the step's new token, which the GPU arm's e2e includes, is not in this arm)"},
             "cpu_baseline": {"value": r["value"], "unit": UNIT, "cores": r["cores"], "kind": "port",
                              "sample": r["sample"]},
             "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -214,8 +218,6 @@ def run_ours(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
     import turboquant_plus_b200 as tq
     from turboquant_plus_b200.layered import LayeredKVCache
 
@@ -265,7 +267,8 @@ def run_ours(args):
 
     def one_step(phases=7, sparse_v=False):
         for i, layer in enumerate(cache.layers):
-            layer.attend(q[i], bt, seq_lens, out=out[i], workspace=ws, phases=phases, overlap=True, sparse_v=sparse_v)
+            # the queries of all layers exist before the step starts: the calls of a step may overlap completely
+            layer.attend(q[i], bt, seq_lens, out=out[i], workspace=ws, phases=phases, overlap="q", sparse_v=sparse_v)
 
     one_step()
     torch.cuda.synchronize(dev)
@@ -347,6 +350,17 @@ def run_ours(args):
     assert torch.isfinite(oh.float()).all()
 
     pre = prefill_probe(torch, tq, dev, gen) if rank == 0 else None
+    # the other configurations of the benchmark family, a few steps each, so that every record carries them; with more
+    # than one rank they run sharded (KV heads / token-balanced batch) and check the shards against one GPU
+    others = {}
+    if not args.headline_only:
+        del cache, graphs, g, st
+        torch.cuda.empty_cache()
+        k_other = max(1, min(args.steps, 5))
+        for name in ("config2", "config4"):
+            others[name] = measure_decode_config(name, k_other, 3)
+            torch.cuda.empty_cache()
+        others["config3"] = measure_config3(k_other, 3)
     if rank == 0:
         peak, peak_src = peaks()
         tokens_step = LAYERS * CTX * HKV * world
@@ -368,9 +382,9 @@ def run_ours(args):
             "quantize_vectors_per_s": vec_per_s,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": f"{peak_src} copy bandwidth",
-                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch, ncu capture summarised in
-                         # profiles/k_decode_attn_turbo3_ctx32768.md
-                         "traffic": 27338240,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch in an ncu capture of this
+                         # workload: a constant taken from that profile, not something this run measures
+                         "traffic": 27338240, "traffic_source": "ncu capture of this workload, not measured in this run",
                          "kernel": "k_decode_attn_g4<3,3,dense V>", "us_per_launch": kernel_s * 1e6,
                          "bytes_per_launch": CTX * HKV * BYTES_PER_KV_TOKEN},
             "sparse_v_option": {"ms_per_step": ms_sparse_step, "kv_tokens_per_s": tokens_step / (ms_sparse_step * 1e-3),
@@ -387,6 +401,7 @@ def run_ours(args):
                     "h2d_bytes_per_step": int(qh.numel() + kh.numel() + vh.numel()) * 2,
                     "d2h_bytes_per_step": int(oh.numel()) * 2},
             "roofline_prefill": pre,
+            "other_configs": others,
             "gpu_launches": LAYERS,
             "clocks": clocks,
         }
@@ -394,10 +409,6 @@ def run_ours(args):
             line["cpu_baseline"] = {"value": cpu["value"], "unit": UNIT, "cores": cpu["cores"], "kind": "port",
                                     "sample": cpu["sample"]}
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
-
 
 
 # ----------------------------------------------------------------------------------------------
@@ -410,57 +421,94 @@ OTHER_WORKLOADS = {
 }
 
 
-def run_other_workload(args):
-    """config2: 32 layers, batch 16, ctx 8,192, K q8_0, V turbo2 (layers 0,1,30,31 q8_0/q8_0), sharded by KV head.
-    config4: batch 256, ragged contexts uniform in [1,024, 32,768], K prod3 (2-bit PolarQuant + QJL), V turbo3,
-    2 layers, sequences sharded over the ranks balanced by cached tokens."""
+def _dist_ctx():
     import torch
-    import torch.distributed as dist
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    return world, rank, torch.device("cuda", local)
+
+
+def _kv_rows(torch, gen, dev, n, hkv, heads=None):
+    """(n, hkv, D) fp16 keys (N(0,1) x lognormal(0, 0.5)) and values on the device; `heads` keeps a head slice."""
+    k = torch.randn((n, hkv, D), generator=gen, device=dev)
+    k *= torch.exp(0.5 * torch.randn((n, hkv, 1), generator=gen, device=dev))
+    v = torch.randn((n, hkv, D), generator=gen, device=dev)
+    if heads is not None:
+        k, v = k[:, heads.start:heads.stop], v[:, heads.start:heads.stop]
+    return k.half().contiguous(), v.half().contiguous()
+
+
+def measure_decode_config(name, steps, warmup):
+    """config2: 32 layers, batch 16, ctx 8,192, K q8_0, V turbo2 (layers 0,1,30,31 q8_0/q8_0), sharded by KV head.
+    config4: batch 256, ragged contexts uniform in [1,024, 32,768], K prod3 (2-bit PolarQuant + QJL), V turbo3,
+    2 layers, sequences sharded over the ranks balanced by cached tokens.
+    Strong scaling: the job is fixed, every rank holds its shard.  With more than one rank, layer 0 is filled from
+    seeds shared by all ranks, rank 0 also builds that layer unsharded, and the all-gathered outputs of the shards are
+    compared with the unsharded result (shard_check)."""
+    import torch
+    import torch.distributed as dist
+    world, rank, dev = _dist_ctx()
     from turboquant_plus_b200.layered import LayeredKVCache, boundary_format_table
     from turboquant_plus_b200 import sharding
     gen = torch.Generator(device=dev)
     gen.manual_seed(99 + rank)
-    if args.workload == "config2":
-        layers, hkv, hq = 32, HKV // world, HQ // world
-        lens = [8192] * 16
+    common = torch.Generator(device=dev)      # layer 0: the same stream on every rank
+    if name == "config2":
+        layers, batch = 32, 16
+        heads = sharding.shard_kv_heads(HKV, world, rank)
+        hkv, hq = len(heads), len(heads) * (HQ // HKV)
+        all_lens = [8192] * batch
+        mine = list(range(batch))
         formats = boundary_format_table(layers, ("q8_0", "turbo2"), ("q8_0", "q8_0"), keep=2)
         par = f"KV heads sharded x{world}"
     else:
-        layers, hkv, hq = 2, HKV, HQ
+        layers, hkv, hq, heads = 2, HKV, HQ, None
         all_lens = np.random.default_rng(4).integers(1024, 32769, size=256).tolist()
-        lens = [all_lens[i] for i in sharding.shard_batch_by_tokens(all_lens, world)[rank]]
+        parts = sharding.shard_batch_by_tokens(all_lens, world)
+        mine = parts[rank]
         formats = [("prod3", "turbo3")] * layers
         par = f"sequences sharded x{world}, balanced by tokens"
-    n_pages = [(n + PT - 1) // PT for n in lens]
-    cache = LayeredKVCache(layers, D, hkv, sum(n_pages), PT, formats, seed=42, device=dev)
-    bt = torch.zeros((len(lens), max(n_pages)), dtype=torch.int32, device=dev)
-    perm = torch.randperm(sum(n_pages), generator=gen, device=dev).to(torch.int32)
-    off = 0
-    for b, npg in enumerate(n_pages):
-        bt[b, :npg] = perm[off:off + npg]
-        off += npg
-    for layer in range(layers):
+    lens = [all_lens[i] for i in mine]
+
+    def tables(seq_lens, g):
+        n_pages = [(n + PT - 1) // PT for n in seq_lens]
+        bt = torch.zeros((len(seq_lens), max(n_pages)), dtype=torch.int32, device=dev)
+        perm = torch.randperm(sum(n_pages), generator=g, device=dev).to(torch.int32)
+        off = 0
+        for b, npg in enumerate(n_pages):
+            bt[b, :npg] = perm[off:off + npg]
+            off += npg
+        return bt, sum(n_pages)
+
+    def fill_layer0(cache_layer, bt, seq_ids, head_slice):
+        for b, s in enumerate(seq_ids):
+            common.manual_seed(5000 + s)
+            k, v = _kv_rows(torch, common, dev, all_lens[s], HKV, head_slice)
+            pos = torch.arange(all_lens[s], device=dev)
+            cache_layer.append(k, v, bt[b, pos // PT].to(torch.int64) * PT + pos % PT)
+
+    bt, total_pages = tables(lens, gen)
+    cache = LayeredKVCache(layers, D, hkv, total_pages, PT, formats, seed=42, device=dev)
+    fill_layer0(cache.layers[0], bt, mine, heads)
+    for layer in range(1, layers):
         for b, n in enumerate(lens):
-            k = torch.randn((n, hkv, D), generator=gen, device=dev)
-            k *= torch.exp(0.5 * torch.randn((n, hkv, 1), generator=gen, device=dev))
-            v = torch.randn((n, hkv, D), generator=gen, device=dev)
+            k, v = _kv_rows(torch, gen, dev, n, hkv)
             pos = torch.arange(n, device=dev)
-            cache.append(layer, k.half(), v.half(), bt[b, pos // PT].to(torch.int64) * PT + pos % PT)
+            cache.append(layer, k, v, bt[b, pos // PT].to(torch.int64) * PT + pos % PT)
     seq_lens = torch.tensor(lens, dtype=torch.int32, device=dev)
+    common.manual_seed(77)
+    q_all = torch.randn((len(all_lens), HQ, D), generator=common, device=dev).half()     # layer-0 queries, every rank alike
     q = torch.randn((layers, len(lens), hq, D), generator=gen, device=dev).half()
+    q0 = q_all[torch.as_tensor(mine, device=dev)]
+    q[0] = q0 if heads is None else q0[:, heads.start * (HQ // HKV):heads.stop * (HQ // HKV)]
     out = torch.empty_like(q)
     ws = cache.layers[0].workspace(len(lens), hq, bt.shape[1])
 
     def one_step():
         for i, layer in enumerate(cache.layers):
-            layer.attend(q[i], bt, seq_lens, out=out[i], workspace=ws, overlap=True)
+            layer.attend(q[i], bt, seq_lens, out=out[i], workspace=ws, overlap="q")
 
     one_step()
     torch.cuda.synchronize(dev)
@@ -468,20 +516,20 @@ def run_other_workload(args):
     g = torch.cuda.CUDAGraph()
     with torch.cuda.graph(g):
         one_step()
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         g.replay()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize(dev)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         g.replay()
     e1.record()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize(dev)
-    ms = e0.elapsed_time(e1) / args.steps
+    ms = e0.elapsed_time(e1) / steps
     tokens = float(sum(lens)) * hkv * layers
     nbytes = float(sum(lens)) * hkv * sum(layer.bytes_per_token for layer in cache.layers)
     if world > 1:
@@ -490,48 +538,75 @@ def run_other_workload(args):
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
         ms, tokens, nbytes = float(tmax[0]), float(t[1]), float(t[2])
-    if rank == 0:
-        peak, src = peaks()
-        print(json.dumps({
-            "metric": "decode_attn_kv_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f16 tensor-core products, f32 accumulate and softmax",
-            "data": "synthetic",
-            "config": {"workload": OTHER_WORKLOADS[args.workload],
-                       "parallelism": par, "l2": "inputs larger than L2"},
-            "hbm_gbs_algorithmic": nbytes / (ms * 1e-3) / 1e9, "frac_of_measured_hbm": nbytes / (ms * 1e-3) / 1e9 / peak / world,
-            "peak_source": src, "gpu_launches": layers}), flush=True)
+    check = None
     if world > 1:
-        dist.destroy_process_group()
+        # the shards' layer-0 outputs, gathered, against the same layer held by one GPU
+        if name == "config2":
+            got = sharding.all_gather_heads(out[0])
+        else:
+            got = sharding.all_gather_batch(out[0], [len(p) for p in parts], parts)
+        if rank == 0:
+            del cache
+            torch.cuda.empty_cache()
+            every = list(range(len(all_lens)))
+            fbt, fpages = tables(all_lens, gen)
+            full = LayeredKVCache(1, D, HKV, fpages, PT, [formats[0]], seed=42, device=dev)
+            fill_layer0(full.layers[0], fbt, every, None)
+            ref = full.layers[0].attend(q_all, fbt, torch.tensor(all_lens, dtype=torch.int32, device=dev))
+            torch.cuda.synchronize(dev)
+            diff = float((got.float() - ref.float()).abs().max())
+            check = {"layer": 0, "max_abs_diff": diff, "max_abs_ref": float(ref.float().abs().max()),
+                     "bit_equal": bool(torch.equal(got, ref)),
+                     "note": "all-gathered shard outputs vs the unsharded layer on one GPU; the split plan depends on "
+                             "the number of (sequence, KV head) pairs a GPU holds, so head sharding changes the "
+                             "summation order (fp32 rounding), batch sharding of a large batch does not"}
+    peak, src = peaks()
+    return {"metric": "decode_attn_kv_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": steps, "warmup": warmup, "ms_per_step": ms, "scaling": "strong",
+            "workload": OTHER_WORKLOADS[name], "parallelism": par,
+            "hbm_gbs_algorithmic": nbytes / (ms * 1e-3) / 1e9, "frac": nbytes / (ms * 1e-3) / 1e9 / peak / world,
+            "frac_of": f"{src} HBM copy bandwidth x {world} GPUs", "gpu_launches": layers, "shard_check": check}
 
 
-def run_config3(args):
+def run_other_workload(args):
+    r = measure_decode_config(args.workload, args.steps, args.warmup)
+    if int(os.environ.get("RANK", "0")) == 0:
+        r.update({"higher_is_better": True, "vs_baseline": None, "data": "synthetic",
+                  "dtype": "f16 tensor-core products, f32 accumulate and softmax",
+                  "config": {"workload": r["workload"], "parallelism": r["parallelism"], "l2": "inputs larger than L2"}})
+        print(json.dumps(r), flush=True)
+
+
+def measure_config3(steps, warmup):
     """config3: Llama-3-70B shape, one layer: 131,072 tokens of fp16 K/V (8 KV heads, sharded over the ranks) are
     quantize-on-appended as turbo3 into 128-token pages in 8,192-token chunks, then one 128-query chunk x 64 query
-    heads runs chunked-prefill attention (tcgen05) over the whole prefix.  Prints append vectors/s (HBM roofline)
-    and prefill TFLOP/s (tensor roofline)."""
+    heads runs chunked-prefill attention (tcgen05) over the whole prefix.  Append vectors/s against the HBM roofline,
+    prefill TFLOP/s against the tensor roofline; with more than one rank the gathered prefill outputs are compared
+    with the unsharded layer on rank 0."""
     import torch
     import torch.distributed as dist
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    world, rank, dev = _dist_ctx()
     import turboquant_plus_b200 as tq
+    from turboquant_plus_b200 import sharding
     n, hq_all, hkv_all, chunk, tq_len = 131072, 64, 8, 8192, 128
-    hkv, hq = hkv_all // world, hq_all // world
-    gen = torch.Generator(device=dev)
-    gen.manual_seed(7 + rank)
+    heads = sharding.shard_kv_heads(hkv_all, world, rank)
+    hkv, hq, grp = len(heads), len(heads) * (hq_all // hkv_all), hq_all // hkv_all
+    common = torch.Generator(device=dev)
+    common.manual_seed(7)
     cache = tq.PagedKVCache(D, hkv, n // PT, PT, "turbo3", "turbo3", seed=42, device=dev)
-    k = torch.randn((n, hkv, D), generator=gen, device=dev).half()
-    v = torch.randn((n, hkv, D), generator=gen, device=dev).half()
+    k_all = torch.randn((n, hkv_all, D), generator=common, device=dev).half()
+    v_all = torch.randn((n, hkv_all, D), generator=common, device=dev).half()
+    q_all = torch.randn((1, tq_len, hq_all, D), generator=common, device=dev).half()
+    k = k_all[:, heads.start:heads.stop].contiguous()
+    v = v_all[:, heads.start:heads.stop].contiguous()
+    q = q_all[:, :, heads.start * grp:heads.stop * grp].contiguous()
+    if not (world > 1 and rank == 0):
+        del k_all, v_all
     slots = torch.arange(n, device=dev)
 
-    def append_all():
+    def append_all(c=cache, kk=k, vv=v):
         for lo in range(0, n, chunk):
-            cache.append(k[lo:lo + chunk], v[lo:lo + chunk], slots[lo:lo + chunk])
+            c.append(kk[lo:lo + chunk], vv[lo:lo + chunk], slots[lo:lo + chunk])
 
     def sync():
         if world > 1:
@@ -540,60 +615,76 @@ def run_config3(args):
 
     append_all()
     torch.cuda.synchronize(dev)
-    graph = torch.cuda.CUDAGraph()      # the 32 launches of one pass, replayed without host overhead
+    graph = torch.cuda.CUDAGraph()      # the launches of one pass, replayed without host overhead
     with torch.cuda.graph(graph):
         append_all()
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         graph.replay()
     sync()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         graph.replay()
     e1.record()
     sync()
-    append_ms = e0.elapsed_time(e1) / args.steps
+    append_ms = e0.elapsed_time(e1) / steps
     bt = torch.arange(n // PT, device=dev, dtype=torch.int32)[None]
     kv_len = torch.tensor([n], dtype=torch.int32, device=dev)
-    q = torch.randn((1, tq_len, hq, D), generator=gen, device=dev).half()
     out = torch.empty_like(q)
     for _ in range(3):
         cache.prefill_attend(q, bt, kv_len, out=out)
     sync()
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         cache.prefill_attend(q, bt, kv_len, out=out)
     e1.record()
     sync()
-    prefill_ms = e0.elapsed_time(e1) / args.steps
+    prefill_ms = e0.elapsed_time(e1) / steps
     assert cache.kernel_status() == 0 and torch.isfinite(out.float()).all()
+    check = None
     if world > 1:
         t = torch.tensor([append_ms, prefill_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         append_ms, prefill_ms = float(t[0]), float(t[1])
-    if rank == 0:
-        vectors = 2.0 * n * hkv_all
-        visible = sum(n - tq_len + i + 1 for i in range(tq_len))
-        flops = 2.0 * 2 * hq_all * D * visible
-        hbm, src = peaks()
-        tpeak, tsrc = tensor_peak()
-        print(json.dumps({
-            "metric": "quantize_append_vectors_per_s", "value": vectors / (append_ms * 1e-3), "unit": "vectors/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": append_ms,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "f16 in, exact +-1 tensor-core products, f32 accumulate", "data": "synthetic",
-            "config": {"workload": "config3: one layer, 64q/8kv heads, d128, 131072 tokens appended as turbo3 K+V in "
-                                   "8192-token chunks, then a 128-query chunk of prefill attention over the prefix",
-                       "parallelism": f"KV heads sharded x{world}", "l2": "inputs larger than L2"},
+        parts = [torch.empty_like(out) for _ in range(world)]
+        dist.all_gather(parts, out)
+        if rank == 0:
+            got = torch.cat(parts, dim=2)
+            del cache
+            torch.cuda.empty_cache()
+            full = tq.PagedKVCache(D, hkv_all, n // PT, PT, "turbo3", "turbo3", seed=42, device=dev)
+            append_all(full, k_all, v_all)
+            ref = full.prefill_attend(q_all, bt, kv_len)
+            torch.cuda.synchronize(dev)
+            check = {"max_abs_diff": float((got.float() - ref.float()).abs().max()),
+                     "max_abs_ref": float(ref.float().abs().max()), "bit_equal": bool(torch.equal(got, ref)),
+                     "note": "gathered prefill outputs of the head shards vs the unsharded layer on one GPU"}
+    vectors = 2.0 * n * hkv_all
+    visible = sum(n - tq_len + i + 1 for i in range(tq_len))
+    flops = 2.0 * 2 * hq_all * D * visible
+    hbm, src = peaks()
+    tpeak, tsrc = tensor_peak()
+    return {"metric": "quantize_append_vectors_per_s", "value": vectors / (append_ms * 1e-3), "unit": "vectors/s",
+            "n_gpus": world, "steps": steps, "warmup": max(warmup, 3), "ms_per_step": append_ms, "scaling": "strong",
+            "workload": "config3: one layer, 64q/8kv heads, d128, 131072 tokens appended as turbo3 K+V in "
+                        "8192-token chunks, then a 128-query chunk of prefill attention over the prefix",
+            "parallelism": f"KV heads sharded x{world}",
             "roofline": {"bound": "hbm", "achieved": vectors * 308 / (append_ms * 1e-3) / 1e9 / world, "peak": hbm,
                          "unit": "GB/s", "frac": vectors * 308 / (append_ms * 1e-3) / 1e9 / world / hbm,
                          "peak_source": src, "kernel": "k_quantize_mma<half,3>", "bytes_per_vector": 308},
             "prefill": {"ms": prefill_ms, "tflops": flops / (prefill_ms * 1e-3) / 1e12,
                         "frac_of_tensor_peak": flops / (prefill_ms * 1e-3) / 1e12 / world / tpeak, "peak": tpeak,
                         "peak_source": tsrc, "kernel": "k_prefill_attn2<3,3> (tcgen05)"},
-            "gpu_launches": 2 * (n // chunk)}), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+            "gpu_launches": 2 * (n // chunk), "shard_check": check}
+
+
+def run_config3(args):
+    r = measure_config3(args.steps, args.warmup)
+    if int(os.environ.get("RANK", "0")) == 0:
+        r.update({"higher_is_better": True, "vs_baseline": None, "data": "synthetic",
+                  "dtype": "f16 in, exact +-1 tensor-core products, f32 accumulate",
+                  "config": {"workload": r["workload"], "parallelism": r["parallelism"], "l2": "inputs larger than L2"}})
+        print(json.dumps(r), flush=True)
 
 
 def run_side_kernels(args):
@@ -674,11 +765,20 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="config1", choices=["config1", "config2", "config3", "config4", "side"],
                     help="config1 is the headline workload; the others print a line of the same shape")
+    ap.add_argument("--headline-only", action="store_true", help="config1 without the other_configs block")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
-    elif args.workload == "config3":
+        return
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if args.workload == "config3":
         run_config3(args)
     elif args.workload == "side":
         run_side_kernels(args)
@@ -686,6 +786,9 @@ def main():
         run_other_workload(args)
     else:
         run_ours(args)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

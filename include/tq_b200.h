@@ -292,6 +292,13 @@ int tq_decode_attn(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cach
  * those three -- e.g. the attention call of another layer; after a tq_cache_append into the same pool launch
  * without it. */
 #define TQ_DECODE_OVERLAP 8
+/* TQ_DECODE_OVERLAP_Q (bits 3 and 6): TQ_DECODE_OVERLAP for a call whose queries the preceding kernel does not
+ * write either -- a chain of attention calls whose queries were all produced beforehand (the layers of a
+ * benchmark step, the calls over the old and the recent part of a sequence that tq_attn_merge joins).  The
+ * kernel then reads its queries and streams its pages while the preceding kernel is still finishing, and waits for
+ * it only before its first write (split partials, tickets, output).  Honoured by the kernel for PolarQuant K and V
+ * with <= 4 query heads per KV head and a sign-WHT K rotation; elsewhere it means TQ_DECODE_OVERLAP. */
+#define TQ_DECODE_OVERLAP_Q (8 | 64)
 /* TQ_DECODE_SPARSE_V (bit 4): sparse V as in the reference's docs/papers/sparse-v-dequant.md:64-84 -- the V
  * dequantization and accumulation are skipped where the attention weight exp(score - running max) is below 1e-6;
  * here per 16-token tile of a warp (skipped when every weight of the tile, for every query head of the group, is

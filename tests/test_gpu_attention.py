@@ -304,25 +304,29 @@ def test_overlap_launch_and_compressor_streaming_api(tq):
     plain = [c.attend(q, bt, sl, workspace=ws).clone() for c, bt in caches]
     outs = [torch.empty_like(q) for _ in caches]
 
-    def chain():
-        for (c, bt), o_ in zip(caches, outs):
-            c.attend(q, bt, sl, out=o_, workspace=ws, overlap=True)
+    for mode in (True, "q"):      # "q": the queries may be read before the preceding call has completed, too
+        def chain():
+            for (c, bt), o_ in zip(caches, outs):
+                c.attend(q, bt, sl, out=o_, workspace=ws, overlap=mode)
 
-    chain()
-    torch.cuda.synchronize()
-    for a, b in zip(plain, outs):
-        assert torch.equal(a, b)
-    g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g):
-        chain()
-    for o_ in outs:
-        o_.zero_()
-    for _ in range(3):
-        g.replay()
-    torch.cuda.synchronize()
-    for a, b in zip(plain, outs):
-        assert torch.equal(a, b)
-    assert caches[0][0].kernel_status(ws) == 0
+        for o_ in outs:
+            o_.zero_()
+        for _ in range(4):        # back to back: a call's page loop runs under the tail of the call before
+            chain()
+        torch.cuda.synchronize()
+        for a, b in zip(plain, outs):
+            assert torch.equal(a, b)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            chain()
+        for o_ in outs:
+            o_.zero_()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        for a, b in zip(plain, outs):
+            assert torch.equal(a, b)
+        assert caches[0][0].kernel_status(ws) == 0
 
     comp = tq.KVCacheCompressor(D, k_bits=3, v_bits=3, seed=42, rotation="wht").init_cache(2, hkv, 12)
     ks = [rng.standard_normal((300, hkv, D)).astype(np.float16)]

@@ -286,7 +286,18 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn(const AttnParams
       s[2] = ok1 ? s[2] : -INFINITY;
       s[3] = ok1 ? s[3] : -INFINITY;
       // ---------------- online softmax (log2 domain), heads 2t and 2t+1 ----------------
-      float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
+      // The running reference is the maximum of score + log2(V scale), not of the score alone: the P operand of the
+      // second product is p * (V scale) in fp16 and then never exceeds 1 whatever the norms of the values are (a
+      // higher reference scales p, the softmax sums and O alike; the final division removes it).
+      float vs0 = 1.0f, vs1 = 1.0f, lv0 = 0.f, lv1 = 0.f;
+      if (!VT::Q8) {
+        const float* vsc = reinterpret_cast<const float*>(st + P.L.v_scale_off);
+        vs0 = ok0 ? vsc[tb + g] : 0.f;     // a stale scale must not meet p = 0
+        vs1 = ok1 ? vsc[tb + g + 8] : 0.f;
+        lv0 = fmaxf(fast_log2(vs0), -100.0f);   // zero vectors have scale 0
+        lv1 = fmaxf(fast_log2(vs1), -100.0f);
+      }
+      float mx0 = fmaxf(s[0] + lv0, s[2] + lv1), mx1 = fmaxf(s[1] + lv0, s[3] + lv1);
 #pragma unroll
       for (int sh = 4; sh < 32; sh <<= 1) {
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
@@ -306,14 +317,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn(const AttnParams
           o[j][0] *= r0; o[j][1] *= r1; o[j][2] *= r0; o[j][3] *= r1;
         }
       }
-      if (P.sparse_v && !__any_sync(0xffffffffu, fmaxf(fmaxf(p00, p01), fmaxf(p10, p11)) >= SPARSE_V_TAU)) continue;
+      // the threshold of the sparse-V option is relative to the largest weight, i.e. to the score maximum
+      if (P.sparse_v && !__any_sync(0xffffffffu, fmaxf(fmaxf(p00 * vs0, p01 * vs0), fmaxf(p10 * vs1, p11 * vs1)) >= SPARSE_V_TAU)) continue;
       // probabilities (* V scale), as fp16, transposed into the B-operand layout (tokens on K)
-      float vs0 = 1.0f, vs1 = 1.0f;
-      if (!VT::Q8) {
-        const float* vsc = reinterpret_cast<const float*>(st + P.L.v_scale_off);
-        vs0 = ok0 ? vsc[tb + g] : 0.f;
-        vs1 = ok1 ? vsc[tb + g + 8] : 0.f;
-      }
       const uint32_t pb0 = movmatrix_trans(pack_h2(p00 * vs0, p01 * vs0));
       const uint32_t pb1 = movmatrix_trans(pack_h2(p10 * vs1, p11 * vs1));
       // ---------------- O^T += V_tile^T . P^T ----------------
@@ -644,6 +650,8 @@ static int decode_impl(const tq_quantizer* kq, const tq_quantizer* vq, const tq_
   P.overlap = (phases & TQ_DECODE_OVERLAP) ? 1 : 0;
   P.sparse_v = (phases & TQ_DECODE_SPARSE_V) ? 1 : 0;
   P.nodeq = (phases & TQ_DECODE_NO_DEQUANT) ? 1 : 0;
+  // queries come from the preceding kernel when the K rotation is dense (k_prepare_queries writes them)
+  P.q_early = ((phases & TQ_DECODE_OVERLAP_Q) == TQ_DECODE_OVERLAP_Q && !k_dense) ? 1 : 0;
   P.L = *L;
   TqFast none;
   memset(&none, 0, sizeof(none));

@@ -77,6 +77,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float fast_log2(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
@@ -122,6 +127,7 @@ struct AttnParams {
   int32_t overlap;     // launched with programmatic stream serialization: see TQ_DECODE_OVERLAP
   int32_t sparse_v;    // skip the V work of a 16-token tile whose weights are all below SPARSE_V_TAU: TQ_DECODE_SPARSE_V
   int32_t nodeq;       // measurement variant without table lookups (results meaningless): TQ_DECODE_NO_DEQUANT
+  int32_t q_early;     // the preceding kernel does not write the queries: they are read before the dependency wait
   tq_cache_layout L;
 };
 

@@ -33,20 +33,19 @@ static_assert(sizeof(AttnQuant) == 80, "AttnQuant layout");
 constexpr int G4_HEADS = 4;
 constexpr int G4_HSTRIDE = TQ_D + 4;  // floats between heads in the warp-merge buffer: 16-byte stores stay conflict-free
 constexpr int G4_PT = 128;            // tokens per page
-constexpr int G4_NS = 3;              // page records in flight per group
 
-// One CTA per SM runs TWO independent 256-thread groups (own split, own pipeline, own barrier), sharing only the
-// pair tables.  Two separate 256-thread CTAs on one SM did the same work, but the warp schedulers favoured the
-// CTA that arrived first: it finished its pages in 9.7 us, its neighbour in 12.6 us, and the SM idled at half
-// occupancy in between.  Warps of one CTA have the same age and progress together.
-constexpr int G4_GROUPS = 2;
-constexpr int G4_THREADS = G4_GROUPS * ATT_THREADS;
+constexpr int G4_NS = 3;              // page records in flight per CTA (4 and 5 measured: no faster)
+// One 256-thread CTA per (KV head, split), two CTAs per SM.  (One 512-thread CTA running two such groups keeps the
+// two in step inside a single launch and is 3 % faster there at 32K tokens; but in a chain of launches with
+// programmatic dependent launch the half-SM CTAs of the next call take the place of finished ones one by one, so
+// that one CTA's latency-bound prologue and tail run under the other's page loop: 11.4 against 13.2 us per call.)
 
 constexpr int up128(int x) { return (x + 127) / 128 * 128; }
 
+
 // Record layout of a (page, head) for 128-token pages, as tq_cache_layout_init lays it out, and the carve-up of
-// the CTA's shared memory: the two pair tables (shared by the groups), then per group the query buffer, the
-// mbarriers and flags, and the pipeline stages (reused as the warp-merge buffer after the page loop).
+// the CTA's shared memory: the two pair tables, the query buffer, the mbarriers and flags, and the pipeline stages
+// (reused as the warp-merge buffer after the page loop).
 template <int KB, int VB> struct G4 {
   static constexpr int KIDXB = 16 * KB, VIDXB = 16 * VB;  // index bytes per token
   static constexpr int K_IDX = 0;
@@ -64,7 +63,7 @@ template <int KB, int VB> struct G4 {
   static constexpr int G_STAGE = G_BAR + 128;
   static constexpr int MERGE = ATT_WARPS * G4_HEADS * (G4_HSTRIDE + 2) * 4;
   static constexpr int GROUP_BYTES = up128(G_STAGE + (G4_NS * REC > MERGE ? G4_NS * REC : MERGE));
-  static constexpr int SMEM = ALIGN + OFF_GROUPS + G4_GROUPS * GROUP_BYTES;
+  static constexpr int SMEM = ALIGN + OFF_GROUPS + GROUP_BYTES;
 };
 
 // ---- shared-memory loads through 32-bit addresses with immediate offsets ----------------------------------------
@@ -174,9 +173,9 @@ __device__ __forceinline__ void g4_tile(G4State& S, uint32_t st, const uint32_t 
   // their use: the loads then wait under it instead of in front of the table lookups
   uint32_t vw[4][2];
   load_v_words<VB, 0>(st + v_thr, vsel0, vsel1, vw[0]);
-  load_v_words<VB, C::VIDXB>(st + v_thr, vsel0, vsel1, vw[1]);
-  load_v_words<VB, 2 * C::VIDXB>(st + v_thr, vsel0, vsel1, vw[2]);
-  load_v_words<VB, 3 * C::VIDXB>(st + v_thr, vsel0, vsel1, vw[3]);
+  load_v_words<VB, 4 * C::VIDXB>(st + v_thr, vsel0, vsel1, vw[1]);
+  load_v_words<VB, 8 * C::VIDXB>(st + v_thr, vsel0, vsel1, vw[2]);
+  load_v_words<VB, 12 * C::VIDXB>(st + v_thr, vsel0, vsel1, vw[3]);
   const float vs_raw = lds_f32<0>(st + vs_thr);
   // hi + lo: the partner lane (t ^ 2) holds the other half of the same heads
   const float give0 = upper ? s[0] : s[2], give1 = upper ? s[1] : s[3];
@@ -184,23 +183,28 @@ __device__ __forceinline__ void g4_tile(G4State& S, uint32_t st, const uint32_t 
   const float sum0 = keep0 + __shfl_xor_sync(0xffffffffu, give0, 2);
   const float sum1 = keep1 + __shfl_xor_sync(0xffffffffu, give1, 2);
   // ---------------- online softmax (log2 domain), heads 2(t&1) and 2(t&1)+1 ----------------
-  // The running maxima move only when a score exceeds them by more than 2^MAX_SLACK: probabilities then stay
-  // below 2^MAX_SLACK (far inside fp16 and fp32 range) and almost every tile skips the warp reduction and the
-  // rescaling of O.  The normalised result is the same up to rounding.
+  // The running maxima move only when a score exceeds them by more than 2^MAX_SLACK, so that almost every tile skips
+  // the warp reduction and the rescaling of O.  What is tracked is the maximum of score + log2(V scale), not of the
+  // score alone: the P operand of the second product is p * (V scale) in fp16, and with this reference it never
+  // exceeds 2^MAX_SLACK whatever the norms of the values are (a reference that is too high only scales p, the
+  // softmax sums and O by the same factor, which the final division removes).
   bool ok = true;
-  float d0 = fmaf(sum0, ks, -S.m0), d1 = fmaf(sum1, ks, -S.m1);   // score - running maximum
+  float vs = vs_raw;
+  float d0 = fmaf(sum0, ks, -S.m0), d1 = fmaf(sum1, ks, -S.m1);   // score - running reference
   if constexpr (MASKED) {
     ok = tok_in_page < valid;
+    vs = ok ? vs_raw : 0.f;                                       // a stale scale must not meet p = 0
     d0 = ok ? d0 : -INFINITY;
     d1 = ok ? d1 : -INFINITY;
   }
-  if (__any_sync(0xffffffffu, (d0 > MAX_SLACK) || (d1 > MAX_SLACK))) {
+  const float lvs = fmaxf(fast_log2(vs), -100.0f);                // zero vectors have scale 0
+  if (__any_sync(0xffffffffu, (d0 + lvs > MAX_SLACK) || (d1 + lvs > MAX_SLACK))) {
     float sc0 = sum0 * ks, sc1 = sum1 * ks;
     if constexpr (MASKED) {
       sc0 = ok ? sc0 : -INFINITY;
       sc1 = ok ? sc1 : -INFINITY;
     }
-    float mx0 = sc0, mx1 = sc1;
+    float mx0 = sc0 + lvs, mx1 = sc1 + lvs;
 #pragma unroll
     for (int sh = 2; sh < 32; sh <<= 1) {
       mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
@@ -225,13 +229,16 @@ __device__ __forceinline__ void g4_tile(G4State& S, uint32_t st, const uint32_t 
   S.l0 += p0;
   S.l1 += p1;
   // a template parameter, not a run-time flag: the possible jump keeps the V loads below it from being issued early
-  if (SPARSE && !__any_sync(0xffffffffu, fmaxf(p0, p1) >= SPARSE_V_TAU)) return;
-  const float vs = MASKED ? (ok ? vs_raw : 0.f) : vs_raw;   // a stale scale must not meet p = 0
+  // (the threshold is applied to p * V scale, the token's weight in the output relative to the largest one)
+  if (SPARSE && !__any_sync(0xffffffffu, fmaxf(p0, p1) * vs >= SPARSE_V_TAU)) return;
   const uint32_t hp = pack_h2(p0 * vs, p1 * vs);
   uint32_t pb[4];
 #pragma unroll
-  for (int q4 = 0; q4 < 4; ++q4) pb[q4] = __byte_perm(__shfl_sync(0xffffffffu, hp, src0 + 4 * q4), 0, psel);
-  // ---------------- O^T += V_tile^T . P^T : tokens 4t .. 4t+3 of the tile, dims 16g .. 16g+15 ----------------
+  for (int q4 = 0; q4 < 4; ++q4)
+    pb[q4] = __byte_perm(__shfl_sync(0xffffffffu, hp, src0 + 16 * (q4 & 1) + 2 * (q4 >> 1)), 0, psel);
+  // ---------------- O^T += V_tile^T . P^T : tokens t, t+4, t+8, t+12 of the tile, dims 16g .. 16g+15 ----------------
+  // (neighbouring lanes read neighbouring token rows: rows are 16 VB bytes apart, which spreads a quad of lanes over
+  // the shared-memory banks; a stride of four rows put lanes t and t+2 on the same banks)
   uint32_t h[4][8];
   constexpr int SHV = PairLut<VB>::SHIFT;
 #pragma unroll
@@ -252,17 +259,13 @@ __device__ __forceinline__ void g4_tile(G4State& S, uint32_t st, const uint32_t 
 }
 
 template <int KB, int VB, bool SPARSE, bool NODEQ>
-__global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_constant__ AttnParams P, const __grid_constant__ AttnQuant fk,
+__global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_constant__ AttnParams P, const __grid_constant__ AttnQuant fk,
                                                                     const __grid_constant__ AttnQuant fv) {
   using C = G4<KB, VB>;
   extern __shared__ __align__(128) uint8_t smem_raw[];
-  const int grp = threadIdx.x >> 8;              // which of the CTA's two groups
-  // groups are numbered (kv head, split) so that an odd number of splits does not leave half a CTA empty
-  const int gidx = G4_GROUPS * blockIdx.x + grp, b = blockIdx.y;
-  const bool exists = gidx < P.num_splits * P.hkv;
-  const int kvh = exists ? gidx / P.num_splits : 0, split = exists ? gidx % P.num_splits : P.num_splits;
-  const int tid = threadIdx.x & 255, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
-  const int bar_id = 1 + grp;
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  constexpr int bar_id = 0;
   {  // one parameter line per warp, all misses in flight together
     const uint32_t* pp = reinterpret_cast<const uint32_t*>(&P);
     uint32_t touch;
@@ -271,10 +274,12 @@ __global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_c
     else touch = warp == 6 ? fv.s1[0] : fv.pad[2];
     asm volatile("" ::"r"(touch));
   }
-  // Programmatic dependent launch: let the next kernel in the stream start its own prologue as soon as SMs free
-  // up.  Everything this kernel does before griddepcontrol.wait below reads only the cache, the block table and
-  // the sequence lengths; queries are read, and the workspace and the output written, after the wait, i.e.
-  // after the preceding kernel has completed and its writes are visible.  Both instructions do nothing in a
+  // Programmatic dependent launch: let the next kernel in the stream start as soon as SMs free up.  Everything
+  // this kernel does before its griddepcontrol.wait reads only the cache, the block table and the sequence
+  // lengths -- and, when the caller says that the preceding kernel does not write the queries either (q_early),
+  // the queries.  What comes after the wait runs after the preceding kernel has completed and its writes are
+  // visible: the workspace and the output are only ever touched there.  Without q_early the wait stands in front of
+  // the query load; with it, in front of the first write (after the page loop).  Both instructions do nothing in a
   // launch without the attribute.
   if (P.overlap) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int page_lo = split * P.chunk_pages;
@@ -282,7 +287,7 @@ __global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_c
   const int32_t* bt = P.block_table + (size_t)b * P.max_pages;
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* sm = smem_raw + (((raw + C::ALIGN - 1) & ~(uint32_t)(C::ALIGN - 1)) - raw);
-  uint8_t* smg = sm + C::OFF_GROUPS + (size_t)grp * C::GROUP_BYTES;   // this group's private part
+  uint8_t* smg = sm + C::OFF_GROUPS;
   float* qbuf = reinterpret_cast<float*>(smg + C::G_Q);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smg + C::G_BAR);
   volatile int* s_flags = reinterpret_cast<volatile int*>(smg + C::G_BAR + 64);
@@ -303,7 +308,7 @@ __global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_c
   // row's max_pages entries and the split count stays inside the plan the workspace was sized for.
   const int seq_len = min(max(P.seq_lens[b], 0), P.max_pages * G4_PT);
   const int n_pages = (seq_len + G4_PT - 1) / G4_PT;
-  const int np = min(n_pages, page_lo + P.chunk_pages) - page_lo;   // pages of this group (<= 0: none)
+  const int np = min(n_pages, page_lo + P.chunk_pages) - page_lo;   // pages of this CTA (<= 0: none)
   int pg_ahead = 0;  // producer: block-table entry of the page issued in the next iteration
   float x[4] = {0.f, 0.f, 0.f, 0.f};
   if (tid == PRODUCER) {
@@ -315,13 +320,12 @@ __global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_c
     s_flags[0] = 0;
     s_flags[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    if (np > 0) {
-      issue(0, pg_next[0]);
-      if (np > 1) issue(1, pg_next[1]);
-      pg_ahead = pg_next[2];
-    }
+#pragma unroll
+    for (int s = 0; s < G4_NS - 1; ++s)
+      if (np > s) issue(s, pg_next[s]);
+    pg_ahead = pg_next[G4_NS - 1];
   } else if (warp < P.group) {
-    if (P.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (P.overlap && !P.q_early) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (P.k_pre) load_q4(P.qrot, TQ_F32, (row0 + warp) * TQ_D + 4 * lane, x);
     else load_q4(P.q, P.q_dtype, (row0 + warp) * TQ_D + 4 * lane, x);
     if (!P.k_pre) {
@@ -338,19 +342,19 @@ __global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_c
   }
   __syncwarp();
   if (warp >= P.group) {
-    const int fh = ATT_THREADS - 32 * P.group;   // table-filling threads per group; both groups share the work
-    lut_fill<KB>(sm + C::OFF_K, fk.cent16, grp * fh + tid - 32 * P.group, G4_GROUPS * fh);
-    lut_fill<VB>(sm + C::OFF_V, fv.cent16, grp * fh + tid - 32 * P.group, G4_GROUPS * fh);
+    const int fh = ATT_THREADS - 32 * P.group;   // table-filling threads
+    lut_fill<KB>(sm + C::OFF_K, fk.cent16, tid - 32 * P.group, fh);
+    lut_fill<VB>(sm + C::OFF_V, fv.cent16, tid - 32 * P.group, fh);
   }
-  // every thread waits before it can touch the workspace or the output (the query warps already have)
-  if (P.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (P.overlap && !P.q_early) asm volatile("griddepcontrol.wait;" ::: "memory");   // the query warps already have
   if (n_pages == 0 && split == 0) {  // empty sequence: zeros (split 0 exists for every kv head)
+    if (P.overlap && P.q_early) asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int e = tid; e < P.group * TQ_D; e += ATT_THREADS) store_out(P.out, P.out_dtype, row0 * TQ_D + e, 0.f);
     if (P.lse && tid < P.group) P.lse[row0 + tid] = -INFINITY;
   }
   const int ns = (n_pages + P.chunk_pages - 1) / P.chunk_pages;
-  __syncthreads();               // the only CTA-wide barrier: tables, query buffers and mbarriers are ready
-  if (np <= 0) return;           // this group has no pages (its split lies beyond the sequence)
+  __syncthreads();               // tables, query buffer and mbarriers are ready
+  if (np <= 0) return;           // this CTA has no pages (its split lies beyond the sequence)
 
   // B operand of S = K q^T: column g is head g & 3, hi half for g < 4, lo half otherwise
   uint32_t qf[8][2];
@@ -371,7 +375,7 @@ __global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_c
   const uint32_t lv_base = smem_u32(sm + C::OFF_V) + (PairLut<VB>::REPL ? lane * 4 : 0);
   // P operand: this thread's column is (head g >> 1, parity g & 1); the owner of p[token][head] is lane
   // 4 (token & 7) + 2 (token >> 3) + (head >> 1), half (head & 1) of its packed pair
-  const int src0 = 16 * (t & 1) + 2 * (t >> 1) + (g >> 2);            // token 4t; token 4t + i is 4 i lanes further
+  const int src0 = 4 * t + (g >> 2);                                  // token t; token 4 i + t: + 16 (i & 1) + 2 (i >> 1)
   const uint32_t psel = ((g >> 1) & 1) ? ((g & 1) ? 0x3244u : 0x4432u) : ((g & 1) ? 0x1044u : 0x4410u);
   const int rsrc = (lane & ~3) | (t >> 1);                             // a lane that tracks head t's running maximum
   const bool upper = t >= 2;                                           // keeps token g + 8 after the exchange
@@ -386,13 +390,13 @@ __global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_c
   const int tok_in_page = 16 * warp + g + (upper ? 8 : 0);
   const uint32_t k_thr = C::K_IDX + (16 * warp + g) * C::KIDXB + t * (C::KIDXB / 4);
   const uint32_t ks_thr = C::K_SCALE + 4 * tok_in_page;
-  const uint32_t v_chunk = C::V_IDX + (16 * warp + 4 * t) * C::VIDXB + g * (2 * VB);
+  const uint32_t v_chunk = C::V_IDX + (16 * warp + t) * C::VIDXB + g * (2 * VB);
   const uint32_t v_thr = v_chunk & ~3u;
   const uint32_t vs_thr = C::V_SCALE + 4 * tok_in_page;
   const bool v_odd = (v_chunk & 2u) != 0;
   const uint32_t vsel0 = v_odd ? 0x2345u : 0x0123u, vsel1 = v_odd ? 0x6744u : 0x4544u;
   const uint32_t stage_addr = smem_u32(stage0);
-  // pages 0 .. np-2 of the group are full; the last one is full unless the sequence ends inside it
+  // pages 0 .. np-2 of the CTA are full; the last one is full unless the sequence ends inside it
   const int last_valid = seq_len - (page_lo + np - 1) * G4_PT;          // >= 1
   const int n_full = last_valid >= G4_PT ? np : np - 1;
 
@@ -400,7 +404,7 @@ __global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_c
   uint32_t parity = 0;
   for (int i = 0; i < np; ++i) {
     if (tid == PRODUCER && i + G4_NS - 1 < np) {
-      issue(stage == 0 ? G4_NS - 1 : stage - 1, pg_ahead);            // stage of page i + 2 = stage of page i - 1
+      issue(stage == 0 ? G4_NS - 1 : stage - 1, pg_ahead);            // the stage the page before this one has left
       pg_ahead = bt[min(page_lo + i + G4_NS, P.max_pages - 1)];
     }
     if (!s_flags[0] && !mbar_wait_bounded(&bars[stage], parity)) s_flags[0] = 1;
@@ -416,13 +420,14 @@ __global__ void __launch_bounds__(G4_THREADS, 1) k_decode_attn_g4(const __grid_c
       g4_tile<KB, VB, true, SPARSE, NODEQ>(S, st, qf, lk_base, lv_base, k_thr, ks_thr, v_thr, vs_thr, vsel0, vsel1, src0, psel,
                                            rsrc, upper, t, tok_in_page, last_valid);
     }
-    group_sync(bar_id);  // every warp of the group is done with this stage before it is refilled
+    group_sync(bar_id);  // every warp is done with this stage before it is refilled
     if (++stage == G4_NS) {
       stage = 0;
       parity ^= 1u;
     }
   }
-
+  // from here on the workspace and the output are written
+  if (P.overlap && P.q_early) asm volatile("griddepcontrol.wait;" ::: "memory");
   // ---------------- merge the eight warps, write the split partial ----------------
 #pragma unroll
   for (int sh = 2; sh < 32; sh <<= 1) {
@@ -484,8 +489,8 @@ int launch_attn_g4(const AttnParams& P, const TqFast& fk, const TqFast& fv, cuda
   memcpy(av.s1, fv.s1, 16); memcpy(av.s2, fv.s2, 16); memcpy(av.cent16, fv.cent16, 32); av.alpha = fv.lut_alpha;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3((P.num_splits * P.hkv + G4_GROUPS - 1) / G4_GROUPS, P.batch);
-  cfg.blockDim = dim3(G4_THREADS);
+  cfg.gridDim = dim3(P.num_splits, P.hkv, P.batch);
+  cfg.blockDim = dim3(ATT_THREADS);
   cfg.dynamicSmemBytes = C::SMEM;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -505,6 +510,7 @@ bool layout_matches(const tq_cache_layout& L) {
 }
 
 }  // namespace
+
 
 bool tq_decode_g4_try(const tqatt::AttnParams& P, const TqFast& fk, const TqFast& fv, cudaStream_t st, int* rc) {
   const int kf = P.L.k_format, vf = P.L.v_format;

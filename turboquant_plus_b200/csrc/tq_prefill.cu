@@ -264,6 +264,7 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
            *o_done = bars + 10;
   uint32_t* tbase = reinterpret_cast<uint32_t*>(sm + SP::OFF_BAR + 96);
   volatile int* fail = reinterpret_cast<volatile int*>(sm + SP::OFF_BAR + 104);
+  uint32_t* vmax = reinterpret_cast<uint32_t*>(sm + SP::OFF_BAR + 112);   // per buffer: largest V scale of the page (bits)
   float* scales = reinterpret_cast<float*>(sm + SP::OFF_SC);
   uint8_t* ktile = sm + SP::OFF_KT;
   uint8_t* vtile = sm + SP::OFF_VT;
@@ -443,6 +444,10 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
       // The row maximum moves only when it grows by more than 2^PF2_SLACK (probabilities stay below 2^PF2_SLACK).
       // O lives in tensor memory and is being accumulated by the MMAs: a rescale waits for the product of the
       // page before, multiplies the row in place, and only then lets this page's product start (p_ready below).
+      // The reference follows score + log2(largest V scale of the page) rather than the score alone: P * (V scale)
+      // is stored as fp16, and with this reference it stays below 2^(2 PF2_SLACK) whatever the norms of the values
+      // are (a higher reference scales p, the row sum and O alike; the final division removes it).
+      mx += fmaxf(log2f(__uint_as_float(vmax[bf])), -100.0f);
       float resc = 1.0f;
       if (i == 0) {
         // the reference starts PF2_SLACK above the first page's maximum: a later page then moves it only when it
@@ -610,6 +615,7 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
       bool ok = !*fail;
       if (ok && i >= 2) ok = pf_wait(&o_done[bf], (uint32_t)(((i - 2) >> 1) & 1));
       if (ok) ok = pf_wait(&rec_full[bf], ph);
+      if (tid == 128) vmax[bf] = 0u;    // ordered before the maxima below by the producers' barrier that follows
       if (!producers_all(ok)) {  // the 128 producers go on or give up together (they share a named barrier below)
         *fail = 1;
         break;
@@ -617,7 +623,16 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
       const uint8_t* st = stage0 + (size_t)bf * rec;
       pf_dequant_token<KB>(st + P.L.k_idx_off + rtid * (16 * KB), ktile + bf * 32768 + tile_row, lk_base);
       scales[bf * 256 + rtid] = reinterpret_cast<const float*>(st + P.L.k_scale_off)[rtid];
-      scales[bf * 256 + 128 + rtid] = reinterpret_cast<const float*>(st + P.L.v_scale_off)[rtid];
+      {
+        // the page's largest V scale over the tokens that exist (scales are >= 0: their bit patterns order like
+        // integers); the row warps fold its logarithm into the softmax reference so that p * scale fits fp16
+        const float vsc = reinterpret_cast<const float*>(st + P.L.v_scale_off)[rtid];
+        scales[bf * 256 + 128 + rtid] = vsc;
+        float mv = (page_lo + i) * PT + rtid < kv_len ? vsc : 0.f;
+#pragma unroll
+        for (int sh = 1; sh < 32; sh <<= 1) mv = fmaxf(mv, __shfl_xor_sync(0xffffffffu, mv, sh));
+        if (lane == 0) atomicMax(&vmax[bf], __float_as_uint(mv));
+      }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       pf_arrive(&k_ready[bf]);
       pf_dequant_token<VB>(st + P.L.v_idx_off + rtid * (16 * VB), vtile + bf * 32768 + tile_row, lv_base);

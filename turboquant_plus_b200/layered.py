@@ -101,7 +101,9 @@ class LayeredKVCache:
                 # only an attention call that follows another layer's attention call may start early: that kernel
                 # writes nothing this one reads before its dependency wait.  The first call follows the append,
                 # which writes the cache page of the new token, so it is launched in stream order.
-                layer.attend(st["q"][i], st["bt"], st["len"], out=st["out"][i], workspace=ws, overlap=(i > 0))
+                # The queries of every layer are in place before the first launch of the step (they arrive with the
+                # step's host-to-device copy), so those calls may read them early as well.
+                layer.attend(st["q"][i], st["bt"], st["len"], out=st["out"][i], workspace=ws, overlap="q" if i > 0 else False)
 
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
