@@ -194,9 +194,12 @@ def test_polar_residual_fused(tq, g_polar):
     ri, rn, rr = o.polar_residual(x, q.rotation, q.centroids)
     rows = (idx == ri).all(axis=1)
     assert rows.mean() > 0.9 and np.allclose(nrm, rn, rtol=1e-6)
-    assert np.abs(res - rr)[rows].max() < 1e-12 * np.abs(x).max()
+    # norms are carried in fp32 (6e-8 relative): against the reference's residual, taken with its fp64 norm, that
+    # much of x_hat remains; against x - dequantize(indices, returned norms), the reference's definition, nothing
+    assert np.abs(res - rr)[rows].max() < 2e-7 * np.abs(x).max()
+    assert np.abs(res - (x - q.dequantize(idx, nrm))).max() < 1e-12 * np.abs(x).max()
     i1, n1, r1 = q.quantize_and_residual(x[2])
-    assert i1.shape == (D,) and np.shape(n1) == () and np.abs(r1 - rr[2]).max() < 1e-12 * np.abs(x).max()
+    assert i1.shape == (D,) and np.shape(n1) == () and np.abs(r1 - rr[2]).max() < 2e-7 * np.abs(x).max()
 
 
 def test_temporal_decay_golden(tq, g_decay):

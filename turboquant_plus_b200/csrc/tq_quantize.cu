@@ -474,8 +474,11 @@ __global__ void __launch_bounds__(128) k_quantize_dense(const TqDenseArgs a, con
     }
 #pragma unroll
     for (int v = 0; v < TV; ++v) {
-      // x_hat = x_hat_unit * norm (norm in the input's precision), residual = x - x_hat
-      const double res = xs[(size_t)j * TV + v] - acc[v] * (WIDE ? s_norm[v] : (double)s_normf[v]);
+      // x_hat = x_hat_unit * norm, residual = x - x_hat.  The norm is the one that is returned and stored (fp32):
+      // the residual is then exactly x - dequantize(indices, norms) for the norms the caller holds, which is how
+      // turboquant/polar_quant.py:121-132 defines it (for fp64 inputs the reference's own norm has 29 more bits;
+      // norms are carried in fp32 here, 6e-8 relative)
+      const double res = xs[(size_t)j * TV + v] - acc[v] * (double)s_normf[v];
       xs[(size_t)j * TV + v] = res;
       racc[v] += res * res;
       if (a.out_res && v < nv) a.out_res[(v0 + v) * a.ld_res + j] = res;
