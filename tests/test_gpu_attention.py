@@ -338,8 +338,14 @@ def test_overlap_launch_and_compressor_streaming_api(tq):
     out = comp.attend(q.float(), 1, torch.tensor([300]), bt).cpu().numpy()
     ref = oracle_attention(comp._layers[1], ks, vs, q.float().cpu().numpy(), [300])
     assert comp._layers[1].k_format == "prod3" and max_rel(out, ref) < TOL
-    with pytest.raises(Exception):      # prefill over PROD keys is not built: the error must surface
-        comp.prefill_attend(torch.zeros((1, 8, hq, D), device="cuda"), 0, torch.tensor([300]), bt)
+    # prefill over PROD keys (the reference's default K quantizer, turboquant/kv_cache.py:89-96): the chunk's queries
+    # go through the decode kernel, each with its causal length
+    qc = rng.standard_normal((1, 8, hq, D)).astype(np.float32)
+    pre = comp.prefill_attend(torch.as_tensor(qc).cuda(), 1, torch.tensor([300]), bt).cpu().numpy()
+    for i in (0, 3, 7):
+        ks_i, vs_i = [ks[0][:300 - 8 + i + 1]], [vs[0][:300 - 8 + i + 1]]
+        ref_i = oracle_attention(comp._layers[1], ks_i, vs_i, qc[:, i], [300 - 8 + i + 1])
+        assert max_rel(pre[:, i], ref_i) < TOL
 
 
 @pytest.mark.gpu

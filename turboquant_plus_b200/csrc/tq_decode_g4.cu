@@ -1,5 +1,6 @@
-// Decode attention, PolarQuant K and V, at most four query heads per KV head, 128-token pages: the shape of the
-// headline workload (Llama-3-8B: 32 query / 8 KV heads, turbo3 K and V).  Same pipeline and the same split /
+// Decode attention for at most four query heads per KV head on 128-token pages: the shape of the headline workload
+// (Llama-3-8B: 32 query / 8 KV heads, turbo3 K and V) and of the other decode configurations (q8_0 keys with turbo2
+// values, PROD keys -- PolarQuant + QJL sign sketch -- with turbo3 values).  Same pipeline and the same split /
 // ticket protocol as k_decode_attn (tq_attention.cu); what changes is how the 8 columns of the MMA tiles are
 // spent, and that everything the page loop needs is a compile-time constant:
 //   * S = K q^T: columns 0..3 carry the fp16 "hi" halves of the four query heads, columns 4..7 the "lo" halves,
@@ -13,22 +14,27 @@
 //   * page size (128 tokens = one 16-token tile per warp and page), pipeline depth (3 records) and every offset
 //     inside a record are template constants; record bytes are read through 32-bit shared-memory addresses with
 //     immediate offsets; only the last page of a sequence runs the variant that masks tokens past the end.
+//   * q8_0 operands are int8 -> fp16 by byte permute + one subtract (exact), the per-block scales applied to the
+//     partial scores of each 32-dim block in fp32 (keys) or to the operand pairs (values); the sign sketch of PROD
+//     keys becomes +-1 operands by one shift and one logic op per pair (dims d and d + 16 of a 32-bit word pair up,
+//     so that their bits land on the two fp16 sign positions together), against the S-projected query.
 #include "tq_attention.cuh"
 
 namespace {
 
 using namespace tqatt;
 
-// What the kernel needs of a quantizer, packed into 80 bytes so that the whole parameter block is six 64-byte
-// lines: parameters live in the constant bank, every line misses once per launch, and the misses of one warp
-// are serial.  The warps therefore touch one line each before anything else happens.
+// What the kernel needs of a quantizer, packed into 112 bytes so that the whole parameter block is a handful of
+// 64-byte lines: parameters live in the constant bank, every line misses once per launch, and the misses of one
+// warp are serial.  The warps therefore touch one line each before anything else happens.
 struct AttnQuant {
-  uint32_t s1[4], s2[4];
+  uint32_t s1[4], s2[4];   // rotation signs
+  uint32_t j1[4], j2[4];   // QJL sign-WHT signs (PROD keys)
   uint16_t cent16[16];
   float alpha;
   uint32_t pad[3];
 };
-static_assert(sizeof(AttnQuant) == 80, "AttnQuant layout");
+static_assert(sizeof(AttnQuant) == 112, "AttnQuant layout");
 
 constexpr int G4_HEADS = 4;
 constexpr int G4_HSTRIDE = TQ_D + 4;  // floats between heads in the warp-merge buffer: 16-byte stores stay conflict-free
@@ -44,22 +50,29 @@ constexpr int up128(int x) { return (x + 127) / 128 * 128; }
 
 
 // Record layout of a (page, head) for 128-token pages, as tq_cache_layout_init lays it out, and the carve-up of
-// the CTA's shared memory: the two pair tables, the query buffer, the mbarriers and flags, and the pipeline stages
+// the CTA's shared memory: the two pair tables, the query buffer(s), the mbarriers and flags, and the pipeline stages
 // (reused as the warp-merge buffer after the page loop).
-template <int KB, int VB> struct G4 {
-  static constexpr int KIDXB = 16 * KB, VIDXB = 16 * VB;  // index bytes per token
+// KK / VK: 2,3,4 = turbo bits; 8 = q8_0; 18,19,20 = PROD with 1,2,3 PolarQuant bits + sign sketch (keys only).
+template <int KK, int VK> struct G4 {
+  using KT = Kind<KK>;
+  using VT = Kind<VK>;
+  static constexpr int KB = KT::BITS, VB = VT::BITS;
+  static constexpr int KIDXB = KT::Q8 ? TQ_D : 16 * KB, VIDXB = VT::Q8 ? TQ_D : 16 * VB;  // index bytes per token
+  static constexpr int KSCB = KT::Q8 ? 8 : 4, VSCB = VT::Q8 ? 8 : 4;                      // scale bytes per token
   static constexpr int K_IDX = 0;
   static constexpr int K_SCALE = K_IDX + G4_PT * KIDXB;
-  static constexpr int V_IDX = K_SCALE + G4_PT * 4;
+  static constexpr int K_QJL = K_SCALE + G4_PT * KSCB;        // PROD keys: sign sketch, then residual scales
+  static constexpr int K_RSCALE = K_QJL + G4_PT * 16;
+  static constexpr int V_IDX = KT::PROD ? K_RSCALE + G4_PT * 4 : K_QJL;
   static constexpr int V_SCALE = V_IDX + G4_PT * VIDXB;
-  static constexpr int REC = V_SCALE + G4_PT * 4;
+  static constexpr int REC = V_SCALE + G4_PT * VSCB;
   static constexpr int LK = PairLut<KB>::BYTES, LV = PairLut<VB>::BYTES;
   static constexpr int ALIGN = (LK > LV ? LK : LV) > 512 ? (LK > LV ? LK : LV) : 512;  // largest table
   static constexpr int OFF_K = LK >= LV ? 0 : LV;   // the larger table first: each stays aligned to its own size
   static constexpr int OFF_V = LK >= LV ? LK : 0;
   static constexpr int OFF_GROUPS = up128(LK + LV);
-  static constexpr int G_Q = 0;                                   // float [4 heads][128]
-  static constexpr int G_BAR = G_Q + G4_HEADS * TQ_D * 4;         // 3 mbarriers, then two flag words at + 64
+  static constexpr int G_Q = 0;                                   // float [4 heads][128] (PROD: + the projected queries)
+  static constexpr int G_BAR = G_Q + (KT::PROD ? 2 : 1) * G4_HEADS * TQ_D * 4;   // 3 mbarriers, two flag words at + 64
   static constexpr int G_STAGE = G_BAR + 128;
   static constexpr int MERGE = ATT_WARPS * G4_HEADS * (G4_HSTRIDE + 2) * 4;
   static constexpr int GROUP_BYTES = up128(G_STAGE + (G4_NS * REC > MERGE ? G4_NS * REC : MERGE));
@@ -72,6 +85,11 @@ template <int KB, int VB> struct G4 {
 template <int OFF> __device__ __forceinline__ uint32_t lds_u32(uint32_t a) {
   uint32_t v;
   asm("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(a), "n"(OFF));
+  return v;
+}
+template <int OFF> __device__ __forceinline__ uint32_t lds_u16(uint32_t a) {
+  uint16_t v;
+  asm("ld.shared.u16 %0, [%1+%2];" : "=h"(v) : "r"(a), "n"(OFF));
   return v;
 }
 template <int OFF> __device__ __forceinline__ float lds_f32(uint32_t a) {
@@ -93,7 +111,9 @@ template <int OFF> __device__ __forceinline__ uint4 lds_u128(uint32_t a) {
 // One row chunk of K indices (a thread's 32 dims of one token: 4 KB bytes at a 4 KB-byte-aligned address) as
 // big-endian words: word k holds stream bits 32 k .. 32 k + 31, first bit in the most significant position.
 template <int KB, int OFF> __device__ __forceinline__ void load_k_words(uint32_t a, uint32_t (&w)[KB]) {
-  if constexpr (KB == 2) {
+  if constexpr (KB == 1) {
+    w[0] = __byte_perm(lds_u32<OFF>(a), 0, 0x0123);
+  } else if constexpr (KB == 2) {
     const uint2 v = lds_u64<OFF>(a);
     w[0] = __byte_perm(v.x, 0, 0x0123);
     w[1] = __byte_perm(v.y, 0, 0x0123);
@@ -135,25 +155,69 @@ struct G4State {
   float m0, m1, l0, l1;
 };
 
-// One 16-token tile of one warp: scores against the four query heads, online softmax, O^T += V^T P^T.
-//   st      shared-memory address of the page record
-//   MASKED  the page may end inside or before this tile (`valid` tokens of the page exist)
-//   NODEQ   measurement variant: the table lookups are left out and the packed words themselves are fed to the
-//           tensor cores (copies, barriers, MMAs, softmax and merges as in the real kernel; results meaningless)
-template <int KB, int VB, bool MASKED, bool SPARSE, bool NODEQ>
-__device__ __forceinline__ void g4_tile(G4State& S, uint32_t st, const uint32_t (&qf)[8][2], uint32_t lk_base, uint32_t lv_base,
-                                        uint32_t k_thr, uint32_t ks_thr, uint32_t v_thr, uint32_t vs_thr, uint32_t vsel0,
-                                        uint32_t vsel1, int src0, uint32_t psel, int rsrc, bool upper, int t, int tok_in_page,
-                                        int valid) {
-  using C = G4<KB, VB>;
-  constexpr float MAX_SLACK = 4.0f;
-  // ---------------- S = K_tile (16 tokens x 128) . [q_hi | q_lo] ----------------
-  const float ks = lds_f32<0>(st + ks_thr);
-  float s[4] = {0.f, 0.f, 0.f, 0.f};
-  {
+// What a thread needs to find its part of a page record: byte offsets inside the record of the data of its warp's
+// tile (tokens 16 warp .. + 15), and the lane roles of the two exchanges.
+struct G4Thr {
+  uint32_t k_thr;    // K indices (or int8 values) of row g: its 32 dims (q8_0: its 8 dims of block 0)
+  uint32_t ks_thr;   // K scale of the token this thread keeps after the exchange (PROD, q8_0: of row g)
+  uint32_t z_thr;    // PROD: sign-sketch word of row g; residual scales follow at rs_thr
+  uint32_t rs_thr;
+  uint32_t v_thr;    // V indices of token t, dims 16 g .. (rounded down to 4 bytes; q8_0: the 16 int8 values)
+  uint32_t vs_thr;   // V scale of the kept token (q8_0: fp16 scale of token t, block g >> 1)
+  uint32_t vsel0, vsel1;
+  uint32_t psel;
+  int src0, rsrc;
+  bool upper;
+  int t, tok_in_page, vtok_in_page;
+};
+
+__device__ __forceinline__ uint32_t s8x2_to_h2(uint32_t biased, uint32_t sel) {
+  // two int8 values, stored as value ^ 0x80 = value + 128, as exact fp16: (b | 0x6400) is 1024 + b; subtract 1152
+  return hsub2_u32(__byte_perm(biased, 0x64646464u, sel), 0x64806480u);
+}
+
+// Scores of one 16-token tile against the four heads (hi halves in columns 0-3, lo halves in 4-7), per thread the
+// MMA accumulator fragment (rows g and g + 8, columns 2t and 2t + 1).  LUT keys return raw sums (the caller applies
+// the K scale of the row it keeps); q8_0 and PROD keys return finished scores of both rows.
+template <int KK, int VK, bool NODEQ>
+__device__ __forceinline__ void g4_scores(float (&s)[4], uint32_t st, const G4Thr& T, const uint32_t (&qf)[8][2],
+                                          const uint32_t (&qp)[Kind<KK>::PROD ? 8 : 1][2], uint32_t lk_base) {
+  using C = G4<KK, VK>;
+  using KT = Kind<KK>;
+  constexpr int KB = KT::BITS;
+  s[0] = s[1] = s[2] = s[3] = 0.f;
+  if constexpr (KT::Q8) {
+    // a 32-value block has one scale: k-steps 2b and 2b+1 cover block b (this thread supplies its dims 8t .. 8t+7 of
+    // the block), and the block's partial scores are scaled in fp32 -- the operands carry no rounding
+    const uint2 sc0 = lds_u64<0>(st + T.ks_thr), sc1 = lds_u64<8 * C::KSCB>(st + T.ks_thr);
+    const uint32_t scw0[2] = {sc0.x, sc0.y}, scw1[2] = {sc1.x, sc1.y};
+#pragma unroll
+    for (int blk = 0; blk < 4; ++blk) {
+      uint2 u0, u1;
+      if (blk == 0) { u0 = lds_u64<0>(st + T.k_thr); u1 = lds_u64<8 * TQ_D>(st + T.k_thr); }
+      if (blk == 1) { u0 = lds_u64<32>(st + T.k_thr); u1 = lds_u64<8 * TQ_D + 32>(st + T.k_thr); }
+      if (blk == 2) { u0 = lds_u64<64>(st + T.k_thr); u1 = lds_u64<8 * TQ_D + 64>(st + T.k_thr); }
+      if (blk == 3) { u0 = lds_u64<96>(st + T.k_thr); u1 = lds_u64<8 * TQ_D + 96>(st + T.k_thr); }
+      const uint32_t x0[2] = {u0.x ^ 0x80808080u, u0.y ^ 0x80808080u};
+      const uint32_t x1[2] = {u1.x ^ 0x80808080u, u1.y ^ 0x80808080u};
+      float sb[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        const int j = 2 * blk + h2;
+        mma16816(sb, s8x2_to_h2(x0[h2], 0x4140), s8x2_to_h2(x1[h2], 0x4140), s8x2_to_h2(x0[h2], 0x4342),
+                 s8x2_to_h2(x1[h2], 0x4342), qf[j][0], qf[j][1]);
+      }
+      const __half2 hs0 = *reinterpret_cast<const __half2*>(&scw0[blk >> 1]);
+      const __half2 hs1 = *reinterpret_cast<const __half2*>(&scw1[blk >> 1]);
+      const float f0 = (blk & 1) ? __high2float(hs0) : __low2float(hs0);
+      const float f1 = (blk & 1) ? __high2float(hs1) : __low2float(hs1);
+      s[0] = fmaf(sb[0], f0, s[0]); s[1] = fmaf(sb[1], f0, s[1]);
+      s[2] = fmaf(sb[2], f1, s[2]); s[3] = fmaf(sb[3], f1, s[3]);
+    }
+  } else {
     uint32_t w0[KB], w1[KB];
-    load_k_words<KB, 0>(st + k_thr, w0);
-    load_k_words<KB, 8 * C::KIDXB>(st + k_thr, w1);
+    load_k_words<KB, 0>(st + T.k_thr, w0);
+    load_k_words<KB, 8 * C::KIDXB>(st + T.k_thr, w1);
     constexpr int SH = PairLut<KB>::SHIFT;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -168,16 +232,78 @@ __device__ __forceinline__ void g4_tile(G4State& S, uint32_t st, const uint32_t 
       }
       mma16816(s, a0, a1, a2, a3, qf[j][0], qf[j][1]);
     }
+    if constexpr (KT::PROD) {
+      // + sqrt(pi/2)/sqrt(d) * ||r|| * <S q, z>: the sign sketch as +-1 operands.  Word t of a row holds its 32 dims
+      // 32t .. 32t+31, first dim in the most significant bit; dims i and i + 16 form a pair, so that after a shift by
+      // i their bits sit on the sign positions of the two fp16 halves (bit set = +1).
+      const uint32_t z0 = __byte_perm(lds_u32<0>(st + T.z_thr), 0, 0x0123);
+      const uint32_t z1 = __byte_perm(lds_u32<8 * 16>(st + T.z_thr), 0, 0x0123);
+      float s2[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t a0 = (~(z0 << (2 * j)) & 0x80008000u) | 0x3C003C00u;
+        const uint32_t a1 = (~(z1 << (2 * j)) & 0x80008000u) | 0x3C003C00u;
+        const uint32_t a2 = (~(z0 << (2 * j + 1)) & 0x80008000u) | 0x3C003C00u;
+        const uint32_t a3 = (~(z1 << (2 * j + 1)) & 0x80008000u) | 0x3C003C00u;
+        mma16816(s2, a0, a1, a2, a3, qp[j][0], qp[j][1]);
+      }
+      const float k0 = lds_f32<0>(st + T.ks_thr), k1 = lds_f32<32>(st + T.ks_thr);
+      const float r0 = lds_f32<0>(st + T.rs_thr), r1 = lds_f32<32>(st + T.rs_thr);
+      s[0] = fmaf(s2[0], r0, s[0] * k0); s[1] = fmaf(s2[1], r0, s[1] * k0);
+      s[2] = fmaf(s2[2], r1, s[2] * k1); s[3] = fmaf(s2[3], r1, s[3] * k1);
+    }
   }
+}
+
+// One 16-token tile of one warp: scores against the four query heads, online softmax, O^T += V^T P^T.
+//   st      shared-memory address of the page record
+//   MASKED  the page may end inside or before this tile (`valid` tokens of the page exist)
+//   NODEQ   measurement variant: the table lookups are left out and the packed words themselves are fed to the
+//           tensor cores (copies, barriers, MMAs, softmax and merges as in the real kernel; results meaningless)
+template <int KK, int VK, bool MASKED, bool SPARSE, bool NODEQ>
+__device__ __forceinline__ void g4_tile(G4State& S, uint32_t st, const G4Thr& T, const uint32_t (&qf)[8][2],
+                                        const uint32_t (&qp)[Kind<KK>::PROD ? 8 : 1][2], uint32_t lk_base, uint32_t lv_base,
+                                        int valid) {
+  using C = G4<KK, VK>;
+  using KT = Kind<KK>;
+  using VT = Kind<VK>;
+  constexpr int VB = VT::BITS;
+  constexpr bool K_LUT = !KT::Q8 && !KT::PROD;   // raw sums, one scale per row
+  constexpr float MAX_SLACK = 4.0f;
+  const int t = T.t;
+  // ---------------- S = K_tile (16 tokens x 128) . [q_hi | q_lo] ----------------
+  float ks = 1.0f;
+  if constexpr (K_LUT) ks = lds_f32<0>(st + T.ks_thr);
+  float s[4];
+  g4_scores<KK, VK, NODEQ>(s, st, T, qf, qp, lk_base);
   // the V words and scale of this tile are fetched here, ahead of the softmax arithmetic that separates them from
   // their use: the loads then wait under it instead of in front of the table lookups
-  uint32_t vw[4][2];
-  load_v_words<VB, 0>(st + v_thr, vsel0, vsel1, vw[0]);
-  load_v_words<VB, 4 * C::VIDXB>(st + v_thr, vsel0, vsel1, vw[1]);
-  load_v_words<VB, 8 * C::VIDXB>(st + v_thr, vsel0, vsel1, vw[2]);
-  load_v_words<VB, 12 * C::VIDXB>(st + v_thr, vsel0, vsel1, vw[3]);
-  const float vs_raw = lds_f32<0>(st + vs_thr);
+  uint32_t vw[4][VT::Q8 ? 4 : 2];
+  uint32_t vsc16[4];   // q8_0 values: fp16 block scale of the thread's four tokens, both halves alike
+  float vs_raw = 1.0f;
+  if constexpr (VT::Q8) {
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) {
+      uint4 v;
+      uint32_t sc;
+      if (q4 == 0) { v = lds_u128<0>(st + T.v_thr); sc = lds_u16<0>(st + T.vs_thr); }
+      if (q4 == 1) { v = lds_u128<4 * TQ_D>(st + T.v_thr); sc = lds_u16<4 * C::VSCB>(st + T.vs_thr); }
+      if (q4 == 2) { v = lds_u128<8 * TQ_D>(st + T.v_thr); sc = lds_u16<8 * C::VSCB>(st + T.vs_thr); }
+      if (q4 == 3) { v = lds_u128<12 * TQ_D>(st + T.v_thr); sc = lds_u16<12 * C::VSCB>(st + T.vs_thr); }
+      vw[q4][0] = v.x ^ 0x80808080u; vw[q4][1] = v.y ^ 0x80808080u;
+      vw[q4][2] = v.z ^ 0x80808080u; vw[q4][3] = v.w ^ 0x80808080u;
+      if constexpr (MASKED) sc = (T.vtok_in_page + 4 * q4 < valid) ? sc : 0u;   // a stale scale must not meet p = 0
+      vsc16[q4] = __byte_perm(sc, 0, 0x1010);
+    }
+  } else {
+    load_v_words<VB, 0>(st + T.v_thr, T.vsel0, T.vsel1, vw[0]);
+    load_v_words<VB, 4 * C::VIDXB>(st + T.v_thr, T.vsel0, T.vsel1, vw[1]);
+    load_v_words<VB, 8 * C::VIDXB>(st + T.v_thr, T.vsel0, T.vsel1, vw[2]);
+    load_v_words<VB, 12 * C::VIDXB>(st + T.v_thr, T.vsel0, T.vsel1, vw[3]);
+    vs_raw = lds_f32<0>(st + T.vs_thr);
+  }
   // hi + lo: the partner lane (t ^ 2) holds the other half of the same heads
+  const bool upper = T.upper;
   const float give0 = upper ? s[0] : s[2], give1 = upper ? s[1] : s[3];
   const float keep0 = upper ? s[2] : s[0], keep1 = upper ? s[3] : s[1];
   const float sum0 = keep0 + __shfl_xor_sync(0xffffffffu, give0, 2);
@@ -192,12 +318,12 @@ __device__ __forceinline__ void g4_tile(G4State& S, uint32_t st, const uint32_t 
   float vs = vs_raw;
   float d0 = fmaf(sum0, ks, -S.m0), d1 = fmaf(sum1, ks, -S.m1);   // score - running reference
   if constexpr (MASKED) {
-    ok = tok_in_page < valid;
+    ok = T.tok_in_page < valid;
     vs = ok ? vs_raw : 0.f;                                       // a stale scale must not meet p = 0
     d0 = ok ? d0 : -INFINITY;
     d1 = ok ? d1 : -INFINITY;
   }
-  const float lvs = fmaxf(fast_log2(vs), -100.0f);                // zero vectors have scale 0
+  const float lvs = VT::Q8 ? 0.f : fmaxf(fast_log2(vs), -100.0f);  // zero vectors have scale 0
   if (__any_sync(0xffffffffu, (d0 + lvs > MAX_SLACK) || (d1 + lvs > MAX_SLACK))) {
     float sc0 = sum0 * ks, sc1 = sum1 * ks;
     if constexpr (MASKED) {
@@ -218,7 +344,7 @@ __device__ __forceinline__ void g4_tile(G4State& S, uint32_t st, const uint32_t 
     S.l1 *= r1;
     d0 = sc0 - mn0;
     d1 = sc1 - mn1;
-    const float ra = __shfl_sync(0xffffffffu, r0, rsrc), rb = __shfl_sync(0xffffffffu, r1, rsrc);
+    const float ra = __shfl_sync(0xffffffffu, r0, T.rsrc), rb = __shfl_sync(0xffffffffu, r1, T.rsrc);
     const float r = (t & 1) ? rb : ra;                        // O of this thread belongs to head t
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -235,7 +361,7 @@ __device__ __forceinline__ void g4_tile(G4State& S, uint32_t st, const uint32_t 
   uint32_t pb[4];
 #pragma unroll
   for (int q4 = 0; q4 < 4; ++q4)
-    pb[q4] = __byte_perm(__shfl_sync(0xffffffffu, hp, src0 + 16 * (q4 & 1) + 2 * (q4 >> 1)), 0, psel);
+    pb[q4] = __byte_perm(__shfl_sync(0xffffffffu, hp, T.src0 + 16 * (q4 & 1) + 2 * (q4 >> 1)), 0, T.psel);
   // ---------------- O^T += V_tile^T . P^T : tokens t, t+4, t+8, t+12 of the tile, dims 16g .. 16g+15 ----------------
   // (neighbouring lanes read neighbouring token rows: rows are 16 VB bytes apart, which spreads a quad of lanes over
   // the shared-memory banks; a stride of four rows put lanes t and t+2 on the same banks)
@@ -249,21 +375,28 @@ __device__ __forceinline__ void g4_tile(G4State& S, uint32_t st, const uint32_t 
     for (int q2 = 0; q2 < 2; ++q2) {
 #pragma unroll
       for (int jj = 0; jj < 8; ++jj) {
-        if constexpr (NODEQ) h[q2][jj] = vw[2 * u + q2][jj & 1] ^ (uint32_t)jj;
-        else h[q2][jj] = lds32(field_off<2 * VB, SHV, 2>(vw[2 * u + q2], jj) | lv_base);
+        if constexpr (VT::Q8) {
+          h[q2][jj] = hmul2_u32(s8x2_to_h2(vw[2 * u + q2][jj >> 1], (jj & 1) ? 0x4342 : 0x4140), vsc16[2 * u + q2]);
+        } else if constexpr (NODEQ) {
+          h[q2][jj] = vw[2 * u + q2][jj & 1] ^ (uint32_t)jj;
+        } else {
+          h[q2][jj] = lds32(field_off<2 * VB, SHV, 2>(vw[2 * u + q2], jj) | lv_base);
+        }
       }
     }
 #pragma unroll
     for (int blk = 0; blk < 4; ++blk)
       mma16816(S.o[blk], h[0][2 * blk], h[0][2 * blk + 1], h[1][2 * blk], h[1][2 * blk + 1], pb[2 * u], pb[2 * u + 1]);
   }
-
 }
 
-template <int KB, int VB, bool SPARSE, bool NODEQ>
+template <int KK, int VK, bool SPARSE, bool NODEQ>
 __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_constant__ AttnParams P, const __grid_constant__ AttnQuant fk,
                                                                     const __grid_constant__ AttnQuant fv) {
-  using C = G4<KB, VB>;
+  using C = G4<KK, VK>;
+  using KT = Kind<KK>;
+  using VT = Kind<VK>;
+  constexpr int KB = KT::BITS, VB = VT::BITS;
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
@@ -272,7 +405,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_
     const uint32_t* pp = reinterpret_cast<const uint32_t*>(&P);
     uint32_t touch;
     if (warp < 4) touch = pp[min(16 * warp, (int)(sizeof(AttnParams) / 4) - 1)];
-    else if (warp < 6) touch = warp == 4 ? fk.s1[0] : fk.pad[2];
+    else if (warp < 6) touch = warp == 4 ? fk.s1[0] : fk.pad[2];   // first and last word of the 112-byte blocks
     else touch = warp == 6 ? fv.s1[0] : fv.pad[2];
     asm volatile("" ::"r"(touch));
   }
@@ -312,7 +445,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_
   const int n_pages = (seq_len + G4_PT - 1) / G4_PT;
   const int np = min(n_pages, page_lo + P.chunk_pages) - page_lo;   // pages of this CTA (<= 0: none)
   int pg_ahead = 0;  // producer: block-table entry of the page issued in the next iteration
-  float x[4] = {0.f, 0.f, 0.f, 0.f};
+  float x[4] = {0.f, 0.f, 0.f, 0.f}, y[4] = {0.f, 0.f, 0.f, 0.f};
   if (tid == PRODUCER) {
     int pg_next[G4_NS];
 #pragma unroll
@@ -328,25 +461,37 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_
     pg_ahead = pg_next[G4_NS - 1];
   } else if (warp < P.group) {
     if (P.overlap && !P.q_early) asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (P.k_pre) load_q4(P.qrot, TQ_F32, (row0 + warp) * TQ_D + 4 * lane, x);
-    else load_q4(P.q, P.q_dtype, (row0 + warp) * TQ_D + 4 * lane, x);
-    if (!P.k_pre) {
-      warp_wht128(x, fk.s1, fk.s2, lane);
+    if (P.k_pre) {   // dense rotations: rotated (and, for PROD keys, projected) queries come from k_prepare_queries
+      load_q4(P.qrot, TQ_F32, (row0 + warp) * TQ_D + 4 * lane, x);
+      if constexpr (KT::PROD) load_q4(P.qproj, TQ_F32, (row0 + warp) * TQ_D + 4 * lane, y);
+    } else {
+      load_q4(P.q, P.q_dtype, (row0 + warp) * TQ_D + 4 * lane, x);
+      if constexpr (KT::PROD) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) y[k] = x[k];
+        warp_wht128(y, fk.j1, fk.j2, lane);
+      }
+      if (!KT::Q8) warp_wht128(x, fk.s1, fk.s2, lane);   // q8_0 tensors are stored unrotated
       const float sk = P.qscale / fk.alpha;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) x[k] *= sk;
+      for (int k = 0; k < 4; ++k) {
+        x[k] *= sk;
+        y[k] *= P.qscale;
+      }
     }
     // 16-byte chunk c = 8 t + j of head h sits at 8 t + (j ^ (t + 4 (h & 1))): the fragment reads below (fixed j,
     // all t and h) then touch every bank group instead of one
     const int tq = lane >> 3, jq = lane & 7;
     *reinterpret_cast<float4*>(qbuf + warp * TQ_D + 4 * (8 * tq + (jq ^ (tq + 4 * (warp & 1))))) =
         make_float4(x[0], x[1], x[2], x[3]);
+    if constexpr (KT::PROD)   // projected queries: plain rows behind the rotated ones
+      *reinterpret_cast<float4*>(qbuf + (G4_HEADS + warp) * TQ_D + 4 * lane) = make_float4(y[0], y[1], y[2], y[3]);
   }
   __syncwarp();
   if (warp >= P.group) {
     const int fh = ATT_THREADS - 32 * P.group;   // table-filling threads
-    lut_fill<KB>(sm + C::OFF_K, fk.cent16, tid - 32 * P.group, fh);
-    lut_fill<VB>(sm + C::OFF_V, fv.cent16, tid - 32 * P.group, fh);
+    if constexpr (KB > 0) lut_fill<KB>(sm + C::OFF_K, fk.cent16, tid - 32 * P.group, fh);
+    if constexpr (VB > 0) lut_fill<VB>(sm + C::OFF_V, fv.cent16, tid - 32 * P.group, fh);
   }
   if (P.overlap && !P.q_early) asm volatile("griddepcontrol.wait;" ::: "memory");   // the query warps already have
   if (n_pages == 0 && split == 0) {  // empty sequence: zeros (split 0 exists for every kv head)
@@ -359,19 +504,35 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_
   if (np <= 0) return;           // this CTA has no pages (its split lies beyond the sequence)
 
   // B operand of S = K q^T: column g is head g & 3, hi half for g < 4, lo half otherwise
-  uint32_t qf[8][2];
+  uint32_t qf[8][2], qp[KT::PROD ? 8 : 1][2];
   {
     const int head = g & 3;
     const bool hv = head < P.group, lo = g >= 4;
-    const float* qp = qbuf + (hv ? head : 0) * TQ_D + 32 * t;
+    const float* qh = qbuf + (hv ? head : 0) * TQ_D;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      float4 v = hv ? *reinterpret_cast<const float4*>(qp + 4 * (j ^ (t + 4 * (head & 1)))) : make_float4(0.f, 0.f, 0.f, 0.f);
+      // dims this thread supplies in k-step j: 32t + 4j .. +3 (packed formats), or, for q8_0 keys, its 8 dims of
+      // block j/2: 32(j/2) + 8t + 4(j%2) .. +3; as the 16-byte chunk (row, col) of the staged query
+      const int crow = KT::Q8 ? (j >> 1) : t, ccol = KT::Q8 ? 2 * t + (j & 1) : j;
+      float4 v = hv ? *reinterpret_cast<const float4*>(qh + 4 * (8 * crow + (ccol ^ (crow + 4 * (head & 1)))))
+                    : make_float4(0.f, 0.f, 0.f, 0.f);
       const __half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
       const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
       qf[j][0] = lo ? pack_h2(v.x - f0.x, v.y - f0.y) : *reinterpret_cast<const uint32_t*>(&h0);
       qf[j][1] = lo ? pack_h2(v.z - f1.x, v.w - f1.y) : *reinterpret_cast<const uint32_t*>(&h1);
+      if constexpr (KT::PROD) {
+        // sign-sketch operands pair dims i and i + 16 of the thread's 32 (i = 2j for the first register of the
+        // k-step, 2j + 1 for the second), dim i + 16 in the low half
+        const float* ph = qh + G4_HEADS * TQ_D + 32 * t;
+        const float a0 = hv ? ph[16 + 2 * j] : 0.f, a1 = hv ? ph[2 * j] : 0.f;
+        const float b0 = hv ? ph[16 + 2 * j + 1] : 0.f, b1 = hv ? ph[2 * j + 1] : 0.f;
+        const __half2 e0 = __floats2half2_rn(a0, a1), e1 = __floats2half2_rn(b0, b1);
+        const float2 r0 = __half22float2(e0), r1 = __half22float2(e1);
+        qp[j][0] = lo ? pack_h2(a0 - r0.x, a1 - r0.y) : *reinterpret_cast<const uint32_t*>(&e0);
+        qp[j][1] = lo ? pack_h2(b0 - r1.x, b1 - r1.y) : *reinterpret_cast<const uint32_t*>(&e1);
+      }
     }
+    if constexpr (!KT::PROD) qp[0][0] = qp[0][1] = 0u;
   }
   const uint32_t lk_base = smem_u32(sm + C::OFF_K) + (PairLut<KB>::REPL ? lane * 4 : 0);
   const uint32_t lv_base = smem_u32(sm + C::OFF_V) + (PairLut<VB>::REPL ? lane * 4 : 0);
@@ -389,14 +550,26 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_
   S.l0 = S.l1 = 0.f;
 
   // byte offsets inside a page record of what this thread reads in its warp's tile (tokens 16 warp .. + 15)
-  const int tok_in_page = 16 * warp + g + (upper ? 8 : 0);
-  const uint32_t k_thr = C::K_IDX + (16 * warp + g) * C::KIDXB + t * (C::KIDXB / 4);
-  const uint32_t ks_thr = C::K_SCALE + 4 * tok_in_page;
-  const uint32_t v_chunk = C::V_IDX + (16 * warp + t) * C::VIDXB + g * (2 * VB);
-  const uint32_t v_thr = v_chunk & ~3u;
-  const uint32_t vs_thr = C::V_SCALE + 4 * tok_in_page;
+  G4Thr T;
+  T.t = t;
+  T.upper = upper;
+  T.src0 = src0;
+  T.rsrc = rsrc;
+  T.psel = psel;
+  T.tok_in_page = 16 * warp + g + (upper ? 8 : 0);
+  T.vtok_in_page = 16 * warp + t;
+  T.k_thr = C::K_IDX + (16 * warp + g) * C::KIDXB + (KT::Q8 ? 8 * t : t * (C::KIDXB / 4));
+  // the row this thread keeps (packed keys: the scale is applied after the exchange), or row g (q8_0 and PROD keys
+  // finish the scores of both rows before the exchange)
+  T.ks_thr = C::K_SCALE + C::KSCB * ((KT::Q8 || KT::PROD) ? 16 * warp + g : T.tok_in_page);
+  T.z_thr = C::K_QJL + (16 * warp + g) * 16 + 4 * t;
+  T.rs_thr = C::K_RSCALE + 4 * (16 * warp + g);
+  const uint32_t v_chunk = C::V_IDX + (16 * warp + t) * C::VIDXB + g * (VT::Q8 ? 16 : 2 * VB);
+  T.v_thr = v_chunk & ~3u;
+  T.vs_thr = VT::Q8 ? C::V_SCALE + (16 * warp + t) * C::VSCB + 2 * (g >> 1) : C::V_SCALE + 4 * T.tok_in_page;
   const bool v_odd = (v_chunk & 2u) != 0;
-  const uint32_t vsel0 = v_odd ? 0x2345u : 0x0123u, vsel1 = v_odd ? 0x6744u : 0x4544u;
+  T.vsel0 = v_odd ? 0x2345u : 0x0123u;
+  T.vsel1 = v_odd ? 0x6744u : 0x4544u;
   const uint32_t stage_addr = smem_u32(stage0);
   // pages 0 .. np-2 of the CTA are full; the last one is full unless the sequence ends inside it
   const int last_valid = seq_len - (page_lo + np - 1) * G4_PT;          // >= 1
@@ -416,11 +589,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_
     asm volatile("mov.u32 %0, 0;" : "=r"(dep)::"memory");
     const uint32_t st = stage_addr + stage * C::REC + dep;
     if (i < n_full) {
-      g4_tile<KB, VB, false, SPARSE, NODEQ>(S, st, qf, lk_base, lv_base, k_thr, ks_thr, v_thr, vs_thr, vsel0, vsel1, src0, psel,
-                                            rsrc, upper, t, tok_in_page, G4_PT);
+      g4_tile<KK, VK, false, SPARSE, NODEQ>(S, st, T, qf, qp, lk_base, lv_base, G4_PT);
     } else if (16 * warp < last_valid) {
-      g4_tile<KB, VB, true, SPARSE, NODEQ>(S, st, qf, lk_base, lv_base, k_thr, ks_thr, v_thr, vs_thr, vsel0, vsel1, src0, psel,
-                                           rsrc, upper, t, tok_in_page, last_valid);
+      g4_tile<KK, VK, true, SPARSE, NODEQ>(S, st, T, qf, qp, lk_base, lv_base, last_valid);
     }
     group_sync(bar_id);  // every warp is done with this stage before it is refilled
     if (++stage == G4_NS) {
@@ -470,24 +641,25 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_
       if (dim == 0) *reinterpret_cast<float2*>(P.part_ml + slot * 2) = make_float2(M, Lsum);
     }
   }
-  finish_splits<false>(P, fv.s1, fv.s2, fv.alpha, qbuf, stage0, s_flags, row0, ns, b, kvh, tid, bar_id);
+  finish_splits<VT::Q8>(P, fv.s1, fv.s2, fv.alpha, qbuf, stage0, s_flags, row0, ns, b, kvh, tid, bar_id);
 }
 
-template <int KB, int VB, bool SPARSE, bool NODEQ>
+template <int KK, int VK, bool SPARSE, bool NODEQ>
 int launch_attn_g4(const AttnParams& P, const TqFast& fk, const TqFast& fv, cudaStream_t st) {
-  using C = G4<KB, VB>;
-  static_assert(C::SMEM <= 227 * 1024, "shared-memory plan of the specialised decode kernel");
+  using C = G4<KK, VK>;
+  static_assert(2 * (C::SMEM + 1024) <= 228 * 1024, "two CTAs of the specialised decode kernel per SM");
   static thread_local int configured_dev = -1;  // per instantiation
   int dev = 0;
   TQ_CUDA(cudaGetDevice(&dev));
   if (configured_dev != dev) {
-    TQ_CUDA(cudaFuncSetAttribute(k_decode_attn_g4<KB, VB, SPARSE, NODEQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+    TQ_CUDA(cudaFuncSetAttribute(k_decode_attn_g4<KK, VK, SPARSE, NODEQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
     configured_dev = dev;
   }
   AttnQuant ak, av;
   memset(&ak, 0, sizeof(ak));
   memset(&av, 0, sizeof(av));
-  memcpy(ak.s1, fk.s1, 16); memcpy(ak.s2, fk.s2, 16); memcpy(ak.cent16, fk.cent16, 32); ak.alpha = fk.lut_alpha;
+  memcpy(ak.s1, fk.s1, 16); memcpy(ak.s2, fk.s2, 16); memcpy(ak.j1, fk.j1, 16); memcpy(ak.j2, fk.j2, 16);
+  memcpy(ak.cent16, fk.cent16, 32); ak.alpha = fk.lut_alpha;
   memcpy(av.s1, fv.s1, 16); memcpy(av.s2, fv.s2, 16); memcpy(av.cent16, fv.cent16, 32); av.alpha = fv.lut_alpha;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -500,32 +672,44 @@ int launch_attn_g4(const AttnParams& P, const TqFast& fk, const TqFast& fv, cuda
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = P.overlap ? 1 : 0;
-  TQ_CUDA(cudaLaunchKernelEx(&cfg, k_decode_attn_g4<KB, VB, SPARSE, NODEQ>, P, ak, av));
+  TQ_CUDA(cudaLaunchKernelEx(&cfg, k_decode_attn_g4<KK, VK, SPARSE, NODEQ>, P, ak, av));
   return tq_launch_check("k_decode_attn_g4");
 }
 
-template <int KB, int VB>
+template <int KK, int VK>
 bool layout_matches(const tq_cache_layout& L) {
-  using C = G4<KB, VB>;
+  using C = G4<KK, VK>;
+  if (Kind<KK>::PROD && (L.k_qjl_off != C::K_QJL || L.k_rscale_off != C::K_RSCALE)) return false;
   return L.page_tokens == G4_PT && L.k_idx_off == C::K_IDX && L.k_scale_off == C::K_SCALE && L.v_idx_off == C::V_IDX &&
          L.v_scale_off == C::V_SCALE && L.record_bytes == C::REC && L.k_idx_bytes == C::KIDXB && L.v_idx_bytes == C::VIDXB;
 }
 
 }  // namespace
 
-
 bool tq_decode_g4_try(const tqatt::AttnParams& P, const TqFast& fk, const TqFast& fv, cudaStream_t st, int* rc) {
   const int kf = P.L.k_format, vf = P.L.v_format;
-  if (P.group > G4_HEADS || kf < TQ_FMT_TURBO2 || kf > TQ_FMT_TURBO4 || vf < TQ_FMT_TURBO2 || vf > TQ_FMT_TURBO4) return false;
+  if (P.group > G4_HEADS) return false;
+  // PolarQuant K and V: every pair of widths, with the sparse-V and the measurement variants
 #define TQ_ATT_G4(K, V)                                                                                              \
   if (kf == K && vf == V) {                                                                                          \
     if (!layout_matches<K, V>(P.L)) return false;                                                                    \
-    if (P.nodeq && K == 3 && V == 3) *rc = launch_attn_g4<3, 3, false, true>(P, fk, fv, st); \
+    if (P.nodeq && K == 3 && V == 3) *rc = launch_attn_g4<3, 3, false, true>(P, fk, fv, st);                         \
     else *rc = P.sparse_v ? launch_attn_g4<K, V, true, false>(P, fk, fv, st) : launch_attn_g4<K, V, false, false>(P, fk, fv, st); \
     return true;                                                                                                     \
   }
   TQ_ATT_G4(2, 2) TQ_ATT_G4(2, 3) TQ_ATT_G4(2, 4) TQ_ATT_G4(3, 2) TQ_ATT_G4(3, 3) TQ_ATT_G4(3, 4) TQ_ATT_G4(4, 2)
   TQ_ATT_G4(4, 3) TQ_ATT_G4(4, 4)
 #undef TQ_ATT_G4
+  // q8_0 and PROD keys (the sparse-V option of these pairs runs the general kernel)
+  if (P.sparse_v) return false;
+#define TQ_ATT_G4X(K, V)                                        \
+  if (kf == K && vf == V) {                                     \
+    if (!layout_matches<K, V>(P.L)) return false;               \
+    *rc = launch_attn_g4<K, V, false, false>(P, fk, fv, st);    \
+    return true;                                                \
+  }
+  TQ_ATT_G4X(8, 2) TQ_ATT_G4X(8, 3) TQ_ATT_G4X(8, 4) TQ_ATT_G4X(8, 8)
+  TQ_ATT_G4X(18, 2) TQ_ATT_G4X(18, 3) TQ_ATT_G4X(19, 2) TQ_ATT_G4X(19, 3) TQ_ATT_G4X(19, 4) TQ_ATT_G4X(20, 3) TQ_ATT_G4X(20, 4)
+#undef TQ_ATT_G4X
   return false;
 }

@@ -192,14 +192,24 @@ class PagedKVCache:
     def prefill_attend(self, q, block_table, kv_lens, scale=None, out=None, workspace=None):
         """Chunked prefill on the tcgen05 tensor cores.  q: (batch, chunk_tokens, num_q_heads, head_dim) CUDA
         tensor of a chunk whose K/V rows are already in the cache; kv_lens: (batch,) cached tokens including
-        the chunk.  Query i of a sequence sees cached positions 0 .. kv_len - chunk_tokens + i.  Formats:
-        turbo2/3/4 K and V."""
+        the chunk.  Query i of a sequence sees cached positions 0 .. kv_len - chunk_tokens + i.  turbo2/3/4 K and V
+        take the tcgen05 kernel; PROD or q8_0 tensors run the chunk's queries through the decode kernel."""
         torch = nv.require_cuda()
         q = q.contiguous()
         bsz, tq, hq, d = q.shape
         assert d == self.head_dim
         bt = block_table.to(device=self.device, dtype=torch.int32).contiguous()
         kl = kv_lens.to(device=self.device, dtype=torch.int32).contiguous()
+        if not (self.k_format.startswith("turbo") and self.v_format.startswith("turbo")):
+            # PROD and q8_0 tensors have no tensor-memory pipeline: every query of the chunk runs as a row of the decode
+            # kernel with its own causal length (the cache is read once per query; the pages of a sequence stay in L2)
+            lens = (kl[:, None] - tq + 1 + torch.arange(tq, device=self.device, dtype=torch.int32)[None, :]).clamp_(min=0)
+            res = self.attend(q.reshape(bsz * tq, hq, d), bt.repeat_interleave(tq, dim=0), lens.reshape(-1), scale=scale)
+            res = res.reshape(bsz, tq, hq, d)
+            if out is not None:
+                out.copy_(res)
+                return out
+            return res
         if workspace is None:
             need = int(nv.load().tq_prefill_workspace_bytes(bsz, tq, hq, self.num_kv_heads, bt.shape[1]))
             nv.check(need)
