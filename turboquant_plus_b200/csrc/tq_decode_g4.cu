@@ -302,6 +302,22 @@ __device__ __forceinline__ void g4_tile(G4State& S, uint32_t st, const G4Thr& T,
     load_v_words<VB, 12 * C::VIDXB>(st + T.v_thr, T.vsel0, T.vsel1, vw[3]);
     vs_raw = lds_f32<0>(st + T.vs_thr);
   }
+  constexpr int SHV = PairLut<VB>::SHIFT;
+  auto v_half = [&](uint32_t (&h)[2][8], int u) {
+#pragma unroll
+    for (int q2 = 0; q2 < 2; ++q2) {
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj) {
+        if constexpr (VT::Q8) {
+          h[q2][jj] = hmul2_u32(s8x2_to_h2(vw[2 * u + q2][jj >> 1], (jj & 1) ? 0x4342 : 0x4140), vsc16[2 * u + q2]);
+        } else if constexpr (NODEQ) {
+          h[q2][jj] = vw[2 * u + q2][jj & 1] ^ (uint32_t)jj;
+        } else {
+          h[q2][jj] = lds32(field_off<2 * VB, SHV, 2>(vw[2 * u + q2], jj) | lv_base);
+        }
+      }
+    }
+  };
   // hi + lo: the partner lane (t ^ 2) holds the other half of the same heads
   const bool upper = T.upper;
   const float give0 = upper ? s[0] : s[2], give1 = upper ? s[1] : s[3];
@@ -365,25 +381,13 @@ __device__ __forceinline__ void g4_tile(G4State& S, uint32_t st, const G4Thr& T,
   // ---------------- O^T += V_tile^T . P^T : tokens t, t+4, t+8, t+12 of the tile, dims 16g .. 16g+15 ----------------
   // (neighbouring lanes read neighbouring token rows: rows are 16 VB bytes apart, which spreads a quad of lanes over
   // the shared-memory banks; a stride of four rows put lanes t and t+2 on the same banks)
-  constexpr int SHV = PairLut<VB>::SHIFT;
   // two halves of eight tokens: the table words of one half (16 registers) are live at a time, which leaves the
-  // compiler room to keep more loads in flight (all four token rows at once: 5 % slower at 256K tokens)
+  // compiler room to keep more loads in flight (all four token rows at once: 5 % slower at 256K tokens; forming
+  // the first half ahead of the softmax arithmetic: no gain)
 #pragma unroll
   for (int u = 0; u < 2; ++u) {
     uint32_t h[2][8];
-#pragma unroll
-    for (int q2 = 0; q2 < 2; ++q2) {
-#pragma unroll
-      for (int jj = 0; jj < 8; ++jj) {
-        if constexpr (VT::Q8) {
-          h[q2][jj] = hmul2_u32(s8x2_to_h2(vw[2 * u + q2][jj >> 1], (jj & 1) ? 0x4342 : 0x4140), vsc16[2 * u + q2]);
-        } else if constexpr (NODEQ) {
-          h[q2][jj] = vw[2 * u + q2][jj & 1] ^ (uint32_t)jj;
-        } else {
-          h[q2][jj] = lds32(field_off<2 * VB, SHV, 2>(vw[2 * u + q2], jj) | lv_base);
-        }
-      }
-    }
+    v_half(h, u);
 #pragma unroll
     for (int blk = 0; blk < 4; ++blk)
       mma16816(S.o[blk], h[0][2 * blk], h[0][2 * blk + 1], h[1][2 * blk], h[1][2 * blk + 1], pb[2 * u], pb[2 * u + 1]);
