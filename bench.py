@@ -259,7 +259,20 @@ def run_ours(args):
     append_ms = statistics.median(qt[2:])
     vec_per_s = 2 * nq / (append_ms * 1e-3)
     append_bytes = 2 * nq * (D * 2 + 52)               # fp16 in, 52 B out per vector
-    del qcache, xq, qslots
+    # the same with fp32 rows (the dtype of the reference's own round-trip configuration): 2^21 vectors, 1 GiB in
+    nq32 = nq // 2
+    x32 = xq[:nq32].float()
+    qt = []
+    for _ in range(6):
+        torch.cuda.synchronize(dev)
+        ev[0].record()
+        qcache.append(x32, x32, qslots[:nq32])
+        ev[1].record()
+        torch.cuda.synchronize(dev)
+        qt.append(ev[0].elapsed_time(ev[1]))
+    append32_ms = statistics.median(qt[2:])
+    append32_bytes = 2 * nq32 * (D * 4 + 52)
+    del qcache, xq, x32, qslots
     seq_lens = torch.full((1,), CTX, dtype=torch.int32, device=dev)
     q = torch.randn((LAYERS, 1, HQ, D), generator=gen, device=dev).half()
     out = torch.empty_like(q)
@@ -396,6 +409,11 @@ def run_ours(args):
                                   "achieved": append_bytes / (append_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                                   "frac": append_bytes / (append_ms * 1e-3) / 1e9 / peak,
                                   "bytes_per_vector": D * 2 + 52},
+            "roofline_quantize_f32": {"bound": "hbm", "kernel": "k_quantize_mma<float,3>, 2 launches of 2^21 fp32 vectors into pages",
+                                      "vectors_per_s": 2 * nq32 / (append32_ms * 1e-3),
+                                      "achieved": append32_bytes / (append32_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                                      "frac": append32_bytes / (append32_ms * 1e-3) / 1e9 / peak,
+                                      "bytes_per_vector": D * 4 + 52},
             "e2e": {"value": LAYERS * CTX * HKV * world / (e2e_ms * 1e-3), "unit": UNIT,
                     "ms_per_step": e2e_ms, "steps": e2e_steps,
                     "h2d_bytes_per_step": int(qh.numel() + kh.numel() + vh.numel()) * 2,

@@ -309,13 +309,21 @@ def test_overlap_launch_and_compressor_streaming_api(tq):
             for (c, bt), o_ in zip(caches, outs):
                 c.attend(q, bt, sl, out=o_, workspace=ws, overlap=mode)
 
+        def same(a, b):
+            # plain overlap runs the very same kernel; "q" runs four-warp CTAs, whose warps add their tiles in another
+            # order: equal to fp32 rounding (the fp16 outputs differ by at most an ulp), and bit-stable run to run
+            if mode is True:
+                return torch.equal(a, b)
+            return float((a.float() - b.float()).abs().max()) <= 2e-3 * float(b.float().abs().max())
+
         for o_ in outs:
             o_.zero_()
         for _ in range(4):        # back to back: a call's page loop runs under the tail of the call before
             chain()
         torch.cuda.synchronize()
+        eager = [o_.clone() for o_ in outs]
         for a, b in zip(plain, outs):
-            assert torch.equal(a, b)
+            assert same(b, a)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             chain()
@@ -324,8 +332,8 @@ def test_overlap_launch_and_compressor_streaming_api(tq):
         for _ in range(3):
             g.replay()
         torch.cuda.synchronize()
-        for a, b in zip(plain, outs):
-            assert torch.equal(a, b)
+        for a, b, e in zip(plain, outs, eager):
+            assert same(b, a) and torch.equal(b, e)
         assert caches[0][0].kernel_status(ws) == 0
 
     comp = tq.KVCacheCompressor(D, k_bits=3, v_bits=3, seed=42, rotation="wht").init_cache(2, hkv, 12)

@@ -55,8 +55,9 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
 
 // Barrier `id` over one 256-thread group.  id 0 with a 256-thread CTA is the block barrier; a 512-thread CTA runs
 // two independent groups on ids 1 and 2.
+template <int NT = ATT_THREADS>
 __device__ __forceinline__ void group_sync(int id) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(ATT_THREADS) : "memory");
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(NT) : "memory");
 }
 
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -285,12 +286,12 @@ __device__ __forceinline__ void fold_splits(const AttnParams& P, float v_alpha, 
 // take a ticket; the last CTA of a (sequence, kv head) folds all splits in a fixed order, un-rotates and stores.
 // One thread publishes the CTA's writes (the block barrier orders the other threads' stores before its
 // release), so the rest of the CTA does not execute a device-wide fence.
-template <bool V_Q8>
+template <bool V_Q8, int NT = ATT_THREADS>
 __device__ __forceinline__ void finish_splits(const AttnParams& P, const uint32_t (&vs1)[4], const uint32_t (&vs2)[4],
                                               float v_alpha, float* qbuf, uint8_t* stage0, volatile int* s_flags,
                                               size_t row0, int ns, int b, int kvh, int tid = threadIdx.x, int bar_id = 0) {
   const int lane = tid & 31, warp = tid >> 5;
-  group_sync(bar_id);
+  group_sync<NT>(bar_id);
   if (tid == 0) {
     if (s_flags[0]) atomicExch(P.status, 1);
     __threadfence();
@@ -301,16 +302,16 @@ __device__ __forceinline__ void finish_splits(const AttnParams& P, const uint32_
       __threadfence();
     }
   }
-  group_sync(bar_id);
+  group_sync<NT>(bar_id);
   if (!s_flags[1]) return;
   // Warp (half, head) folds the splits of one head.  With at most four heads there are two warps per head and each
   // takes 64 of the 128 dims: lanes 0..15 then read even splits, lanes 16..31 odd ones (16 bytes each), and one
   // lane exchange joins the two at the end; with more heads a warp takes the whole row and every split.
-  if (2 * P.group <= ATT_WARPS) fold_splits<2, V_Q8>(P, v_alpha, qbuf, row0, ns, warp);
+  if (2 * P.group <= NT / 32) fold_splits<2, V_Q8>(P, v_alpha, qbuf, row0, ns, warp);
   else fold_splits<1, V_Q8>(P, v_alpha, qbuf, row0, ns, warp);
-  group_sync(bar_id);
+  group_sync<NT>(bar_id);
   if (P.v_rot) {  // dense rotation: x = R^T y
-    for (int e = tid; e < P.group * TQ_D; e += ATT_THREADS) {
+    for (int e = tid; e < P.group * TQ_D; e += NT) {
       const int head = e >> 7, j = e & 127;
       float x = 0.f;
 #pragma unroll 8

@@ -40,7 +40,6 @@ constexpr int G4_HEADS = 4;
 constexpr int G4_HSTRIDE = TQ_D + 4;  // floats between heads in the warp-merge buffer: 16-byte stores stay conflict-free
 constexpr int G4_PT = 128;            // tokens per page
 
-constexpr int G4_NS = 3;              // page records in flight per CTA (4 and 5 measured: no faster)
 // One 256-thread CTA per (KV head, split), two CTAs per SM.  (One 512-thread CTA running two such groups keeps the
 // two in step inside a single launch and is 3 % faster there at 32K tokens; but in a chain of launches with
 // programmatic dependent launch the half-SM CTAs of the next call take the place of finished ones one by one, so
@@ -53,7 +52,7 @@ constexpr int up128(int x) { return (x + 127) / 128 * 128; }
 // the CTA's shared memory: the two pair tables, the query buffer(s), the mbarriers and flags, and the pipeline stages
 // (reused as the warp-merge buffer after the page loop).
 // KK / VK: 2,3,4 = turbo bits; 8 = q8_0; 18,19,20 = PROD with 1,2,3 PolarQuant bits + sign sketch (keys only).
-template <int KK, int VK> struct G4 {
+template <int KK, int VK, int NW = ATT_WARPS> struct G4 {
   using KT = Kind<KK>;
   using VT = Kind<VK>;
   static constexpr int KB = KT::BITS, VB = VT::BITS;
@@ -74,8 +73,10 @@ template <int KK, int VK> struct G4 {
   static constexpr int G_Q = 0;                                   // float [4 heads][128] (PROD: + the projected queries)
   static constexpr int G_BAR = G_Q + (KT::PROD ? 2 : 1) * G4_HEADS * TQ_D * 4;   // 3 mbarriers, two flag words at + 64
   static constexpr int G_STAGE = G_BAR + 128;
-  static constexpr int MERGE = ATT_WARPS * G4_HEADS * (G4_HSTRIDE + 2) * 4;
-  static constexpr int GROUP_BYTES = up128(G_STAGE + (G4_NS * REC > MERGE ? G4_NS * REC : MERGE));
+  // page records in flight: 3 (4 and 5 measured: no faster); 2 for the four-warp CTAs, four of which share an SM
+  static constexpr int NS = NW == 4 ? 2 : 3;
+  static constexpr int MERGE = NW * G4_HEADS * (G4_HSTRIDE + 2) * 4;
+  static constexpr int GROUP_BYTES = up128(G_STAGE + (NS * REC > MERGE ? NS * REC : MERGE));
   static constexpr int SMEM = ALIGN + OFF_GROUPS + GROUP_BYTES;
 };
 
@@ -179,7 +180,7 @@ __device__ __forceinline__ uint32_t s8x2_to_h2(uint32_t biased, uint32_t sel) {
 // Scores of one 16-token tile against the four heads (hi halves in columns 0-3, lo halves in 4-7), per thread the
 // MMA accumulator fragment (rows g and g + 8, columns 2t and 2t + 1).  LUT keys return raw sums (the caller applies
 // the K scale of the row it keeps); q8_0 and PROD keys return finished scores of both rows.
-template <int KK, int VK, bool NODEQ>
+template <int KK, int VK, bool NODEQ, int TOK0>
 __device__ __forceinline__ void g4_scores(float (&s)[4], uint32_t st, const G4Thr& T, const uint32_t (&qf)[8][2],
                                           const uint32_t (&qp)[Kind<KK>::PROD ? 8 : 1][2], uint32_t lk_base) {
   using C = G4<KK, VK>;
@@ -189,15 +190,16 @@ __device__ __forceinline__ void g4_scores(float (&s)[4], uint32_t st, const G4Th
   if constexpr (KT::Q8) {
     // a 32-value block has one scale: k-steps 2b and 2b+1 cover block b (this thread supplies its dims 8t .. 8t+7 of
     // the block), and the block's partial scores are scaled in fp32 -- the operands carry no rounding
-    const uint2 sc0 = lds_u64<0>(st + T.ks_thr), sc1 = lds_u64<8 * C::KSCB>(st + T.ks_thr);
+    const uint2 sc0 = lds_u64<TOK0 * C::KSCB>(st + T.ks_thr), sc1 = lds_u64<(TOK0 + 8) * C::KSCB>(st + T.ks_thr);
     const uint32_t scw0[2] = {sc0.x, sc0.y}, scw1[2] = {sc1.x, sc1.y};
 #pragma unroll
     for (int blk = 0; blk < 4; ++blk) {
       uint2 u0, u1;
-      if (blk == 0) { u0 = lds_u64<0>(st + T.k_thr); u1 = lds_u64<8 * TQ_D>(st + T.k_thr); }
-      if (blk == 1) { u0 = lds_u64<32>(st + T.k_thr); u1 = lds_u64<8 * TQ_D + 32>(st + T.k_thr); }
-      if (blk == 2) { u0 = lds_u64<64>(st + T.k_thr); u1 = lds_u64<8 * TQ_D + 64>(st + T.k_thr); }
-      if (blk == 3) { u0 = lds_u64<96>(st + T.k_thr); u1 = lds_u64<8 * TQ_D + 96>(st + T.k_thr); }
+      constexpr int R0 = TOK0 * TQ_D, R1 = (TOK0 + 8) * TQ_D;   // rows g and g + 8 of this tile
+      if (blk == 0) { u0 = lds_u64<R0>(st + T.k_thr); u1 = lds_u64<R1>(st + T.k_thr); }
+      if (blk == 1) { u0 = lds_u64<R0 + 32>(st + T.k_thr); u1 = lds_u64<R1 + 32>(st + T.k_thr); }
+      if (blk == 2) { u0 = lds_u64<R0 + 64>(st + T.k_thr); u1 = lds_u64<R1 + 64>(st + T.k_thr); }
+      if (blk == 3) { u0 = lds_u64<R0 + 96>(st + T.k_thr); u1 = lds_u64<R1 + 96>(st + T.k_thr); }
       const uint32_t x0[2] = {u0.x ^ 0x80808080u, u0.y ^ 0x80808080u};
       const uint32_t x1[2] = {u1.x ^ 0x80808080u, u1.y ^ 0x80808080u};
       float sb[4] = {0.f, 0.f, 0.f, 0.f};
@@ -216,8 +218,8 @@ __device__ __forceinline__ void g4_scores(float (&s)[4], uint32_t st, const G4Th
     }
   } else {
     uint32_t w0[KB], w1[KB];
-    load_k_words<KB, 0>(st + T.k_thr, w0);
-    load_k_words<KB, 8 * C::KIDXB>(st + T.k_thr, w1);
+    load_k_words<KB, TOK0 * C::KIDXB>(st + T.k_thr, w0);
+    load_k_words<KB, (TOK0 + 8) * C::KIDXB>(st + T.k_thr, w1);
     constexpr int SH = PairLut<KB>::SHIFT;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -236,8 +238,8 @@ __device__ __forceinline__ void g4_scores(float (&s)[4], uint32_t st, const G4Th
       // + sqrt(pi/2)/sqrt(d) * ||r|| * <S q, z>: the sign sketch as +-1 operands.  Word t of a row holds its 32 dims
       // 32t .. 32t+31, first dim in the most significant bit; dims i and i + 16 form a pair, so that after a shift by
       // i their bits sit on the sign positions of the two fp16 halves (bit set = +1).
-      const uint32_t z0 = __byte_perm(lds_u32<0>(st + T.z_thr), 0, 0x0123);
-      const uint32_t z1 = __byte_perm(lds_u32<8 * 16>(st + T.z_thr), 0, 0x0123);
+      const uint32_t z0 = __byte_perm(lds_u32<TOK0 * 16>(st + T.z_thr), 0, 0x0123);
+      const uint32_t z1 = __byte_perm(lds_u32<(TOK0 + 8) * 16>(st + T.z_thr), 0, 0x0123);
       float s2[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -247,8 +249,8 @@ __device__ __forceinline__ void g4_scores(float (&s)[4], uint32_t st, const G4Th
         const uint32_t a3 = (~(z1 << (2 * j + 1)) & 0x80008000u) | 0x3C003C00u;
         mma16816(s2, a0, a1, a2, a3, qp[j][0], qp[j][1]);
       }
-      const float k0 = lds_f32<0>(st + T.ks_thr), k1 = lds_f32<32>(st + T.ks_thr);
-      const float r0 = lds_f32<0>(st + T.rs_thr), r1 = lds_f32<32>(st + T.rs_thr);
+      const float k0 = lds_f32<TOK0 * 4>(st + T.ks_thr), k1 = lds_f32<TOK0 * 4 + 32>(st + T.ks_thr);
+      const float r0 = lds_f32<TOK0 * 4>(st + T.rs_thr), r1 = lds_f32<TOK0 * 4 + 32>(st + T.rs_thr);
       s[0] = fmaf(s2[0], r0, s[0] * k0); s[1] = fmaf(s2[1], r0, s[1] * k0);
       s[2] = fmaf(s2[2], r1, s[2] * k1); s[3] = fmaf(s2[3], r1, s[3] * k1);
     }
@@ -260,7 +262,8 @@ __device__ __forceinline__ void g4_scores(float (&s)[4], uint32_t st, const G4Th
 //   MASKED  the page may end inside or before this tile (`valid` tokens of the page exist)
 //   NODEQ   measurement variant: the table lookups are left out and the packed words themselves are fed to the
 //           tensor cores (copies, barriers, MMAs, softmax and merges as in the real kernel; results meaningless)
-template <int KK, int VK, bool MASKED, bool SPARSE, bool NODEQ>
+//   TOK0    first token of the tile relative to the warp's first tile of the page (a multiple of 16)
+template <int KK, int VK, bool MASKED, bool SPARSE, bool NODEQ, int TOK0>
 __device__ __forceinline__ void g4_tile(G4State& S, uint32_t st, const G4Thr& T, const uint32_t (&qf)[8][2],
                                         const uint32_t (&qp)[Kind<KK>::PROD ? 8 : 1][2], uint32_t lk_base, uint32_t lv_base,
                                         int valid) {
@@ -273,9 +276,9 @@ __device__ __forceinline__ void g4_tile(G4State& S, uint32_t st, const G4Thr& T,
   const int t = T.t;
   // ---------------- S = K_tile (16 tokens x 128) . [q_hi | q_lo] ----------------
   float ks = 1.0f;
-  if constexpr (K_LUT) ks = lds_f32<0>(st + T.ks_thr);
+  if constexpr (K_LUT) ks = lds_f32<TOK0 * 4>(st + T.ks_thr);
   float s[4];
-  g4_scores<KK, VK, NODEQ>(s, st, T, qf, qp, lk_base);
+  g4_scores<KK, VK, NODEQ, TOK0>(s, st, T, qf, qp, lk_base);
   // the V words and scale of this tile are fetched here, ahead of the softmax arithmetic that separates them from
   // their use: the loads then wait under it instead of in front of the table lookups
   uint32_t vw[4][VT::Q8 ? 4 : 2];
@@ -286,21 +289,21 @@ __device__ __forceinline__ void g4_tile(G4State& S, uint32_t st, const G4Thr& T,
     for (int q4 = 0; q4 < 4; ++q4) {
       uint4 v;
       uint32_t sc;
-      if (q4 == 0) { v = lds_u128<0>(st + T.v_thr); sc = lds_u16<0>(st + T.vs_thr); }
-      if (q4 == 1) { v = lds_u128<4 * TQ_D>(st + T.v_thr); sc = lds_u16<4 * C::VSCB>(st + T.vs_thr); }
-      if (q4 == 2) { v = lds_u128<8 * TQ_D>(st + T.v_thr); sc = lds_u16<8 * C::VSCB>(st + T.vs_thr); }
-      if (q4 == 3) { v = lds_u128<12 * TQ_D>(st + T.v_thr); sc = lds_u16<12 * C::VSCB>(st + T.vs_thr); }
+      if (q4 == 0) { v = lds_u128<TOK0 * TQ_D>(st + T.v_thr); sc = lds_u16<TOK0 * C::VSCB>(st + T.vs_thr); }
+      if (q4 == 1) { v = lds_u128<(TOK0 + 4) * TQ_D>(st + T.v_thr); sc = lds_u16<(TOK0 + 4) * C::VSCB>(st + T.vs_thr); }
+      if (q4 == 2) { v = lds_u128<(TOK0 + 8) * TQ_D>(st + T.v_thr); sc = lds_u16<(TOK0 + 8) * C::VSCB>(st + T.vs_thr); }
+      if (q4 == 3) { v = lds_u128<(TOK0 + 12) * TQ_D>(st + T.v_thr); sc = lds_u16<(TOK0 + 12) * C::VSCB>(st + T.vs_thr); }
       vw[q4][0] = v.x ^ 0x80808080u; vw[q4][1] = v.y ^ 0x80808080u;
       vw[q4][2] = v.z ^ 0x80808080u; vw[q4][3] = v.w ^ 0x80808080u;
-      if constexpr (MASKED) sc = (T.vtok_in_page + 4 * q4 < valid) ? sc : 0u;   // a stale scale must not meet p = 0
+      if constexpr (MASKED) sc = (T.vtok_in_page + TOK0 + 4 * q4 < valid) ? sc : 0u;   // a stale scale must not meet p = 0
       vsc16[q4] = __byte_perm(sc, 0, 0x1010);
     }
   } else {
-    load_v_words<VB, 0>(st + T.v_thr, T.vsel0, T.vsel1, vw[0]);
-    load_v_words<VB, 4 * C::VIDXB>(st + T.v_thr, T.vsel0, T.vsel1, vw[1]);
-    load_v_words<VB, 8 * C::VIDXB>(st + T.v_thr, T.vsel0, T.vsel1, vw[2]);
-    load_v_words<VB, 12 * C::VIDXB>(st + T.v_thr, T.vsel0, T.vsel1, vw[3]);
-    vs_raw = lds_f32<0>(st + T.vs_thr);
+    load_v_words<VB, TOK0 * C::VIDXB>(st + T.v_thr, T.vsel0, T.vsel1, vw[0]);
+    load_v_words<VB, (TOK0 + 4) * C::VIDXB>(st + T.v_thr, T.vsel0, T.vsel1, vw[1]);
+    load_v_words<VB, (TOK0 + 8) * C::VIDXB>(st + T.v_thr, T.vsel0, T.vsel1, vw[2]);
+    load_v_words<VB, (TOK0 + 12) * C::VIDXB>(st + T.v_thr, T.vsel0, T.vsel1, vw[3]);
+    vs_raw = lds_f32<TOK0 * 4>(st + T.vs_thr);
   }
   constexpr int SHV = PairLut<VB>::SHIFT;
   auto v_half = [&](uint32_t (&h)[2][8], int u) {
@@ -334,7 +337,7 @@ __device__ __forceinline__ void g4_tile(G4State& S, uint32_t st, const G4Thr& T,
   float vs = vs_raw;
   float d0 = fmaf(sum0, ks, -S.m0), d1 = fmaf(sum1, ks, -S.m1);   // score - running reference
   if constexpr (MASKED) {
-    ok = T.tok_in_page < valid;
+    ok = T.tok_in_page + TOK0 < valid;
     vs = ok ? vs_raw : 0.f;                                       // a stale scale must not meet p = 0
     d0 = ok ? d0 : -INFINITY;
     d1 = ok ? d1 : -INFINITY;
@@ -394,10 +397,26 @@ __device__ __forceinline__ void g4_tile(G4State& S, uint32_t st, const G4Thr& T,
   }
 }
 
-template <int KK, int VK, bool SPARSE, bool NODEQ>
-__global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_constant__ AttnParams P, const __grid_constant__ AttnQuant fk,
-                                                                    const __grid_constant__ AttnQuant fv) {
-  using C = G4<KK, VK>;
+// the warp's tiles of one page: tile TT covers tokens 16 (warp + NW TT) .. + 15
+template <int KK, int VK, bool SPARSE, bool NODEQ, int NW, int TT>
+__device__ __forceinline__ void g4_page(G4State& S, uint32_t st, const G4Thr& T, const uint32_t (&qf)[8][2],
+                                        const uint32_t (&qp)[Kind<KK>::PROD ? 8 : 1][2], uint32_t lk_base, uint32_t lv_base,
+                                        bool full, int last_valid, int warp) {
+  constexpr int TOK0 = 16 * NW * TT;
+  if (full) g4_tile<KK, VK, false, SPARSE, NODEQ, TOK0>(S, st, T, qf, qp, lk_base, lv_base, G4_PT);
+  else if (16 * warp + TOK0 < last_valid) g4_tile<KK, VK, true, SPARSE, NODEQ, TOK0>(S, st, T, qf, qp, lk_base, lv_base, last_valid);
+  if constexpr (TT + 1 < ATT_WARPS / NW) g4_page<KK, VK, SPARSE, NODEQ, NW, TT + 1>(S, st, T, qf, qp, lk_base, lv_base, full, last_valid, warp);
+}
+
+// NW warps per CTA: 8 (two CTAs per SM), or 4 (four per SM, two tiles per warp and page) for chains of calls that may
+// overlap completely: the CTAs of two consecutive calls then share an SM four at a time, each in a phase of its own,
+// and the SM's warps are in a page loop 80 % of the time instead of 67 %.
+template <int KK, int VK, bool SPARSE, bool NODEQ, int NW>
+__global__ void __launch_bounds__(32 * NW, 16 / NW) k_decode_attn_g4(const __grid_constant__ AttnParams P, const __grid_constant__ AttnQuant fk,
+                                                                      const __grid_constant__ AttnQuant fv) {
+  using C = G4<KK, VK, NW>;
+  constexpr int NT = 32 * NW;          // threads
+  constexpr int G4_NS = C::NS;
   using KT = Kind<KK>;
   using VT = Kind<VK>;
   constexpr int KB = KT::BITS, VB = VT::BITS;
@@ -431,7 +450,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_
   uint64_t* bars = reinterpret_cast<uint64_t*>(smg + C::G_BAR);
   volatile int* s_flags = reinterpret_cast<volatile int*>(smg + C::G_BAR + 64);
   uint8_t* stage0 = smg + C::G_STAGE;
-  constexpr int PRODUCER = ATT_THREADS - 32;  // lane 0 of the last warp issues every bulk copy
+  constexpr int PRODUCER = NT - 32;  // lane 0 of the last warp issues every bulk copy
   const uint8_t* pool_head = P.pool + (int64_t)kvh * P.L.head_stride;
 
   auto issue = [&](int stage, int64_t page) {
@@ -450,7 +469,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_
   const int np = min(n_pages, page_lo + P.chunk_pages) - page_lo;   // pages of this CTA (<= 0: none)
   int pg_ahead = 0;  // producer: block-table entry of the page issued in the next iteration
   float x[4] = {0.f, 0.f, 0.f, 0.f}, y[4] = {0.f, 0.f, 0.f, 0.f};
-  if (tid == PRODUCER) {
+  if (tid == PRODUCER) {   // (with four warps and four heads this warp rotates a query as well, afterwards)
     int pg_next[G4_NS];
 #pragma unroll
     for (int i = 0; i < G4_NS; ++i) pg_next[i] = bt[min(page_lo + i, P.max_pages - 1)];
@@ -463,7 +482,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_
     for (int s = 0; s < G4_NS - 1; ++s)
       if (np > s) issue(s, pg_next[s]);
     pg_ahead = pg_next[G4_NS - 1];
-  } else if (warp < P.group) {
+  }
+  if (warp < P.group && (tid != PRODUCER || NW == 4)) {
     if (P.overlap && !P.q_early) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (P.k_pre) {   // dense rotations: rotated (and, for PROD keys, projected) queries come from k_prepare_queries
       load_q4(P.qrot, TQ_F32, (row0 + warp) * TQ_D + 4 * lane, x);
@@ -492,15 +512,18 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_
       *reinterpret_cast<float4*>(qbuf + (G4_HEADS + warp) * TQ_D + 4 * lane) = make_float4(y[0], y[1], y[2], y[3]);
   }
   __syncwarp();
-  if (warp >= P.group) {
-    const int fh = ATT_THREADS - 32 * P.group;   // table-filling threads
+  if (NW == 4) {   // every warp may have rotated a query: all of them fill the tables afterwards
+    if constexpr (KB > 0) lut_fill<KB>(sm + C::OFF_K, fk.cent16, tid, NT);
+    if constexpr (VB > 0) lut_fill<VB>(sm + C::OFF_V, fv.cent16, tid, NT);
+  } else if (warp >= P.group) {
+    const int fh = NT - 32 * P.group;   // table-filling threads
     if constexpr (KB > 0) lut_fill<KB>(sm + C::OFF_K, fk.cent16, tid - 32 * P.group, fh);
     if constexpr (VB > 0) lut_fill<VB>(sm + C::OFF_V, fv.cent16, tid - 32 * P.group, fh);
   }
   if (P.overlap && !P.q_early) asm volatile("griddepcontrol.wait;" ::: "memory");   // the query warps already have
   if (n_pages == 0 && split == 0) {  // empty sequence: zeros (split 0 exists for every kv head)
     if (P.overlap && P.q_early) asm volatile("griddepcontrol.wait;" ::: "memory");
-    for (int e = tid; e < P.group * TQ_D; e += ATT_THREADS) store_out(P.out, P.out_dtype, row0 * TQ_D + e, 0.f);
+    for (int e = tid; e < P.group * TQ_D; e += NT) store_out(P.out, P.out_dtype, row0 * TQ_D + e, 0.f);
     if (P.lse && tid < P.group) P.lse[row0 + tid] = -INFINITY;
   }
   const int ns = (n_pages + P.chunk_pages - 1) / P.chunk_pages;
@@ -592,12 +615,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_
     uint32_t dep;
     asm volatile("mov.u32 %0, 0;" : "=r"(dep)::"memory");
     const uint32_t st = stage_addr + stage * C::REC + dep;
-    if (i < n_full) {
-      g4_tile<KK, VK, false, SPARSE, NODEQ>(S, st, T, qf, qp, lk_base, lv_base, G4_PT);
-    } else if (16 * warp < last_valid) {
-      g4_tile<KK, VK, true, SPARSE, NODEQ>(S, st, T, qf, qp, lk_base, lv_base, last_valid);
-    }
-    group_sync(bar_id);  // every warp is done with this stage before it is refilled
+    g4_page<KK, VK, SPARSE, NODEQ, NW, 0>(S, st, T, qf, qp, lk_base, lv_base, i < n_full, last_valid, warp);
+    group_sync<NT>(bar_id);  // every warp is done with this stage before it is refilled
     if (++stage == G4_NS) {
       stage = 0;
       parity ^= 1u;
@@ -612,7 +631,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_
     S.l1 += __shfl_xor_sync(0xffffffffu, S.l1, sh);
   }
   float* so = reinterpret_cast<float*>(stage0);                    // [warp][head 4][G4_HSTRIDE]
-  float* sml = so + ATT_WARPS * G4_HEADS * G4_HSTRIDE;             // [warp][head 4][2]
+  float* sml = so + NW * G4_HEADS * G4_HSTRIDE;                    // [warp][head 4][2]
 #pragma unroll
   for (int blk = 0; blk < 4; ++blk)
     *reinterpret_cast<float4*>(so + (size_t)(warp * G4_HEADS + t) * G4_HSTRIDE + 16 * g + 4 * blk) =
@@ -620,43 +639,49 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) k_decode_attn_g4(const __grid_
   if (g == 0 && t < 2) {
     *reinterpret_cast<float4*>(sml + (warp * G4_HEADS + 2 * t) * 2) = make_float4(S.m0, S.l0, S.m1, S.l1);
   }
-  group_sync(bar_id);
+  group_sync<NT>(bar_id);
   {
-    // thread (head, pair of dims): 4 heads x 64 pairs = 256 threads; the eight warps' rows are added in warp order
-    const int head = tid >> 6, dim = 2 * (tid & 63);
+    // thread (head, DPT consecutive dims): 4 heads x 128 dims over the CTA's threads; the warps' rows are added in
+    // warp order
+    constexpr int DPT = G4_HEADS * TQ_D / NT;     // 2 or 4
+    const int head = tid / (TQ_D / DPT), dim = DPT * (tid % (TQ_D / DPT));
     if (head < P.group) {
-      float mw[ATT_WARPS], M = -INFINITY;
+      float mw[NW], M = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < ATT_WARPS; ++w) {
+      for (int w = 0; w < NW; ++w) {
         mw[w] = sml[(w * G4_HEADS + head) * 2];
         M = fmaxf(M, mw[w]);
       }
-      float a0 = 0.f, a1 = 0.f, Lsum = 0.f;
+      float a[DPT], Lsum = 0.f;
 #pragma unroll
-      for (int w = 0; w < ATT_WARPS; ++w) {
+      for (int k = 0; k < DPT; ++k) a[k] = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) {
         const float f = mw[w] == -INFINITY ? 0.f : fast_exp2(mw[w] - M);
-        const float2 v = *reinterpret_cast<const float2*>(so + (size_t)(w * G4_HEADS + head) * G4_HSTRIDE + dim);
-        a0 = fmaf(v.x, f, a0);
-        a1 = fmaf(v.y, f, a1);
+        const float* v = so + (size_t)(w * G4_HEADS + head) * G4_HSTRIDE + dim;
+#pragma unroll
+        for (int k = 0; k < DPT; ++k) a[k] = fmaf(v[k], f, a[k]);
         Lsum = fmaf(sml[(w * G4_HEADS + head) * 2 + 1], f, Lsum);
       }
       const size_t slot = (row0 + head) * P.num_splits + split;
-      *reinterpret_cast<float2*>(P.part_o + slot * TQ_D + dim) = make_float2(a0, a1);
+#pragma unroll
+      for (int k = 0; k < DPT; k += 2)
+        *reinterpret_cast<float2*>(P.part_o + slot * TQ_D + dim + k) = make_float2(a[k], a[k + 1]);
       if (dim == 0) *reinterpret_cast<float2*>(P.part_ml + slot * 2) = make_float2(M, Lsum);
     }
   }
-  finish_splits<VT::Q8>(P, fv.s1, fv.s2, fv.alpha, qbuf, stage0, s_flags, row0, ns, b, kvh, tid, bar_id);
+  finish_splits<VT::Q8, NT>(P, fv.s1, fv.s2, fv.alpha, qbuf, stage0, s_flags, row0, ns, b, kvh, tid, bar_id);
 }
 
-template <int KK, int VK, bool SPARSE, bool NODEQ>
+template <int KK, int VK, bool SPARSE, bool NODEQ, int NW = ATT_WARPS>
 int launch_attn_g4(const AttnParams& P, const TqFast& fk, const TqFast& fv, cudaStream_t st) {
-  using C = G4<KK, VK>;
-  static_assert(2 * (C::SMEM + 1024) <= 228 * 1024, "two CTAs of the specialised decode kernel per SM");
+  using C = G4<KK, VK, NW>;
+  static_assert((16 / NW) * (C::SMEM + 1024) <= 228 * 1024, "CTAs of the specialised decode kernel per SM");
   static thread_local int configured_dev = -1;  // per instantiation
   int dev = 0;
   TQ_CUDA(cudaGetDevice(&dev));
   if (configured_dev != dev) {
-    TQ_CUDA(cudaFuncSetAttribute(k_decode_attn_g4<KK, VK, SPARSE, NODEQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+    TQ_CUDA(cudaFuncSetAttribute(k_decode_attn_g4<KK, VK, SPARSE, NODEQ, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
     configured_dev = dev;
   }
   AttnQuant ak, av;
@@ -668,7 +693,7 @@ int launch_attn_g4(const AttnParams& P, const TqFast& fk, const TqFast& fv, cuda
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(P.num_splits, P.hkv, P.batch);
-  cfg.blockDim = dim3(ATT_THREADS);
+  cfg.blockDim = dim3(32 * NW);
   cfg.dynamicSmemBytes = C::SMEM;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -676,7 +701,7 @@ int launch_attn_g4(const AttnParams& P, const TqFast& fk, const TqFast& fv, cuda
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = P.overlap ? 1 : 0;
-  TQ_CUDA(cudaLaunchKernelEx(&cfg, k_decode_attn_g4<KK, VK, SPARSE, NODEQ>, P, ak, av));
+  TQ_CUDA(cudaLaunchKernelEx(&cfg, k_decode_attn_g4<KK, VK, SPARSE, NODEQ, NW>, P, ak, av));
   return tq_launch_check("k_decode_attn_g4");
 }
 
@@ -698,7 +723,9 @@ bool tq_decode_g4_try(const tqatt::AttnParams& P, const TqFast& fk, const TqFast
   if (kf == K && vf == V) {                                                                                          \
     if (!layout_matches<K, V>(P.L)) return false;                                                                    \
     if (P.nodeq && K == 3 && V == 3) *rc = launch_attn_g4<3, 3, false, true>(P, fk, fv, st);                         \
-    else *rc = P.sparse_v ? launch_attn_g4<K, V, true, false>(P, fk, fv, st) : launch_attn_g4<K, V, false, false>(P, fk, fv, st); \
+    else if (P.sparse_v) *rc = launch_attn_g4<K, V, true, false>(P, fk, fv, st);                                     \
+    else if (P.q_early) *rc = launch_attn_g4<K, V, false, false, 4>(P, fk, fv, st);                                  \
+    else *rc = launch_attn_g4<K, V, false, false>(P, fk, fv, st);                                                    \
     return true;                                                                                                     \
   }
   TQ_ATT_G4(2, 2) TQ_ATT_G4(2, 3) TQ_ATT_G4(2, 4) TQ_ATT_G4(3, 2) TQ_ATT_G4(3, 3) TQ_ATT_G4(3, 4) TQ_ATT_G4(4, 2)

@@ -1,6 +1,6 @@
-// d = 128 sign-WHT quantizer for 16-bit inputs, with the Hadamard transform on the tensor cores.
+// d = 128 sign-WHT quantizer with the Hadamard transform on the tensor cores.
 //
-//   k_quantize_mma<Tin, BITS, NORMC>   Tin = __half or __nv_bfloat16, symmetric codebook, packed output.
+//   k_quantize_mma<Tin, BITS, NORMC>   Tin = __half, __nv_bfloat16 or float, symmetric codebook, packed output.
 //
 // H128 = H8 (x) H16 (element e = 16 i + j).  A warp takes 16 vectors at a time:
 //   * the 16 x 128 tile is copied to shared memory with 16-byte asynchronous copies (double buffered) and read
@@ -19,7 +19,9 @@
 //   * a 4 x 4 transpose of words inside each quad of lanes leaves every lane with 32 consecutive indices of its
 //     vector, which it stores as the reference's most-significant-bit-first stream (turboquant/utils.py pack_indices
 //     order, the layout the cache keeps).
-// Everything else (fp32 input, QJL stage, asymmetric codebooks, unpacked output) stays with k_quantize_wht.
+//   * fp32 inputs are split into three bf16 terms (8 + 8 + 8 significant bits, by truncation: the split is exact)
+//     that go through the same MMAs one after the other into one fp32 accumulator; products with +-1 stay exact.
+// Everything else (QJL stage, asymmetric codebooks, unpacked output) stays with k_quantize_wht.
 #include "tq_internal.cuh"
 
 namespace {
@@ -27,7 +29,9 @@ namespace {
 constexpr int QM_THREADS = 128;
 constexpr int QM_WARPS = 4;
 constexpr int QM_ROWS = 16;
-constexpr int QM_ROWB = 272;  // 256 data bytes + 16 bytes of padding
+// bytes between the rows of a staged tile: 16-bit rows 256 + 16 (the eight rows of an ldmatrix fall into different bank
+// groups), fp32 rows 512 + 32 (rows g = 0..3 of a half-warp's 8-byte loads start 8 banks apart)
+template <typename T> constexpr int qm_rowb() { return sizeof(T) == 4 ? 544 : 272; }
 
 template <typename T> struct QmIn;
 template <> struct QmIn<__half> {
@@ -46,7 +50,26 @@ template <> struct QmIn<__nv_bfloat16> {
                  : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
   }
+  // c += a . b
+  static __device__ __forceinline__ void mma_acc(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
 };
+template <> struct QmIn<float> : QmIn<__nv_bfloat16> {};   // fp32 rows are fed as bf16 terms
+
+// (x0, x1) = hi + mid + lo, each term a pair of bf16 values obtained by truncation: every term keeps the eight leading
+// significant bits of what is left, so three terms hold all 24 and every subtraction is exact.  Low half = x0.
+__device__ __forceinline__ void qm_split3(float x0, float x1, uint32_t& hi, uint32_t& mid, uint32_t& lo) {
+  const uint32_t u0 = __float_as_uint(x0), u1 = __float_as_uint(x1);
+  hi = __byte_perm(u0, u1, 0x7632);
+  const float r0 = x0 - __uint_as_float(u0 & 0xffff0000u), r1 = x1 - __uint_as_float(u1 & 0xffff0000u);
+  const uint32_t v0 = __float_as_uint(r0), v1 = __float_as_uint(r1);
+  mid = __byte_perm(v0, v1, 0x7632);
+  const float s0 = r0 - __uint_as_float(v0 & 0xffff0000u), s1 = r1 - __uint_as_float(v1 & 0xffff0000u);
+  lo = __byte_perm(__float_as_uint(s0), __float_as_uint(s1), 0x7632);
+}
 
 __device__ __forceinline__ uint32_t qm_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ uint32_t qm_bit(const uint32_t (&m)[4], int e) { return (m[e >> 5] >> (e & 31)) & 1u; }
@@ -57,9 +80,13 @@ __device__ __forceinline__ float qm_gt(float a, float b) {
   return d;
 }
 
+// `tile`: the CTA's staging memory, QM_WARPS x 2 buffers of QM_ROWS rows of qm_rowb<Tin>() bytes
 template <typename Tin, int BITS, bool NORMC>
 __device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__ x, int64_t ld, int64_t n,
-                                        const TqQuantDst& dst, uint8_t (&tile)[QM_WARPS][2][QM_ROWS * QM_ROWB]) {
+                                        const TqQuantDst& dst, uint8_t* tile) {
+  constexpr int QM_ROWB = qm_rowb<Tin>();
+  constexpr int BUFB = QM_ROWS * QM_ROWB;                      // bytes of one staged tile
+  constexpr int CHUNKS = (int)(TQ_D * sizeof(Tin) / 16);       // 16-byte chunks per row
   constexpr int NC = 1 << BITS, HALF = NC / 2, NT = HALF - 1;  // NT positive boundaries
   constexpr int IDXB = 16 * BITS;
   constexpr float RADIX = (float)NC;
@@ -105,19 +132,21 @@ __device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__
     dsq[j] = f.cent[HALF + j + 1] * f.cent[HALF + j + 1] - f.cent[HALF + j] * f.cent[HALF + j];
   }
   const float c0sq = f.cent[HALF] * f.cent[HALF];
+  const uint32_t zero_idx = 0.f > f.bnd[HALF - 1] ? HALF : HALF - 1;   // index of the value 0
 
   const int64_t ntiles = (n + QM_ROWS - 1) / QM_ROWS;
   const int64_t stride = (int64_t)gridDim.x * QM_WARPS;
   int64_t ti = (int64_t)blockIdx.x * QM_WARPS + warp;
+  uint8_t* wtile = tile + (size_t)warp * 2 * BUFB;
   auto issue = [&](int64_t tile_i, int buf) {
     const int64_t v0 = tile_i * QM_ROWS;
-    const uint32_t sbase = qm_smem(&tile[warp][buf][0]);
+    const uint32_t sbase = qm_smem(wtile + buf * BUFB);
 #pragma unroll
-    for (int r2 = 0; r2 < 8; ++r2) {
-      const int row = 2 * r2 + (lane >> 4), chunk = lane & 15;
+    for (int r2 = 0; r2 < QM_ROWS * CHUNKS / 32; ++r2) {
+      const int row = (32 * r2 + lane) / CHUNKS, chunk = (32 * r2 + lane) % CHUNKS;
       if (v0 + row < n)
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sbase + row * QM_ROWB + chunk * 16),
-                     "l"(x + (v0 + row) * ld + chunk * 8)
+                     "l"(reinterpret_cast<const uint8_t*>(x + (v0 + row) * ld) + chunk * 16)
                      : "memory");
     }
   };
@@ -133,8 +162,29 @@ __device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__
 
     // ---- 16-point stage on the tensor cores ----
     float acc[8][2][4];
-    {
-      const uint32_t abase = qm_smem(&tile[warp][it & 1][0]) + ((lane & 7) + 8 * ((lane >> 3) & 1)) * QM_ROWB + 16 * (lane >> 4);
+    if constexpr (sizeof(Tin) == 4) {
+      // thread (g, t): rows g and g + 8, columns 16 i + 2t, + 1 (registers 0, 1) and 16 i + 2t + 8, + 9 (2, 3)
+      const uint8_t* abase = wtile + (it & 1) * BUFB + g * QM_ROWB + 8 * t;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float2 x0 = *reinterpret_cast<const float2*>(abase + 64 * i);
+        const float2 x1 = *reinterpret_cast<const float2*>(abase + 8 * QM_ROWB + 64 * i);
+        const float2 x2 = *reinterpret_cast<const float2*>(abase + 64 * i + 32);
+        const float2 x3 = *reinterpret_cast<const float2*>(abase + 8 * QM_ROWB + 64 * i + 32);
+        uint32_t a[3][4];
+        qm_split3(x0.x, x0.y, a[0][0], a[1][0], a[2][0]);
+        qm_split3(x1.x, x1.y, a[0][1], a[1][1], a[2][1]);
+        qm_split3(x2.x, x2.y, a[0][2], a[1][2], a[2][2]);
+        qm_split3(x3.x, x3.y, a[0][3], a[1][3], a[2][3]);
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          QmIn<Tin>::mma(acc[i][nt], a[0], bfr[i][nt][0], bfr[i][nt][1]);
+          QmIn<Tin>::mma_acc(acc[i][nt], a[1], bfr[i][nt][0], bfr[i][nt][1]);
+          QmIn<Tin>::mma_acc(acc[i][nt], a[2], bfr[i][nt][0], bfr[i][nt][1]);
+        }
+      }
+    } else {
+      const uint32_t abase = qm_smem(wtile + (it & 1) * BUFB) + ((lane & 7) + 8 * ((lane >> 3) & 1)) * QM_ROWB + 16 * (lane >> 4);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         uint32_t a[4];
@@ -229,9 +279,10 @@ __device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__
           constexpr float OFF = ((float)HALF - 0.5f) * (float)(((1u << (8 * BITS)) - 1) / (NC - 1));
           w[tp] = __float2uint_rn(wf[0] + OFF);
         }
-        // a zero vector takes the index of the value 0 in every coordinate (no mirroring either)
-        constexpr uint32_t ZERO_WORD = (uint32_t)(((1ull << (8 * BITS)) - 1) / (NC - 1)) * (HALF - 1);
-        w[tp] = nrm > 0.f ? (w[tp] ^ flip[tp]) : ZERO_WORD;
+        // a zero vector takes the index of the value 0 in every coordinate (no mirroring either): the upper central
+        // index when the centre boundary, a midpoint of two fp64 centroids, has come out a hair below zero
+        constexpr uint32_t ONES = (uint32_t)(((1ull << (8 * BITS)) - 1) / (NC - 1));   // bit 0 of every field
+        w[tp] = nrm > 0.f ? (w[tp] ^ flip[tp]) : ONES * zero_idx;
       }
       float invn = 1.0f;
       if (NORMC && BITS != 4) {
@@ -315,11 +366,23 @@ __device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
+// staging memory of one CTA: 16-bit rows fit the static limit, fp32 rows (68 KB) are dynamic
+template <typename Tin> constexpr int qm_tile_bytes() { return QM_WARPS * 2 * QM_ROWS * qm_rowb<Tin>(); }
+template <typename Tin> constexpr int qm_ctas_per_sm() { return sizeof(Tin) == 4 ? 3 : 4; }
+template <typename Tin> __device__ __forceinline__ uint8_t* qm_tile() {
+  if constexpr (sizeof(Tin) == 4) {
+    extern __shared__ __align__(16) uint8_t qm_dyn[];
+    return qm_dyn;
+  } else {
+    __shared__ __align__(16) uint8_t qm_static[qm_tile_bytes<Tin>()];
+    return qm_static;
+  }
+}
+
 template <typename Tin, int BITS, bool NORMC>
-__global__ void __launch_bounds__(QM_THREADS, 4) k_quantize_mma(const TqFast f, const Tin* __restrict__ x, int64_t ld,
-                                                                int64_t n, const TqQuantDst dst) {
-  __shared__ __align__(16) uint8_t tile[QM_WARPS][2][QM_ROWS * QM_ROWB];
-  qm_body<Tin, BITS, NORMC>(f, x, ld, n, dst, tile);
+__global__ void __launch_bounds__(QM_THREADS, qm_ctas_per_sm<Tin>()) k_quantize_mma(const TqFast f, const Tin* __restrict__ x, int64_t ld,
+                                                                                   int64_t n, const TqQuantDst dst) {
+  qm_body<Tin, BITS, NORMC>(f, x, ld, n, dst, qm_tile<Tin>());
 }
 
 // Two tensors of the same shape in one launch (the K and V rows of a cache append): blockIdx.y picks the job.
@@ -329,23 +392,47 @@ struct QmJob {
   TqQuantDst dst;
 };
 template <typename Tin, int BITS, bool NORMC>
-__global__ void __launch_bounds__(QM_THREADS, 4) k_quantize_mma_pair(const __grid_constant__ QmJob j0,
-                                                                     const __grid_constant__ QmJob j1, int64_t ld, int64_t n) {
-  __shared__ __align__(16) uint8_t tile[QM_WARPS][2][QM_ROWS * QM_ROWB];
+__global__ void __launch_bounds__(QM_THREADS, qm_ctas_per_sm<Tin>()) k_quantize_mma_pair(const __grid_constant__ QmJob j0,
+                                                                                        const __grid_constant__ QmJob j1, int64_t ld,
+                                                                                        int64_t n) {
+  uint8_t* tile = qm_tile<Tin>();
   if (blockIdx.y == 0) qm_body<Tin, BITS, NORMC>(j0.f, reinterpret_cast<const Tin*>(j0.x), ld, n, j0.dst, tile);
   else qm_body<Tin, BITS, NORMC>(j1.f, reinterpret_cast<const Tin*>(j1.x), ld, n, j1.dst, tile);
+}
+
+// dynamic shared memory of a launch (0 for 16-bit rows); raises the kernel's limit once per device
+template <typename Tin, auto kernel>
+int qm_dyn_smem(size_t* bytes) {
+  *bytes = 0;
+  if constexpr (sizeof(Tin) == 4) {
+    *bytes = qm_tile_bytes<Tin>();
+    static thread_local int configured_dev = -1;  // one per kernel: the kernel is a template argument
+    int dev = 0;
+    TQ_CUDA(cudaGetDevice(&dev));
+    if (configured_dev != dev) {
+      TQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, qm_tile_bytes<Tin>()));
+      configured_dev = dev;
+    }
+  }
+  return TQ_OK;
 }
 
 template <typename Tin, int BITS>
 int launch_mma(const TqFast& f, const Tin* x, int64_t ld, int64_t n, const TqQuantDst& dst, cudaStream_t st) {
   const int64_t tiles = (n + QM_ROWS - 1) / QM_ROWS;
   const int64_t ctas = (tiles + QM_WARPS - 1) / QM_WARPS;
-  const int64_t cap = (int64_t)tq_num_sms() * 4;
+  const int64_t cap = (int64_t)tq_num_sms() * qm_ctas_per_sm<Tin>();
   const int grid = (int)(ctas < cap ? ctas : cap);
-  if (f.norm_correction && dst.scale)
-    k_quantize_mma<Tin, BITS, true><<<grid, QM_THREADS, 0, st>>>(f, x, ld, n, dst);
-  else
-    k_quantize_mma<Tin, BITS, false><<<grid, QM_THREADS, 0, st>>>(f, x, ld, n, dst);
+  size_t smem = 0;
+  if (f.norm_correction && dst.scale) {
+    const int rc = qm_dyn_smem<Tin, k_quantize_mma<Tin, BITS, true>>(&smem);
+    if (rc != TQ_OK) return rc;
+    k_quantize_mma<Tin, BITS, true><<<grid, QM_THREADS, smem, st>>>(f, x, ld, n, dst);
+  } else {
+    const int rc = qm_dyn_smem<Tin, k_quantize_mma<Tin, BITS, false>>(&smem);
+    if (rc != TQ_OK) return rc;
+    k_quantize_mma<Tin, BITS, false><<<grid, QM_THREADS, smem, st>>>(f, x, ld, n, dst);
+  }
   return tq_launch_check("k_quantize_mma");
 }
 
@@ -355,15 +442,24 @@ int launch_mma_pair(const QmJob& j0, const QmJob& j1, int64_t ld, int64_t n, boo
   const int64_t ctas = (tiles + QM_WARPS - 1) / QM_WARPS;
   const int64_t cap = (int64_t)tq_num_sms() * 2;  // two jobs share the SMs
   dim3 grid((unsigned)(ctas < cap ? ctas : cap), 2);
-  if (normc) k_quantize_mma_pair<Tin, BITS, true><<<grid, QM_THREADS, 0, st>>>(j0, j1, ld, n);
-  else k_quantize_mma_pair<Tin, BITS, false><<<grid, QM_THREADS, 0, st>>>(j0, j1, ld, n);
+  size_t smem = 0;
+  if (normc) {
+    const int rc = qm_dyn_smem<Tin, k_quantize_mma_pair<Tin, BITS, true>>(&smem);
+    if (rc != TQ_OK) return rc;
+    k_quantize_mma_pair<Tin, BITS, true><<<grid, QM_THREADS, smem, st>>>(j0, j1, ld, n);
+  } else {
+    const int rc = qm_dyn_smem<Tin, k_quantize_mma_pair<Tin, BITS, false>>(&smem);
+    if (rc != TQ_OK) return rc;
+    k_quantize_mma_pair<Tin, BITS, false><<<grid, QM_THREADS, smem, st>>>(j0, j1, ld, n);
+  }
   return tq_launch_check("k_quantize_mma_pair");
 }
 
 bool qm_serves(const TqFast& f, int32_t dtype, int64_t ld, const TqQuantDst& dst, bool want_qjl) {
   if (want_qjl || !f.symmetric || !dst.idx || dst.idx_u8 || dst.qjl || dst.rnorm) return false;
-  if (dtype != TQ_F16 && dtype != TQ_BF16) return false;
-  return f.bits >= 2 && f.bits <= 4 && ld % 8 == 0;  // (1-bit codebooks have no magnitude levels to test)
+  if (dtype != TQ_F16 && dtype != TQ_BF16 && dtype != TQ_F32) return false;
+  // rows must start on 16-byte boundaries (1-bit codebooks have no magnitude levels to test)
+  return f.bits >= 2 && f.bits <= 4 && ld % (dtype == TQ_F32 ? 4 : 8) == 0;
 }
 
 }  // namespace
@@ -380,8 +476,9 @@ bool tq_quantize_mma_try_pair(const TqFast& f0, const void* x0, const TqQuantDst
   const bool normc = f0.norm_correction && d0.scale;
 #define TQ_CASE(B)                                                                              \
   case B:                                                                                       \
-    *rc = dtype == TQ_F16 ? launch_mma_pair<__half, B>(j0, j1, ld, n, normc, st)                \
-                          : launch_mma_pair<__nv_bfloat16, B>(j0, j1, ld, n, normc, st);        \
+    *rc = dtype == TQ_F16    ? launch_mma_pair<__half, B>(j0, j1, ld, n, normc, st)             \
+          : dtype == TQ_BF16 ? launch_mma_pair<__nv_bfloat16, B>(j0, j1, ld, n, normc, st)      \
+                             : launch_mma_pair<float, B>(j0, j1, ld, n, normc, st);             \
     return true;
   switch (f0.bits) {
     TQ_CASE(2)
@@ -398,8 +495,9 @@ bool tq_quantize_mma_try(const TqFast& f, const void* x, int32_t dtype, int64_t 
   if (!qm_serves(f, dtype, ld, dst, want_qjl)) return false;
 #define TQ_CASE(B)                                                                                           \
   case B:                                                                                                    \
-    *rc = dtype == TQ_F16 ? launch_mma<__half, B>(f, (const __half*)x, ld, n, dst, st)                       \
-                          : launch_mma<__nv_bfloat16, B>(f, (const __nv_bfloat16*)x, ld, n, dst, st);        \
+    *rc = dtype == TQ_F16    ? launch_mma<__half, B>(f, (const __half*)x, ld, n, dst, st)                    \
+          : dtype == TQ_BF16 ? launch_mma<__nv_bfloat16, B>(f, (const __nv_bfloat16*)x, ld, n, dst, st)      \
+                             : launch_mma<float, B>(f, (const float*)x, ld, n, dst, st);                     \
     return true;
   switch (f.bits) {
     TQ_CASE(2)
