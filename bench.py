@@ -791,6 +791,9 @@ def main():
         return
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1:
+        # the one line on stdout is the JSON line: NCCL's version banner (NCCL_DEBUG=VERSION) would come before it
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
         import torch
         import torch.distributed as dist
         local = int(os.environ.get("LOCAL_RANK", "0"))
