@@ -144,8 +144,9 @@ __device__ __forceinline__ void pf_lut_fill(uint8_t* lut, const uint16_t* c16, i
 
 // One token's packed indices (16*BITS bytes at `src`) -> 128 fp16 values written as sixteen 16-byte rows of the
 // operand tile: chunk c (dims 8c..8c+7) goes to tile + c*128 (+ the token's row offset, already in `dst`).
-template <int BITS>
-__device__ __forceinline__ void pf_dequant_token(const uint8_t* src, uint8_t* dst, uint32_t lut_base) {
+// SCALED: every pair is multiplied by `scale2` (one fp16 factor in both halves) on its way to the tile.
+template <int BITS, bool SCALED = false>
+__device__ __forceinline__ void pf_dequant_token(const uint8_t* src, uint8_t* dst, uint32_t lut_base, uint32_t scale2 = 0) {
   constexpr int SH = PfLut<BITS>::SHIFT;
   constexpr uint32_t MASK = ((1u << (2 * BITS)) - 1) << SH;
   constexpr int NW = 4 * BITS;  // 32-bit words per token
@@ -173,6 +174,7 @@ __device__ __forceinline__ void pf_dequant_token(const uint8_t* src, uint8_t* ds
         f = __funnelshift_l(w[k + 1 < NW ? k + 1 : k], w[k], o) >> (32 - 2 * BITS - SH);
       }
       o4[p] = pf_lds((f & MASK) + lut_base);
+      if constexpr (SCALED) asm("mul.f16x2 %0, %0, %1;" : "+r"(o4[p]) : "r"(scale2));
     }
     *reinterpret_cast<uint4*>(dst + c * 128) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
   }
@@ -264,7 +266,6 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
            *o_done = bars + 10;
   uint32_t* tbase = reinterpret_cast<uint32_t*>(sm + SP::OFF_BAR + 96);
   volatile int* fail = reinterpret_cast<volatile int*>(sm + SP::OFF_BAR + 104);
-  uint32_t* vmax = reinterpret_cast<uint32_t*>(sm + SP::OFF_BAR + 112);   // per buffer: largest V scale of the page (bits)
   float* scales = reinterpret_cast<float*>(sm + SP::OFF_SC);
   uint8_t* ktile = sm + SP::OFF_KT;
   uint8_t* vtile = sm + SP::OFF_VT;
@@ -414,7 +415,6 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
       if (!pf_wait_warp(&s_full[bf], ph)) { *fail = 1; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float4* ksc4 = reinterpret_cast<const float4*>(scales + bf * 256);
-      const float4* vsc4 = ksc4 + 32;
       const uint32_t ts = tm + TSc + 128 * bf;
       const int t0 = (page_lo + i) * PT;
       // a page that every row of this warp sees completely needs no causal mask (rows without a query count as
@@ -444,10 +444,6 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
       // The row maximum moves only when it grows by more than 2^PF2_SLACK (probabilities stay below 2^PF2_SLACK).
       // O lives in tensor memory and is being accumulated by the MMAs: a rescale waits for the product of the
       // page before, multiplies the row in place, and only then lets this page's product start (p_ready below).
-      // The reference follows score + log2(largest V scale of the page) rather than the score alone: P * (V scale)
-      // is stored as fp16, and with this reference it stays below 2^(2 PF2_SLACK) whatever the norms of the values
-      // are (a higher reference scales p, the row sum and O alike; the final division removes it).
-      mx += fmaxf(log2f(__uint_as_float(vmax[bf])), -100.0f);
       float resc = 1.0f;
       if (i == 0) {
         // the reference starts PF2_SLACK above the first page's maximum: a later page then moves it only when it
@@ -471,19 +467,19 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
-      // pass 2: probabilities (masked scores are -inf and give 0), row sum, P * (V scale) as packed fp16
+      // pass 2: probabilities (masked scores are -inf and give 0), row sum, P as packed fp16 (the V scales are in the
+      // V operand tile)
       const float m_use = m_run == -INFINITY ? 0.f : m_run;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t u[16];
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
-          const float4 s4 = vsc4[8 * c + (j >> 2)];
           const float p0 = pf_exp2(sv[32 * c + j] - m_use), p1 = pf_exp2(sv[32 * c + j + 1] - m_use);
           const float p2 = pf_exp2(sv[32 * c + j + 2] - m_use), p3 = pf_exp2(sv[32 * c + j + 3] - m_use);
           l_run += (p0 + p1) + (p2 + p3);
-          u[j >> 1] = pf_pack(p0 * s4.x, p1 * s4.y);
-          u[(j >> 1) + 1] = pf_pack(p2 * s4.z, p3 * s4.w);
+          u[j >> 1] = pf_pack(p0, p1);
+          u[(j >> 1) + 1] = pf_pack(p2, p3);
         }
         tmem_st16(ts + 16 * c, u);  // P chunk c overlays S columns that have been consumed
       }
@@ -615,7 +611,6 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
       bool ok = !*fail;
       if (ok && i >= 2) ok = pf_wait(&o_done[bf], (uint32_t)(((i - 2) >> 1) & 1));
       if (ok) ok = pf_wait(&rec_full[bf], ph);
-      if (tid == 128) vmax[bf] = 0u;    // ordered before the maxima below by the producers' barrier that follows
       if (!producers_all(ok)) {  // the 128 producers go on or give up together (they share a named barrier below)
         *fail = 1;
         break;
@@ -623,19 +618,18 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
       const uint8_t* st = stage0 + (size_t)bf * rec;
       pf_dequant_token<KB>(st + P.L.k_idx_off + rtid * (16 * KB), ktile + bf * 32768 + tile_row, lk_base);
       scales[bf * 256 + rtid] = reinterpret_cast<const float*>(st + P.L.k_scale_off)[rtid];
-      {
-        // the page's largest V scale over the tokens that exist (scales are >= 0: their bit patterns order like
-        // integers); the row warps fold its logarithm into the softmax reference so that p * scale fits fp16
-        const float vsc = reinterpret_cast<const float*>(st + P.L.v_scale_off)[rtid];
-        scales[bf * 256 + 128 + rtid] = vsc;
-        float mv = (page_lo + i) * PT + rtid < kv_len ? vsc : 0.f;
-#pragma unroll
-        for (int sh = 1; sh < 32; sh <<= 1) mv = fmaxf(mv, __shfl_xor_sync(0xffffffffu, mv, sh));
-        if (lane == 0) atomicMax(&vmax[bf], __float_as_uint(mv));
-      }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       pf_arrive(&k_ready[bf]);
-      pf_dequant_token<VB>(st + P.L.v_idx_off + rtid * (16 * VB), vtile + bf * 32768 + tile_row, lv_base);
+      {
+        // The token's V scale goes into its row of the operand tile (fp16 product, rounding 2^-11 per element), so
+        // that the P operand is the bare probability, bounded by 2^(2 PF2_SLACK) whatever the norms of the values
+        // are; a token past the end of the sequence may hold anything: its row is zeroed (its P is zero too, but
+        // 0 x inf would not be).  Scales beyond the fp16 range saturate.
+        const float vsc = (page_lo + i) * PT + rtid < kv_len ? reinterpret_cast<const float*>(st + P.L.v_scale_off)[rtid] : 0.f;
+        const __half2 s2 = __float2half2_rn(fminf(vsc, 65504.0f));
+        pf_dequant_token<VB, true>(st + P.L.v_idx_off + rtid * (16 * VB), vtile + bf * 32768 + tile_row, lv_base,
+                                   *reinterpret_cast<const uint32_t*>(&s2));
+      }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       pf_arrive(&v_ready[bf]);
       asm volatile("bar.sync 1, 128;" ::: "memory");   // every producer has read this record: its stage can be refilled
