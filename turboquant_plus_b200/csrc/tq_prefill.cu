@@ -11,7 +11,6 @@
 
 namespace {
 
-constexpr int PF_THREADS = 128;
 constexpr int PF_ROWS = 128;
 constexpr long long PF_WAIT_CYCLES = 1LL << 30;
 
@@ -19,8 +18,10 @@ __device__ __forceinline__ uint32_t sptr(const void* p) { return (uint32_t)__cvt
 
 __device__ __forceinline__ bool pf_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
-  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-               : "=r"(ok) : "r"(sptr(bar)), "r"(parity) : "memory");
+  // the hint lets the hardware keep the thread suspended for up to that many nanoseconds before the instruction returns
+  // false: a waiting role then spends few issue slots on polling
+  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(sptr(bar)), "r"(parity), "r"(20000u) : "memory");
   return ok != 0;
 }
 __device__ __forceinline__ bool pf_wait(uint64_t* bar, uint32_t parity) {
@@ -70,6 +71,24 @@ __device__ __forceinline__ float pf_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// two fp32 operations per instruction (sm_100 packed fp32), and the three-input maximum
+__device__ __forceinline__ float2 pf_mul2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n .reg .b64 ra, rb, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n mul.rn.f32x2 rd, ra, rb;\n mov.b64 {%0, %1}, rd;\n}\n"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 pf_add2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n .reg .b64 ra, rb, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n add.rn.f32x2 rd, ra, rb;\n mov.b64 {%0, %1}, rd;\n}\n"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float pf_max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ uint32_t pf_pack(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
@@ -80,14 +99,21 @@ __device__ __forceinline__ uint32_t pf_lds(uint32_t addr) {
   return v;
 }
 
-// 128-point sign * Walsh-Hadamard of a row held by one thread: y = post (H/sqrt d) pre x
-__device__ __forceinline__ void row_wht128(float (&x)[TQ_D], const uint32_t (&pre)[4], const uint32_t (&post)[4]) {
+// 128-point sign * Walsh-Hadamard of a row, y = post (H/sqrt d) pre x, held by two threads, 64 elements each (thread `half` has elements 64 half ... 64 half + 63):
+// a 64-point transform in registers, then the last butterfly through `xs` ([element][row] floats, 64 KB of shared
+// memory that nothing else uses meanwhile).  Called by all 256 row threads (named barrier 2).
+constexpr int PF_HALF = TQ_D / 2;
+__device__ __forceinline__ void rows_sync() { asm volatile("bar.sync 2, 256;" ::: "memory"); }
+__device__ __forceinline__ void row_wht128_pair(float (&x)[PF_HALF], const uint32_t (&pre)[4], const uint32_t (&post)[4],
+                                                int half, float* xs, int r) {
+  const uint32_t pre0 = half ? pre[2] : pre[0], pre1 = half ? pre[3] : pre[1];
+  const uint32_t post0 = half ? post[2] : post[0], post1 = half ? post[3] : post[1];
 #pragma unroll
-  for (int e = 0; e < TQ_D; ++e) x[e] = ((pre[e >> 5] >> (e & 31)) & 1u) ? -x[e] : x[e];
+  for (int e = 0; e < PF_HALF; ++e) x[e] = (((e < 32 ? pre0 : pre1) >> (e & 31)) & 1u) ? -x[e] : x[e];
 #pragma unroll
-  for (int h = 1; h < TQ_D; h <<= 1) {
+  for (int h = 1; h < PF_HALF; h <<= 1) {
 #pragma unroll
-    for (int i = 0; i < TQ_D; ++i) {
+    for (int i = 0; i < PF_HALF; ++i) {
       if ((i & h) == 0) {
         const float a = x[i], b = x[i + h];
         x[i] = a + b;
@@ -96,7 +122,14 @@ __device__ __forceinline__ void row_wht128(float (&x)[TQ_D], const uint32_t (&pr
     }
   }
 #pragma unroll
-  for (int e = 0; e < TQ_D; ++e) x[e] = (((post[e >> 5] >> (e & 31)) & 1u) ? -x[e] : x[e]) * TQ_RSQRT_D;
+  for (int e = 0; e < PF_HALF; ++e) xs[(PF_HALF * half + e) * PF_ROWS + r] = x[e];
+  rows_sync();
+#pragma unroll
+  for (int e = 0; e < PF_HALF; ++e) {
+    const float y = xs[(PF_HALF * (half ^ 1) + e) * PF_ROWS + r];
+    const float z = half ? y - x[e] : x[e] + y;
+    x[e] = ((((e < 32 ? post0 : post1) >> (e & 31)) & 1u) ? -z : z) * TQ_RSQRT_D;
+  }
 }
 
 struct PrefillParams {
@@ -125,22 +158,6 @@ template <int BITS> struct PfLut {
   static constexpr int SHIFT = REPL ? 7 : 2;
   static constexpr int BYTES = ENTRIES << SHIFT;
 };
-
-template <int BITS>
-__device__ __forceinline__ void pf_lut_fill(uint8_t* lut, const uint16_t* c16, int tid) {
-  using T = PfLut<BITS>;
-  if (T::REPL) {
-    for (int i = tid; i < T::ENTRIES * 8; i += PF_THREADS) {
-      const int e = i >> 3;
-      const uint32_t v = (uint32_t)c16[e >> BITS] | ((uint32_t)c16[e & ((1 << BITS) - 1)] << 16);
-      reinterpret_cast<uint4*>(lut)[i] = make_uint4(v, v, v, v);
-    }
-  } else {
-    uint32_t* w = reinterpret_cast<uint32_t*>(lut);
-    for (int e = tid; e < T::ENTRIES; e += PF_THREADS)
-      w[e] = (uint32_t)c16[e >> BITS] | ((uint32_t)c16[e & ((1 << BITS) - 1)] << 16);
-  }
-}
 
 // One token's packed indices (16*BITS bytes at `src`) -> 128 fp16 values written as sixteen 16-byte rows of the
 // operand tile: chunk c (dims 8c..8c+7) goes to tile + c*128 (+ the token's row offset, already in `dst`).
@@ -173,7 +190,7 @@ __device__ __forceinline__ void pf_dequant_token(const uint8_t* src, uint8_t* ds
       } else {
         f = __funnelshift_l(w[k + 1 < NW ? k + 1 : k], w[k], o) >> (32 - 2 * BITS - SH);
       }
-      o4[p] = pf_lds((f & MASK) + lut_base);
+      o4[p] = pf_lds((f & MASK) | lut_base);   // the table starts on a multiple of its size: one logic instruction
       if constexpr (SCALED) asm("mul.f16x2 %0, %0, %1;" : "+r"(o4[p]) : "r"(scale2));
     }
     *reinterpret_cast<uint4*>(dst + c * 128) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
@@ -183,12 +200,18 @@ __device__ __forceinline__ void pf_dequant_token(const uint8_t* src, uint8_t* ds
 
 // ------------------------------------------------------------------------------------------
 // k_prefill_attn2: the work split over specialised warps (one CTA per SM, 288 threads):
-//   warps 0-3  rows: thread r owns row r = lane r of tensor memory: reads S, online softmax, writes P, rescales O
-//              (lazily: only when its row maximum grows by more than 2^4), epilogue;
-//   warps 4-7  producer: thread t dequantizes token t of the page (K, then V) into double-buffered operand tiles
-//              and copies the per-token scales beside them; one of them issues the bulk copies of the page records;
-//   warp 8     one lane issues every tcgen05.mma: S_{i+1} = Q K_{i+1}^T is queued before O += P_i V_i, so the
+//   warps 0-7  rows: two threads per row r = lane r of tensor memory (warps w and w + 4 reach the same 32 lanes), one
+//              per half of a page's 128 score columns: reads S, online softmax (the halves exchange their maxima
+//              through shared memory), writes P, rescales O (lazily: only when the row maximum grows by more than
+//              2^4); the thread of the first half also stages the query and writes the output;
+//   warps 8-15 producer: thread t of warps 8-11 dequantizes the K row of token t of the page, thread t of warps
+//              12-15 its V row (times the V scale), into double-buffered operand tiles; the K scales are copied beside
+//              them; one of them issues the bulk copies of the page records;
+//   warp 16    one lane issues every tcgen05.mma: S_{i+1} = Q K_{i+1}^T is queued before O += P_i V_i, so the
 //              tensor core works on the next page while the row warps are in the softmax of this one.
+// (With one warp per row quarter and one per token quarter -- nine warps -- the row warps needed 4,200 cycles per
+// page and the producers 3,450, against 1,630 of tensor work: two warps per scheduler cannot hide their own
+// latencies.  Seventeen warps give every scheduler four.)
 // Tensor memory, all 512 columns: Q hi 0-63 | Q lo 64-127 | S0 128-255 | S1 256-383 | O 384-511 (fp32, accumulated
 // by the MMAs across pages).  P overlays the first 64 columns of its S buffer.  Hand-offs are mbarriers (counts in
 // brackets): k_ready/v_ready [128 producer arrivals], s_full/o_done [tcgen05.commit], p_ready [128 row arrivals];
@@ -196,17 +219,17 @@ __device__ __forceinline__ void pf_dequant_token(const uint8_t* src, uint8_t* ds
 // wait is bounded; a role that gives up raises the CTA's fail flag, the others see it or run out of time
 // themselves, and the tensor memory is released on every path.
 // ------------------------------------------------------------------------------------------
-constexpr int PF2_THREADS = 288;
+constexpr int PF2_THREADS = 544;
 constexpr float PF2_SLACK = 4.0f;
 
 template <int KB, int VB> struct PfSmem2 {
-  static constexpr int LK = PfLut<KB>::BYTES, LV = PfLut<VB>::BYTES;
-  static constexpr int ALIGN = 128;
+  static constexpr int ALIGN = 8192;                    // each table starts on a multiple of its size (at most 8 KB)
   static constexpr int OFF_K = 0;
-  static constexpr int OFF_V = LK;
-  static constexpr int OFF_BAR = LK + LV;               // 12 mbarriers, tensor-memory base, fail flag
-  static constexpr int OFF_SC = OFF_BAR + 128;          // float scales[2 buffers][K, V][128 tokens]
-  static constexpr int OFF_KT = OFF_SC + 2048;          // K operand tiles, 2 x 32 KB
+  static constexpr int OFF_V = 8192;
+  static constexpr int OFF_BAR = 16384;              // 12 mbarriers, tensor-memory base, fail flag, 4 exchange mbarriers
+  static constexpr int OFF_SC = OFF_BAR + 256;          // float scales[2 buffers][K, -][128 tokens], then the row
+                                                        // halves' exchange area float[2 buffers][2 halves][128 rows]
+  static constexpr int OFF_KT = OFF_SC + 4096;          // K operand tiles, 2 x 32 KB
   static constexpr int OFF_VT = OFF_KT + 65536;         // V operand tiles
   static constexpr int OFF_ST = OFF_VT + 65536;         // two page records
   static size_t bytes(int record_bytes) { return (size_t)ALIGN + OFF_ST + 2 * (size_t)record_bytes; }
@@ -223,15 +246,14 @@ __device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t (&v)[32]
         "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
         "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31]) : "memory");
 }
-__device__ __forceinline__ void rows_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
 // bounded wait whose verdict is the same in every lane of the warp (warp-collective tcgen05 instructions follow)
 __device__ __forceinline__ bool pf_wait_warp(uint64_t* bar, uint32_t parity) {
   return __all_sync(0xffffffffu, pf_wait(bar, parity));
 }
-// AND of a predicate over the 128 producer threads (named barrier 1)
+// AND of a predicate over the 256 producer threads (named barrier 1)
 __device__ __forceinline__ bool producers_all(bool ok) {
   uint32_t r;
-  asm volatile("{\n .reg .pred p, q;\n setp.ne.b32 p, %1, 0;\n bar.red.and.pred q, 1, 128, p;\n selp.u32 %0, 1, 0, q;\n}\n"
+  asm volatile("{\n .reg .pred p, q;\n setp.ne.b32 p, %1, 0;\n bar.red.and.pred q, 1, 256, p;\n selp.u32 %0, 1, 0, q;\n}\n"
                : "=r"(r) : "r"((uint32_t)ok) : "memory");
   return r != 0;
 }
@@ -245,9 +267,11 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
   const int PT = P.L.page_tokens;  // 128 (checked on the host)
   const int kv_len = P.kv_lens[b];
   const int nrows = P.tq * P.group;
-  const int rtid = tid & 127;                        // row (warps 0-3) or token (warps 4-7) this thread serves
+  const int rtid = tid & 127;                        // row (warps 0-7) or token (warps 8-15) this thread serves
   const int row = rb * PF_ROWS + rtid;
-  const bool is_row = tid < 128, is_prod = tid >= 128 && tid < 256;
+  const bool is_row = tid < 256, is_prod = tid >= 256 && tid < 512;
+  const bool is_prim = tid < 128;                    // the row thread that stages the query and writes the output
+  const int hf = (tid >> 7) & 1;                     // row threads: half of a page's columns; producers: 0 = K, 1 = V
   const bool row_ok = is_row && row < nrows;
   const int qi = row_ok ? row / P.group : 0, hl = row_ok ? row - qi * P.group : 0;
   const int pos = row_ok ? kv_len - P.tq + qi : -1;
@@ -264,6 +288,7 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + SP::OFF_BAR);
   uint64_t *rec_full = bars, *k_ready = bars + 2, *v_ready = bars + 4, *s_full = bars + 6, *p_ready = bars + 8,
            *o_done = bars + 10;
+  uint64_t* xbar = bars + 16;   // one per row quarter: both halves' maxima of a page are in shared memory [64 arrivals]
   uint32_t* tbase = reinterpret_cast<uint32_t*>(sm + SP::OFF_BAR + 96);
   volatile int* fail = reinterpret_cast<volatile int*>(sm + SP::OFF_BAR + 104);
   float* scales = reinterpret_cast<float*>(sm + SP::OFF_SC);
@@ -280,15 +305,17 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                      sptr(stage0 + (size_t)(i & 1) * rec)), "l"(src), "r"(rec), "r"(sptr(&rec_full[i & 1])) : "memory");
   };
-  if (tid == 128) {
+  if (tid == 256) {
     for (int i = 0; i < 2; ++i) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sptr(&rec_full[i])) : "memory");
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;" ::"r"(sptr(&k_ready[i])) : "memory");
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;" ::"r"(sptr(&v_ready[i])) : "memory");
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sptr(&s_full[i])) : "memory");
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;" ::"r"(sptr(&p_ready[i])) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 256;" ::"r"(sptr(&p_ready[i])) : "memory");
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sptr(&o_done[i])) : "memory");
     }
+    for (int i = 0; i < 4; ++i)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 64;" ::"r"(sptr(&xbar[i])) : "memory");
     *fail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     if (np > 0) issue(0);
@@ -298,8 +325,8 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sptr(tbase)), "r"(512u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  if (!is_row) {
-    // table fill by the 160 threads that do not rotate a query
+  if (!is_prim) {
+    // table fill by the 416 threads that do not rotate a query
     for (int i = tid - 128; i < PfLut<KB>::BYTES / 16; i += PF2_THREADS - 128) {
       if (PfLut<KB>::REPL) {
         const int e = i >> 3;
@@ -332,12 +359,13 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
     }
   }
 
-  // ---- prologue (row warps): this row's query, rotated by the K rotation, scaled, fp16 hi + lo into tensor memory ----
-  float o[TQ_D];
+  // ---- prologue (row warps): this row's query, rotated by the K rotation, scaled, fp16 hi + lo into tensor memory;
+  // each of the row's two threads holds one half of its elements ----
+  float o[PF_HALF];
   if (is_row) {
-    const size_t qoff = (((size_t)b * P.tq + qi) * P.hq + (size_t)kvh * P.group + hl) * TQ_D;
+    const size_t qoff = (((size_t)b * P.tq + qi) * P.hq + (size_t)kvh * P.group + hl) * TQ_D + PF_HALF * hf;
 #pragma unroll
-    for (int e = 0; e < TQ_D; e += 4) {
+    for (int e = 0; e < PF_HALF; e += 4) {
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
       if (row_ok) {
         if (P.q_dtype == TQ_F32) {
@@ -356,25 +384,26 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
       }
       o[e] = v.x; o[e + 1] = v.y; o[e + 2] = v.z; o[e + 3] = v.w;
     }
+    float* xs = reinterpret_cast<float*>(ktile);  // [k][row], 64 KB: the operand tiles are not in use yet
     if (P.k_rot_t) {
-      // dense rotation: stage the rows transposed in the (still unused) operand tiles, then y = R x per thread
-      float* xs = reinterpret_cast<float*>(ktile);  // [k][row], 64 KB
+      // dense rotation: the rows staged transposed, then this thread's 64 elements of y = R x
 #pragma unroll
-      for (int k = 0; k < TQ_D; ++k) xs[k * PF_ROWS + rtid] = o[k];
+      for (int k = 0; k < PF_HALF; ++k) xs[(PF_HALF * hf + k) * PF_ROWS + rtid] = o[k];
+      rows_sync();
 #pragma unroll
-      for (int j = 0; j < TQ_D; ++j) o[j] = 0.f;
+      for (int j = 0; j < PF_HALF; ++j) o[j] = 0.f;
       for (int k = 0; k < TQ_D; ++k) {
         const float xv = xs[k * PF_ROWS + rtid];
-        const float4* rr = reinterpret_cast<const float4*>(P.k_rot_t + (size_t)k * TQ_D);
+        const float4* rr = reinterpret_cast<const float4*>(P.k_rot_t + (size_t)k * TQ_D + PF_HALF * hf);
 #pragma unroll
-        for (int j = 0; j < TQ_D; j += 4) {
+        for (int j = 0; j < PF_HALF; j += 4) {
           const float4 r4 = __ldg(rr + (j >> 2));
           o[j] = fmaf(r4.x, xv, o[j]); o[j + 1] = fmaf(r4.y, xv, o[j + 1]);
           o[j + 2] = fmaf(r4.z, xv, o[j + 2]); o[j + 3] = fmaf(r4.w, xv, o[j + 3]);
         }
       }
     } else {
-      row_wht128(o, fk.s1, fk.s2);
+      row_wht128_pair(o, fk.s1, fk.s2, hf, xs, rtid);
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -385,62 +414,73 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
 
   if (is_row) {
     // =========================== row warps ===========================
-    const uint32_t tm = tb + ((uint32_t)(warp * 32) << 16);  // this warp's 32 lanes
+    const uint32_t tm = tb + ((uint32_t)((warp & 3) * 32) << 16);  // this warp's 32 lanes
+    float* xch = scales + 512;                                     // [buffer][half][row]
     {
       const float sk = P.qscale / fk.lut_alpha;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t u[16], ul[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const float a = o[32 * c + 2 * j] * sk, bq = o[32 * c + 2 * j + 1] * sk;
           const __half2 h = __floats2half2_rn(a, bq);
-          const float2 hf = __half22float2(h);
+          const float2 hv = __half22float2(h);
           u[j] = *reinterpret_cast<const uint32_t*>(&h);
-          ul[j] = pf_pack(a - hf.x, bq - hf.y);
+          ul[j] = pf_pack(a - hv.x, bq - hv.y);
         }
-        tmem_st16(tm + TQc + 16 * c, u);
-        tmem_st16(tm + TQLc + 16 * c, ul);
+        tmem_st16(tm + TQc + 32 * hf + 16 * c, u);
+        tmem_st16(tm + TQLc + 32 * hf + 16 * c, ul);
       }
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
-    asm volatile("bar.sync 3, 160;" ::: "memory");   // with the MMA warp: the queries are in tensor memory
+    asm volatile("bar.sync 3, 288;" ::: "memory");   // with the MMA warp: the queries are in tensor memory
 
-    float m_run = -INFINITY, l_run = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;   // l_run: this half's part of the row sum
     for (int i = 0; i < np; ++i) {
       if (*fail) break;
       const int bf = i & 1;
       const uint32_t ph = (uint32_t)((i >> 1) & 1);
       if (!pf_wait_warp(&s_full[bf], ph)) { *fail = 1; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const float4* ksc4 = reinterpret_cast<const float4*>(scales + bf * 256);
+      const float4* ksc4 = reinterpret_cast<const float4*>(scales + bf * 256 + 64 * hf);
       const uint32_t ts = tm + TSc + 128 * bf;
       const int t0 = (page_lo + i) * PT;
       // a page that every row of this warp sees completely needs no causal mask (rows without a query count as
       // seeing everything: nothing of theirs is stored)
       const bool masked = !__all_sync(0xffffffffu, !row_ok || t0 + PT - 1 <= pos);
-      // pass 1: scaled scores into registers, row maximum
-      float sv[128];
+      // pass 1: this half's scaled scores into registers, row maximum
+      float sv[64];
       float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
-        tmem_ld32(ts + 32 * c, v);
+        tmem_ld32(ts + 64 * hf + 32 * c, v);
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
           const float4 k4 = ksc4[8 * c + (j >> 2)];
-          const float kk[4] = {k4.x, k4.y, k4.z, k4.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int t = 32 * c + j + e;
-            float x = __uint_as_float(v[j + e]) * kk[e];
-            if (masked) x = (t0 + t <= pos) ? x : -INFINITY;
-            sv[t] = x;
-            mx = fmaxf(mx, x);
+          float2 x01 = pf_mul2(make_float2(__uint_as_float(v[j]), __uint_as_float(v[j + 1])), make_float2(k4.x, k4.y));
+          float2 x23 = pf_mul2(make_float2(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])), make_float2(k4.z, k4.w));
+          if (masked) {
+            const int tt = t0 + 64 * hf + 32 * c + j;
+            x01.x = tt <= pos ? x01.x : -INFINITY;
+            x01.y = tt + 1 <= pos ? x01.y : -INFINITY;
+            x23.x = tt + 2 <= pos ? x23.x : -INFINITY;
+            x23.y = tt + 3 <= pos ? x23.y : -INFINITY;
           }
+          sv[32 * c + j] = x01.x; sv[32 * c + j + 1] = x01.y;
+          sv[32 * c + j + 2] = x23.x; sv[32 * c + j + 3] = x23.y;
+          mx = pf_max3(mx, x01.x, x01.y);
+          mx = pf_max3(mx, x23.x, x23.y);
         }
       }
+      // the other half's maximum: both threads of a row then take the same decisions below.  (The arrival also tells
+      // the other half that this one has read its scores: the P columns that half writes overlay them.)
+      xch[(bf * 2 + hf) * PF_ROWS + rtid] = mx;
+      pf_arrive(&xbar[warp & 3]);
+      if (!pf_wait_warp(&xbar[warp & 3], (uint32_t)(i & 1))) { *fail = 1; break; }
+      mx = fmaxf(mx, xch[(bf * 2 + (hf ^ 1)) * PF_ROWS + rtid]);
       // The row maximum moves only when it grows by more than 2^PF2_SLACK (probabilities stay below 2^PF2_SLACK).
       // O lives in tensor memory and is being accumulated by the MMAs: a rescale waits for the product of the
       // page before, multiplies the row in place, and only then lets this page's product start (p_ready below).
@@ -458,47 +498,51 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
         if (!pf_wait_warp(&o_done[(i - 1) & 1], (uint32_t)(((i - 1) >> 1) & 1))) { *fail = 1; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {   // this half's 64 columns of O
           uint32_t v[32];
-          tmem_ld32(tm + TOc + 32 * c, v);
+          tmem_ld32(tm + TOc + 64 * hf + 32 * c, v);
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * resc);
-          tmem_st32(tm + TOc + 32 * c, v);
+          tmem_st32(tm + TOc + 64 * hf + 32 * c, v);
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
       // pass 2: probabilities (masked scores are -inf and give 0), row sum, P as packed fp16 (the V scales are in the
       // V operand tile)
       const float m_use = m_run == -INFINITY ? 0.f : m_run;
+      const float2 nm2 = make_float2(-m_use, -m_use);
+      float2 ls2 = make_float2(0.f, 0.f);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t u[16];
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          const float p0 = pf_exp2(sv[32 * c + j] - m_use), p1 = pf_exp2(sv[32 * c + j + 1] - m_use);
-          const float p2 = pf_exp2(sv[32 * c + j + 2] - m_use), p3 = pf_exp2(sv[32 * c + j + 3] - m_use);
-          l_run += (p0 + p1) + (p2 + p3);
-          u[j >> 1] = pf_pack(p0, p1);
-          u[(j >> 1) + 1] = pf_pack(p2, p3);
+        for (int j = 0; j < 32; j += 2) {
+          float2 p = pf_add2(make_float2(sv[32 * c + j], sv[32 * c + j + 1]), nm2);
+          p.x = pf_exp2(p.x);
+          p.y = pf_exp2(p.y);
+          ls2 = pf_add2(ls2, p);
+          u[j >> 1] = pf_pack(p.x, p.y);
         }
-        tmem_st16(ts + 16 * c, u);  // P chunk c overlays S columns that have been consumed
+        tmem_st16(ts + 32 * hf + 16 * c, u);  // P overlays S columns 0-63, which the first half has consumed
       }
+      l_run += ls2.x + ls2.y;
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       pf_arrive(&p_ready[bf]);
     }
-    // the accumulated row of O, once the last product has completed
+    // this thread's half of the accumulated row of O, once the last product has completed
+    scales[(hf * 2 + 1) * PF_ROWS + rtid] = l_run;   // the halves' parts of the row sum (slots otherwise unused)
 #pragma unroll
-    for (int j = 0; j < TQ_D; ++j) o[j] = 0.f;
+    for (int j = 0; j < PF_HALF; ++j) o[j] = 0.f;
     if (np > 0 && !*fail) {
       if (!pf_wait_warp(&o_done[(np - 1) & 1], (uint32_t)(((np - 1) >> 1) & 1))) {
         *fail = 1;
       } else {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t v[32];
-          tmem_ld32(tm + TOc + 32 * c, v);
+          tmem_ld32(tm + TOc + PF_HALF * hf + 32 * c, v);
 #pragma unroll
           for (int j = 0; j < 32; ++j) o[32 * c + j] = __uint_as_float(v[j]);
         }
@@ -507,20 +551,21 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();  // every role is done with tensor memory
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tb), "r"(512u) : "memory");
+    l_run = scales[PF_ROWS + rtid] + scales[3 * PF_ROWS + rtid];
     // A CTA that gave up a wait reports it, writes no partial and merges nothing, but still takes its ticket below:
     // the counter of its (sequence, KV head, row block) then returns to zero like after a clean call, and a later
     // call on the same workspace cannot elect its merger too early.
     const bool failed = *fail != 0;   // stable: every role has passed the barrier above
     if (failed && tid == 0) atomicExch(P.status, 1);
     if (failed && ns <= 1) return;
-    // ---- split partial / merge by the last split / epilogue: the 128 row threads only ----
+    // ---- split partial / merge by the last split / epilogue: the 256 row threads only ----
     if (ns > 1) {
       const size_t slot0 = (((size_t)b * P.hkv + kvh) * P.row_blocks + rb) * P.num_splits;
       if (!failed) {
-        float4* po = reinterpret_cast<float4*>(P.part_o + ((slot0 + split) * PF_ROWS + tid) * TQ_D);
+        float4* po = reinterpret_cast<float4*>(P.part_o + ((slot0 + split) * PF_ROWS + rtid) * TQ_D + PF_HALF * hf);
 #pragma unroll
-        for (int j = 0; j < TQ_D; j += 4) po[j >> 2] = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
-        reinterpret_cast<float2*>(P.part_ml)[(slot0 + split) * PF_ROWS + tid] = make_float2(m_run, l_run);
+        for (int j = 0; j < PF_HALF; j += 4) po[j >> 2] = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+        if (is_prim) reinterpret_cast<float2*>(P.part_ml)[(slot0 + split) * PF_ROWS + rtid] = make_float2(m_run, l_run);
       }
       __threadfence();
       rows_sync();
@@ -539,17 +584,17 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
       __threadfence();
       float M = -INFINITY;
       for (int s_i = 0; s_i < ns; ++s_i)
-        M = fmaxf(M, __ldcg(reinterpret_cast<const float2*>(P.part_ml) + (slot0 + s_i) * PF_ROWS + tid).x);
+        M = fmaxf(M, __ldcg(reinterpret_cast<const float2*>(P.part_ml) + (slot0 + s_i) * PF_ROWS + rtid).x);
 #pragma unroll
-      for (int j = 0; j < TQ_D; ++j) o[j] = 0.f;
+      for (int j = 0; j < PF_HALF; ++j) o[j] = 0.f;
       l_run = 0.f;
       for (int s_i = 0; s_i < ns; ++s_i) {
-        const float2 ml = __ldcg(reinterpret_cast<const float2*>(P.part_ml) + (slot0 + s_i) * PF_ROWS + tid);
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(P.part_ml) + (slot0 + s_i) * PF_ROWS + rtid);
         const float f = ml.x == -INFINITY ? 0.f : exp2f(ml.x - M);
         l_run = fmaf(ml.y, f, l_run);
-        const float4* po = reinterpret_cast<const float4*>(P.part_o + ((slot0 + s_i) * PF_ROWS + tid) * TQ_D);
+        const float4* po = reinterpret_cast<const float4*>(P.part_o + ((slot0 + s_i) * PF_ROWS + rtid) * TQ_D + PF_HALF * hf);
 #pragma unroll
-        for (int j = 0; j < TQ_D; j += 4) {
+        for (int j = 0; j < PF_HALF; j += 4) {
           const float4 v = __ldcg(po + (j >> 2));
           o[j] = fmaf(v.x, f, o[j]); o[j + 1] = fmaf(v.y, f, o[j + 1]);
           o[j + 2] = fmaf(v.z, f, o[j + 2]); o[j + 3] = fmaf(v.w, f, o[j + 3]);
@@ -559,40 +604,41 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
     {
       const float inv = l_run > 0.f ? 1.0f / (l_run * fv.lut_alpha) : 0.f;
 #pragma unroll
-      for (int j = 0; j < TQ_D; ++j) o[j] *= inv;
+      for (int j = 0; j < PF_HALF; ++j) o[j] *= inv;
+      float* ys = reinterpret_cast<float*>(ktile);  // [k][row]; the operand tiles are idle by now
       if (P.v_rot) {
-        float* ys = reinterpret_cast<float*>(ktile);  // [k][row]; the operand tiles are idle by now
 #pragma unroll
-        for (int k = 0; k < TQ_D; ++k) ys[k * PF_ROWS + tid] = o[k];
+        for (int k = 0; k < PF_HALF; ++k) ys[(PF_HALF * hf + k) * PF_ROWS + rtid] = o[k];
+        rows_sync();
 #pragma unroll
-        for (int j = 0; j < TQ_D; ++j) o[j] = 0.f;
+        for (int j = 0; j < PF_HALF; ++j) o[j] = 0.f;
         for (int k = 0; k < TQ_D; ++k) {
-          const float yv = ys[k * PF_ROWS + tid];
-          const float4* rr = reinterpret_cast<const float4*>(P.v_rot + (size_t)k * TQ_D);
+          const float yv = ys[k * PF_ROWS + rtid];
+          const float4* rr = reinterpret_cast<const float4*>(P.v_rot + (size_t)k * TQ_D + PF_HALF * hf);
 #pragma unroll
-          for (int j = 0; j < TQ_D; j += 4) {
+          for (int j = 0; j < PF_HALF; j += 4) {
             const float4 r4 = __ldg(rr + (j >> 2));
             o[j] = fmaf(r4.x, yv, o[j]); o[j + 1] = fmaf(r4.y, yv, o[j + 1]);
             o[j + 2] = fmaf(r4.z, yv, o[j + 2]); o[j + 3] = fmaf(r4.w, yv, o[j + 3]);
           }
         }
       } else {
-        row_wht128(o, fv.s2, fv.s1);  // R^T = D1 (H/sqrt d) D2
+        row_wht128_pair(o, fv.s2, fv.s1, hf, ys, rtid);  // R^T = D1 (H/sqrt d) D2
       }
       if (row_ok) {
-        const size_t ooff = (((size_t)b * P.tq + qi) * P.hq + (size_t)kvh * P.group + hl) * TQ_D;
+        const size_t ooff = (((size_t)b * P.tq + qi) * P.hq + (size_t)kvh * P.group + hl) * TQ_D + PF_HALF * hf;
         if (P.out_dtype == TQ_F32) {
           float4* op = reinterpret_cast<float4*>(reinterpret_cast<float*>(P.out) + ooff);
 #pragma unroll
-          for (int j = 0; j < TQ_D; j += 4) op[j >> 2] = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+          for (int j = 0; j < PF_HALF; j += 4) op[j >> 2] = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
         } else if (P.out_dtype == TQ_F16) {
           uint2* op = reinterpret_cast<uint2*>(reinterpret_cast<__half*>(P.out) + ooff);
 #pragma unroll
-          for (int j = 0; j < TQ_D; j += 4) op[j >> 2] = make_uint2(pf_pack(o[j], o[j + 1]), pf_pack(o[j + 2], o[j + 3]));
+          for (int j = 0; j < PF_HALF; j += 4) op[j >> 2] = make_uint2(pf_pack(o[j], o[j + 1]), pf_pack(o[j + 2], o[j + 3]));
         } else {
           __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(P.out) + ooff;
 #pragma unroll
-          for (int j = 0; j < TQ_D; ++j) op[j] = __float2bfloat16_rn(o[j]);
+          for (int j = 0; j < PF_HALF; ++j) op[j] = __float2bfloat16_rn(o[j]);
         }
       }
     }
@@ -611,16 +657,17 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
       bool ok = !*fail;
       if (ok && i >= 2) ok = pf_wait(&o_done[bf], (uint32_t)(((i - 2) >> 1) & 1));
       if (ok) ok = pf_wait(&rec_full[bf], ph);
-      if (!producers_all(ok)) {  // the 128 producers go on or give up together (they share a named barrier below)
+      if (!producers_all(ok)) {  // the 256 producers go on or give up together (they share a named barrier below)
         *fail = 1;
         break;
       }
       const uint8_t* st = stage0 + (size_t)bf * rec;
-      pf_dequant_token<KB>(st + P.L.k_idx_off + rtid * (16 * KB), ktile + bf * 32768 + tile_row, lk_base);
-      scales[bf * 256 + rtid] = reinterpret_cast<const float*>(st + P.L.k_scale_off)[rtid];
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      pf_arrive(&k_ready[bf]);
-      {
+      if (hf == 0) {
+        pf_dequant_token<KB>(st + P.L.k_idx_off + rtid * (16 * KB), ktile + bf * 32768 + tile_row, lk_base);
+        scales[bf * 256 + rtid] = reinterpret_cast<const float*>(st + P.L.k_scale_off)[rtid];
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        pf_arrive(&k_ready[bf]);
+      } else {
         // The token's V scale goes into its row of the operand tile (fp16 product, rounding 2^-11 per element), so
         // that the P operand is the bare probability, bounded by 2^(2 PF2_SLACK) whatever the norms of the values
         // are; a token past the end of the sequence may hold anything: its row is zeroed (its P is zero too, but
@@ -629,18 +676,18 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
         const __half2 s2 = __float2half2_rn(fminf(vsc, 65504.0f));
         pf_dequant_token<VB, true>(st + P.L.v_idx_off + rtid * (16 * VB), vtile + bf * 32768 + tile_row, lv_base,
                                    *reinterpret_cast<const uint32_t*>(&s2));
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        pf_arrive(&v_ready[bf]);
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      pf_arrive(&v_ready[bf]);
-      asm volatile("bar.sync 1, 128;" ::: "memory");   // every producer has read this record: its stage can be refilled
-      if (tid == 128 && i + 2 < np) issue(i + 2);
+      asm volatile("bar.sync 1, 256;" ::: "memory");   // every producer has read this record: its stage can be refilled
+      if (tid == 256 && i + 2 < np) issue(i + 2);
     }
-    if (*fail && tid == 128) {  // copies in flight get the same bounded time before the CTA leaves
+    if (*fail && tid == 256) {  // copies in flight get the same bounded time before the CTA leaves
       for (int st_i = 0; st_i < 2; ++st_i) pf_wait(&rec_full[st_i], 0), pf_wait(&rec_full[st_i], 1);
     }
   } else {
     // =========================== MMA warp ===========================
-    asm volatile("bar.sync 3, 160;" ::: "memory");
+    asm volatile("bar.sync 3, 288;" ::: "memory");
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (lane == 0 && np > 0) {
       const uint32_t idesc_s = umma_idesc(128, 128, false), idesc_o = umma_idesc(128, 128, true);
