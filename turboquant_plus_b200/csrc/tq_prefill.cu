@@ -227,9 +227,10 @@ template <int KB, int VB> struct PfSmem2 {
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = 8192;
   static constexpr int OFF_BAR = 16384;              // 12 mbarriers, tensor-memory base, fail flag, 4 exchange mbarriers
-  static constexpr int OFF_SC = OFF_BAR + 256;          // float scales[2 buffers][K, -][128 tokens], then the row
-                                                        // halves' exchange area float[2 buffers][2 halves][128 rows]
-  static constexpr int OFF_KT = OFF_SC + 4096;          // K operand tiles, 2 x 32 KB
+  static constexpr int OFF_SC = OFF_BAR + 256;          // float K scales[4 slots][128 tokens], then the row halves'
+                                                        // exchange area float[2 buffers][2 halves][128 rows], then
+                                                        // their parts of the row sum float[2 halves][128 rows]
+  static constexpr int OFF_KT = OFF_SC + 5120;          // K operand tiles, 2 x 32 KB
   static constexpr int OFF_VT = OFF_KT + 65536;         // V operand tiles
   static constexpr int OFF_ST = OFF_VT + 65536;         // two page records
   static size_t bytes(int record_bytes) { return (size_t)ALIGN + OFF_ST + 2 * (size_t)record_bytes; }
@@ -250,10 +251,10 @@ __device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t (&v)[32]
 __device__ __forceinline__ bool pf_wait_warp(uint64_t* bar, uint32_t parity) {
   return __all_sync(0xffffffffu, pf_wait(bar, parity));
 }
-// AND of a predicate over the 256 producer threads (named barrier 1)
+// AND of a predicate over the 128 V producer threads (named barrier 1)
 __device__ __forceinline__ bool producers_all(bool ok) {
   uint32_t r;
-  asm volatile("{\n .reg .pred p, q;\n setp.ne.b32 p, %1, 0;\n bar.red.and.pred q, 1, 256, p;\n selp.u32 %0, 1, 0, q;\n}\n"
+  asm volatile("{\n .reg .pred p, q;\n setp.ne.b32 p, %1, 0;\n bar.red.and.pred q, 1, 128, p;\n selp.u32 %0, 1, 0, q;\n}\n"
                : "=r"(r) : "r"((uint32_t)ok) : "memory");
   return r != 0;
 }
@@ -444,7 +445,7 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
       const uint32_t ph = (uint32_t)((i >> 1) & 1);
       if (!pf_wait_warp(&s_full[bf], ph)) { *fail = 1; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const float4* ksc4 = reinterpret_cast<const float4*>(scales + bf * 256 + 64 * hf);
+      const float4* ksc4 = reinterpret_cast<const float4*>(scales + (i & 3) * PF_ROWS + 64 * hf);
       const uint32_t ts = tm + TSc + 128 * bf;
       const int t0 = (page_lo + i) * PT;
       // a page that every row of this warp sees completely needs no causal mask (rows without a query count as
@@ -531,7 +532,7 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
       pf_arrive(&p_ready[bf]);
     }
     // this thread's half of the accumulated row of O, once the last product has completed
-    scales[(hf * 2 + 1) * PF_ROWS + rtid] = l_run;   // the halves' parts of the row sum (slots otherwise unused)
+    scales[(8 + hf) * PF_ROWS + rtid] = l_run;   // the halves' parts of the row sum
 #pragma unroll
     for (int j = 0; j < PF_HALF; ++j) o[j] = 0.f;
     if (np > 0 && !*fail) {
@@ -551,7 +552,7 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();  // every role is done with tensor memory
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tb), "r"(512u) : "memory");
-    l_run = scales[PF_ROWS + rtid] + scales[3 * PF_ROWS + rtid];
+    l_run = scales[8 * PF_ROWS + rtid] + scales[9 * PF_ROWS + rtid];
     // A CTA that gave up a wait reports it, writes no partial and merges nothing, but still takes its ticket below:
     // the counter of its (sequence, KV head, row block) then returns to zero like after a clean call, and a later
     // call on the same workspace cannot elect its merger too early.
@@ -650,24 +651,34 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
     const uint32_t lk_base = sptr(sm + SP::OFF_K) + (PfLut<KB>::REPL ? lane * 4 : 0);
     const uint32_t lv_base = sptr(sm + SP::OFF_V) + (PfLut<VB>::REPL ? lane * 4 : 0);
     const uint32_t tile_row = (uint32_t)(rtid >> 3) * 2048 + (uint32_t)(rtid & 7) * 16;  // token rtid inside an operand tile
-    for (int i = 0; i < np; ++i) {
-      const int bf = i & 1;
-      const uint32_t ph = (uint32_t)((i >> 1) & 1);
-      // tiles and scales of buffer bf are free once the product of page i - 2 has completed
-      bool ok = !*fail;
-      if (ok && i >= 2) ok = pf_wait(&o_done[bf], (uint32_t)(((i - 2) >> 1) & 1));
-      if (ok) ok = pf_wait(&rec_full[bf], ph);
-      if (!producers_all(ok)) {  // the 256 producers go on or give up together (they share a named barrier below)
-        *fail = 1;
-        break;
-      }
-      const uint8_t* st = stage0 + (size_t)bf * rec;
-      if (hf == 0) {
+    if (hf == 0) {
+      // K producers.  The K tile of buffer bf is free once S of page i - 2 is complete, and so is the scale slot
+      // i & 3 (the rows finished page i - 4 long before): they run one page ahead of the V producers, whose tile is
+      // free only after the product of page i - 2, and S of the next page is ready before the rows ask for it.
+      for (int i = 0; i < np; ++i) {
+        const int bf = i & 1;
+        if (*fail) break;
+        if (i >= 2 && !pf_wait(&s_full[bf], (uint32_t)(((i - 2) >> 1) & 1))) { *fail = 1; break; }
+        if (!pf_wait(&rec_full[bf], (uint32_t)((i >> 1) & 1))) { *fail = 1; break; }
+        const uint8_t* st = stage0 + (size_t)bf * rec;
         pf_dequant_token<KB>(st + P.L.k_idx_off + rtid * (16 * KB), ktile + bf * 32768 + tile_row, lk_base);
-        scales[bf * 256 + rtid] = reinterpret_cast<const float*>(st + P.L.k_scale_off)[rtid];
+        scales[(i & 3) * PF_ROWS + rtid] = reinterpret_cast<const float*>(st + P.L.k_scale_off)[rtid];
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        pf_arrive(&k_ready[bf]);
-      } else {
+        pf_arrive(&k_ready[bf]);   // also: this thread has read its part of the record
+      }
+    } else {
+      // V producers; one of them refills a record's stage once both groups have read it
+      for (int i = 0; i < np; ++i) {
+        const int bf = i & 1;
+        const uint32_t ph = (uint32_t)((i >> 1) & 1);
+        bool ok = !*fail;
+        if (ok && i >= 2) ok = pf_wait(&o_done[bf], (uint32_t)(((i - 2) >> 1) & 1));
+        if (ok) ok = pf_wait(&rec_full[bf], ph);
+        if (!producers_all(ok)) {  // the 128 V producers go on or give up together (they share a named barrier below)
+          *fail = 1;
+          break;
+        }
+        const uint8_t* st = stage0 + (size_t)bf * rec;
         // The token's V scale goes into its row of the operand tile (fp16 product, rounding 2^-11 per element), so
         // that the P operand is the bare probability, bounded by 2^(2 PF2_SLACK) whatever the norms of the values
         // are; a token past the end of the sequence may hold anything: its row is zeroed (its P is zero too, but
@@ -678,10 +689,13 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
                                    *reinterpret_cast<const uint32_t*>(&s2));
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         pf_arrive(&v_ready[bf]);
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // every V producer has read this record
+        if (tid == 384 && i + 2 < np) {
+          if (!pf_wait(&k_ready[bf], ph)) { *fail = 1; } else { issue(i + 2); }   // ... and every K producer
+        }
       }
-      asm volatile("bar.sync 1, 256;" ::: "memory");   // every producer has read this record: its stage can be refilled
-      if (tid == 256 && i + 2 < np) issue(i + 2);
     }
+    asm volatile("bar.sync 5, 256;" ::: "memory");   // both groups have left their loops: no copy will be issued any more
     if (*fail && tid == 256) {  // copies in flight get the same bounded time before the CTA leaves
       for (int st_i = 0; st_i < 2; ++st_i) pf_wait(&rec_full[st_i], 0), pf_wait(&rec_full[st_i], 1);
     }
