@@ -7,6 +7,7 @@
 // (fp16 hi + lo halves), S, P and O all in tensor memory; the row warps do the online softmax between the two
 // products.  The kernel, its roles, its tensor-memory map and its hand-offs are described above k_prefill_attn2.
 // Every wait is bounded in time; a CTA that gives up sets the status word and still frees its tensor memory.
+#include <type_traits>
 #include "tq_internal.cuh"
 
 namespace {
@@ -57,6 +58,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&v)[32]) {
         "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
         "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
         "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(addr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
       : "r"(addr) : "memory");
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -454,28 +463,32 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
       // pass 1: this half's scaled scores into registers, row maximum
       float sv[64];
       float mx = -INFINITY;
+      auto pass1 = [&](auto masked_c) {   // two copies behind a warp-uniform branch: only the diagonal pages pay for the mask
+        constexpr bool MASKED = decltype(masked_c)::value;
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t v[32];
-        tmem_ld32(ts + 64 * hf + 32 * c, v);
+        for (int c = 0; c < 4; ++c) {   // sixteen columns at a time: with the 64 scores of the page, 96 registers hold
+          uint32_t v[16];
+          tmem_ld16(ts + 64 * hf + 16 * c, v);
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          const float4 k4 = ksc4[8 * c + (j >> 2)];
-          float2 x01 = pf_mul2(make_float2(__uint_as_float(v[j]), __uint_as_float(v[j + 1])), make_float2(k4.x, k4.y));
-          float2 x23 = pf_mul2(make_float2(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])), make_float2(k4.z, k4.w));
-          if (masked) {
-            const int tt = t0 + 64 * hf + 32 * c + j;
-            x01.x = tt <= pos ? x01.x : -INFINITY;
-            x01.y = tt + 1 <= pos ? x01.y : -INFINITY;
-            x23.x = tt + 2 <= pos ? x23.x : -INFINITY;
-            x23.y = tt + 3 <= pos ? x23.y : -INFINITY;
+          for (int j = 0; j < 16; j += 4) {
+            const float4 k4 = ksc4[4 * c + (j >> 2)];
+            float2 x01 = pf_mul2(make_float2(__uint_as_float(v[j]), __uint_as_float(v[j + 1])), make_float2(k4.x, k4.y));
+            float2 x23 = pf_mul2(make_float2(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])), make_float2(k4.z, k4.w));
+            if (MASKED) {
+              const int tt = t0 + 64 * hf + 16 * c + j;
+              x01.x = tt <= pos ? x01.x : -INFINITY;
+              x01.y = tt + 1 <= pos ? x01.y : -INFINITY;
+              x23.x = tt + 2 <= pos ? x23.x : -INFINITY;
+              x23.y = tt + 3 <= pos ? x23.y : -INFINITY;
+            }
+            sv[16 * c + j] = x01.x; sv[16 * c + j + 1] = x01.y;
+            sv[16 * c + j + 2] = x23.x; sv[16 * c + j + 3] = x23.y;
+            mx = pf_max3(mx, x01.x, x01.y);
+            mx = pf_max3(mx, x23.x, x23.y);
           }
-          sv[32 * c + j] = x01.x; sv[32 * c + j + 1] = x01.y;
-          sv[32 * c + j + 2] = x23.x; sv[32 * c + j + 3] = x23.y;
-          mx = pf_max3(mx, x01.x, x01.y);
-          mx = pf_max3(mx, x23.x, x23.y);
         }
-      }
+      };
+      if (masked) pass1(std::true_type{}); else pass1(std::false_type{});
       // the other half's maximum: both threads of a row then take the same decisions below.  (The arrival also tells
       // the other half that this one has read its scores: the P columns that half writes overlay them.)
       xch[(bf * 2 + hf) * PF_ROWS + rtid] = mx;
