@@ -723,6 +723,7 @@ bool tq_decode_g4_try(const tqatt::AttnParams& P, const TqFast& fk, const TqFast
   if (kf == K && vf == V) {                                                                                          \
     if (!layout_matches<K, V>(P.L)) return false;                                                                    \
     if (P.nodeq && K == 3 && V == 3) *rc = launch_attn_g4<3, 3, false, true>(P, fk, fv, st);                         \
+    else if (P.sparse_v && P.q_early) *rc = launch_attn_g4<K, V, true, false, 4>(P, fk, fv, st);                     \
     else if (P.sparse_v) *rc = launch_attn_g4<K, V, true, false>(P, fk, fv, st);                                     \
     else if (P.q_early) *rc = launch_attn_g4<K, V, false, false, 4>(P, fk, fv, st);                                  \
     else *rc = launch_attn_g4<K, V, false, false>(P, fk, fv, st);                                                    \

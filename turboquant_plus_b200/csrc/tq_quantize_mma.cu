@@ -80,6 +80,34 @@ __device__ __forceinline__ float qm_gt(float a, float b) {
   return d;
 }
 
+// packed fp32 arithmetic (two operations per instruction); operands are register pairs as the MMA leaves them
+__device__ __forceinline__ float2 qm_add2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n .reg .b64 ra, rb, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n add.rn.f32x2 rd, ra, rb;\n mov.b64 {%0, %1}, rd;\n}\n"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 qm_sub2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n .reg .b64 ra, rb, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n sub.rn.f32x2 rd, ra, rb;\n mov.b64 {%0, %1}, rd;\n}\n"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 qm_mul2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n .reg .b64 ra, rb, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n mul.rn.f32x2 rd, ra, rb;\n mov.b64 {%0, %1}, rd;\n}\n"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 qm_fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n .reg .b64 ra, rb, rc, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n mov.b64 rc, {%6, %7};\n"
+      " fma.rn.f32x2 rd, ra, rb, rc;\n mov.b64 {%0, %1}, rd;\n}\n"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 qm_dup(float v) { return make_float2(v, v); }
+
 // `tile`: the CTA's staging memory, QM_WARPS x 2 buffers of QM_ROWS rows of qm_rowb<Tin>() bytes
 template <typename Tin, int BITS, bool NORMC>
 __device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__ x, int64_t ld, int64_t n,
@@ -199,24 +227,30 @@ __device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int r = 0; r < 4; ++r)
+      for (int r = 0; r < 4; r += 2)   // register pairs (r, r + 1): two butterflies per instruction
 #pragma unroll
         for (int h = 1; h < 8; h <<= 1)
 #pragma unroll
           for (int i = 0; i < 8; ++i)
             if ((i & h) == 0) {
-              const float a = acc[i][nt][r], b = acc[i + h][nt][r];
+              const float2 a = make_float2(acc[i][nt][r], acc[i][nt][r + 1]);
+              const float2 b = make_float2(acc[i + h][nt][r], acc[i + h][nt][r + 1]);
+              float2 lo, hi;
               if (h < 4) {
-                acc[i][nt][r] = a + b;
-                acc[i + h][nt][r] = a - b;
+                lo = qm_add2(a, b);
+                hi = qm_sub2(a, b);
               } else {
-                // The last stage produces the NEGATED transform: "sign bit clear" then means value <= 0 for every
-                // nonzero value and for zeros that arise by cancellation (x - x = +0), which is how the reference
-                // decides the centre boundary (not above it -> lower index).  A zero formed from two zero inputs
-                // can come out as -0 and take the upper of the two central indices; it sits exactly on the boundary.
-                acc[i][nt][r] = (-a) - b;
-                acc[i + h][nt][r] = b - a;
+                // The last stage produces the NEGATED transform, (-a) - b and b - a: "sign bit clear" then means
+                // value <= 0 for every nonzero value and for zeros that arise by cancellation (x - x = +0), which is
+                // how the reference decides the centre boundary (not above it -> lower index).  A zero formed from
+                // two zero inputs can come out as -0 and take the upper of the two central indices; it sits exactly
+                // on the boundary.
+                const float2 na = qm_mul2(a, qm_dup(-1.0f));
+                lo = qm_sub2(na, b);
+                hi = qm_add2(b, na);
               }
+              acc[i][nt][r] = lo.x; acc[i][nt][r + 1] = lo.y;
+              acc[i + h][nt][r] = hi.x; acc[i + h][nt][r + 1] = hi.y;
             }
 
     // ---- the lane's two vectors: rows g (registers 0,1) and g + 8 (registers 2,3) ----
@@ -224,13 +258,15 @@ __device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__
     for (int vs = 0; vs < 2; ++vs) {
       const int64_t v = v0 + g + 8 * vs;
       const bool ok = v < n;
-      float ss = 0.f;
+      float2 ss2 = make_float2(0.f, 0.f);
 #pragma unroll
       for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-          for (int c = 0; c < 2; ++c) ss = fmaf(acc[i][nt][2 * vs + c], acc[i][nt][2 * vs + c], ss);
+        for (int nt = 0; nt < 2; ++nt) {
+          const float2 y = make_float2(acc[i][nt][2 * vs], acc[i][nt][2 * vs + 1]);
+          ss2 = qm_fma2(y, y, ss2);
+        }
+      float ss = ss2.x + ss2.y;
       ss += __shfl_xor_sync(0xffffffffu, ss, 1);
       ss += __shfl_xor_sync(0xffffffffu, ss, 2);
       const float nrm = sqrtf(ss) * TQ_RSQRT_D;          // ||H x|| = sqrt(d) ||x||
@@ -241,36 +277,47 @@ __device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__
       for (int j = 0; j < NT; ++j) thr[j] = bnd[j] * ts;
       const float d31 = BITS == 3 ? thr[2] - thr[0] : 0.f;
 
-      float cc = 0.f;
+      float2 cc2 = make_float2(0.f, 0.f);
       uint32_t w[4];
 #pragma unroll
       for (int tp = 0; tp < 4; ++tp) {
-        float wf[2] = {0.f, 0.f};
+        // Coordinates in pairs (the two columns of an accumulator row), digits in two Horner chains of radix
+        // RADIX^2 -- the even and the odd digits of a word -- joined at the end: every sum stays a half-integer
+        // below 2^23, exact in fp32.
+        constexpr int HG = BITS == 4 ? 4 : 8;              // digits per exact fp32 Horner sum (<= 24 bits)
+        float2 ch[8 / HG];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const float nu = acc[2 * tp + (k >> 2)][(k >> 1) & 1][2 * vs + (k & 1)];  // minus the transformed value
-          const float a = fabsf(nu);
-          float m5;                                        // magnitude level + 1/2
+        for (int q = 0; q < 8 / HG; ++q) ch[q] = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < 8; k += 2) {
+          // minus the transformed values of elements k and k + 1 of the word
+          const float2 nu = make_float2(acc[2 * tp + (k >> 2)][(k >> 1) & 1][2 * vs], acc[2 * tp + (k >> 2)][(k >> 1) & 1][2 * vs + 1]);
+          const float a0 = fabsf(nu.x), a1 = fabsf(nu.y);
+          float2 m5;                                       // magnitude level + 1/2
           if constexpr (BITS == 3) {
             // two tests instead of three: against the middle boundary, then against the lower or the upper one
             // (picked arithmetically; the upper one is thr[0] + d31, within an ulp of thr[2])
-            const float p2 = qm_gt(a, thr[1]);
-            const float p1 = qm_gt(a, fmaf(p2, d31, thr[0]));
-            m5 = fmaf(p2, 2.0f, p1 + 0.5f);
+            const float2 p2 = make_float2(qm_gt(a0, thr[1]), qm_gt(a1, thr[1]));
+            const float2 th = qm_fma2(p2, qm_dup(d31), qm_dup(thr[0]));
+            const float2 p1 = make_float2(qm_gt(a0, th.x), qm_gt(a1, th.y));
+            m5 = qm_fma2(p2, qm_dup(2.0f), qm_add2(p1, qm_dup(0.5f)));
           } else {
-            m5 = 0.5f;
+            m5 = make_float2(0.5f, 0.5f);
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
-              const float p = qm_gt(a, thr[j]);
-              m5 += p;
-              if (NORMC && BITS == 4) cc = fmaf(p, dsq[j], cc);
+              const float2 p = make_float2(qm_gt(a0, thr[j]), qm_gt(a1, thr[j]));
+              m5 = qm_add2(m5, p);
+              if (NORMC && BITS == 4) cc2 = qm_fma2(p, qm_dup(dsq[j]), cc2);
             }
           }
           // index = HALF - 1/2 + sign * m5, sign = -1 where the value is <= 0, i.e. where nu's sign bit is clear
-          const float digit = __int_as_float(__float_as_int(m5) | (~__float_as_int(nu) & 0x80000000));
-          constexpr int HG = BITS == 4 ? 4 : 8;            // digits per exact fp32 Horner sum (<= 24 bits)
-          wf[k / HG] = fmaf(wf[k / HG], RADIX, digit);
+          const float2 digit = make_float2(__int_as_float(__float_as_int(m5.x) | (~__float_as_int(nu.x) & 0x80000000)),
+                                           __int_as_float(__float_as_int(m5.y) | (~__float_as_int(nu.y) & 0x80000000)));
+          ch[k / HG] = qm_fma2(ch[k / HG], qm_dup(RADIX * RADIX), digit);
         }
+        float wf[8 / HG];
+#pragma unroll
+        for (int q = 0; q < 8 / HG; ++q) wf[q] = fmaf(ch[q].x, RADIX, ch[q].y);
         // + (HALF - 1/2) in every digit turns the signed digits into indices; the sums are whole numbers < 2^24
         if constexpr (BITS == 4) {
           constexpr float OFF = 7.5f * 4369.0f;            // 4369 = (16^4 - 1) / 15
@@ -285,6 +332,7 @@ __device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__
         w[tp] = nrm > 0.f ? (w[tp] ^ flip[tp]) : ONES * zero_idx;
       }
       float invn = 1.0f;
+      float cc = cc2.x + cc2.y;
       if (NORMC && BITS != 4) {
         // ||c[idx]||^2 from a histogram of magnitude levels: field = [s | low], level m = s ? low : ~low, and
         // n_j = #{m >= j} is a population count over the packed words (mirroring an index keeps its level)
