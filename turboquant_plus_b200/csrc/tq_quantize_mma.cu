@@ -108,7 +108,8 @@ __device__ __forceinline__ float2 qm_fma2(float2 a, float2 b, float2 c) {
 }
 __device__ __forceinline__ float2 qm_dup(float v) { return make_float2(v, v); }
 
-// `tile`: the CTA's staging memory, QM_WARPS x 2 buffers of QM_ROWS rows of qm_rowb<Tin>() bytes
+// `tile`: the CTA's staging memory, QM_WARPS x 2 buffers of QM_ROWS rows of qm_rowb<Tin>() bytes, then 4 KB for the
+// B operands of the MMAs
 template <typename Tin, int BITS, bool NORMC>
 __device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__ x, int64_t ld, int64_t n,
                                         const TqQuantDst& dst, uint8_t* tile) {
@@ -123,23 +124,32 @@ __device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__
   // B operands: rows k = 2t, 2t+1 (register 0) and 2t+8, 2t+9 (register 1) of sign1 * H16.  The 16 output columns
   // are dealt to the two n-tiles so that the accumulator columns of lane t (2t, 2t+1 of each tile) are the four
   // consecutive outputs j = 4t .. 4t+3.
-  uint32_t bfr[8][2][2];
+  // They depend on the lane only: the first warp writes them to shared memory once ([i][lane] x 16 bytes) and every
+  // warp reads the four words of a step just before its two MMAs -- 32 registers less per thread, a fifth CTA per SM.
+  uint8_t* bsm = tile + QM_WARPS * 2 * BUFB;
+  if (warp == 0) {
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < 8; ++i) {
+      uint32_t b4[4];
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
+      for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int col = 4 * (g >> 1) + 2 * nt + (g & 1);  // this lane's B column g of tile nt is output j = col
-        uint32_t r = 0;
+        for (int h = 0; h < 2; ++h) {
+          const int col = 4 * (g >> 1) + 2 * nt + (g & 1);  // this lane's B column g of tile nt is output j = col
+          uint32_t r = 0;
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int k = 2 * t + 8 * h + e;
-          const uint32_t neg = qm_bit(f.s1, 16 * i + k) ^ (uint32_t)(__popc(k & col) & 1);
-          r |= (neg ? QmIn<Tin>::MINUS : QmIn<Tin>::ONE) << (16 * e);
+          for (int e = 0; e < 2; ++e) {
+            const int k = 2 * t + 8 * h + e;
+            const uint32_t neg = qm_bit(f.s1, 16 * i + k) ^ (uint32_t)(__popc(k & col) & 1);
+            r |= (neg ? QmIn<Tin>::MINUS : QmIn<Tin>::ONE) << (16 * e);
+          }
+          b4[2 * nt + h] = r;
         }
-        bfr[i][nt][h] = r;
-      }
+      *reinterpret_cast<uint4*>(bsm + (i * 32 + lane) * 16) = make_uint4(b4[0], b4[1], b4[2], b4[3]);
+    }
+  }
+  __syncthreads();
+  const uint4* bfr4 = reinterpret_cast<const uint4*>(bsm) + lane;
   // sign2 mirrors an index (i -> 2^b - 1 - i): an XOR of the packed word.  Word tp of this lane packs, most
   // significant first, the elements 16 (2 tp + (k >> 2)) + 4 t + (k & 3), k = 0..7.
   uint32_t flip[4];
@@ -166,16 +176,29 @@ __device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__
   const int64_t stride = (int64_t)gridDim.x * QM_WARPS;
   int64_t ti = (int64_t)blockIdx.x * QM_WARPS + warp;
   uint8_t* wtile = tile + (size_t)warp * 2 * BUFB;
+  // a lane copies the same 16-byte chunk of rows row0, row0 + RSTEP, ... of every tile
+  constexpr int RSTEP = 32 / CHUNKS;
+  const int row0 = lane / CHUNKS;
+  const uint8_t* xlane = reinterpret_cast<const uint8_t*>(x + (int64_t)row0 * ld) + (lane % CHUNKS) * 16;
+  const int64_t row_step = (int64_t)RSTEP * ld * (int64_t)sizeof(Tin), tile_step = (int64_t)QM_ROWS * ld * (int64_t)sizeof(Tin);
+  const uint32_t slane = qm_smem(wtile) + row0 * QM_ROWB + (lane % CHUNKS) * 16;
   auto issue = [&](int64_t tile_i, int buf) {
     const int64_t v0 = tile_i * QM_ROWS;
-    const uint32_t sbase = qm_smem(wtile + buf * BUFB);
+    const uint8_t* src = xlane + tile_i * tile_step;
+    const uint32_t sdst = slane + buf * BUFB;
+    if (v0 + QM_ROWS <= n) {   // a whole tile (all but the last one): no row tests
 #pragma unroll
-    for (int r2 = 0; r2 < QM_ROWS * CHUNKS / 32; ++r2) {
-      const int row = (32 * r2 + lane) / CHUNKS, chunk = (32 * r2 + lane) % CHUNKS;
-      if (v0 + row < n)
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sbase + row * QM_ROWB + chunk * 16),
-                     "l"(reinterpret_cast<const uint8_t*>(x + (v0 + row) * ld) + chunk * 16)
-                     : "memory");
+      for (int r2 = 0; r2 < QM_ROWS / RSTEP; ++r2) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sdst + r2 * RSTEP * QM_ROWB), "l"(src) : "memory");
+        src += row_step;
+      }
+    } else {
+#pragma unroll
+      for (int r2 = 0; r2 < QM_ROWS / RSTEP; ++r2) {
+        if (v0 + row0 + r2 * RSTEP < n)
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sdst + r2 * RSTEP * QM_ROWB), "l"(src) : "memory");
+        src += row_step;
+      }
     }
   };
   if (ti < ntiles) issue(ti, 0);
@@ -204,11 +227,13 @@ __device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__
         qm_split3(x1.x, x1.y, a[0][1], a[1][1], a[2][1]);
         qm_split3(x2.x, x2.y, a[0][2], a[1][2], a[2][2]);
         qm_split3(x3.x, x3.y, a[0][3], a[1][3], a[2][3]);
+        const uint4 b4 = bfr4[32 * i];
+        const uint32_t bfr[2][2] = {{b4.x, b4.y}, {b4.z, b4.w}};
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
-          QmIn<Tin>::mma(acc[i][nt], a[0], bfr[i][nt][0], bfr[i][nt][1]);
-          QmIn<Tin>::mma_acc(acc[i][nt], a[1], bfr[i][nt][0], bfr[i][nt][1]);
-          QmIn<Tin>::mma_acc(acc[i][nt], a[2], bfr[i][nt][0], bfr[i][nt][1]);
+          QmIn<Tin>::mma(acc[i][nt], a[0], bfr[nt][0], bfr[nt][1]);
+          QmIn<Tin>::mma_acc(acc[i][nt], a[1], bfr[nt][0], bfr[nt][1]);
+          QmIn<Tin>::mma_acc(acc[i][nt], a[2], bfr[nt][0], bfr[nt][1]);
         }
       }
     } else {
@@ -219,8 +244,9 @@ __device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__
         asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                      : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
                      : "r"(abase + 32 * i));
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) QmIn<Tin>::mma(acc[i][nt], a, bfr[i][nt][0], bfr[i][nt][1]);
+        const uint4 b4 = bfr4[32 * i];
+        QmIn<Tin>::mma(acc[i][0], a, b4.x, b4.y);
+        QmIn<Tin>::mma(acc[i][1], a, b4.z, b4.w);
       }
     }
     // ---- 8-point stage over i, in registers ----
@@ -414,9 +440,9 @@ __device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
-// staging memory of one CTA: 16-bit rows fit the static limit, fp32 rows (68 KB) are dynamic
-template <typename Tin> constexpr int qm_tile_bytes() { return QM_WARPS * 2 * QM_ROWS * qm_rowb<Tin>(); }
-template <typename Tin> constexpr int qm_ctas_per_sm() { return sizeof(Tin) == 4 ? 3 : 4; }
+// staging memory of one CTA (tiles + B operands): 16-bit rows fit the static limit, fp32 rows (72 KB) are dynamic
+template <typename Tin> constexpr int qm_tile_bytes() { return QM_WARPS * 2 * QM_ROWS * qm_rowb<Tin>() + 8 * 32 * 16; }
+template <typename Tin> constexpr int qm_ctas_per_sm() { return sizeof(Tin) == 4 ? 3 : 5; }
 template <typename Tin> __device__ __forceinline__ uint8_t* qm_tile() {
   if constexpr (sizeof(Tin) == 4) {
     extern __shared__ __align__(16) uint8_t qm_dyn[];
