@@ -514,7 +514,7 @@ template <typename Tin, int BITS>
 int launch_mma_pair(const QmJob& j0, const QmJob& j1, int64_t ld, int64_t n, bool normc, cudaStream_t st) {
   const int64_t tiles = (n + QM_ROWS - 1) / QM_ROWS;
   const int64_t ctas = (tiles + QM_WARPS - 1) / QM_WARPS;
-  const int64_t cap = (int64_t)tq_num_sms() * 2;  // two jobs share the SMs
+  const int64_t cap = (int64_t)tq_num_sms() * qm_ctas_per_sm<Tin>() / 2;  // two jobs share the SMs
   dim3 grid((unsigned)(ctas < cap ? ctas : cap), 2);
   size_t smem = 0;
   if (normc) {
