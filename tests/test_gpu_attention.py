@@ -334,6 +334,12 @@ def test_overlap_launch_and_compressor_streaming_api(tq):
         torch.cuda.synchronize()
         for a, b, e in zip(plain, outs, eager):
             assert same(b, a) and torch.equal(b, e)
+        # the sparse-V option has both forms too; on this flat softmax no tile is skipped: the dense bytes
+        for (c, bt), o_, e in zip(caches, outs, eager):
+            c.attend(q, bt, sl, out=o_, workspace=ws, overlap=mode, sparse_v=True)
+        torch.cuda.synchronize()
+        for o_, e in zip(outs, eager):
+            assert torch.equal(o_, e)
         assert caches[0][0].kernel_status(ws) == 0
 
     comp = tq.KVCacheCompressor(D, k_bits=3, v_bits=3, seed=42, rotation="wht").init_cache(2, hkv, 12)
