@@ -19,7 +19,9 @@ import sys
 
 import numpy as np
 
-REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("TQ_REFERENCE", "/root/reference")
+# path of the reference checkout: argument, $TQ_REFERENCE, or a directory `reference` beside the repository
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get(
+    "TQ_REFERENCE", os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))), "reference"))
 sys.path.insert(0, REF)
 
 from turboquant import KVCacheCompressor, PolarQuant, QJL, TurboQuant, TurboQuantMSE  # noqa: E402

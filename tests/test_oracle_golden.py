@@ -169,14 +169,21 @@ def test_live_reference_if_present():
     """Differential check against the reference tree itself where it is mounted."""
     import os
     import sys
-    ref = os.environ.get("TQ_REFERENCE", "/root/reference")
+    # path of the reference checkout: $TQ_REFERENCE, or a directory `reference` beside the repository
+    ref = os.environ.get("TQ_REFERENCE", os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference"))
     if not os.path.isdir(os.path.join(ref, "turboquant")):
         pytest.skip("reference tree not present")
+    # the reference suite's conftest may have aliased `turboquant` to this package in the same session: set those
+    # entries aside while the real one is imported, and put them back afterwards
+    aliased = {k: sys.modules.pop(k) for k in list(sys.modules) if k == "turboquant" or k.startswith("turboquant.")}
     sys.path.insert(0, ref)
     try:
         from turboquant import TurboQuant, TurboQuantMSE
     finally:
         sys.path.remove(ref)
+        for k in [k for k in sys.modules if k == "turboquant" or k.startswith("turboquant.")]:
+            del sys.modules[k]
+        sys.modules.update(aliased)
     x = o.synth_keys(2048, seed=0)
     for b in (2, 3, 4):
         m = TurboQuantMSE(D, b, seed=42)
