@@ -43,6 +43,19 @@ METRIC = "turbo3_decode_attn_kv_tokens_per_s"
 UNIT = "KV-tokens/s"
 
 
+_STDOUT_FD = None
+
+
+def emit(record):
+    """Writes one JSON line to the process's original stdout."""
+    data = (json.dumps(record) + "\n").encode()
+    if _STDOUT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_STDOUT_FD, data)
+
+
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -188,7 +201,7 @@ def run_reference(args):
                              "sample": r["sample"]},
             "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ----------------------------------------------------------------------------------------------
@@ -426,7 +439,7 @@ def run_ours(args):
         if cpu:
             line["cpu_baseline"] = {"value": cpu["value"], "unit": UNIT, "cores": cpu["cores"], "kind": "port",
                                     "sample": cpu["sample"]}
-        print(json.dumps(line), flush=True)
+        emit(line)
 
 
 # ----------------------------------------------------------------------------------------------
@@ -592,7 +605,7 @@ def run_other_workload(args):
         r.update({"higher_is_better": True, "vs_baseline": None, "data": "synthetic",
                   "dtype": "f16 tensor-core products, f32 accumulate and softmax",
                   "config": {"workload": r["workload"], "parallelism": r["parallelism"], "l2": "inputs larger than L2"}})
-        print(json.dumps(r), flush=True)
+        emit(r)
 
 
 def measure_config3(steps, warmup):
@@ -702,7 +715,7 @@ def run_config3(args):
         r.update({"higher_is_better": True, "vs_baseline": None, "data": "synthetic",
                   "dtype": "f16 in, exact +-1 tensor-core products, f32 accumulate",
                   "config": {"workload": r["workload"], "parallelism": r["parallelism"], "l2": "inputs larger than L2"}})
-        print(json.dumps(r), flush=True)
+        emit(r)
 
 
 def run_side_kernels(args):
@@ -791,9 +804,13 @@ def main():
         return
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1:
-        # the one line on stdout is the JSON line: NCCL's version banner (NCCL_DEBUG=VERSION) would come before it
-        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"
+        # The one line on stdout is the JSON line.  NCCL writes its version banner to stdout when the first communicator
+        # is made (whatever set NCCL_DEBUG, the environment or a configuration file): from here on file descriptor 1
+        # leads to stderr, and emit() writes the JSON line to the descriptor that was stdout.
+        global _STDOUT_FD
+        sys.stdout.flush()
+        _STDOUT_FD = os.dup(1)
+        os.dup2(2, 1)
         import torch
         import torch.distributed as dist
         local = int(os.environ.get("LOCAL_RANK", "0"))
