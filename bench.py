@@ -586,11 +586,13 @@ def measure_decode_config(name, steps, warmup):
             ref = full.layers[0].attend(q_all, fbt, torch.tensor(all_lens, dtype=torch.int32, device=dev))
             torch.cuda.synchronize(dev)
             diff = float((got.float() - ref.float()).abs().max())
-            check = {"layer": 0, "max_abs_diff": diff, "max_abs_ref": float(ref.float().abs().max()),
-                     "bit_equal": bool(torch.equal(got, ref)),
+            ref_max = float(ref.float().abs().max())
+            assert diff <= 2e-3 * ref_max, f"sharded outputs differ from the unsharded layer by {diff} (of {ref_max})"
+            check = {"layer": 0, "max_abs_diff": diff, "max_abs_ref": ref_max,
+                     "bit_equal": bool(torch.equal(got, ref)), "tolerance": "2e-3 of max_abs_ref, asserted",
                      "note": "all-gathered shard outputs vs the unsharded layer on one GPU; the split plan depends on "
-                             "the number of (sequence, KV head) pairs a GPU holds, so head sharding changes the "
-                             "summation order (fp32 rounding), batch sharding of a large batch does not"}
+                             "the number of (sequence, KV head) pairs a GPU holds, so sharding can change the order in "
+                             "which split partials are summed (fp32 rounding: an fp16 ulp or two in the output)"}
     peak, src = peaks()
     return {"metric": "decode_attn_kv_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": steps, "warmup": warmup, "ms_per_step": ms, "scaling": "strong",
@@ -687,9 +689,12 @@ def measure_config3(steps, warmup):
             append_all(full, k_all, v_all)
             ref = full.prefill_attend(q_all, bt, kv_len)
             torch.cuda.synchronize(dev)
-            check = {"max_abs_diff": float((got.float() - ref.float()).abs().max()),
-                     "max_abs_ref": float(ref.float().abs().max()), "bit_equal": bool(torch.equal(got, ref)),
-                     "note": "gathered prefill outputs of the head shards vs the unsharded layer on one GPU"}
+            diff, ref_max = float((got.float() - ref.float()).abs().max()), float(ref.float().abs().max())
+            assert diff <= 2e-3 * ref_max, f"sharded prefill outputs differ from the unsharded layer by {diff} (of {ref_max})"
+            check = {"max_abs_diff": diff, "max_abs_ref": ref_max, "bit_equal": bool(torch.equal(got, ref)),
+                     "tolerance": "2e-3 of max_abs_ref, asserted",
+                     "note": "gathered prefill outputs of the head shards vs the unsharded layer on one GPU (the page "
+                             "split of a row block depends on how many row blocks a GPU holds)"}
     vectors = 2.0 * n * hkv_all
     visible = sum(n - tq_len + i + 1 for i in range(tq_len))
     flops = 2.0 * 2 * hq_all * D * visible
