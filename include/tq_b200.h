@@ -263,6 +263,11 @@ int tq_decode_workspace_init(void* workspace_dev, int64_t workspace_bytes, void*
  * (results of the calls since then are invalid).  The kernels only ever set the word; this call copies it to
  * the host (4 bytes, synchronous) and, when it was set, clears it. */
 int tq_decode_status_sync(void* workspace_dev, int64_t workspace_bytes, int32_t* status_out);
+/* Self-test of the give-up path (new surface; the reference has no device code): enqueues a one-warp kernel that
+ * waits on a barrier nothing arrives at, with a limit of 2^20 SM clocks (about half a millisecond) instead of the
+ * attention kernels' 2^30, gives up, and raises this workspace's status word the way those kernels do.  The
+ * kernel returns normally and the context stays usable; tq_decode_status_sync then reads 1 once. */
+int tq_selftest_wait_gives_up(void* workspace_dev, int64_t workspace_bytes, void* stream);
 
 /* Decode attention straight off the packed cache: for every sequence b and query head h,
  * softmax(q k^T * scale) v over the first seq_lens[b] cached tokens of KV head

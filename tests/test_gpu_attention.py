@@ -284,6 +284,31 @@ def test_prefill_split_pages(tq):
 
 
 @pytest.mark.gpu
+def test_bounded_wait_gives_up_and_reports(tq):
+    """The give-up path of the kernels' bounded waits, run where it is harmless (tq_selftest_wait_gives_up: a wait that
+    nothing satisfies, limited to 2^20 clocks): the status word of the workspace reads 1 once, then 0 again, and the
+    same workspace serves the next attention call with the same bytes as before."""
+    import torch
+    from turboquant_plus_b200 import _native as nv
+    rng = np.random.default_rng(5)
+    hkv, hq, n = 2, 8, 700
+    c = tq.PagedKVCache(D, hkv, num_pages=6, seed=42)
+    ks = [rng.standard_normal((n, hkv, D)).astype(np.float16)]
+    vs = [rng.standard_normal((n, hkv, D)).astype(np.float16)]
+    bt = fill_cache(c, ks, vs, [n], rng).cuda()
+    sl = torch.tensor([n], dtype=torch.int32, device="cuda")
+    q = torch.as_tensor(rng.standard_normal((1, hq, D)).astype(np.float16)).cuda()
+    ws = c.workspace(1, hq, 6)
+    before = c.attend(q, bt, sl, workspace=ws).clone()
+    assert c.kernel_status(ws) == 0
+    nv.call("tq_selftest_wait_gives_up", nv.ptr(ws), ws.numel(), nv.stream_ptr())
+    torch.cuda.synchronize()
+    assert c.kernel_status(ws) == 1       # a wait gave up since the last read ...
+    assert c.kernel_status(ws) == 0       # ... and reading it cleared it
+    after = c.attend(q, bt, sl, workspace=ws)
+    assert torch.equal(after, before) and c.kernel_status(ws) == 0
+
+
 def test_overlap_launch_and_compressor_streaming_api(tq):
     """(1) TQ_DECODE_OVERLAP (programmatic dependent launch) changes when the kernel starts, never what it computes:
     a chain of overlapped calls, eager and replayed from a CUDA graph, returns the bytes of the plain calls.

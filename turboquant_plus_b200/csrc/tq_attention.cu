@@ -537,6 +537,28 @@ extern "C" int tq_decode_workspace_init(void* workspace_dev, int64_t workspace_b
   return TQ_OK;
 }
 
+// The give-up path of the bounded waits, run on purpose where it is harmless: one warp waits on an mbarrier that
+// nothing ever arrives at, with a limit of 2^20 clocks (about half a millisecond) instead of the kernels' 2^30, gives up,
+// raises the workspace's status word exactly as the attention kernels do, and returns.  Nothing hangs and nothing
+// faults: the context stays usable, which is what the test after it checks.
+__global__ void k_selftest_wait_gives_up(int32_t* status) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    tqatt::mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  const bool done = tqatt::mbar_wait_bounded(&bar, 0, 1LL << 20);
+  if (!__all_sync(0xffffffffu, done) && threadIdx.x == 0) atomicExch(status, 1);
+}
+
+extern "C" int tq_selftest_wait_gives_up(void* workspace_dev, int64_t workspace_bytes, void* stream) {
+  TQ_REQUIRE(workspace_dev && workspace_bytes >= 256, TQ_ERR_INVALID, "bad workspace");
+  int32_t* word = reinterpret_cast<int32_t*>((uint8_t*)workspace_dev + workspace_bytes - 256);
+  k_selftest_wait_gives_up<<<1, 32, 0, (cudaStream_t)stream>>>(word);
+  return tq_launch_check("k_selftest_wait_gives_up");
+}
+
 extern "C" int tq_decode_status_sync(void* workspace_dev, int64_t workspace_bytes, int32_t* status_out) {
   TQ_REQUIRE(workspace_dev && status_out && workspace_bytes >= 256, TQ_ERR_INVALID, "bad workspace");
   uint8_t* word = (uint8_t*)workspace_dev + workspace_bytes - 256;

@@ -45,10 +45,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait: polls until the phase completes or WAIT_CYCLES SM clocks have passed, then gives up and
 // reports it instead of spinning forever.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, long long limit = WAIT_CYCLES) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
-  while (clock64() - t0 < WAIT_CYCLES)
+  while (clock64() - t0 < limit)
     if (mbar_try_wait(bar, parity)) return true;
   return false;
 }
