@@ -285,7 +285,22 @@ def run_ours(args):
         qt.append(ev[0].elapsed_time(ev[1]))
     append32_ms = statistics.median(qt[2:])
     append32_bytes = 2 * nq32 * (D * 4 + 52)
-    del qcache, xq, x32, qslots
+    del qcache, x32
+    # keys through the reference's default K quantizer (TurboQuant = PolarQuant + 1-bit QJL sketch of the residual,
+    # turboquant/kv_cache.py:89-96), 3 bits in all: 2^21 fp16 vectors as prod3 K beside turbo3 V
+    pcache = tq.PagedKVCache(D, 1, nq32 // PT, PT, "prod3", "turbo3", seed=42, device=dev)
+    xp, pslots = xq[:nq32], torch.arange(nq32, device=dev)
+    qt = []
+    for _ in range(6):
+        torch.cuda.synchronize(dev)
+        ev[0].record()
+        pcache.append(xp, xp, pslots)
+        ev[1].record()
+        torch.cuda.synchronize(dev)
+        qt.append(ev[0].elapsed_time(ev[1]))
+    appendp_ms = statistics.median(qt[2:])
+    appendp_bytes = nq32 * (D * 2 + 56) + nq32 * (D * 2 + 52)   # prod3 K: 32 B indices, 16 B sketch, two scales
+    del pcache, xq, xp, qslots, pslots
     seq_lens = torch.full((1,), CTX, dtype=torch.int32, device=dev)
     q = torch.randn((LAYERS, 1, HQ, D), generator=gen, device=dev).half()
     out = torch.empty_like(q)
@@ -427,6 +442,11 @@ def run_ours(args):
                                       "achieved": append32_bytes / (append32_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                                       "frac": append32_bytes / (append32_ms * 1e-3) / 1e9 / peak,
                                       "bytes_per_vector": D * 4 + 52},
+            "roofline_quantize_prod": {"bound": "hbm", "kernel": "k_quantize_mma<half,2,QJL stage> for the K rows + k_quantize_mma<half,3> for the V rows, 2^21 vectors each",
+                                       "vectors_per_s": 2 * nq32 / (appendp_ms * 1e-3),
+                                       "achieved": appendp_bytes / (appendp_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                                       "frac": appendp_bytes / (appendp_ms * 1e-3) / 1e9 / peak,
+                                       "bytes_per_vector": "K 312, V 308"},
             "e2e": {"value": LAYERS * CTX * HKV * world / (e2e_ms * 1e-3), "unit": UNIT,
                     "ms_per_step": e2e_ms, "steps": e2e_steps,
                     "h2d_bytes_per_step": int(qh.numel() + kh.numel() + vh.numel()) * 2,

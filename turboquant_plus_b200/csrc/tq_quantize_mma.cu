@@ -21,7 +21,11 @@
 //     order, the layout the cache keeps).
 //   * fp32 inputs are split into three bf16 terms (8 + 8 + 8 significant bits, by truncation: the split is exact)
 //     that go through the same MMAs one after the other into one fp32 accumulator; products with +-1 stay exact.
-// Everything else (QJL stage, asymmetric codebooks, unpacked output) stays with k_quantize_wht.
+//   * QJLS (PROD keys with a 2..4-bit PolarQuant stage): the residual against the chosen centroids is formed in place
+//     in the rotated domain, its norm taken, and sign(S r) computed as two more 128-point transforms in the same
+//     register layout (element 16 i + 4 t + c of lane t: the bits of i and c are butterflies in registers, the two
+//     bits of t two lane exchanges), with the sign flips in between from a lane-indexed table in shared memory.
+// Everything else (1-bit PolarQuant stages, asymmetric codebooks, unpacked output) stays with k_quantize_wht.
 #include "tq_internal.cuh"
 
 namespace {
@@ -110,7 +114,7 @@ __device__ __forceinline__ float2 qm_dup(float v) { return make_float2(v, v); }
 
 // `tile`: the CTA's staging memory, QM_WARPS x 2 buffers of QM_ROWS rows of qm_rowb<Tin>() bytes, then 4 KB for the
 // B operands of the MMAs
-template <typename Tin, int BITS, bool NORMC>
+template <typename Tin, int BITS, bool NORMC, bool QJLS = false>
 __device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__ x, int64_t ld, int64_t n,
                                         const TqQuantDst& dst, uint8_t* tile) {
   constexpr int QM_ROWB = qm_rowb<Tin>();
@@ -148,6 +152,25 @@ __device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__
       *reinterpret_cast<uint4*>(bsm + (i * 32 + lane) * 16) = make_uint4(b4[0], b4[1], b4[2], b4[3]);
     }
   }
+  // QJL stage: +-1 factors of sign1 ^ j1 for this lane's 32 elements, [i][lane] x (c = 0..3), and the j2 flips as a
+  // mask word in the order the sketch bits are gathered (i, then c, most significant first)
+  float4* m12f = reinterpret_cast<float4*>(bsm + 8 * 32 * 16);
+  uint32_t j2w = 0;
+  if constexpr (QJLS) {
+    if (warp == 0) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float v4[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) v4[c] = (qm_bit(f.s1, 16 * i + 4 * t + c) ^ qm_bit(f.j1, 16 * i + 4 * t + c)) ? -1.0f : 1.0f;
+        m12f[i * 32 + lane] = make_float4(v4[0], v4[1], v4[2], v4[3]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) j2w = (j2w << 1) | qm_bit(f.j2, 16 * i + 4 * t + c);
+  }
   __syncthreads();
   const uint4* bfr4 = reinterpret_cast<const uint4*>(bsm) + lane;
   // sign2 mirrors an index (i -> 2^b - 1 - i): an XOR of the packed word.  Word tp of this lane packs, most
@@ -170,6 +193,19 @@ __device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__
     dsq[j] = f.cent[HALF + j + 1] * f.cent[HALF + j + 1] - f.cent[HALF + j] * f.cent[HALF + j];
   }
   const float c0sq = f.cent[HALF] * f.cent[HALF];
+  // QJL stage: the chosen centroid's magnitude from the test results.  3 bits (levels 2 p2 + p1): c4 + p2 (c6 - c4) +
+  // p1 ((c5 - c4) + p2 ((c7 - c6) - (c5 - c4))); otherwise the first magnitude and the steps between neighbours.
+  float cst[HALF > 3 ? HALF : 4];
+  if constexpr (BITS == 3) {
+    cst[0] = f.cent[4];
+    cst[1] = f.cent[6] - f.cent[4];
+    cst[2] = f.cent[5] - f.cent[4];
+    cst[3] = (f.cent[7] - f.cent[6]) - (f.cent[5] - f.cent[4]);
+  } else {
+    cst[0] = f.cent[HALF];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) cst[1 + j] = f.cent[HALF + j + 1] - f.cent[HALF + j];
+  }
   const uint32_t zero_idx = 0.f > f.bnd[HALF - 1] ? HALF : HALF - 1;   // index of the value 0
 
   const int64_t ntiles = (n + QM_ROWS - 1) / QM_ROWS;
@@ -434,6 +470,128 @@ __device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__
         if (dst.norm) dst.norm[v] = nrm;
         if (dst.scale && good) *reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(dst.scale) + rec_off + within * 4) = nrm * invn;
       }
+      if constexpr (QJLS) {
+        // ---- residual in the rotated domain, in place (negated like the values): -(u - c * cs), cs = ts / ||c|| ----
+        const float cs = invn * ts;
+        float2 ee2 = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt) {
+            const float2 nu = make_float2(acc[i][nt][2 * vs], acc[i][nt][2 * vs + 1]);
+            const float a0 = fabsf(nu.x), a1 = fabsf(nu.y);
+            float2 cm;                                     // magnitude of the chosen centroid
+            if constexpr (BITS == 3) {
+              const float2 p2 = make_float2(qm_gt(a0, thr[1]), qm_gt(a1, thr[1]));
+              const float2 th = qm_fma2(p2, qm_dup(d31), qm_dup(thr[0]));
+              const float2 p1 = make_float2(qm_gt(a0, th.x), qm_gt(a1, th.y));
+              // level 2 p2 + p1: c4, c5, c6, c7
+              const float2 base = qm_fma2(p2, qm_dup(cst[1]), qm_dup(cst[0]));
+              const float2 slope = qm_fma2(p2, qm_dup(cst[3]), qm_dup(cst[2]));
+              cm = qm_fma2(p1, slope, base);
+            } else {
+              cm = qm_dup(cst[0]);
+#pragma unroll
+              for (int j = 0; j < NT; ++j) {
+                const float2 p = make_float2(qm_gt(a0, thr[j]), qm_gt(a1, thr[j]));
+                cm = qm_fma2(p, qm_dup(cst[1 + j]), cm);
+              }
+            }
+            // the centroid carries the value's sign; the registers hold minus the value
+            cm.x = __int_as_float(__float_as_int(cm.x) | (~__float_as_int(nu.x) & 0x80000000));
+            cm.y = __int_as_float(__float_as_int(cm.y) | (~__float_as_int(nu.y) & 0x80000000));
+            const float2 r = qm_fma2(cm, qm_dup(cs), nu);
+            ee2 = qm_fma2(r, r, ee2);
+            acc[i][nt][2 * vs] = r.x;
+            acc[i][nt][2 * vs + 1] = r.y;
+          }
+        float ee = ee2.x + ee2.y;
+        ee += __shfl_xor_sync(0xffffffffu, ee, 1);
+        ee += __shfl_xor_sync(0xffffffffu, ee, 2);
+        const float rn = nrm > 0.f ? sqrtf(ee) * TQ_RSQRT_D : 0.f;   // ||r|| = ||x|| * ||y - yhat'||
+        // ---- sign(S r), S r ~ J2 H J1 D1 H E (positive factors dropped): two transforms with the flips between ----
+        auto wht = [&]() {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {   // element bit 0: the two columns of a register pair
+              const float a = acc[i][nt][2 * vs], b = acc[i][nt][2 * vs + 1];
+              acc[i][nt][2 * vs] = a + b;
+              acc[i][nt][2 * vs + 1] = a - b;
+            }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {        // bit 1: the two n-tiles
+            const float2 a = make_float2(acc[i][0][2 * vs], acc[i][0][2 * vs + 1]);
+            const float2 b = make_float2(acc[i][1][2 * vs], acc[i][1][2 * vs + 1]);
+            const float2 s = qm_add2(a, b), d = qm_sub2(a, b);
+            acc[i][0][2 * vs] = s.x; acc[i][0][2 * vs + 1] = s.y;
+            acc[i][1][2 * vs] = d.x; acc[i][1][2 * vs + 1] = d.y;
+          }
+#pragma unroll
+          for (int m = 1; m <= 2; m <<= 1) {   // bits 2, 3: the lanes of the quad
+            const float2 sg = qm_dup((t & m) ? -1.0f : 1.0f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+              for (int nt = 0; nt < 2; ++nt) {
+                const float2 own = make_float2(acc[i][nt][2 * vs], acc[i][nt][2 * vs + 1]);
+                const float2 oth = make_float2(__shfl_xor_sync(0xffffffffu, own.x, m), __shfl_xor_sync(0xffffffffu, own.y, m));
+                const float2 r = qm_fma2(own, sg, oth);   // bit clear: own + other; bit set: other - own
+                acc[i][nt][2 * vs] = r.x;
+                acc[i][nt][2 * vs + 1] = r.y;
+              }
+          }
+#pragma unroll
+          for (int h = 1; h < 8; h <<= 1)      // bits 4-6: the eight blocks
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if ((i & h) == 0)
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                  const float2 a = make_float2(acc[i][nt][2 * vs], acc[i][nt][2 * vs + 1]);
+                  const float2 b = make_float2(acc[i + h][nt][2 * vs], acc[i + h][nt][2 * vs + 1]);
+                  const float2 s = qm_add2(a, b), d = qm_sub2(a, b);
+                  acc[i][nt][2 * vs] = s.x; acc[i][nt][2 * vs + 1] = s.y;
+                  acc[i + h][nt][2 * vs] = d.x; acc[i + h][nt][2 * vs + 1] = d.y;
+                }
+        };
+        wht();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float4 s4 = m12f[i * 32 + lane];
+          const float2 a = qm_mul2(make_float2(acc[i][0][2 * vs], acc[i][0][2 * vs + 1]), make_float2(s4.x, s4.y));
+          const float2 b = qm_mul2(make_float2(acc[i][1][2 * vs], acc[i][1][2 * vs + 1]), make_float2(s4.z, s4.w));
+          acc[i][0][2 * vs] = a.x; acc[i][0][2 * vs + 1] = a.y;
+          acc[i][1][2 * vs] = b.x; acc[i][1][2 * vs + 1] = b.y;
+        }
+        wht();
+        // sketch bit = 1 where j2 * (S r) >= 0 (turboquant/qjl.py:89-90).  The registers hold minus the projection:
+        // its sign bit is the sketch bit before the j2 flip, which is an XOR of the gathered word.  (A projection
+        // that is exactly zero, of a nonzero residual, takes the bit its zero's sign gives.)
+        uint32_t sk = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int c = 0; c < 2; ++c) sk = __funnelshift_l(__float_as_uint(acc[i][nt][2 * vs + c]), sk, 1);
+        sk ^= j2w;
+        if (!(nrm > 0.f)) sk = 0xffffffffu;   // zero input -> zero residual -> all +1
+        // Lane t holds, for every block i, the nibble of elements 16 i + 4 t .. + 3 (nibble 4 i + t of the sketch).
+        // Bytes 4 t .. 4 t + 3 of the sketch are the nibbles of blocks 2 t and 2 t + 1 from all four lanes: byte t
+        // (from the top) of every lane's word.
+        const int quad = lane & ~3;
+        uint32_t xb[4];
+#pragma unroll
+        for (int s = 0; s < 4; ++s) xb[s] = (__shfl_sync(0xffffffffu, sk, quad + s) >> (24 - 8 * t)) & 0xffu;
+        const uint32_t b0 = ((xb[0] >> 4) << 4) | (xb[1] >> 4), b1 = ((xb[2] >> 4) << 4) | (xb[3] >> 4);
+        const uint32_t b2 = ((xb[0] & 15) << 4) | (xb[1] & 15), b3 = ((xb[2] & 15) << 4) | (xb[3] & 15);
+        if (good && dst.qjl)
+          *reinterpret_cast<uint32_t*>(dst.qjl + rec_off + within * 16 + 4 * t) = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+        if (ok && t == 0 && good && dst.rnorm)   // sqrt(pi/2)/sqrt(d): turboquant/qjl.py:32,131
+          *reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(dst.rnorm) + rec_off + within * 4) =
+              dst.rscale_const ? rn * (1.2533141373155001f * TQ_RSQRT_D) : rn;
+      }
     }
     __syncwarp();  // every lane is done with this buffer before the copies of the tile after next land in it
   }
@@ -441,22 +599,25 @@ __device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__
 }
 
 // staging memory of one CTA (tiles + B operands): 16-bit rows fit the static limit, fp32 rows (72 KB) are dynamic
-template <typename Tin> constexpr int qm_tile_bytes() { return QM_WARPS * 2 * QM_ROWS * qm_rowb<Tin>() + 8 * 32 * 16; }
-template <typename Tin> constexpr int qm_ctas_per_sm() { return sizeof(Tin) == 4 ? 3 : 5; }
-template <typename Tin> __device__ __forceinline__ uint8_t* qm_tile() {
+// (the QJL stage adds 4 KB of sign factors and keeps more values live: one CTA less per SM)
+template <typename Tin, bool QJLS = false> constexpr int qm_tile_bytes() {
+  return QM_WARPS * 2 * QM_ROWS * qm_rowb<Tin>() + 8 * 32 * 16 + (QJLS ? 8 * 32 * 16 : 0);
+}
+template <typename Tin, bool QJLS = false> constexpr int qm_ctas_per_sm() { return (sizeof(Tin) == 4 ? 3 : 5) - (QJLS ? 1 : 0); }
+template <typename Tin, bool QJLS = false> __device__ __forceinline__ uint8_t* qm_tile() {
   if constexpr (sizeof(Tin) == 4) {
     extern __shared__ __align__(16) uint8_t qm_dyn[];
     return qm_dyn;
   } else {
-    __shared__ __align__(16) uint8_t qm_static[qm_tile_bytes<Tin>()];
+    __shared__ __align__(16) uint8_t qm_static[qm_tile_bytes<Tin, QJLS>()];
     return qm_static;
   }
 }
 
-template <typename Tin, int BITS, bool NORMC>
-__global__ void __launch_bounds__(QM_THREADS, qm_ctas_per_sm<Tin>()) k_quantize_mma(const TqFast f, const Tin* __restrict__ x, int64_t ld,
-                                                                                   int64_t n, const TqQuantDst dst) {
-  qm_body<Tin, BITS, NORMC>(f, x, ld, n, dst, qm_tile<Tin>());
+template <typename Tin, int BITS, bool NORMC, bool QJLS = false>
+__global__ void __launch_bounds__(QM_THREADS, qm_ctas_per_sm<Tin, QJLS>()) k_quantize_mma(const TqFast f, const Tin* __restrict__ x,
+                                                                                         int64_t ld, int64_t n, const TqQuantDst dst) {
+  qm_body<Tin, BITS, NORMC, QJLS>(f, x, ld, n, dst, qm_tile<Tin, QJLS>());
 }
 
 // Two tensors of the same shape in one launch (the K and V rows of a cache append): blockIdx.y picks the job.
@@ -475,16 +636,16 @@ __global__ void __launch_bounds__(QM_THREADS, qm_ctas_per_sm<Tin>()) k_quantize_
 }
 
 // dynamic shared memory of a launch (0 for 16-bit rows); raises the kernel's limit once per device
-template <typename Tin, auto kernel>
+template <typename Tin, auto kernel, bool QJLS = false>
 int qm_dyn_smem(size_t* bytes) {
   *bytes = 0;
   if constexpr (sizeof(Tin) == 4) {
-    *bytes = qm_tile_bytes<Tin>();
+    *bytes = qm_tile_bytes<Tin, QJLS>();
     static thread_local int configured_dev = -1;  // one per kernel: the kernel is a template argument
     int dev = 0;
     TQ_CUDA(cudaGetDevice(&dev));
     if (configured_dev != dev) {
-      TQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, qm_tile_bytes<Tin>()));
+      TQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, qm_tile_bytes<Tin, QJLS>()));
       configured_dev = dev;
     }
   }
@@ -492,12 +653,28 @@ int qm_dyn_smem(size_t* bytes) {
 }
 
 template <typename Tin, int BITS>
-int launch_mma(const TqFast& f, const Tin* x, int64_t ld, int64_t n, const TqQuantDst& dst, cudaStream_t st) {
+int launch_mma(const TqFast& f, const Tin* x, int64_t ld, int64_t n, const TqQuantDst& dst, bool want_qjl, cudaStream_t st) {
   const int64_t tiles = (n + QM_ROWS - 1) / QM_ROWS;
   const int64_t ctas = (tiles + QM_WARPS - 1) / QM_WARPS;
+  size_t smem = 0;
+  if constexpr (BITS == 4) {
+    if (want_qjl) return TQ_ERR_UNSUPPORTED;   // not offered by qm_serves: seven tests and their centroid steps spill
+  } else if (want_qjl) {   // the residual needs the norm correction whether or not the scale is stored
+    const int64_t capq = (int64_t)tq_num_sms() * qm_ctas_per_sm<Tin, true>();
+    const int gridq = (int)(ctas < capq ? ctas : capq);
+    if (f.norm_correction) {
+      const int rc = qm_dyn_smem<Tin, k_quantize_mma<Tin, BITS, true, true>, true>(&smem);
+      if (rc != TQ_OK) return rc;
+      k_quantize_mma<Tin, BITS, true, true><<<gridq, QM_THREADS, smem, st>>>(f, x, ld, n, dst);
+    } else {
+      const int rc = qm_dyn_smem<Tin, k_quantize_mma<Tin, BITS, false, true>, true>(&smem);
+      if (rc != TQ_OK) return rc;
+      k_quantize_mma<Tin, BITS, false, true><<<gridq, QM_THREADS, smem, st>>>(f, x, ld, n, dst);
+    }
+    return tq_launch_check("k_quantize_mma");
+  }
   const int64_t cap = (int64_t)tq_num_sms() * qm_ctas_per_sm<Tin>();
   const int grid = (int)(ctas < cap ? ctas : cap);
-  size_t smem = 0;
   if (f.norm_correction && dst.scale) {
     const int rc = qm_dyn_smem<Tin, k_quantize_mma<Tin, BITS, true>>(&smem);
     if (rc != TQ_OK) return rc;
@@ -530,7 +707,10 @@ int launch_mma_pair(const QmJob& j0, const QmJob& j1, int64_t ld, int64_t n, boo
 }
 
 bool qm_serves(const TqFast& f, int32_t dtype, int64_t ld, const TqQuantDst& dst, bool want_qjl) {
-  if (want_qjl || !f.symmetric || !dst.idx || dst.idx_u8 || dst.qjl || dst.rnorm) return false;
+  if (!f.symmetric || !dst.idx || dst.idx_u8) return false;
+  if (!want_qjl && (dst.qjl || dst.rnorm)) return false;
+  if (want_qjl && f.bits == 4) return false;   // 5-bit PROD: the butterfly kernel
+  if (dst.qjl && !tq_aligned(dst.qjl, 4)) return false;
   if (dtype != TQ_F16 && dtype != TQ_BF16 && dtype != TQ_F32) return false;
   // rows must start on 16-byte boundaries (1-bit codebooks have no magnitude levels to test)
   return f.bits >= 2 && f.bits <= 4 && ld % (dtype == TQ_F32 ? 4 : 8) == 0;
@@ -569,9 +749,9 @@ bool tq_quantize_mma_try(const TqFast& f, const void* x, int32_t dtype, int64_t 
   if (!qm_serves(f, dtype, ld, dst, want_qjl)) return false;
 #define TQ_CASE(B)                                                                                           \
   case B:                                                                                                    \
-    *rc = dtype == TQ_F16    ? launch_mma<__half, B>(f, (const __half*)x, ld, n, dst, st)                    \
-          : dtype == TQ_BF16 ? launch_mma<__nv_bfloat16, B>(f, (const __nv_bfloat16*)x, ld, n, dst, st)      \
-                             : launch_mma<float, B>(f, (const float*)x, ld, n, dst, st);                     \
+    *rc = dtype == TQ_F16    ? launch_mma<__half, B>(f, (const __half*)x, ld, n, dst, want_qjl, st)               \
+          : dtype == TQ_BF16 ? launch_mma<__nv_bfloat16, B>(f, (const __nv_bfloat16*)x, ld, n, dst, want_qjl, st) \
+                             : launch_mma<float, B>(f, (const float*)x, ld, n, dst, want_qjl, st);                \
     return true;
   switch (f.bits) {
     TQ_CASE(2)
