@@ -372,6 +372,31 @@ def test_kv_compressor_matches_reference(tq, g_kv):
         comp.compress(np.zeros((1, 1, 4, 64)), np.zeros((1, 1, 4, 64)))
 
 
+@pytest.mark.parametrize("b", [3, 4])
+def test_prod_packed_path_matches_unpacked(tq, b):
+    """PROD quantization with packed output (the tensor-core kernel with its QJL stage, what a cache append runs)
+    against the same call with unpacked output (the butterfly kernel, which the golden vectors pin): indices, norms,
+    residual norms and sketch bits, for fp32, fp16 and bf16 rows, a zero vector among them."""
+    import torch
+    from turboquant_plus_b200 import utils
+    x = o.synth_keys(8192, seed=11).astype(np.float32)
+    x[5] = 0.0
+    t = tq.TurboQuant(D, b, seed=42, rotation="wht")
+    for dt in (torch.float32, torch.float16, torch.bfloat16):
+        xt = torch.as_tensor(x).cuda().to(dt)
+        fast = t.quantize_device(xt, packed=True, want_scale=True)
+        ref = t.quantize_device(xt.float(), packed=False, want_scale=True)
+        ref_packed = utils.pack_indices(ref["idx"].cpu().numpy(), b - 1)
+        rows = (fast["packed"].cpu().numpy() == ref_packed.reshape(len(x), -1)).all(axis=1)
+        flips = int(np.unpackbits(fast["qjl"].cpu().numpy()[rows] ^ ref["qjl"].cpu().numpy()[rows]).sum())
+        print(f"prod{b} {dt}: {int((~rows).sum())} rows with an index mismatch, {flips} sketch bits differ of {rows.sum() * D}")
+        assert (~rows).sum() <= 4 and flips <= 16
+        for key, tol in (("norm", 1e-6), ("scale", 2e-6), ("rnorm", 2e-5)):
+            torch.testing.assert_close(fast[key][torch.as_tensor(rows).cuda()], ref[key][torch.as_tensor(rows).cuda()],
+                                       rtol=tol, atol=0)
+        assert rows[5] and (fast["qjl"][5] == 0xFF).all() and float(fast["rnorm"][5]) == 0.0
+
+
 def test_input_dtypes_and_errors(tq):
     import torch
     x = o.synth_keys(1000, seed=5)
@@ -381,8 +406,8 @@ def test_input_dtypes_and_errors(tq):
     h16 = q.quantize_device(torch.as_tensor(x).cuda().half(), packed=True)
     b16 = q.quantize_device(torch.as_tensor(x).cuda().bfloat16(), packed=True)
     b32 = q.quantize_device(torch.as_tensor(x).cuda().bfloat16().float(), packed=True)
-    # 16-bit inputs run the Hadamard transform on the tensor cores, fp32 inputs in registers: the same values
-    # up to fp32 rounding, so indices may differ only for coordinates that sit on a decision boundary
+    # 16-bit rows go through the tensor-core Hadamard as they are, fp32 rows as three exact bf16 terms: the same
+    # values up to fp32 rounding, so indices may differ only for coordinates that sit on a decision boundary
     for lo, hi in ((h, h16), (b32, b16)):
         differ = (lo["packed"] != hi["packed"]).any(dim=1).sum().item()
         assert differ <= 2, differ
