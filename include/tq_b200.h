@@ -210,6 +210,15 @@ int tq_cache_append(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cac
                     uint8_t* pool_dev, const void* k_dev, const void* v_dev, int32_t dtype,
                     int64_t n_tokens, const int64_t* slot_dev, void* stream);
 
+/* Bookkeeping of a decode step in one launch (new surface; the reference appends in Python): for every sequence b
+ * the slot of its next token, block_table[b][seq_lens[b] / page_tokens] * page_tokens + seq_lens[b] % page_tokens,
+ * written `copies` times -- slots_dev[c][b] = slot + c * copy_stride, for layers whose pages follow one another in one
+ * pool -- and seq_lens[b] incremented.  A sequence whose block-table row is full gets slot -1 (tq_cache_append skips
+ * it) and keeps its length. */
+int tq_decode_step_slots(const int32_t* block_table_dev, int32_t max_pages_per_seq, int32_t* seq_lens_dev,
+                         int32_t page_tokens, int32_t batch, int32_t copies, int64_t copy_stride,
+                         int64_t* slots_dev, void* stream);
+
 /* Stores rows that were quantized elsewhere (tq_quantize with a dense-mode quantizer, whose
  * kernel does not address pages) into the records of a paged cache: which = 0 writes the K
  * arrays, 1 the V arrays.  packed_dev [n_tokens][num_kv_heads][idx_bytes], scale_dev

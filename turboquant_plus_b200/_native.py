@@ -80,6 +80,7 @@ SIGNATURES = {
     "tq_cache_store": (C.c_int, [C.POINTER(CacheLayout), _P, _I32, _P, _P, _P, _P, _I64, _P, _P]),
     "tq_decode_workspace_bytes": (C.c_int64, [_I32, _I32, _I32, _I32]),
     "tq_decode_workspace_init": (C.c_int, [_P, _I64, _P]),
+    "tq_decode_step_slots": (C.c_int, [_P, _I32, _P, _I32, _I32, _I32, _I64, _P, _P]),
     "tq_decode_status_sync": (C.c_int, [_P, _I64, C.POINTER(_I32)]),
     "tq_selftest_wait_gives_up": (C.c_int, [_P, _I64, _P]),
     "tq_decode_attn": (C.c_int, [_P, _P, C.POINTER(CacheLayout), _P, _P, _I32, _P, _P, _I32, _I32, _I32, _F,

@@ -1,6 +1,32 @@
 // Quantize-on-append into the paged cache (dispatch over the per-tensor formats).
 #include "tq_internal.cuh"
 
+// Slots of the next token of every sequence, for a decode step: sequence b appends at position seq_lens[b], which the
+// block table maps to a page.  One launch instead of a chain of elementwise tensor operations in front of the append.
+__global__ void k_decode_step_slots(const int32_t* __restrict__ block_table, int32_t max_pages, int32_t* seq_lens,
+                                    int32_t page_tokens, int32_t batch, int32_t copies, int64_t copy_stride,
+                                    int64_t* __restrict__ slots) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= batch) return;
+  const int pos = seq_lens[b];
+  const int pg = pos / page_tokens;
+  int64_t slot = -1;   // a sequence whose block-table row is full (or whose length is negative) appends nothing
+  if (pos >= 0 && pg < max_pages) slot = (int64_t)block_table[(int64_t)b * max_pages + pg] * page_tokens + (pos - pg * page_tokens);
+  for (int c = 0; c < copies; ++c) slots[(int64_t)c * batch + b] = slot < 0 ? -1 : slot + c * copy_stride;
+  if (slot >= 0) seq_lens[b] = pos + 1;
+}
+
+extern "C" int tq_decode_step_slots(const int32_t* block_table_dev, int32_t max_pages_per_seq, int32_t* seq_lens_dev,
+                                    int32_t page_tokens, int32_t batch, int32_t copies, int64_t copy_stride,
+                                    int64_t* slots_dev, void* stream) {
+  TQ_REQUIRE(batch >= 0 && copies >= 1 && page_tokens >= 1 && max_pages_per_seq >= 1, TQ_ERR_INVALID, "bad sizes");
+  if (batch == 0) return TQ_OK;
+  TQ_REQUIRE(block_table_dev && seq_lens_dev && slots_dev, TQ_ERR_INVALID, "tq_decode_step_slots: null buffer");
+  k_decode_step_slots<<<(batch + 127) / 128, 128, 0, (cudaStream_t)stream>>>(block_table_dev, max_pages_per_seq, seq_lens_dev,
+                                                                            page_tokens, batch, copies, copy_stride, slots_dev);
+  return tq_launch_check("k_decode_step_slots");
+}
+
 extern "C" int tq_cache_append(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cache_layout* L,
                                uint8_t* pool_dev, const void* k_dev, const void* v_dev, int32_t dtype, int64_t n_tokens,
                                const int64_t* slot_dev, void* stream) {

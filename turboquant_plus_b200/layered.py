@@ -74,8 +74,9 @@ class LayeredKVCache:
             "out": torch.zeros((L, batch, num_q_heads, d), dtype=dtype, device=dev),
             "bt": block_table.to(device=dev, dtype=torch.int32).contiguous(),
             "len": seq_lens.to(device=dev, dtype=torch.int32).clone(),
-            "slots": torch.zeros((batch,), dtype=torch.int64, device=dev),
-            "rows": torch.arange(batch, device=dev),
+            # slots of the step's new tokens, once per layer of the largest format group: layer l of a group has its
+            # pages at l * num_pages in the group's pool
+            "slots": torch.zeros((max(len(m) for _, m in self.groups), batch), dtype=torch.int64, device=dev),
         }
         ws = self.layers[0].workspace(batch, num_q_heads, st["bt"].shape[1])
 
@@ -83,27 +84,34 @@ class LayeredKVCache:
         plans = []
         for whole, members in self.groups:
             idx = None if members == list(range(L)) else torch.tensor(members, device=dev)
-            base = (torch.arange(len(members), device=dev, dtype=torch.int64) * (self.num_pages * self.page_tokens))[:, None]
-            plans.append((whole, idx, base, len(members)))
+            plans.append((whole, idx, len(members)))
 
-        def body():
-            pos = st["len"].to(torch.int64)
-            page = st["bt"][st["rows"], pos // self.page_tokens].to(torch.int64)
-            st["slots"].copy_(page * self.page_tokens + pos % self.page_tokens)
-            st["len"].add_(1)
+        def append_part():
+            # slots of the new tokens and the lengths' increment: one launch
+            with torch.cuda.device(dev):
+                nv.call("tq_decode_step_slots", nv.ptr(st["bt"]), st["bt"].shape[1], nv.ptr(st["len"]), self.page_tokens,
+                        batch, st["slots"].shape[0], self.num_pages * self.page_tokens, nv.ptr(st["slots"]),
+                        nv.stream_ptr())
             # one quantize-on-append launch per format group: the new token of every layer of the group at once
-            for whole, idx, base, n in plans:
+            for whole, idx, n in plans:
                 k = st["k"] if idx is None else st["k"].index_select(0, idx)
                 v = st["v"] if idx is None else st["v"].index_select(0, idx)
                 whole.append(k.reshape(n * batch, self.num_kv_heads, d), v.reshape(n * batch, self.num_kv_heads, d),
-                             (base + st["slots"][None, :]).reshape(-1))
-            for i, layer in enumerate(self.layers):
+                             st["slots"][:n].reshape(-1))
+
+        def attend_part(lo, hi):
+            for i in range(lo, hi):
+                layer = self.layers[i]
                 # only an attention call that follows another layer's attention call may start early: that kernel
                 # writes nothing this one reads before its dependency wait.  The first call follows the append,
                 # which writes the cache page of the new token, so it is launched in stream order.
                 # The queries of every layer are in place before the first launch of the step (they arrive with the
                 # step's host-to-device copy), so those calls may read them early as well.
                 layer.attend(st["q"][i], st["bt"], st["len"], out=st["out"][i], workspace=ws, overlap="q" if i > 0 else False)
+
+        def body():
+            append_part()
+            attend_part(0, L)
 
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
@@ -119,6 +127,8 @@ class LayeredKVCache:
         st["len"].copy_(saved)
         st["graph"] = graph
         st["body"] = body
+        st["parts"] = (append_part, attend_part)
+        st["io_stream"] = side
         self._step = st
         return st
 
@@ -158,10 +168,27 @@ class LayeredKVCache:
             key = tuple(t.data_ptr() for t in hosts)
             if st.get("io_key") != key:
                 graph = torch.cuda.CUDAGraph()
+                append_part, attend_part = st["parts"]
+                side, half = st["io_stream"], self.num_layers // 2
                 with torch.cuda.graph(graph):
-                    self._copy_in(q_host, k_host, v_host)
-                    st["body"]()
-                    out_host.copy_(st["out"], non_blocking=True)
+                    # The copies are branches of the graph.  In: the new K/V rows first, then the queries on a side
+                    # branch under the append, which needs only the rows.  Out: the outputs of the lower half of the
+                    # layers leave while the upper half is still computing.
+                    main = torch.cuda.current_stream(self.device)
+                    st["k"].copy_(k_host, non_blocking=True)
+                    st["v"].copy_(v_host, non_blocking=True)
+                    side.wait_stream(main)
+                    with torch.cuda.stream(side):
+                        st["q"].copy_(q_host, non_blocking=True)
+                    append_part()
+                    main.wait_stream(side)
+                    attend_part(0, half)
+                    side.wait_stream(main)
+                    with torch.cuda.stream(side):
+                        out_host[:half].copy_(st["out"][:half], non_blocking=True)
+                    attend_part(half, self.num_layers)
+                    out_host[half:].copy_(st["out"][half:], non_blocking=True)
+                    main.wait_stream(side)
                 st["io_graph"], st["io_key"], st["io_refs"] = graph, key, hosts   # the graph holds raw host pointers
             st["io_graph"].replay()
         else:
