@@ -164,8 +164,9 @@ class LayeredKVCache:
         torch = nv.require_cuda()
         st = self._step
         hosts = (q_host, k_host, v_host, out_host)
-        if all(t.is_pinned() for t in hosts):
-            key = tuple(t.data_ptr() for t in hosts)
+        key = (q_host.data_ptr(), k_host.data_ptr(), v_host.data_ptr(), out_host.data_ptr())
+        # (buffers seen before are known to be pinned: the query of that attribute costs microseconds per tensor)
+        if st.get("io_key") == key or all(t.is_pinned() for t in hosts):
             if st.get("io_key") != key:
                 graph = torch.cuda.CUDAGraph()
                 append_part, attend_part = st["parts"]
