@@ -734,11 +734,18 @@ bool tq_decode_g4_try(const tqatt::AttnParams& P, const TqFast& fk, const TqFast
 #undef TQ_ATT_G4
   // q8_0 and PROD keys (the sparse-V option of these pairs runs the general kernel)
   if (P.sparse_v) return false;
-#define TQ_ATT_G4X(K, V)                                        \
-  if (kf == K && vf == V) {                                     \
-    if (!layout_matches<K, V>(P.L)) return false;               \
-    *rc = launch_attn_g4<K, V, false, false>(P, fk, fv, st);    \
-    return true;                                                \
+#define TQ_ATT_G4X(K, V)                                                                                   \
+  if (kf == K && vf == V) {                                                                                \
+    if (!layout_matches<K, V>(P.L)) return false;                                                          \
+    /* the four-warp form where four CTAs with two page records each fit an SM */                         \
+    if constexpr (4 * (G4<K, V, 4>::SMEM + 1024) <= 228 * 1024) {                                          \
+      if (P.q_early) {                                                                                     \
+        *rc = launch_attn_g4<K, V, false, false, 4>(P, fk, fv, st);                                        \
+        return true;                                                                                       \
+      }                                                                                                    \
+    }                                                                                                      \
+    *rc = launch_attn_g4<K, V, false, false>(P, fk, fv, st);                                               \
+    return true;                                                                                           \
   }
   TQ_ATT_G4X(8, 2) TQ_ATT_G4X(8, 3) TQ_ATT_G4X(8, 4) TQ_ATT_G4X(8, 8)
   TQ_ATT_G4X(18, 2) TQ_ATT_G4X(18, 3) TQ_ATT_G4X(19, 2) TQ_ATT_G4X(19, 3) TQ_ATT_G4X(19, 4) TQ_ATT_G4X(20, 3) TQ_ATT_G4X(20, 4)
