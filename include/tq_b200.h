@@ -313,6 +313,13 @@ int tq_decode_attn(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cach
  * it only before its first write (split partials, tickets, output).  Honoured by the kernel for PolarQuant K and V
  * with <= 4 query heads per KV head and a sign-WHT K rotation; elsewhere it means TQ_DECODE_OVERLAP. */
 #define TQ_DECODE_OVERLAP_Q (8 | 64)
+/* TQ_DECODE_OVERLAP_APPEND (bits 3, 6 and 7): for the attention call that follows the append of the step's new token.
+ * The caller states that, of everything this call reads, the preceding kernel writes at most the last cached position
+ * of each sequence (slot seq_lens[b] - 1): not the queries, not the block table, not the sequence lengths, no other
+ * page.  The kernel then streams every page but the last of each sequence while that kernel is still running,
+ * fetches the last page once it has completed, and writes afterwards.  (tq_cache_append and tq_quantize let their
+ * dependents start early for this.)  Honoured where TQ_DECODE_OVERLAP_Q is; elsewhere the call runs in stream order. */
+#define TQ_DECODE_OVERLAP_APPEND (8 | 64 | 128)
 /* TQ_DECODE_SPARSE_V (bit 4): sparse V as in the reference's docs/papers/sparse-v-dequant.md:64-84 -- the V
  * dequantization and accumulation are skipped where the attention weight exp(score - running max) is below 1e-6;
  * here per 16-token tile of a warp (skipped when every weight of the tile, for every query head of the group, is

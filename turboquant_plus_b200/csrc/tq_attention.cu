@@ -674,6 +674,11 @@ static int decode_impl(const tq_quantizer* kq, const tq_quantizer* vq, const tq_
   P.nodeq = (phases & TQ_DECODE_NO_DEQUANT) ? 1 : 0;
   // queries come from the preceding kernel when the K rotation is dense (k_prepare_queries writes them)
   P.q_early = ((phases & TQ_DECODE_OVERLAP_Q) == TQ_DECODE_OVERLAP_Q && !k_dense) ? 1 : 0;
+  // After an append only the specialised kernel knows to fetch the page of the new token late; everything else runs
+  // in stream order.
+  const bool after_append = (phases & TQ_DECODE_OVERLAP_APPEND) == TQ_DECODE_OVERLAP_APPEND;
+  P.tail_late = after_append && P.q_early ? 1 : 0;
+  if (after_append && !P.tail_late) P.overlap = 0;
   P.L = *L;
   TqFast none;
   memset(&none, 0, sizeof(none));
@@ -685,6 +690,7 @@ static int decode_impl(const tq_quantizer* kq, const tq_quantizer* vq, const tq_
   // PolarQuant K and V with at most four query heads per KV head on 128-token pages take the kernel specialised
   // for that shape (tq_decode_g4.cu)
   if (tq_decode_g4_try(P, fk, fv, st, &rc)) return rc;
+  if (after_append) P.overlap = P.q_early = P.tail_late = 0;   // the general kernel: stream order
   rc = TQ_ERR_UNSUPPORTED;
 #define TQ_ATT(K, V) \
   if (L->k_format == K && L->v_format == V) rc = launch_attn<K, V>(P, fk, fv, st);

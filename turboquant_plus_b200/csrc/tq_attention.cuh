@@ -129,6 +129,8 @@ struct AttnParams {
   int32_t sparse_v;    // skip the V work of a 16-token tile whose weights are all below SPARSE_V_TAU: TQ_DECODE_SPARSE_V
   int32_t nodeq;       // measurement variant without table lookups (results meaningless): TQ_DECODE_NO_DEQUANT
   int32_t q_early;     // the preceding kernel does not write the queries: they are read before the dependency wait
+  int32_t tail_late;   // the preceding kernel may write the last cached position of a sequence: its page is fetched
+                       // after the dependency wait, every other page before (TQ_DECODE_OVERLAP_APPEND)
   tq_cache_layout L;
 };
 

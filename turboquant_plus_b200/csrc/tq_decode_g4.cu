@@ -480,7 +480,12 @@ __global__ void __launch_bounds__(32 * NW, 16 / NW) k_decode_attn_g4(const __gri
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 #pragma unroll
     for (int s = 0; s < G4_NS - 1; ++s)
-      if (np > s) issue(s, pg_next[s]);
+      if (np > s) {
+        // after an append the last page of the sequence is what the preceding kernel writes: it is fetched once that
+        // kernel has completed (the wait costs nothing when it already has), every other page right away
+        if (P.tail_late && page_lo + s == n_pages - 1) asm volatile("griddepcontrol.wait;" ::: "memory");
+        issue(s, pg_next[s]);
+      }
     pg_ahead = pg_next[G4_NS - 1];
   }
   if (warp < P.group && (tid != PRODUCER || NW == 4)) {
@@ -606,6 +611,7 @@ __global__ void __launch_bounds__(32 * NW, 16 / NW) k_decode_attn_g4(const __gri
   uint32_t parity = 0;
   for (int i = 0; i < np; ++i) {
     if (tid == PRODUCER && i + G4_NS - 1 < np) {
+      if (P.tail_late && page_lo + i + G4_NS - 1 == n_pages - 1) asm volatile("griddepcontrol.wait;" ::: "memory");
       issue(stage == 0 ? G4_NS - 1 : stage - 1, pg_ahead);            // the stage the page before this one has left
       pg_ahead = bt[min(page_lo + i + G4_NS, P.max_pages - 1)];
     }

@@ -21,6 +21,9 @@
 template <typename Tin, int BITS, bool SYM, bool QJL>
 __global__ void __launch_bounds__(256) k_quantize_wht(const TqFast f, const Tin* __restrict__ x, int64_t ld, int64_t n,
                                                       const TqQuantDst dst) {
+  // a dependent kernel launched with programmatic stream serialization may start now (it waits for this grid's
+  // completion itself before it touches what this grid writes); without such a dependent this does nothing
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   constexpr int NC = 1 << BITS, HALF = NC / 2;
   constexpr int IDXB = 16 * BITS;              // packed bytes per vector
   constexpr int GS = BITS == 4 ? 4 : 8;        // indices per fp32 Horner group (GS * BITS <= 24 bits)
@@ -629,6 +632,7 @@ __global__ void __launch_bounds__(256) k_q8_0_append(const Tin* __restrict__ x, 
                                                      uint8_t* q_base, uint8_t* scale_base,
                                                      const int64_t* __restrict__ slots, int32_t page_tokens,
                                                      int64_t page_stride, int64_t head_stride) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // see k_quantize_wht
   const int lane = threadIdx.x & 31, sub = lane & 7;
   const int64_t v = ((int64_t)blockIdx.x * 256 + threadIdx.x) >> 3;
   const bool ok = v < n_vec;

@@ -117,6 +117,9 @@ __device__ __forceinline__ float2 qm_dup(float v) { return make_float2(v, v); }
 template <typename Tin, int BITS, bool NORMC, bool QJLS = false>
 __device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__ x, int64_t ld, int64_t n,
                                         const TqQuantDst& dst, uint8_t* tile) {
+  // a dependent kernel launched with programmatic stream serialization may start now (it waits for this grid's
+  // completion itself before it touches what this grid writes); without such a dependent this does nothing
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   constexpr int QM_ROWB = qm_rowb<Tin>();
   constexpr int BUFB = QM_ROWS * QM_ROWB;                      // bytes of one staged tile
   constexpr int CHUNKS = (int)(TQ_D * sizeof(Tin) / 16);       // 16-byte chunks per row

@@ -102,12 +102,14 @@ class LayeredKVCache:
         def attend_part(lo, hi):
             for i in range(lo, hi):
                 layer = self.layers[i]
-                # only an attention call that follows another layer's attention call may start early: that kernel
-                # writes nothing this one reads before its dependency wait.  The first call follows the append,
-                # which writes the cache page of the new token, so it is launched in stream order.
-                # The queries of every layer are in place before the first launch of the step (they arrive with the
-                # step's host-to-device copy), so those calls may read them early as well.
-                layer.attend(st["q"][i], st["bt"], st["len"], out=st["out"][i], workspace=ws, overlap="q" if i > 0 else False)
+                # An attention call that follows another layer's attention call may start early: that kernel writes
+                # nothing this one reads before its dependency wait.  The first call follows the append, which writes
+                # the cache slot of the new token and nothing else this call reads: it streams every page but the
+                # last of each sequence while the append runs.  The queries of every layer are in place before the
+                # first launch of the step (they arrive with the step's host-to-device copy), so all calls may read
+                # them early as well.
+                layer.attend(st["q"][i], st["bt"], st["len"], out=st["out"][i], workspace=ws,
+                             overlap="q" if i > 0 else "append")
 
         def body():
             append_part()

@@ -140,12 +140,15 @@ class PagedKVCache:
         only when the preceding kernel writes none of those (another layer's attention call); after an append
         into this cache launch in stream order (overlap=False).  overlap="q" says in addition that the preceding
         kernel does not write ``q`` either (a chain of calls whose queries all exist beforehand): the kernel then
-        waits for its predecessor only before it writes.
+        waits for its predecessor only before it writes.  overlap="append" is for the call that follows the append
+        of the step's new token into this cache: of what the call reads, the preceding kernel writes only the last
+        position of each sequence; every other page is streamed while it runs.
 
         return_lse=True returns (out, lse) with lse (batch, num_q_heads) fp32, the natural log of the softmax
         denominator: what merge_attention needs to join calls over disjoint parts of a sequence."""
         if overlap:   # "q": the preceding kernel does not write the queries either (they are read early too)
-            phases = int(phases) | (nv.DECODE_OVERLAP_Q if overlap == "q" else nv.DECODE_OVERLAP)
+            phases = int(phases) | (nv.DECODE_OVERLAP_Q if overlap == "q" else
+                                    nv.DECODE_OVERLAP_APPEND if overlap == "append" else nv.DECODE_OVERLAP)
         if sparse_v:  # skip V work where every weight of a 16-token tile is below 1e-6 (the reference's sparse V)
             phases = int(phases) | nv.DECODE_SPARSE_V
         torch = nv.require_cuda()
