@@ -615,6 +615,9 @@ __global__ void __launch_bounds__(32 * NW, 16 / NW) k_decode_attn_g4(const __gri
       issue(stage == 0 ? G4_NS - 1 : stage - 1, pg_ahead);            // the stage the page before this one has left
       pg_ahead = bt[min(page_lo + i + G4_NS, P.max_pages - 1)];
     }
+    // (the page the preceding kernel writes is only fetched once that kernel has completed: the bounded wait for it
+    // starts then, however long that kernel runs)
+    if (P.tail_late && page_lo + i == n_pages - 1) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (!s_flags[0] && !mbar_wait_bounded(&bars[stage], parity)) s_flags[0] = 1;
     // the stage address carries a value the wait above produced (always zero), so that no load of the stage can
     // be scheduled ahead of the wait
