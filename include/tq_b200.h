@@ -320,6 +320,11 @@ int tq_decode_attn(const tq_quantizer* kq, const tq_quantizer* vq, const tq_cach
  * fetches the last page once it has completed, and writes afterwards.  (tq_cache_append and tq_quantize let their
  * dependents start early for this.)  Honoured where TQ_DECODE_OVERLAP_Q is; elsewhere the call runs in stream order. */
 #define TQ_DECODE_OVERLAP_APPEND (8 | 64 | 128)
+/* TQ_DECODE_CHAIN_HEAD (bit 8): a hint without any effect on the result.  Attention calls launched with
+ * TQ_DECODE_OVERLAP_Q follow this call in the stream (it is the first of a chain: the first layer of a decode step
+ * whose queries all exist beforehand): the kernel then takes the form those calls take, whose CTAs leave room on
+ * an SM for the CTAs of the next call.  Not combined with TQ_DECODE_OVERLAP_APPEND. */
+#define TQ_DECODE_CHAIN_HEAD 256
 /* TQ_DECODE_SPARSE_V (bit 4): sparse V as in the reference's docs/papers/sparse-v-dequant.md:64-84 -- the V
  * dequantization and accumulation are skipped where the attention weight exp(score - running max) is below 1e-6;
  * here per 16-token tile of a warp (skipped when every weight of the tile, for every query head of the group, is

@@ -20,6 +20,7 @@ FMT_PROD2, FMT_PROD3, FMT_PROD4 = 18, 19, 20
 DECODE_OVERLAP = 8  # tq_decode_attn_phases: TQ_DECODE_OVERLAP
 DECODE_OVERLAP_Q = 8 | 64  # TQ_DECODE_OVERLAP_Q: the queries may be read early too
 DECODE_OVERLAP_APPEND = 8 | 64 | 128  # TQ_DECODE_OVERLAP_APPEND: after the append of the step's token
+DECODE_CHAIN_HEAD = 256  # TQ_DECODE_CHAIN_HEAD: calls with DECODE_OVERLAP_Q follow this one
 DECODE_SPARSE_V = 16  # TQ_DECODE_SPARSE_V
 DECODE_NO_DEQUANT = 32  # TQ_DECODE_NO_DEQUANT (measurement only)
 FORMATS = {"turbo2": FMT_TURBO2, "turbo3": FMT_TURBO3, "turbo4": FMT_TURBO4, "q8_0": FMT_Q8_0,

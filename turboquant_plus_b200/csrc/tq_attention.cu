@@ -677,8 +677,9 @@ static int decode_impl(const tq_quantizer* kq, const tq_quantizer* vq, const tq_
   // After an append only the specialised kernel knows to fetch the page of the new token late; everything else runs
   // in stream order.
   const bool after_append = (phases & TQ_DECODE_OVERLAP_APPEND) == TQ_DECODE_OVERLAP_APPEND;
-  P.tail_late = after_append && P.q_early ? 1 : 0;
-  if (after_append && !P.tail_late) P.overlap = 0;
+  P.tail_late = after_append && P.q_early && !P.sparse_v ? 1 : 0;
+  if (after_append && !P.tail_late) P.overlap = P.q_early = 0;
+  P.chain_head = (phases & TQ_DECODE_CHAIN_HEAD) ? 1 : 0;
   P.L = *L;
   TqFast none;
   memset(&none, 0, sizeof(none));

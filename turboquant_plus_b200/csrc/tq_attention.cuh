@@ -131,6 +131,7 @@ struct AttnParams {
   int32_t q_early;     // the preceding kernel does not write the queries: they are read before the dependency wait
   int32_t tail_late;   // the preceding kernel may write the last cached position of a sequence: its page is fetched
                        // after the dependency wait, every other page before (TQ_DECODE_OVERLAP_APPEND)
+  int32_t chain_head;  // attention calls with TQ_DECODE_OVERLAP_Q follow this one (TQ_DECODE_CHAIN_HEAD)
   tq_cache_layout L;
 };
 

@@ -411,7 +411,9 @@ __device__ __forceinline__ void g4_page(G4State& S, uint32_t st, const G4Thr& T,
 // NW warps per CTA: 8 (two CTAs per SM), or 4 (four per SM, two tiles per warp and page) for chains of calls that may
 // overlap completely: the CTAs of two consecutive calls then share an SM four at a time, each in a phase of its own,
 // and the SM's warps are in a page loop 80 % of the time instead of 67 %.
-template <int KK, int VK, bool SPARSE, bool NODEQ, int NW>
+// TAIL: the call follows the append of the step's token (TQ_DECODE_OVERLAP_APPEND).  A template parameter, so that the
+// page loop of every other instantiation carries nothing for it.
+template <int KK, int VK, bool SPARSE, bool NODEQ, int NW, bool TAIL = false>
 __global__ void __launch_bounds__(32 * NW, 16 / NW) k_decode_attn_g4(const __grid_constant__ AttnParams P, const __grid_constant__ AttnQuant fk,
                                                                       const __grid_constant__ AttnQuant fv) {
   using C = G4<KK, VK, NW>;
@@ -483,7 +485,7 @@ __global__ void __launch_bounds__(32 * NW, 16 / NW) k_decode_attn_g4(const __gri
       if (np > s) {
         // after an append the last page of the sequence is what the preceding kernel writes: it is fetched once that
         // kernel has completed (the wait costs nothing when it already has), every other page right away
-        if (P.tail_late && page_lo + s == n_pages - 1) asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (TAIL && page_lo + s == n_pages - 1) asm volatile("griddepcontrol.wait;" ::: "memory");
         issue(s, pg_next[s]);
       }
     pg_ahead = pg_next[G4_NS - 1];
@@ -611,13 +613,13 @@ __global__ void __launch_bounds__(32 * NW, 16 / NW) k_decode_attn_g4(const __gri
   uint32_t parity = 0;
   for (int i = 0; i < np; ++i) {
     if (tid == PRODUCER && i + G4_NS - 1 < np) {
-      if (P.tail_late && page_lo + i + G4_NS - 1 == n_pages - 1) asm volatile("griddepcontrol.wait;" ::: "memory");
+      if (TAIL && page_lo + i + G4_NS - 1 == n_pages - 1) asm volatile("griddepcontrol.wait;" ::: "memory");
       issue(stage == 0 ? G4_NS - 1 : stage - 1, pg_ahead);            // the stage the page before this one has left
       pg_ahead = bt[min(page_lo + i + G4_NS, P.max_pages - 1)];
     }
     // (the page the preceding kernel writes is only fetched once that kernel has completed: the bounded wait for it
     // starts then, however long that kernel runs)
-    if (P.tail_late && page_lo + i == n_pages - 1) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (TAIL && page_lo + i == n_pages - 1) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (!s_flags[0] && !mbar_wait_bounded(&bars[stage], parity)) s_flags[0] = 1;
     // the stage address carries a value the wait above produced (always zero), so that no load of the stage can
     // be scheduled ahead of the wait
@@ -682,7 +684,7 @@ __global__ void __launch_bounds__(32 * NW, 16 / NW) k_decode_attn_g4(const __gri
   finish_splits<VT::Q8, NT>(P, fv.s1, fv.s2, fv.alpha, qbuf, stage0, s_flags, row0, ns, b, kvh, tid, bar_id);
 }
 
-template <int KK, int VK, bool SPARSE, bool NODEQ, int NW = ATT_WARPS>
+template <int KK, int VK, bool SPARSE, bool NODEQ, int NW = ATT_WARPS, bool TAIL = false>
 int launch_attn_g4(const AttnParams& P, const TqFast& fk, const TqFast& fv, cudaStream_t st) {
   using C = G4<KK, VK, NW>;
   static_assert((16 / NW) * (C::SMEM + 1024) <= 228 * 1024, "CTAs of the specialised decode kernel per SM");
@@ -690,7 +692,7 @@ int launch_attn_g4(const AttnParams& P, const TqFast& fk, const TqFast& fv, cuda
   int dev = 0;
   TQ_CUDA(cudaGetDevice(&dev));
   if (configured_dev != dev) {
-    TQ_CUDA(cudaFuncSetAttribute(k_decode_attn_g4<KK, VK, SPARSE, NODEQ, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+    TQ_CUDA(cudaFuncSetAttribute(k_decode_attn_g4<KK, VK, SPARSE, NODEQ, NW, TAIL>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
     configured_dev = dev;
   }
   AttnQuant ak, av;
@@ -710,7 +712,7 @@ int launch_attn_g4(const AttnParams& P, const TqFast& fk, const TqFast& fv, cuda
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = P.overlap ? 1 : 0;
-  TQ_CUDA(cudaLaunchKernelEx(&cfg, k_decode_attn_g4<KK, VK, SPARSE, NODEQ, NW>, P, ak, av));
+  TQ_CUDA(cudaLaunchKernelEx(&cfg, k_decode_attn_g4<KK, VK, SPARSE, NODEQ, NW, TAIL>, P, ak, av));
   return tq_launch_check("k_decode_attn_g4");
 }
 
@@ -727,14 +729,20 @@ bool layout_matches(const tq_cache_layout& L) {
 bool tq_decode_g4_try(const tqatt::AttnParams& P, const TqFast& fk, const TqFast& fv, cudaStream_t st, int* rc) {
   const int kf = P.L.k_format, vf = P.L.v_format;
   if (P.group > G4_HEADS) return false;
+  // The four-warp form pays in a chain of attention calls, where the CTAs of consecutive calls share an SM in
+  // different phases: calls launched with TQ_DECODE_OVERLAP_Q, and the call in front of them when the caller says so
+  // (TQ_DECODE_CHAIN_HEAD).  A call that follows an append overlaps only its start with that short kernel: it takes
+  // the eight-warp form, which is the faster one for a call on its own.
+  const bool chain = (P.q_early || P.chain_head) && !P.tail_late;
   // PolarQuant K and V: every pair of widths, with the sparse-V and the measurement variants
 #define TQ_ATT_G4(K, V)                                                                                              \
   if (kf == K && vf == V) {                                                                                          \
     if (!layout_matches<K, V>(P.L)) return false;                                                                    \
     if (P.nodeq && K == 3 && V == 3) *rc = launch_attn_g4<3, 3, false, true>(P, fk, fv, st);                         \
-    else if (P.sparse_v && P.q_early) *rc = launch_attn_g4<K, V, true, false, 4>(P, fk, fv, st);                     \
+    else if (P.sparse_v && chain) *rc = launch_attn_g4<K, V, true, false, 4>(P, fk, fv, st);                         \
     else if (P.sparse_v) *rc = launch_attn_g4<K, V, true, false>(P, fk, fv, st);                                     \
-    else if (P.q_early) *rc = launch_attn_g4<K, V, false, false, 4>(P, fk, fv, st);                                  \
+    else if (P.tail_late) *rc = launch_attn_g4<K, V, false, false, ATT_WARPS, true>(P, fk, fv, st);                  \
+    else if (chain) *rc = launch_attn_g4<K, V, false, false, 4>(P, fk, fv, st);                                      \
     else *rc = launch_attn_g4<K, V, false, false>(P, fk, fv, st);                                                    \
     return true;                                                                                                     \
   }
@@ -748,12 +756,13 @@ bool tq_decode_g4_try(const tqatt::AttnParams& P, const TqFast& fk, const TqFast
     if (!layout_matches<K, V>(P.L)) return false;                                                          \
     /* the four-warp form where four CTAs with two page records each fit an SM */                         \
     if constexpr (4 * (G4<K, V, 4>::SMEM + 1024) <= 228 * 1024) {                                          \
-      if (P.q_early) {                                                                                     \
+      if (chain) {                                                                                         \
         *rc = launch_attn_g4<K, V, false, false, 4>(P, fk, fv, st);                                        \
         return true;                                                                                       \
       }                                                                                                    \
     }                                                                                                      \
-    *rc = launch_attn_g4<K, V, false, false>(P, fk, fv, st);                                               \
+    if (P.tail_late) *rc = launch_attn_g4<K, V, false, false, ATT_WARPS, true>(P, fk, fv, st);             \
+    else *rc = launch_attn_g4<K, V, false, false>(P, fk, fv, st);                                          \
     return true;                                                                                           \
   }
   TQ_ATT_G4X(8, 2) TQ_ATT_G4X(8, 3) TQ_ATT_G4X(8, 4) TQ_ATT_G4X(8, 8)

@@ -103,13 +103,12 @@ class LayeredKVCache:
             for i in range(lo, hi):
                 layer = self.layers[i]
                 # An attention call that follows another layer's attention call may start early: that kernel writes
-                # nothing this one reads before its dependency wait.  The first call follows the append, which writes
-                # the cache slot of the new token and nothing else this call reads: it streams every page but the
-                # last of each sequence while the append runs.  The queries of every layer are in place before the
-                # first launch of the step (they arrive with the step's host-to-device copy), so all calls may read
-                # them early as well.
+                # nothing this one reads before its dependency wait, and the queries of every layer are in place
+                # before the first launch of the step (they arrive with the step's host-to-device copy).  The first
+                # call follows the append, which writes the cache slot of the new token: it runs in stream order, in
+                # the form of the calls that follow it.
                 layer.attend(st["q"][i], st["bt"], st["len"], out=st["out"][i], workspace=ws,
-                             overlap="q" if i > 0 else "append")
+                             overlap="q" if i > 0 else False, chain_head=(i == 0))
 
         def body():
             append_part()

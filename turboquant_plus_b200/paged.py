@@ -131,7 +131,7 @@ class PagedKVCache:
         return self._ws
 
     def attend(self, q, block_table, seq_lens, scale=None, out=None, workspace=None, phases=7, overlap=False,
-               sparse_v=False, return_lse=False):
+               sparse_v=False, return_lse=False, chain_head=False):
         """q: (batch, num_q_heads, head_dim) CUDA tensor; block_table: (batch, max_pages) int32 page
         numbers; seq_lens: (batch,) int32.  Returns (batch, num_q_heads, head_dim) in q's dtype.
 
@@ -142,13 +142,16 @@ class PagedKVCache:
         kernel does not write ``q`` either (a chain of calls whose queries all exist beforehand): the kernel then
         waits for its predecessor only before it writes.  overlap="append" is for the call that follows the append
         of the step's new token into this cache: of what the call reads, the preceding kernel writes only the last
-        position of each sequence; every other page is streamed while it runs.
+        position of each sequence; every other page is streamed while it runs.  chain_head=True is a hint for a call
+        in stream order that is followed by calls with overlap="q" (the first layer of a step).
 
         return_lse=True returns (out, lse) with lse (batch, num_q_heads) fp32, the natural log of the softmax
         denominator: what merge_attention needs to join calls over disjoint parts of a sequence."""
         if overlap:   # "q": the preceding kernel does not write the queries either (they are read early too)
             phases = int(phases) | (nv.DECODE_OVERLAP_Q if overlap == "q" else
                                     nv.DECODE_OVERLAP_APPEND if overlap == "append" else nv.DECODE_OVERLAP)
+        if chain_head:
+            phases = int(phases) | nv.DECODE_CHAIN_HEAD
         if sparse_v:  # skip V work where every weight of a 16-token tile is below 1e-6 (the reference's sparse V)
             phases = int(phases) | nv.DECODE_SPARSE_V
         torch = nv.require_cuda()
