@@ -365,13 +365,16 @@ def test_attend_right_after_append(tq, fmt):
     assert np.median(per_seq) < 1e-3 and (per_seq < TOL).sum() >= B - 6 and per_seq.max() < 5e-2
 
 
-def test_overlap_launch_and_compressor_streaming_api(tq):
+@pytest.mark.parametrize("hq", [16, 32])
+def test_overlap_launch_and_compressor_streaming_api(tq, hq):
     """(1) TQ_DECODE_OVERLAP (programmatic dependent launch) changes when the kernel starts, never what it computes:
-    a chain of overlapped calls, eager and replayed from a CUDA graph, returns the bytes of the plain calls.
+    a chain of overlapped calls, eager and replayed from a CUDA graph, returns the bytes of the plain calls.  With
+    eight query heads per KV head (hq = 32) the chain mode "q" deals a group to two CTAs of the specialised kernel,
+    the plain calls run the general kernel.
     (2) KVCacheCompressor.init_cache / append / attend / prefill_attend give what the paged cache gives."""
     import torch
     rng = np.random.default_rng(21)
-    hkv, hq, n = 4, 16, 1500
+    hkv, n = 4, 1500
     caches = []
     for i in range(3):
         c = tq.PagedKVCache(D, hkv, num_pages=12, seed=42)

@@ -680,6 +680,7 @@ static int decode_impl(const tq_quantizer* kq, const tq_quantizer* vq, const tq_
   P.tail_late = after_append && P.q_early && !P.sparse_v ? 1 : 0;
   if (after_append && !P.tail_late) P.overlap = P.q_early = 0;
   P.chain_head = (phases & TQ_DECODE_CHAIN_HEAD) ? 1 : 0;
+  P.kv_div = 1;
   P.L = *L;
   TqFast none;
   memset(&none, 0, sizeof(none));
@@ -835,7 +836,9 @@ extern "C" int tq_decode_attn_static(const tq_quantizer* kq, const tq_quantizer*
   // synchronisation); a call that was torn down half-way then cannot mislead the next one.  Partials are written
   // before they are read.
   uint8_t* tail = (uint8_t*)scratch + TQ_STATIC_SCRATCH_BYTES - TAIL_BYTES;
-  TQ_CUDA(cudaMemsetAsync(tail, 0, (size_t)batch * L->num_kv_heads * 4, (cudaStream_t)stream));
+  // (up to four counters per (sequence, KV head): groups of more than four query heads are dealt to several CTAs)
+  const size_t counters = (size_t)batch * L->num_kv_heads * 4;
+  TQ_CUDA(cudaMemsetAsync(tail, 0, (counters < (size_t)MAX_TICKETS ? counters : (size_t)MAX_TICKETS) * 4, (cudaStream_t)stream));
   return tq_decode_attn_phases(kq, vq, L, pool_dev, block_table_dev, max_pages_per_seq, seq_lens_dev, q_dev, q_dtype,
                                batch, num_q_heads, scale, scratch, TQ_STATIC_SCRATCH_BYTES, out_dev, out_dtype, 3,
                                stream);

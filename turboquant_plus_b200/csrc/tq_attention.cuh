@@ -132,6 +132,8 @@ struct AttnParams {
   int32_t tail_late;   // the preceding kernel may write the last cached position of a sequence: its page is fetched
                        // after the dependency wait, every other page before (TQ_DECODE_OVERLAP_APPEND)
   int32_t chain_head;  // attention calls with TQ_DECODE_OVERLAP_Q follow this one (TQ_DECODE_CHAIN_HEAD)
+  int32_t kv_div;      // CTAs (grid.y entries) per KV head of the cache: hkv and group describe the query-head groups
+                       // that a CTA serves, kv_div of which share a KV head (specialised kernel, groups of 5..16 heads)
   tq_cache_layout L;
 };
 

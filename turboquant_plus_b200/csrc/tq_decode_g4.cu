@@ -453,7 +453,8 @@ __global__ void __launch_bounds__(32 * NW, 16 / NW) k_decode_attn_g4(const __gri
   volatile int* s_flags = reinterpret_cast<volatile int*>(smg + C::G_BAR + 64);
   uint8_t* stage0 = smg + C::G_STAGE;
   constexpr int PRODUCER = NT - 32;  // lane 0 of the last warp issues every bulk copy
-  const uint8_t* pool_head = P.pool + (int64_t)kvh * P.L.head_stride;
+  // kvh names a group of query heads; kv_div of them share a KV head of the cache
+  const uint8_t* pool_head = P.pool + (int64_t)(P.kv_div == 1 ? kvh : kvh / P.kv_div) * P.L.head_stride;
 
   auto issue = [&](int stage, int64_t page) {
     uint64_t* bar = &bars[stage];
@@ -726,9 +727,25 @@ bool layout_matches(const tq_cache_layout& L) {
 
 }  // namespace
 
-bool tq_decode_g4_try(const tqatt::AttnParams& P, const TqFast& fk, const TqFast& fv, cudaStream_t st, int* rc) {
-  const int kf = P.L.k_format, vf = P.L.v_format;
-  if (P.group > G4_HEADS) return false;
+bool tq_decode_g4_try(const tqatt::AttnParams& P_in, const TqFast& fk, const TqFast& fv, cudaStream_t st, int* rc) {
+  const int kf = P_in.L.k_format, vf = P_in.L.v_format;
+  tqatt::AttnParams P = P_in;
+  if (P.group > G4_HEADS) {
+    // 5..16 query heads per KV head: the group is dealt to 2..4 CTAs of up to four heads each, which run side by side
+    // over the same pages (one of them brings a page in from HBM, the others find it in L2).  Query heads of a KV
+    // head are neighbours, so a CTA's first row is still (grid.y index) * (heads per CTA); only the cache head differs.
+    // This pays in a chain of calls (8 heads, 32K tokens: 16.7 us per call against 25.6 for the general kernel, which
+    // has no early-start form); a call on its own is served better by the general kernel (25.6 against 28.2 us), whose
+    // CTAs dequantize a page once for all eight heads.
+    if (!((P.q_early || P.chain_head) && !P.tail_late)) return false;
+    const int parts = (P.group + G4_HEADS - 1) / G4_HEADS;
+    if (P.group > 4 * G4_HEADS || P.group % parts != 0 || (int64_t)P.hkv * parts > 65535 ||
+        (int64_t)P.batch * P.hkv * parts > MAX_TICKETS)
+      return false;
+    P.group /= parts;
+    P.hkv *= parts;
+    P.kv_div = parts;
+  }
   // The four-warp form pays in a chain of attention calls, where the CTAs of consecutive calls share an SM in
   // different phases: calls launched with TQ_DECODE_OVERLAP_Q, and the call in front of them when the caller says so
   // (TQ_DECODE_CHAIN_HEAD).  A call that follows an append overlaps only its start with that short kernel: it takes
