@@ -435,7 +435,7 @@ def run_ours(args):
                          "peak_source": f"{peak_src} copy bandwidth",
                          # dram__bytes_read.sum + dram__bytes_write.sum of one launch in an ncu capture of this
                          # workload: a constant taken from that profile, not something this run measures
-                         "traffic": 27338240, "traffic_source": "ncu capture of this workload, not measured in this run",
+                         "traffic": 27343104, "traffic_source": "ncu capture of this workload, not measured in this run",
                          "kernel": "k_decode_attn_g4<3,3,dense V>", "us_per_launch": kernel_s * 1e6,
                          "bytes_per_launch": CTX * HKV * BYTES_PER_KV_TOKEN},
             "sparse_v_option": {"ms_per_step": ms_sparse_step, "kv_tokens_per_s": tokens_step / (ms_sparse_step * 1e-3),
