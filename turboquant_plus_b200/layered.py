@@ -177,8 +177,15 @@ class LayeredKVCache:
                     # branch under the append, which needs only the rows.  Out: the outputs of the lower half of the
                     # layers leave while the upper half is still computing.
                     main = torch.cuda.current_stream(self.device)
-                    st["k"].copy_(k_host, non_blocking=True)
-                    st["v"].copy_(v_host, non_blocking=True)
+                    nq, nk = st["q"].numel(), st["k"].numel()
+                    if (k_host.is_contiguous() and v_host.is_contiguous() and k_host.dtype == st["qkv"].dtype
+                            and k_host.numel() == nk and v_host.numel() == nk
+                            and v_host.data_ptr() == k_host.data_ptr() + nk * k_host.element_size()):
+                        # rows of K and V adjacent on the host (host_buffers()): one copy
+                        st["qkv"][nq:].copy_(k_host.reshape(-1).as_strided((2 * nk,), (1,)), non_blocking=True)
+                    else:
+                        st["k"].copy_(k_host, non_blocking=True)
+                        st["v"].copy_(v_host, non_blocking=True)
                     side.wait_stream(main)
                     with torch.cuda.stream(side):
                         st["q"].copy_(q_host, non_blocking=True)
