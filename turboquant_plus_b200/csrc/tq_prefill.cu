@@ -208,19 +208,22 @@ __device__ __forceinline__ void pf_dequant_token(const uint8_t* src, uint8_t* ds
 
 
 // ------------------------------------------------------------------------------------------
-// k_prefill_attn2: the work split over specialised warps (one CTA per SM, 288 threads):
+// k_prefill_attn2: the work split over specialised warps (one CTA per SM, 544 threads):
 //   warps 0-7  rows: two threads per row r = lane r of tensor memory (warps w and w + 4 reach the same 32 lanes), one
 //              per half of a page's 128 score columns: reads S, online softmax (the halves exchange their maxima
-//              through shared memory), writes P, rescales O (lazily: only when the row maximum grows by more than
-//              2^4); the thread of the first half also stages the query and writes the output;
-//   warps 8-15 producer: thread t of warps 8-11 dequantizes the K row of token t of the page, thread t of warps
-//              12-15 its V row (times the V scale), into double-buffered operand tiles; the K scales are copied beside
-//              them; one of them issues the bulk copies of the page records;
+//              through shared memory), writes P, rescales its half of O (lazily: only when the row maximum grows by
+//              more than 2^4); both threads share the query rotation, the split partial, the merge and the output
+//              (64 elements each);
+//   warps 8-11 K producers: thread t dequantizes the K row of token t of the page into a double-buffered operand tile
+//              and copies its scale; they wait for the score MMA of page i - 2 only, one page ahead of
+//   warps 12-15 V producers: the V row of token t times its V scale; their tile is free after the product of page
+//              i - 2; one of them issues the bulk copies of the page records;
 //   warp 16    one lane issues every tcgen05.mma: S_{i+1} = Q K_{i+1}^T is queued before O += P_i V_i, so the
 //              tensor core works on the next page while the row warps are in the softmax of this one.
-// (With one warp per row quarter and one per token quarter -- nine warps -- the row warps needed 4,200 cycles per
-// page and the producers 3,450, against 1,630 of tensor work: two warps per scheduler cannot hide their own
-// latencies.  Seventeen warps give every scheduler four.)
+// (With one warp per row quarter and one per token quarter -- nine warps -- a page took 4,350 cycles.  Seventeen warps
+// alone changed nothing: the time went into executed instructions -- a causal mask evaluated on every page, scalar
+// fp32 arithmetic, polling loops -- and into the K producers waiting for the product of page i - 2 when the score MMA
+// was all they needed.  Now ~3,300 cycles, against 1,536 of tensor work; the shared-memory pipe is the next limit.)
 // Tensor memory, all 512 columns: Q hi 0-63 | Q lo 64-127 | S0 128-255 | S1 256-383 | O 384-511 (fp32, accumulated
 // by the MMAs across pages).  P overlays the first 64 columns of its S buffer.  Hand-offs are mbarriers (counts in
 // brackets): k_ready/v_ready [128 producer arrivals], s_full/o_done [tcgen05.commit], p_ready [128 row arrivals];
