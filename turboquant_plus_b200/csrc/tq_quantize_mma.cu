@@ -131,12 +131,14 @@ __device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__
   // B operands: rows k = 2t, 2t+1 (register 0) and 2t+8, 2t+9 (register 1) of sign1 * H16.  The 16 output columns
   // are dealt to the two n-tiles so that the accumulator columns of lane t (2t, 2t+1 of each tile) are the four
   // consecutive outputs j = 4t .. 4t+3.
-  // They depend on the lane only: the first warp writes them to shared memory once ([i][lane] x 16 bytes) and every
-  // warp reads the four words of a step just before its two MMAs -- 32 registers less per thread, a fifth CTA per SM.
+  // They depend on the lane only: the warps write them to shared memory once ([i][lane] x 16 bytes, two values of i
+  // per warp) and every warp reads the four words of a step just before its two MMAs -- 32 registers less per thread,
+  // a fifth CTA per SM.
   uint8_t* bsm = tile + QM_WARPS * 2 * BUFB;
-  if (warp == 0) {
+  {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int ii = 0; ii < 8 / QM_WARPS; ++ii) {
+      const int i = warp * (8 / QM_WARPS) + ii;
       uint32_t b4[4];
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt)
@@ -160,9 +162,10 @@ __device__ __forceinline__ void qm_body(const TqFast& f, const Tin* __restrict__
   float4* m12f = reinterpret_cast<float4*>(bsm + 8 * 32 * 16);
   uint32_t j2w = 0;
   if constexpr (QJLS) {
-    if (warp == 0) {
+    {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int ii = 0; ii < 8 / QM_WARPS; ++ii) {
+        const int i = warp * (8 / QM_WARPS) + ii;
         float v4[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) v4[c] = (qm_bit(f.s1, 16 * i + 4 * t + c) ^ qm_bit(f.j1, 16 * i + 4 * t + c)) ? -1.0f : 1.0f;
