@@ -400,6 +400,36 @@ def run_ours(args):
     e2e_ms = statistics.median([e2e_region() for _ in range(9)])
     assert torch.isfinite(oh.float()).all()
 
+    # The order of a model's own decode loop, on the device: per layer, append the layer's new token, then attend.
+    # Every attention call then follows an append into its cache; reported for the call in stream order and with
+    # overlap="append" (all pages but the last of the sequence stream while the append runs).
+    loop = {}
+    if rank == 0:
+        kn = torch.randn((LAYERS, 1, HKV, D), generator=gen, device=dev).half()
+        slot1 = (bt[0, CTX // PT].to(torch.int64) * PT)[None]
+        len1 = torch.full((1,), CTX + 1, dtype=torch.int32, device=dev)
+        for mode in (False, "append"):
+            def loop_step():
+                for i, layer in enumerate(cache.layers):
+                    layer.append(kn[i], kn[i], slot1)
+                    layer.attend(q[i], bt, len1, out=out[i], workspace=ws, overlap=mode)
+            loop_step()
+            torch.cuda.synchronize(dev)
+            lg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(lg):
+                loop_step()
+            for _ in range(3):
+                lg.replay()
+            torch.cuda.synchronize(dev)
+            le = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            le[0].record()
+            for _ in range(10):
+                lg.replay()
+            le[1].record()
+            torch.cuda.synchronize(dev)
+            loop["overlap_append" if mode else "stream_order"] = le[0].elapsed_time(le[1]) / 10 * 1e3 / LAYERS
+        assert cache.layers[0].kernel_status(ws) == 0
+
     pre = prefill_probe(torch, tq, dev, gen) if rank == 0 else None
     # the other configurations of the benchmark family, a few steps each, so that every record carries them; with more
     # than one rank they run sharded (KV heads / token-balanced batch) and check the shards against one GPU
@@ -452,6 +482,9 @@ def run_ours(args):
                                       "achieved": append32_bytes / (append32_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                                       "frac": append32_bytes / (append32_ms * 1e-3) / 1e9 / peak,
                                       "bytes_per_vector": D * 4 + 52},
+            "decode_loop_us_per_layer": {"stream_order": loop.get("stream_order"), "overlap_append": loop.get("overlap_append"),
+                                         "note": "per layer: quantize-on-append of one token, then decode attention over "
+                                                 "ctx + 1 tokens; 40 layers, one graph, no host copies"},
             "roofline_quantize_prod": {"bound": "hbm", "kernel": "k_quantize_mma<half,2,QJL stage> for the K rows + k_quantize_mma<half,3> for the V rows, 2^21 vectors each",
                                        "vectors_per_s": 2 * nq32 / (appendp_ms * 1e-3),
                                        "achieved": appendp_bytes / (appendp_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
