@@ -284,6 +284,29 @@ def test_prefill_split_pages(tq):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+def test_prefill_16bit_rows_equal_the_fp32_call(tq, dtype):
+    """Queries and outputs of a chunk in fp16 / bf16: the kernel widens the queries exactly and rounds the outputs to
+    nearest, so the call gives the bits of the fp32 call on the widened queries, rounded by torch.  A ragged last row
+    block (40 queries x 8 heads = 2.5 row blocks) and a split page range are part of the case."""
+    import torch
+    dt = getattr(torch, dtype)
+    rng = np.random.default_rng(31)
+    hkv, g, tq_len = 2, 8, 40
+    kv_lens = [2500, 700]
+    cache = tq.PagedKVCache(D, hkv, num_pages=32, seed=42)
+    ks = [rng.standard_normal((n, hkv, D)).astype(np.float32) for n in kv_lens]
+    vs = [rng.standard_normal((n, hkv, D)).astype(np.float32) for n in kv_lens]
+    bt = fill_cache(cache, ks, vs, kv_lens, rng)
+    q = torch.as_tensor(rng.standard_normal((2, tq_len, hkv * g, D)).astype(np.float32)).cuda().to(dt)
+    out16 = cache.prefill_attend(q, bt, torch.tensor(kv_lens))
+    out32 = cache.prefill_attend(q.float(), bt, torch.tensor(kv_lens))
+    assert cache.kernel_status() == 0 and out16.dtype == dt and out32.dtype == torch.float32
+    assert torch.isfinite(out32).all() and float(out32.abs().max()) > 0
+    assert torch.equal(out16, out32.to(dt))
+
+
+@pytest.mark.gpu
 def test_bounded_wait_gives_up_and_reports(tq):
     """The give-up path of the kernels' bounded waits, run where it is harmless (tq_selftest_wait_gives_up: a wait that
     nothing satisfies, limited to 2^20 clocks): the status word of the workspace reads 1 once, then 0 again, and the

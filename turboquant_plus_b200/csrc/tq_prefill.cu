@@ -69,6 +69,16 @@ __device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&v)[16]) {
       : "r"(addr) : "memory");
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// sixteen columns into v[OFF .. OFF + 15], no wait: the caller waits once for all of its loads
+template <int OFF, int N>
+__device__ __forceinline__ void tmem_ld16_nowait(uint32_t addr, uint32_t (&v)[N]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(v[OFF]), "=r"(v[OFF + 1]), "=r"(v[OFF + 2]), "=r"(v[OFF + 3]), "=r"(v[OFF + 4]), "=r"(v[OFF + 5]),
+        "=r"(v[OFF + 6]), "=r"(v[OFF + 7]), "=r"(v[OFF + 8]), "=r"(v[OFF + 9]), "=r"(v[OFF + 10]), "=r"(v[OFF + 11]),
+        "=r"(v[OFF + 12]), "=r"(v[OFF + 13]), "=r"(v[OFF + 14]), "=r"(v[OFF + 15])
+      : "r"(addr) : "memory");
+}
 __device__ __forceinline__ void tmem_st16(uint32_t addr, const uint32_t (&v)[16]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
@@ -154,7 +164,7 @@ struct PrefillParams {
   int32_t q_dtype, out_dtype;
   int32_t max_pages, batch, tq, hq, hkv, group;
   // split of the page range over several CTAs (flash-decoding style), merged by the last CTA to finish
-  float* part_o;            // [slot][128 rows][128]
+  float* part_o;            // [slot][16 four-element groups][2 halves][128 rows][4]
   float* part_ml;           // [slot][128 rows][2]
   int32_t* tickets;         // [(b * hkv + kvh) * row_blocks + rb], zero between calls
   int32_t chunk_pages, num_splits, row_blocks;
@@ -376,26 +386,47 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
   // each of the row's two threads holds one half of its elements ----
   float o[PF_HALF];
   if (is_row) {
-    const size_t qoff = (((size_t)b * P.tq + qi) * P.hq + (size_t)kvh * P.group + hl) * TQ_D + PF_HALF * hf;
+    // The rows come in through shared memory: read directly, a thread's own half row would put the lanes of a load
+    // 256 or 512 bytes apart (one line per lane and instruction); staged, a warp reads whole rows.  Row stride: the
+    // row plus 16 bytes, so that the 16-byte accesses of consecutive rows fall into different banks.
+    {
+      const int esz = P.q_dtype == TQ_F32 ? 4 : 2;
+      const int cpr = TQ_D * esz / 16, stride = TQ_D * esz + 16;   // 16-byte chunks per row
+      uint8_t* stg = ktile;                                        // the operand tiles are not in use yet
+#pragma unroll 8
+      for (int it = 0; it < cpr / 2; ++it) {
+        const int c = it * 256 + tid, r = c / cpr, w = c - r * cpr;
+        const int grow = rb * PF_ROWS + r;
+        uint4 val = make_uint4(0u, 0u, 0u, 0u);
+        if (grow < nrows) {
+          const int gq = grow / P.group, gh = grow - gq * P.group;
+          const size_t off = ((((size_t)b * P.tq + gq) * P.hq + (size_t)kvh * P.group + gh) * TQ_D) * esz + w * 16;
+          val = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(P.q) + off);
+        }
+        *reinterpret_cast<uint4*>(stg + r * stride + w * 16) = val;
+      }
+      rows_sync();
+      const uint8_t* mine = stg + rtid * stride + hf * PF_HALF * esz;
+      if (P.q_dtype == TQ_F32) {
 #pragma unroll
-    for (int e = 0; e < PF_HALF; e += 4) {
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (row_ok) {
-        if (P.q_dtype == TQ_F32) {
-          v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(P.q) + qoff + e);
-        } else if (P.q_dtype == TQ_F16) {
-          const uint2 w = *reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(P.q) + qoff + e);
-          const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
-          const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
-          v = make_float4(a.x, a.y, c.x, c.y);
-        } else {
-          const uint2 w = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(P.q) + qoff + e);
-          const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w.x));
-          const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w.y));
-          v = make_float4(a.x, a.y, c.x, c.y);
+        for (int e = 0; e < PF_HALF; e += 4) {
+          const float4 v = *reinterpret_cast<const float4*>(mine + e * 4);
+          o[e] = v.x; o[e + 1] = v.y; o[e + 2] = v.z; o[e + 3] = v.w;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < PF_HALF; e += 8) {
+          const uint4 w4 = *reinterpret_cast<const uint4*>(mine + e * 2);
+          const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float2 f = P.q_dtype == TQ_F16 ? __half22float2(*reinterpret_cast<const __half2*>(&ww[k]))
+                                                 : __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ww[k]));
+            o[e + 2 * k] = f.x; o[e + 2 * k + 1] = f.y;
+          }
         }
       }
-      o[e] = v.x; o[e + 1] = v.y; o[e + 2] = v.z; o[e + 3] = v.w;
+      rows_sync();   // the staged rows are read: the exchange area of the rotation below is the same memory
     }
     float* xs = reinterpret_cast<float*>(ktile);  // [k][row], 64 KB: the operand tiles are not in use yet
     if (P.k_rot_t) {
@@ -466,12 +497,17 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
       // pass 1: this half's scaled scores into registers, row maximum
       float sv[64];
       float mx = -INFINITY;
+      uint32_t raw[64];   // the four loads fly together; each score replaces its raw value (same registers)
+      tmem_ld16_nowait<0>(ts + 64 * hf, raw);
+      tmem_ld16_nowait<16>(ts + 64 * hf + 16, raw);
+      tmem_ld16_nowait<32>(ts + 64 * hf + 32, raw);
+      tmem_ld16_nowait<48>(ts + 64 * hf + 48, raw);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       auto pass1 = [&](auto masked_c) {   // two copies behind a warp-uniform branch: only the diagonal pages pay for the mask
         constexpr bool MASKED = decltype(masked_c)::value;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {   // sixteen columns at a time: with the 64 scores of the page, 96 registers hold
-          uint32_t v[16];
-          tmem_ld16(ts + 64 * hf + 16 * c, v);
+        for (int c = 0; c < 4; ++c) {
+          const uint32_t* v = raw + 16 * c;
 #pragma unroll
           for (int j = 0; j < 16; j += 4) {
             const float4 k4 = ksc4[4 * c + (j >> 2)];
@@ -579,9 +615,10 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
     if (ns > 1) {
       const size_t slot0 = (((size_t)b * P.hkv + kvh) * P.row_blocks + rb) * P.num_splits;
       if (!failed) {
-        float4* po = reinterpret_cast<float4*>(P.part_o + ((slot0 + split) * PF_ROWS + rtid) * TQ_D + PF_HALF * hf);
+        // partial of a slot: [16 four-element groups][half][128 rows] float4 -- a warp's stores and loads are contiguous
+        float4* po = reinterpret_cast<float4*>(P.part_o + (slot0 + split) * PF_ROWS * TQ_D) + hf * PF_ROWS + rtid;
 #pragma unroll
-        for (int j = 0; j < PF_HALF; j += 4) po[j >> 2] = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+        for (int j = 0; j < PF_HALF; j += 4) po[(j >> 2) * 2 * PF_ROWS] = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
         if (is_prim) reinterpret_cast<float2*>(P.part_ml)[(slot0 + split) * PF_ROWS + rtid] = make_float2(m_run, l_run);
       }
       __threadfence();
@@ -609,10 +646,10 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
         const float2 ml = __ldcg(reinterpret_cast<const float2*>(P.part_ml) + (slot0 + s_i) * PF_ROWS + rtid);
         const float f = ml.x == -INFINITY ? 0.f : exp2f(ml.x - M);
         l_run = fmaf(ml.y, f, l_run);
-        const float4* po = reinterpret_cast<const float4*>(P.part_o + ((slot0 + s_i) * PF_ROWS + rtid) * TQ_D + PF_HALF * hf);
+        const float4* po = reinterpret_cast<const float4*>(P.part_o + (slot0 + s_i) * PF_ROWS * TQ_D) + hf * PF_ROWS + rtid;
 #pragma unroll
         for (int j = 0; j < PF_HALF; j += 4) {
-          const float4 v = __ldcg(po + (j >> 2));
+          const float4 v = __ldcg(po + (j >> 2) * 2 * PF_ROWS);
           o[j] = fmaf(v.x, f, o[j]); o[j + 1] = fmaf(v.y, f, o[j + 1]);
           o[j + 2] = fmaf(v.z, f, o[j + 2]); o[j + 3] = fmaf(v.w, f, o[j + 3]);
         }
@@ -642,20 +679,45 @@ __global__ void __launch_bounds__(PF2_THREADS, 1) k_prefill_attn2(const PrefillP
       } else {
         row_wht128_pair(o, fv.s2, fv.s1, hf, ys, rtid);  // R^T = D1 (H/sqrt d) D2
       }
-      if (row_ok) {
-        const size_t ooff = (((size_t)b * P.tq + qi) * P.hq + (size_t)kvh * P.group + hl) * TQ_D + PF_HALF * hf;
+      // The rows leave through shared memory like they came in: staged, a warp writes whole rows.
+      rows_sync();   // the exchange area of the rotation is read: the staging below is the same memory
+      {
+        const int esz = P.out_dtype == TQ_F32 ? 4 : 2;
+        const int cpr = TQ_D * esz / 16, stride = TQ_D * esz + 16;
+        uint8_t* stg = ktile;
+        uint8_t* mine = stg + rtid * stride + hf * PF_HALF * esz;
         if (P.out_dtype == TQ_F32) {
-          float4* op = reinterpret_cast<float4*>(reinterpret_cast<float*>(P.out) + ooff);
 #pragma unroll
-          for (int j = 0; j < PF_HALF; j += 4) op[j >> 2] = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+          for (int j = 0; j < PF_HALF; j += 4)
+            *reinterpret_cast<float4*>(mine + j * 4) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
         } else if (P.out_dtype == TQ_F16) {
-          uint2* op = reinterpret_cast<uint2*>(reinterpret_cast<__half*>(P.out) + ooff);
 #pragma unroll
-          for (int j = 0; j < PF_HALF; j += 4) op[j >> 2] = make_uint2(pf_pack(o[j], o[j + 1]), pf_pack(o[j + 2], o[j + 3]));
+          for (int j = 0; j < PF_HALF; j += 8)
+            *reinterpret_cast<uint4*>(mine + j * 2) = make_uint4(pf_pack(o[j], o[j + 1]), pf_pack(o[j + 2], o[j + 3]),
+                                                                 pf_pack(o[j + 4], o[j + 5]), pf_pack(o[j + 6], o[j + 7]));
         } else {
-          __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(P.out) + ooff;
 #pragma unroll
-          for (int j = 0; j < PF_HALF; ++j) op[j] = __float2bfloat16_rn(o[j]);
+          for (int j = 0; j < PF_HALF; j += 8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const __nv_bfloat162 h = __floats2bfloat162_rn(o[j + 2 * k], o[j + 2 * k + 1]);
+              w[k] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(mine + j * 2) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+        rows_sync();
+#pragma unroll 8
+        for (int it = 0; it < cpr / 2; ++it) {
+          const int c = it * 256 + tid, r = c / cpr, w = c - r * cpr;
+          const int grow = rb * PF_ROWS + r;
+          if (grow < nrows) {
+            const int gq = grow / P.group, gh = grow - gq * P.group;
+            const size_t off = ((((size_t)b * P.tq + gq) * P.hq + (size_t)kvh * P.group + gh) * TQ_D) * esz + w * 16;
+            *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(P.out) + off) =
+                *reinterpret_cast<const uint4*>(stg + r * stride + w * 16);
+          }
         }
       }
     }
