@@ -223,7 +223,8 @@ __device__ __forceinline__ void pf_dequant_token(const uint8_t* src, uint8_t* ds
 //              per half of a page's 128 score columns: reads S, online softmax (the halves exchange their maxima
 //              through shared memory), writes P, rescales its half of O (lazily: only when the row maximum grows by
 //              more than 2^4); both threads share the query rotation, the split partial, the merge and the output
-//              (64 elements each);
+//              (64 elements each; query and output rows pass through shared memory and the partials are laid out
+//              by warp, so that every global access of a warp covers whole lines);
 //   warps 8-11 K producers: thread t dequantizes the K row of token t of the page into a double-buffered operand tile
 //              and copies its scale; they wait for the score MMA of page i - 2 only, one page ahead of
 //   warps 12-15 V producers: the V row of token t times its V scale; their tile is free after the product of page
